@@ -1,0 +1,144 @@
+/*
+ * tt_attn.h -- C ABI of the B200 (sm_100a) attention kernels for TinyTensor.
+ *
+ * This is the boundary a host framework binds: plain pointers and sizes, no C++ or
+ * torch types.  The reference project (TinyTensor) reaches its GPU code through C++
+ * free functions over `TinyTensor<T>` bound with pybind11; each entry point below names
+ * the reference interface it sits under.  Paths are relative to the reference project
+ * root (`Task3/Tinytensor/`).
+ *
+ * Conventions
+ *   - All tensors are dense row-major, contiguous: q/out/dout/dq `[B,H,S,D]`,
+ *     k/v/dk/dv `[B,H,L,D]`, lse `[B,H,S]` (float, natural log of the softmax
+ *     denominator including the row maximum).
+ *   - Pointers are DEVICE pointers unless the function name ends in `_host`.
+ *   - `stream` is a `cudaStream_t` passed as `void*`; calls are asynchronous on it.
+ *   - `scale <= 0` selects `1/sqrt(D)`.
+ *   - causal: query i attends to keys j <= i + (L - S) (bottom-right aligned);
+ *     causal with L < S is rejected (some rows would have no key).
+ *   - Every function returns a `tt_status`; none throws or aborts.  A human-readable
+ *     message for the last failure on the calling thread is at `tt_last_error()`.
+ *   - There is no CPU path: a call on a machine without a usable sm_100 device returns
+ *     TT_ERR_BAD_DEVICE.
+ */
+#ifndef TT_ATTN_H
+#define TT_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef enum tt_status {
+    TT_OK = 0,
+    TT_ERR_NULL = 1,        /* a required pointer is null */
+    TT_ERR_BAD_SHAPE = 2,   /* non-positive extent, unsupported head dim, causal with L < S */
+    TT_ERR_BAD_DTYPE = 3,
+    TT_ERR_BAD_DEVICE = 4,  /* no CUDA device, or not compute capability 10.x */
+    TT_ERR_WORKSPACE = 5,   /* workspace missing or smaller than *_workspace_bytes() */
+    TT_ERR_CUDA = 6,        /* a CUDA runtime/driver call failed */
+    TT_ERR_TIMEOUT = 7,     /* a bounded device-side wait expired (reported after a sync) */
+    TT_ERR_UNSUPPORTED = 8
+} tt_status;
+
+typedef enum tt_dtype { TT_F32 = 0, TT_BF16 = 1 } tt_dtype;
+
+/* Problem description shared by every entry point. */
+typedef struct tt_attn_desc {
+    int32_t B, H;     /* batch, heads: B*H independent slices */
+    int32_t S;        /* queries per slice */
+    int32_t L;        /* keys/values per slice */
+    int32_t D;        /* head dim: 1..256 (tensor-core path: 64 or 128, bf16) */
+    int32_t dtype;    /* tt_dtype of q,k,v,out and gradients */
+    int32_t causal;   /* 0 / 1 */
+    float scale;      /* <= 0 -> 1/sqrt(D) */
+} tt_attn_desc;
+
+/* ---- forward -------------------------------------------------------------------------
+ * out = softmax(scale * q k^T [+ causal mask]) v, lse = log sum exp of the scaled scores.
+ * Replaces the composition MatMul/Transpose/MulScalar/EWiseAdd/Exp/Summation/Reshape/
+ * BroadcastTo/EWiseDiv/MatMul of optimizer/operators.py:194-199,234-242,289-298,323-340,
+ * 348-380,388-408,416-429,464-470, and on the native side the cudaGemm + SoftmaxForward
+ * sequence of src/Layers_kernels.cu:10-30 and src/Layers.cu:324-349.
+ * `lse` may be null when no backward will follow.  Needs no workspace. */
+int tt_attn_fwd(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                void* out, float* lse, void* stream);
+
+/* ---- backward ------------------------------------------------------------------------
+ * dq, dk, dv of sum(out * dout); `out` and `lse` are the forward's results.
+ * Replaces the reverse sweep of optimizer/autodiff.py:33-61 over the gradient methods of
+ * the ops listed above (operators.py:198-199,241-242,296-298,338-340,356-358,373-380,
+ * 400-408,421-429,469-470).
+ * Workspace: tt_attn_bwd_workspace_bytes() bytes of device memory, 256-byte aligned;
+ * contents on entry are ignored. */
+size_t tt_attn_bwd_workspace_bytes(const tt_attn_desc* desc);
+int tt_attn_bwd(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                const void* out, const float* lse, const void* dout,
+                void* dq, void* dk, void* dv,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- single-query decode (S == 1) ----------------------------------------------------
+ * Split-KV kernel for the memory-bound case: each (slice, key range) unit streams its
+ * K and V rows once with 16-byte loads, a second small kernel merges the partial
+ * (max, sum, out) triples.  Same mathematics as tt_attn_fwd with S == 1, no mask.
+ * Workspace: tt_attn_decode_workspace_bytes() bytes (partials), 256-byte aligned.
+ * `lse` may be null. */
+size_t tt_attn_decode_workspace_bytes(const tt_attn_desc* desc);
+int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                   void* out, float* lse, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- host-buffer calls (what the reference's Python ops do around each native op:
+ * upload NumPy -> run -> download, optimizer/operators.py:502-512) ----------------------
+ * Pointers are HOST pointers (pinned memory gives the best copy rate).  Device buffers
+ * come from the pool below; the call uploads, runs, downloads and synchronises. */
+int tt_attn_fwd_host(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                     void* out, float* lse);
+int tt_attn_bwd_host(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                     const void* out, const float* lse, const void* dout,
+                     void* dq, void* dk, void* dv);
+int tt_attn_decode_host(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                        void* out, float* lse);
+
+/* ---- pooled device storage -----------------------------------------------------------
+ * Replaces the per-object cudaMalloc/cudaFree of src/Tinytensor.cu:17-22,85-93: freed
+ * blocks go to size-bucketed free lists of the current device and are reused. */
+int tt_alloc(size_t bytes, void** out_ptr);
+int tt_free(void* ptr);
+int tt_pool_trim(void);                                     /* return cached blocks to the driver */
+int tt_pool_stats(size_t* bytes_in_use, size_t* bytes_cached, uint64_t* n_driver_allocs);
+
+/* ---- sharding of the B*H independent slices over ranks -------------------------------
+ * Contiguous ranges, remainder spread over the first ranks; pure host arithmetic.
+ * (The reference has no multi-GPU path; Task2/mnist.py:53-54 is torch DataParallel.) */
+int tt_shard_range(int64_t n_slices, int32_t world, int32_t rank, int64_t* begin, int64_t* count);
+
+/* ---- diagnostics ---------------------------------------------------------------------*/
+const char* tt_last_error(void);
+/* Number of kernels this library has launched in this process (for launch accounting). */
+uint64_t tt_kernel_launch_count(void);
+/* Name of the kernel family the given problem dispatches to: "tcgen05" or "simt". */
+const char* tt_attn_fwd_path(const tt_attn_desc* desc);
+const char* tt_attn_bwd_path(const tt_attn_desc* desc);
+/* Reads (and clears) the device-side status word after synchronising `stream`:
+ * TT_OK, or TT_ERR_TIMEOUT with details in tt_last_error(). */
+int tt_check_device_status(void* stream);
+
+/* Building-block self test of the tensor-core plumbing (TMA load -> tcgen05.mma from
+ * shared memory -> tcgen05.ld, tcgen05.st -> tcgen05.mma with A in tensor memory and an
+ * MN-major B).  a,b: bf16 [128,128] row-major; vt: bf16 [128,D] row-major (D = 64|128).
+ * Outputs: s = a b^T as float [128,128]; o = bf16(s) vt as float [128,D]. */
+int tt_debug_umma_probe(const void* a, const void* b, const void* vt, int32_t D,
+                        float* s_out, float* o_out, void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* TT_ATTN_H */

@@ -1,0 +1,523 @@
+// Flash-style fused attention forward for B200 (sm_100a), bf16 in / bf16 out, fp32
+// softmax and accumulation.  Head dim 64 or 128.
+//
+// One CTA owns 256 consecutive query rows of one (batch, head) slice as two 128-row
+// tiles and walks over the keys in tiles of 128.
+//
+//   warps 0-3   softmax warpgroup of query tile 0   (thread <-> one query row)
+//   warps 4-7   softmax warpgroup of query tile 1
+//   warp  8     MMA issuer (one elected lane issues every tcgen05.mma)
+//   warp  9     TMA loader (one elected lane issues every cp.async.bulk.tensor)
+//   warps 10-11 idle (they only complete the third warpgroup for setmaxnreg)
+//
+// Tensor memory (512 columns x 128 lanes x 32 bit):
+//   S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D)
+//   P_i (bf16, packed two per column) overlays columns [0,64) of S_i.
+//
+// Per key tile j and query tile i:  S_i = Q_i K_j^T (A,B from shared memory, K-major) ->
+// softmax warpgroup reads S_i row-per-thread, keeps the running max/sum, rescales O_i in
+// tensor memory only when the max grew by more than 2^8, writes P_i as bf16 into tensor
+// memory -> O_i += P_i V_j (A from tensor memory, B = V_j from shared memory, MN-major).
+// The issuer alternates the two query tiles so the tensor pipe works on one tile while
+// the other tile's softmax runs.
+//
+// Shared memory: Q tiles (2) + a ring of K/V tiles, each tile stored by TMA as D/64
+// sub-blocks of [128 rows x 128 bytes] with the 128-byte swizzle.
+#include "common.h"
+#include "sm100_ptx.cuh"
+
+namespace ttk {
+using namespace sm100;
+
+template <int D>
+struct FwdCfg {
+    static constexpr int kTile = 128;                     // rows per Q tile and keys per K/V tile
+    static constexpr int kSub = D / 64;                   // 64-column sub-blocks per tile
+    static constexpr int kSubBytes = kTile * 128;         // 16 KiB
+    static constexpr int kTileBytes = kSub * kSubBytes;   // 32 KiB (D=128), 16 KiB (D=64)
+    static constexpr int kStages = (D == 128) ? 4 : 8;    // K/V ring depth (tiles)
+    static constexpr int kThreads = 384;
+    static constexpr int kTmemCols = 512;
+    static constexpr int kBarBytes = 1024;
+    static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + kBarBytes + 1024;  // +1024: alignment slack
+};
+
+enum FwdBarId { BAR_QFULL = 0, BAR_KVFULL = 10, BAR_KVEMPTY = 30, BAR_SFULL = 50, BAR_PFULL = 60, BAR_OFINAL = 70 };
+
+struct FwdParams {
+    __nv_bfloat16* out;
+    float* lse;
+    int S, L;
+    int n_qblk;       // 256-row query blocks per slice
+    int causal;
+    float scale_log2; // scale * log2(e)
+    unsigned int* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FwdCfg<D>::kThreads, 1)
+attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+    using Cfg = FwdCfg<D>;
+    constexpr int kStages = Cfg::kStages;
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment: required by the 128-byte swizzle pattern shared by TMA and UMMA.
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = smem;                                  // 2 tiles
+    unsigned char* sKV = smem + 2 * Cfg::kTileBytes;           // kStages tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + kStages) * Cfg::kTileBytes);
+    uint64_t* bar_q_full = bars;               // [2]
+    uint64_t* bar_kv_full = bars + 2;          // [kStages]
+    uint64_t* bar_kv_empty = bars + 2 + kStages;
+    uint64_t* bar_s_full = bars + 2 + 2 * kStages;   // [2]
+    uint64_t* bar_p_full = bar_s_full + 2;           // [2]
+    uint64_t* bar_o_final = bar_p_full + 2;          // [2]
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bar_o_final + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // ---- which rows / how many key tiles
+    const int bh = blockIdx.x / p.n_qblk;
+    const int qb = p.n_qblk - 1 - (int)(blockIdx.x % p.n_qblk);   // heavy (late) query blocks first
+    const int q0 = qb * 256;
+    const int off = p.L - p.S;
+    const int n_kv_total = (p.L + 127) >> 7;
+    int n_tiles[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        int r0 = q0 + 128 * i;
+        if (r0 >= p.S) {
+            n_tiles[i] = 0;
+        } else if (p.causal) {
+            int last_row = min(r0 + 127, p.S - 1);
+            n_tiles[i] = min(n_kv_total, ((last_row + off) >> 7) + 1);
+        } else {
+            n_tiles[i] = n_kv_total;
+        }
+    }
+    const int n_max = max(n_tiles[0], n_tiles[1]);
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_q_full[i], 1);
+            mbar_init(&bar_s_full[i], 1);
+            mbar_init(&bar_p_full[i], 128);
+            mbar_init(&bar_o_final[i], 1);
+        }
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bar_kv_full[s], 1);
+            mbar_init(&bar_kv_empty[s], 1);
+        }
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 8) {
+        tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 9 && lane == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+    WaitCtx wctx{p.status, abort_flag, warp};
+
+    if (warp < 8) {
+        // =========================================================== softmax warpgroups
+        setmaxnreg_inc<224>();
+        const int i = warp >> 2;                    // query tile
+        const int nt = n_tiles[i];
+        const int wq = warp & 3;                    // TMEM lane quarter of this warp
+        const int row = q0 + 128 * i + wq * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_off + (uint32_t)(i * 128);
+        const uint32_t tP = tS;
+        const uint32_t tO = tmem_base + lane_off + (uint32_t)(256 + i * D);
+        const float c = p.scale_log2;
+        float m2 = -INFINITY;   // running max in the scaled log2 domain
+        float l = 0.f;          // running sum of exp2(s*c - m2)
+        for (int j = 0; j < nt; ++j) {
+            mbar_wait(&bar_s_full[i], j & 1, wctx, BAR_SFULL + i, j);
+            __syncwarp();
+            tc_fence_after();
+            uint32_t sr[4][32];
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, sr[cc]);
+            tmem_wait_ld();
+            // mask: key index must be < L and (causal) <= row + off
+            const int kv0 = j << 7;
+            const bool need_mask = (kv0 + 128 > p.L) || (p.causal && (kv0 + 127 > (q0 + 128 * i) + off));
+            if (need_mask) {
+                int lim = p.L;
+                if (p.causal) lim = min(lim, row + off + 1);
+                lim -= kv0;   // columns [0, lim) of this tile are visible
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if (cc * 32 + e >= lim) sr[cc][e] = 0xff800000u;  // -inf
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                mx0 = fmaxf(mx0, __uint_as_float(sr[0][e]));
+                mx1 = fmaxf(mx1, __uint_as_float(sr[1][e]));
+                mx2 = fmaxf(mx2, __uint_as_float(sr[2][e]));
+                mx3 = fmaxf(mx3, __uint_as_float(sr[3][e]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
+            float resc = 1.0f;
+            bool grow = false;
+            if (j == 0) {
+                m2 = mx;
+            } else if (mx > m2 + 8.0f) {   // lazy rescale: only when the max grew by > 2^8
+                resc = ex2_approx(m2 - mx);
+                m2 = mx;
+                l *= resc;
+                grow = true;
+            }
+            if (__any_sync(0xffffffffu, grow)) {
+                // O_i *= resc  (the previous P V of this tile has completed: its commit precedes
+                // the S commit just waited on)
+#pragma unroll
+                for (int cc = 0; cc < D / 32; ++cc) {
+                    uint32_t orr[32];
+                    tmem_ld32(tO + cc * 32, orr);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * resc);
+                    tmem_st32(tO + cc * 32, orr);
+                }
+            }
+            const float nm = -m2;
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float p0 = ex2_approx(fmaf(__uint_as_float(sr[cc][e]), c, nm));
+                    float p1 = ex2_approx(fmaf(__uint_as_float(sr[cc][e + 1]), c, nm));
+                    sum0 += p0;
+                    sum1 += p1;
+                    pk[e >> 1] = pack_bf16x2(p0, p1);
+                }
+                tmem_st16(tP + cc * 16, pk);
+            }
+            l += sum0 + sum1;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bar_p_full[i]);
+        }
+        if (nt > 0) {
+            // ---- epilogue: O_i / l -> bf16 -> global, LSE
+            mbar_wait(&bar_o_final[i], 0, wctx, BAR_OFINAL + i, 0);
+            __syncwarp();
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const bool row_ok = row < p.S;
+            __nv_bfloat16* orow = p.out + ((long long)bh * p.S + row) * D;
+#pragma unroll
+            for (int cc = 0; cc < D / 32; ++cc) {
+                uint32_t orr[32];
+                __syncwarp();
+                tmem_ld32(tO + cc * 32, orr);
+                tmem_wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 w;
+                        w.x = pack_bf16x2(__uint_as_float(orr[e + 0]) * inv, __uint_as_float(orr[e + 1]) * inv);
+                        w.y = pack_bf16x2(__uint_as_float(orr[e + 2]) * inv, __uint_as_float(orr[e + 3]) * inv);
+                        w.z = pack_bf16x2(__uint_as_float(orr[e + 4]) * inv, __uint_as_float(orr[e + 5]) * inv);
+                        w.w = pack_bf16x2(__uint_as_float(orr[e + 6]) * inv, __uint_as_float(orr[e + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + cc * 32 + e) = w;
+                    }
+                }
+            }
+            if (row_ok && p.lse != nullptr)
+                p.lse[(long long)bh * p.S + row] = (m2 + log2f(l)) * 0.6931471805599453f;
+        }
+    } else {
+        setmaxnreg_dec<56>();
+        if (warp == 9 && lane == 0) {
+            // ======================================================= TMA loader
+            // ring order: K_0, V_0, K_1, V_1, ...
+            auto load_tile = [&](unsigned char* dst, const CUtensorMap* tm, uint64_t* bar, int row_start) {
+                mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
+#pragma unroll
+                for (int sb = 0; sb < Cfg::kSub; ++sb) tma_load_3d(dst + sb * Cfg::kSubBytes, tm, bar, sb * 64, row_start, bh);
+            };
+            if (n_tiles[0] > 0) load_tile(sQ, &tmQ, &bar_q_full[0], q0);
+            int t = 0;   // ring item counter
+            auto load_kv = [&](const CUtensorMap* tm, int j) {
+                const int slot = t % kStages;
+                mbar_wait(&bar_kv_empty[slot], ((t / kStages) & 1) ^ 1, wctx, BAR_KVEMPTY + slot, t);
+                load_tile(sKV + slot * Cfg::kTileBytes, tm, &bar_kv_full[slot], j * 128);
+                ++t;
+            };
+            if (n_max > 0) load_kv(&tmK, 0);
+            if (n_tiles[1] > 0) load_tile(sQ + Cfg::kTileBytes, &tmQ, &bar_q_full[1], q0 + 128);
+            for (int j = 0; j < n_max; ++j) {
+                load_kv(&tmV, j);
+                if (j + 1 < n_max) load_kv(&tmK, j + 1);
+            }
+        } else if (warp == 8 && lane == 0) {
+            // ======================================================= MMA issuer
+            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(128, D, false, true);
+            const uint32_t sQ_addr = smem_u32(sQ);
+            const uint32_t sKV_addr = smem_u32(sKV);
+            int t = 0;   // ring item counter (consumer side)
+            auto wait_item = [&](int item) {
+                const int slot = item % kStages;
+                mbar_wait(&bar_kv_full[slot], (item / kStages) & 1, wctx, BAR_KVFULL + slot, item);
+            };
+            auto release_item = [&](int item) { tc_commit(&bar_kv_empty[item % kStages]); };
+            // S_i = Q_i K^T with K in ring item `item`
+            auto issue_s = [&](int i, int item) {
+                const uint32_t a0 = sQ_addr + i * Cfg::kTileBytes;
+                const uint32_t b0 = sKV_addr + (item % kStages) * Cfg::kTileBytes;
+                const uint32_t d = tmem_base + (uint32_t)(i * 128);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t o = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
+                    umma_ss(d, umma_smem_desc(a0 + o, 16, 1024), umma_smem_desc(b0 + o, 16, 1024), idesc_s, kk > 0);
+                }
+            };
+            // O_i (+)= P_i V with V in ring item `item`
+            auto issue_pv = [&](int i, int item, bool accumulate) {
+                const uint32_t b0 = sKV_addr + (item % kStages) * Cfg::kTileBytes;
+                const uint32_t d = tmem_base + (uint32_t)(256 + i * D);
+                const uint32_t a = tmem_base + (uint32_t)(i * 128);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    umma_ts(d, a + kk * 8, umma_smem_desc(b0 + kk * 2048, Cfg::kSubBytes, 1024), idesc_pv,
+                            (accumulate || kk > 0) ? 1u : 0u);
+            };
+            if (n_max > 0) {
+                wait_item(0);   // K_0
+                tc_fence_after();
+                for (int i = 0; i < 2; ++i) {
+                    if (n_tiles[i] > 0) {
+                        mbar_wait(&bar_q_full[i], 0, wctx, BAR_QFULL + i, 0);
+                        tc_fence_after();
+                        issue_s(i, 0);
+                        tc_commit(&bar_s_full[i]);
+                    }
+                }
+                release_item(0);
+            }
+            for (int j = 0; j < n_max; ++j) {
+                const int item_v = 2 * j + 1, item_k = 2 * j + 2;
+                wait_item(item_v);
+                bool k_waited = false;
+                for (int i = 0; i < 2; ++i) {
+                    if (j < n_tiles[i]) {
+                        mbar_wait(&bar_p_full[i], j & 1, wctx, BAR_PFULL + i, j);
+                        tc_fence_after();
+                        issue_pv(i, item_v, j > 0);
+                        if (j + 1 < n_tiles[i]) {
+                            if (!k_waited) {
+                                wait_item(item_k);
+                                tc_fence_after();
+                                k_waited = true;
+                            }
+                            issue_s(i, item_k);
+                            tc_commit(&bar_s_full[i]);
+                        } else {
+                            tc_commit(&bar_o_final[i]);
+                        }
+                    }
+                }
+                release_item(item_v);
+                if (j + 1 < n_max) release_item(item_k);
+            }
+            (void)t;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------ host side
+bool attn_fwd_sm100_supported(const AttnArgs& a) {
+    return a.bf16 && (a.D == 64 || a.D == 128) && a.S >= 1 && a.L >= 1 && a.BH * (long long)((a.S + 255) / 256) < (1LL << 31);
+}
+
+template <int D>
+static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
+    using Cfg = FwdCfg<D>;
+    TmapStorage tq, tk, tv;
+    const char* why = nullptr;
+    if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    FwdParams p;
+    p.out = (__nv_bfloat16*)a.out;
+    p.lse = a.lse;
+    p.S = a.S;
+    p.L = a.L;
+    p.n_qblk = (a.S + 255) / 256;
+    p.causal = a.causal;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.status = device_status_word();
+    unsigned grid = (unsigned)(a.BH * p.n_qblk);
+    attn_fwd_sm100_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
+        *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t attn_fwd_sm100(const AttnArgs& a, cudaStream_t st) {
+    return a.D == 128 ? launch_fwd<128>(a, st) : launch_fwd<64>(a, st);
+}
+
+// ------------------------------------------------------------------------------ self test
+// One CTA, 128 threads: S = A B^T (K = 128) from shared memory, S -> global; P = bf16(S)
+// into tensor memory; O = P Vt (A from tensor memory, B MN-major) -> global.
+template <int D>
+__global__ void __launch_bounds__(128, 1)
+umma_probe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmV, float* s_out, float* o_out, unsigned int* status) {
+    constexpr int kSubBytes = 128 * 128;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + 2 * kSubBytes;
+    unsigned char* sV = smem + 4 * kSubBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kSubBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_init(&bars[2], 1);
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    __syncwarp();
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    WaitCtx wctx{status, abort_flag, warp};
+    if (threadIdx.x == 0) {
+        mbar_arrive_expect_tx(&bars[0], (4 + D / 64) * kSubBytes);
+        for (int sb = 0; sb < 2; ++sb) {
+            tma_load_3d(sA + sb * kSubBytes, &tmA, &bars[0], sb * 64, 0, 0);
+            tma_load_3d(sB + sb * kSubBytes, &tmB, &bars[0], sb * 64, 0, 0);
+        }
+        for (int sb = 0; sb < D / 64; ++sb) tma_load_3d(sV + sb * kSubBytes, &tmV, &bars[0], sb * 64, 0, 0);
+        mbar_wait(&bars[0], 0, wctx, 0, 0);
+        tc_fence_after();
+        constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);
+        for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t o = (kk >> 2) * kSubBytes + (kk & 3) * 32;
+            umma_ss(tmem_base, umma_smem_desc(smem_u32(sA) + o, 16, 1024), umma_smem_desc(smem_u32(sB) + o, 16, 1024),
+                    idesc_s, kk > 0);
+        }
+        tc_commit(&bars[1]);
+    }
+    __syncwarp();
+    mbar_wait(&bars[1], 0, wctx, 1, 0);
+    __syncwarp();
+    tc_fence_after();
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const int row = warp * 32 + lane;
+    {
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) tmem_ld32(tmem_base + lane_off + cc * 32, sr[cc]);
+        tmem_wait_ld();
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+                s_out[row * 128 + cc * 32 + e] = __uint_as_float(sr[cc][e]);
+                s_out[row * 128 + cc * 32 + e + 1] = __uint_as_float(sr[cc][e + 1]);
+                pk[e >> 1] = pack_bf16x2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1]));
+            }
+            tmem_st16(tmem_base + lane_off + cc * 16, pk);
+        }
+        tmem_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        tc_fence_after();
+        constexpr uint32_t idesc_pv = umma_idesc_bf16(128, D, false, true);
+        for (int kk = 0; kk < 8; ++kk)
+            umma_ts(tmem_base + 128, tmem_base + kk * 8, umma_smem_desc(smem_u32(sV) + kk * 2048, kSubBytes, 1024),
+                    idesc_pv, kk > 0);
+        tc_commit(&bars[2]);
+    }
+    __syncwarp();
+    mbar_wait(&bars[2], 0, wctx, 2, 0);
+    __syncwarp();
+    tc_fence_after();
+#pragma unroll
+    for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t orr[32];
+        tmem_ld32(tmem_base + lane_off + 128 + cc * 32, orr);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o_out[row * D + cc * 32 + e] = __uint_as_float(orr[e]);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 256);
+    }
+}
+
+template <int D>
+static cudaError_t launch_probe(const void* a, const void* b, const void* vt, float* s_out, float* o_out,
+                                cudaStream_t st) {
+    TmapStorage ta, tb, tv;
+    const char* why = nullptr;
+    if (!make_tmap_bf16(&ta, a, 128, 128, 1, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tb, b, 128, 128, 1, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tv, vt, D, 128, 1, 128, &why)) return cudaErrorInvalidValue;
+    const int smem = 6 * 128 * 128 + 1024 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(umma_probe_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    umma_probe_kernel<D><<<1, 128, smem, st>>>(*reinterpret_cast<CUtensorMap*>(ta.bytes),
+                                               *reinterpret_cast<CUtensorMap*>(tb.bytes),
+                                               *reinterpret_cast<CUtensorMap*>(tv.bytes), s_out, o_out,
+                                               device_status_word());
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t umma_probe(const void* a, const void* b, const void* vt, int D, float* s_out, float* o_out,
+                       cudaStream_t st) {
+    if (D == 128) return launch_probe<128>(a, b, vt, s_out, o_out, st);
+    if (D == 64) return launch_probe<64>(a, b, vt, s_out, o_out, st);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace ttk

@@ -1,0 +1,57 @@
+// Internal declarations shared by the kernel translation units and the C-ABI layer.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace ttk {
+
+// Fully resolved launch arguments (device pointers, scale already defaulted).
+struct AttnArgs {
+    long long BH;   // B*H independent slices
+    int S, L, D;
+    int causal;
+    int bf16;       // 1: __nv_bfloat16 tensors, 0: float
+    float scale;
+    const void *q, *k, *v, *dout;
+    void* out;
+    float* lse;     // forward: written (may be null); backward: read
+    void *dq, *dk, *dv;
+};
+
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+void count_launch();
+unsigned int* device_status_word();  // 4 x uint32 in global memory of the current device (zeroed)
+
+// --- SIMT fp32-arithmetic kernels (any D <= 256, float or bf16 tensors)
+cudaError_t attn_fwd_simt(const AttnArgs& a, cudaStream_t st);
+cudaError_t attn_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t st);
+size_t attn_bwd_simt_workspace(const AttnArgs& a);
+
+// --- tcgen05 / TMA kernels (bf16, D in {64,128})
+bool attn_fwd_sm100_supported(const AttnArgs& a);
+cudaError_t attn_fwd_sm100(const AttnArgs& a, cudaStream_t st);
+bool attn_bwd_sm100_supported(const AttnArgs& a);
+size_t attn_bwd_sm100_workspace(const AttnArgs& a);
+cudaError_t attn_bwd_sm100(const AttnArgs& a, void* workspace, cudaStream_t st);
+cudaError_t umma_probe(const void* a, const void* b, const void* vt, int D, float* s_out, float* o_out,
+                       cudaStream_t st);
+
+// --- split-KV decode (S == 1, bf16 or float)
+struct DecodePlan {
+    int splits;        // key ranges per slice
+    int chunk;         // keys per range (multiple of 64)
+    size_t ws_bytes;   // partials: splits * BH * (D + 2) floats (0 when splits == 1)
+};
+DecodePlan attn_decode_plan(const AttnArgs& a);
+cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& plan, void* workspace, cudaStream_t st);
+
+// Builds a 3-D bf16 tensor map over a dense [slices, rows, cols] array, box
+// [1, box_rows, 64] with 128-byte swizzle.  Returns false (and sets `why`) on failure.
+struct TmapStorage { alignas(64) unsigned char bytes[128]; };
+bool make_tmap_bf16(TmapStorage* out, const void* base, uint64_t cols, uint64_t rows, uint64_t slices,
+                    uint32_t box_rows, const char** why);
+
+}  // namespace ttk

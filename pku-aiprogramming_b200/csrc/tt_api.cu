@@ -1,0 +1,495 @@
+// C-ABI layer: argument validation, dispatch to the kernel families, pooled device
+// storage, tensor-map construction, error reporting.  See include/tt_attn.h.
+#include "../../include/tt_attn.h"
+#include "common.h"
+
+#include <cuda.h>
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+namespace ttk {
+
+// ------------------------------------------------------------------------------ errors
+static thread_local char g_err[512] = "";
+static int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+static int cuda_fail(cudaError_t e, const char* what) {
+    return fail(TT_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// ------------------------------------------------------------------------------ device status word
+__device__ unsigned int g_device_status[4];
+static std::mutex g_status_mu;
+static std::unordered_map<int, unsigned int*> g_status_ptr;
+unsigned int* device_status_word() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_status_mu);
+    auto it = g_status_ptr.find(dev);
+    if (it != g_status_ptr.end()) return it->second;
+    unsigned int* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_device_status) != cudaSuccess) p = nullptr;
+    if (p) cudaMemset(p, 0, 4 * sizeof(unsigned int));
+    g_status_ptr[dev] = p;
+    return p;
+}
+
+// ------------------------------------------------------------------------------ device check
+static int check_device() {
+    static thread_local int cached_dev = -1;
+    static thread_local int cached_ok = 0;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(TT_ERR_BAD_DEVICE, "no usable CUDA device: %s", cudaGetErrorString(e));
+    if (dev == cached_dev && cached_ok) return TT_OK;
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return fail(TT_ERR_BAD_DEVICE, "cannot query device %d: %s", dev, cudaGetErrorString(e));
+    if (major != 10)
+        return fail(TT_ERR_BAD_DEVICE, "device %d has compute capability %d.x; these kernels are built for sm_100a only",
+                    dev, major);
+    cached_dev = dev;
+    cached_ok = 1;
+    return TT_OK;
+}
+
+// ------------------------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+bool make_tmap_bf16(TmapStorage* out, const void* base, uint64_t cols, uint64_t rows, uint64_t slices,
+                    uint32_t box_rows, const char** why) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) {
+        *why = "cuTensorMapEncodeTiled entry point not available";
+        fail(TT_ERR_CUDA, "%s", *why);
+        return false;
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (cols * 2) % 16 != 0) {
+        *why = "tensor base or row pitch not 16-byte aligned";
+        fail(TT_ERR_BAD_SHAPE, "%s", *why);
+        return false;
+    }
+    cuuint64_t gdim[3] = {cols, rows, slices};
+    cuuint64_t gstride[2] = {cols * 2, cols * rows * 2};
+    cuuint32_t box[3] = {64, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(reinterpret_cast<CUtensorMap*>(out->bytes), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                    const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        *why = "cuTensorMapEncodeTiled failed";
+        fail(TT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (cols=%llu rows=%llu slices=%llu)", (int)r,
+             (unsigned long long)cols, (unsigned long long)rows, (unsigned long long)slices);
+        return false;
+    }
+    return true;
+}
+
+// ------------------------------------------------------------------------------ pooled storage
+struct Pool {
+    std::mutex mu;
+    std::map<size_t, std::vector<void*>> free_by_size;   // bucket size -> cached blocks
+    std::unordered_map<void*, size_t> live;               // ptr -> bucket size
+    size_t in_use = 0, cached = 0;
+    uint64_t driver_allocs = 0;
+};
+static std::mutex g_pools_mu;
+static std::unordered_map<int, Pool*> g_pools;
+static Pool* pool_for_current_device() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_pools_mu);
+    auto it = g_pools.find(dev);
+    if (it != g_pools.end()) return it->second;
+    Pool* p = new Pool();
+    g_pools[dev] = p;
+    return p;
+}
+// Buckets: powers of two up to 1 MiB, multiples of 2 MiB above.
+static size_t bucket_of(size_t n) {
+    if (n <= 512) return 512;
+    if (n <= (1u << 20)) {
+        size_t b = 512;
+        while (b < n) b <<= 1;
+        return b;
+    }
+    const size_t g = (size_t)2 << 20;
+    return (n + g - 1) / g * g;
+}
+
+}  // namespace ttk
+
+using namespace ttk;
+
+extern "C" {
+
+const char* tt_last_error(void) { return g_err; }
+uint64_t tt_kernel_launch_count(void) { return g_launches.load(); }
+
+int tt_alloc(size_t bytes, void** out_ptr) {
+    if (!out_ptr) return fail(TT_ERR_NULL, "tt_alloc: out_ptr is null");
+    *out_ptr = nullptr;
+    if (bytes == 0) return TT_OK;
+    Pool* pool = pool_for_current_device();
+    const size_t b = bucket_of(bytes);
+    {
+        std::lock_guard<std::mutex> lk(pool->mu);
+        auto it = pool->free_by_size.find(b);
+        if (it != pool->free_by_size.end() && !it->second.empty()) {
+            void* p = it->second.back();
+            it->second.pop_back();
+            pool->cached -= b;
+            pool->in_use += b;
+            pool->live[p] = b;
+            *out_ptr = p;
+            return TT_OK;
+        }
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, b);
+    if (e == cudaErrorMemoryAllocation) {   // give cached blocks back and retry once
+        cudaGetLastError();
+        tt_pool_trim();
+        e = cudaMalloc(&p, b);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "tt_alloc: cudaMalloc");
+    std::lock_guard<std::mutex> lk(pool->mu);
+    pool->driver_allocs++;
+    pool->in_use += b;
+    pool->live[p] = b;
+    *out_ptr = p;
+    return TT_OK;
+}
+
+int tt_free(void* ptr) {
+    if (!ptr) return TT_OK;
+    Pool* pool = pool_for_current_device();
+    std::lock_guard<std::mutex> lk(pool->mu);
+    auto it = pool->live.find(ptr);
+    if (it == pool->live.end()) return fail(TT_ERR_NULL, "tt_free: pointer %p was not allocated by tt_alloc on this device", ptr);
+    size_t b = it->second;
+    pool->live.erase(it);
+    pool->in_use -= b;
+    pool->cached += b;
+    pool->free_by_size[b].push_back(ptr);
+    return TT_OK;
+}
+
+int tt_pool_trim(void) {
+    Pool* pool = pool_for_current_device();
+    std::vector<void*> victims;
+    {
+        std::lock_guard<std::mutex> lk(pool->mu);
+        for (auto& kv : pool->free_by_size)
+            for (void* p : kv.second) victims.push_back(p);
+        pool->free_by_size.clear();
+        pool->cached = 0;
+    }
+    for (void* p : victims) cudaFree(p);
+    return TT_OK;
+}
+
+int tt_pool_stats(size_t* bytes_in_use, size_t* bytes_cached, uint64_t* n_driver_allocs) {
+    Pool* pool = pool_for_current_device();
+    std::lock_guard<std::mutex> lk(pool->mu);
+    if (bytes_in_use) *bytes_in_use = pool->in_use;
+    if (bytes_cached) *bytes_cached = pool->cached;
+    if (n_driver_allocs) *n_driver_allocs = pool->driver_allocs;
+    return TT_OK;
+}
+
+int tt_shard_range(int64_t n_slices, int32_t world, int32_t rank, int64_t* begin, int64_t* count) {
+    if (!begin || !count) return fail(TT_ERR_NULL, "tt_shard_range: null output");
+    if (n_slices < 0 || world < 1 || rank < 0 || rank >= world)
+        return fail(TT_ERR_BAD_SHAPE, "tt_shard_range: n_slices=%lld world=%d rank=%d", (long long)n_slices, world, rank);
+    int64_t base = n_slices / world, rem = n_slices % world;
+    *begin = rank * base + (rank < rem ? rank : rem);
+    *count = base + (rank < rem ? 1 : 0);
+    return TT_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------ validation
+namespace ttk {
+static int resolve(const tt_attn_desc* d, AttnArgs* a, const char* who) {
+    if (!d) return fail(TT_ERR_NULL, "%s: desc is null", who);
+    if (d->B < 1 || d->H < 1 || d->S < 1 || d->L < 1)
+        return fail(TT_ERR_BAD_SHAPE, "%s: B=%d H=%d S=%d L=%d must all be >= 1", who, d->B, d->H, d->S, d->L);
+    if (d->D < 1 || d->D > 256) return fail(TT_ERR_BAD_SHAPE, "%s: head dim D=%d outside 1..256", who, d->D);
+    if (d->dtype != TT_F32 && d->dtype != TT_BF16) return fail(TT_ERR_BAD_DTYPE, "%s: dtype %d unknown", who, d->dtype);
+    if (d->causal && d->L < d->S)
+        return fail(TT_ERR_BAD_SHAPE, "%s: causal with L=%d < S=%d leaves query rows without keys", who, d->L, d->S);
+    if (!std::isfinite(d->scale)) return fail(TT_ERR_BAD_SHAPE, "%s: scale is not finite", who);
+    memset(a, 0, sizeof(*a));
+    a->BH = (long long)d->B * d->H;
+    a->S = d->S;
+    a->L = d->L;
+    a->D = d->D;
+    a->causal = d->causal ? 1 : 0;
+    a->bf16 = d->dtype == TT_BF16;
+    a->scale = d->scale > 0.f ? d->scale : 1.0f / sqrtf((float)d->D);
+    long long nblk = ((long long)(d->S > d->L ? d->S : d->L) + 31) / 32;
+    if (a->BH * nblk >= (1LL << 31)) return fail(TT_ERR_BAD_SHAPE, "%s: problem too large for a 1-D grid", who);
+    return TT_OK;
+}
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+}  // namespace ttk
+
+extern "C" {
+
+const char* tt_attn_fwd_path(const tt_attn_desc* desc) {
+    AttnArgs a;
+    if (resolve(desc, &a, "tt_attn_fwd_path") != TT_OK) return "invalid";
+    return attn_fwd_sm100_supported(a) ? "tcgen05" : "simt";
+}
+const char* tt_attn_bwd_path(const tt_attn_desc* desc) {
+    AttnArgs a;
+    if (resolve(desc, &a, "tt_attn_bwd_path") != TT_OK) return "invalid";
+    return attn_bwd_sm100_supported(a) ? "tcgen05" : "simt";
+}
+
+int tt_attn_fwd(const tt_attn_desc* desc, const void* q, const void* k, const void* v, void* out, float* lse,
+                void* stream) {
+    AttnArgs a;
+    int rc = resolve(desc, &a, "tt_attn_fwd");
+    if (rc != TT_OK) return rc;
+    if (!q || !k || !v || !out) return fail(TT_ERR_NULL, "tt_attn_fwd: q, k, v and out must be non-null");
+    if ((rc = check_device()) != TT_OK) return rc;
+    g_err[0] = 0;
+    a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (attn_fwd_sm100_supported(a) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out)) {
+        e = attn_fwd_sm100(a, st);
+        if (e == cudaErrorInvalidValue && g_err[0]) return TT_ERR_CUDA;
+    } else {
+        e = attn_fwd_simt(a, st);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "tt_attn_fwd: launch");
+    return TT_OK;
+}
+
+size_t tt_attn_bwd_workspace_bytes(const tt_attn_desc* desc) {
+    AttnArgs a;
+    if (resolve(desc, &a, "tt_attn_bwd_workspace_bytes") != TT_OK) return 0;
+    size_t simt = attn_bwd_simt_workspace(a);
+    size_t tc = attn_bwd_sm100_supported(a) ? attn_bwd_sm100_workspace(a) : 0;
+    return simt > tc ? simt : tc;
+}
+
+int tt_attn_bwd(const tt_attn_desc* desc, const void* q, const void* k, const void* v, const void* out,
+                const float* lse, const void* dout, void* dq, void* dk, void* dv, void* workspace,
+                size_t workspace_bytes, void* stream) {
+    AttnArgs a;
+    int rc = resolve(desc, &a, "tt_attn_bwd");
+    if (rc != TT_OK) return rc;
+    if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv)
+        return fail(TT_ERR_NULL, "tt_attn_bwd: all tensor pointers must be non-null");
+    size_t need = tt_attn_bwd_workspace_bytes(desc);
+    if (!workspace || workspace_bytes < need)
+        return fail(TT_ERR_WORKSPACE, "tt_attn_bwd: workspace of %zu bytes required, %zu given", need, workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+        return fail(TT_ERR_WORKSPACE, "tt_attn_bwd: workspace must be 256-byte aligned");
+    if ((rc = check_device()) != TT_OK) return rc;
+    g_err[0] = 0;
+    a.q = q; a.k = k; a.v = v; a.out = const_cast<void*>(out); a.lse = const_cast<float*>(lse); a.dout = dout;
+    a.dq = dq; a.dk = dk; a.dv = dv;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    bool al = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(dout) && aligned16(dq) &&
+              aligned16(dk) && aligned16(dv);
+    if (attn_bwd_sm100_supported(a) && al) {
+        e = attn_bwd_sm100(a, workspace, st);
+        if (e == cudaErrorInvalidValue && g_err[0]) return TT_ERR_CUDA;
+    } else {
+        e = attn_bwd_simt(a, (float*)workspace, st);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "tt_attn_bwd: launch");
+    return TT_OK;
+}
+
+size_t tt_attn_decode_workspace_bytes(const tt_attn_desc* desc) {
+    AttnArgs a;
+    if (resolve(desc, &a, "tt_attn_decode_workspace_bytes") != TT_OK) return 0;
+    if (a.S != 1) return 0;
+    return attn_decode_plan(a).ws_bytes;
+}
+
+int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const void* v, void* out, float* lse,
+                   void* workspace, size_t workspace_bytes, void* stream) {
+    AttnArgs a;
+    int rc = resolve(desc, &a, "tt_attn_decode");
+    if (rc != TT_OK) return rc;
+    if (a.S != 1) return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode: S must be 1, got %d", a.S);
+    if (!q || !k || !v || !out) return fail(TT_ERR_NULL, "tt_attn_decode: q, k, v and out must be non-null");
+    if ((rc = check_device()) != TT_OK) return rc;
+    a.causal = 0;   // a single query aligned bottom-right sees every key
+    DecodePlan pl = attn_decode_plan(a);
+    if (pl.ws_bytes > 0) {
+        if (!workspace || workspace_bytes < pl.ws_bytes)
+            return fail(TT_ERR_WORKSPACE, "tt_attn_decode: workspace of %zu bytes required, %zu given", pl.ws_bytes,
+                        workspace_bytes);
+        if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+            return fail(TT_ERR_WORKSPACE, "tt_attn_decode: workspace must be 256-byte aligned");
+    }
+    if (a.bf16 && (a.D == 64 || a.D == 128) && !(aligned16(q) && aligned16(k) && aligned16(v)))
+        return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode: q, k, v must be 16-byte aligned");
+    a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
+    cudaError_t e = attn_decode(a, pl, workspace, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "tt_attn_decode: launch");
+    return TT_OK;
+}
+
+int tt_check_device_status(void* stream) {
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "tt_check_device_status: synchronize");
+    unsigned int* dptr = device_status_word();
+    if (!dptr) return fail(TT_ERR_CUDA, "tt_check_device_status: status word unavailable");
+    unsigned int h[4] = {0, 0, 0, 0};
+    e = cudaMemcpy(h, dptr, sizeof(h), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "tt_check_device_status: copy");
+    if (h[0] == 0) return TT_OK;
+    cudaMemset(dptr, 0, sizeof(h));
+    return fail(TT_ERR_TIMEOUT, "a device-side wait expired: block %u, barrier id %u, iteration %u, warp %u",
+                h[0] & 0xffffu, h[1], h[2], h[3]);
+}
+
+int tt_debug_umma_probe(const void* a, const void* b, const void* vt, int32_t D, float* s_out, float* o_out,
+                        void* stream) {
+    if (!a || !b || !vt || !s_out || !o_out) return fail(TT_ERR_NULL, "tt_debug_umma_probe: null pointer");
+    if (D != 64 && D != 128) return fail(TT_ERR_BAD_SHAPE, "tt_debug_umma_probe: D must be 64 or 128");
+    int rc = check_device();
+    if (rc != TT_OK) return rc;
+    g_err[0] = 0;
+    cudaError_t e = umma_probe(a, b, vt, D, s_out, o_out, (cudaStream_t)stream);
+    if (e == cudaErrorInvalidValue && g_err[0]) return TT_ERR_CUDA;
+    if (e != cudaSuccess) return cuda_fail(e, "tt_debug_umma_probe: launch");
+    return TT_OK;
+}
+
+// ------------------------------------------------------------------------------ host-buffer calls
+namespace {
+struct DevBuf {
+    void* p = nullptr;
+    ~DevBuf() { if (p) tt_free(p); }
+    int get(size_t n) { return tt_alloc(n, &p); }
+};
+cudaStream_t host_call_stream() {
+    static thread_local cudaStream_t st = nullptr;
+    static thread_local int st_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!st || st_dev != dev) {
+        if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess) st = nullptr;
+        st_dev = dev;
+    }
+    return st;
+}
+#define TT_TRY(x) do { int rc__ = (x); if (rc__ != TT_OK) return rc__; } while (0)
+#define TT_CUDA(x, what) do { cudaError_t e__ = (x); if (e__ != cudaSuccess) return cuda_fail(e__, what); } while (0)
+}  // namespace
+
+int tt_attn_fwd_host(const tt_attn_desc* d, const void* q, const void* k, const void* v, void* out, float* lse) {
+    AttnArgs a;
+    TT_TRY(resolve(d, &a, "tt_attn_fwd_host"));
+    if (!q || !k || !v || !out) return fail(TT_ERR_NULL, "tt_attn_fwd_host: q, k, v and out must be non-null");
+    TT_TRY(check_device());
+    const size_t es = a.bf16 ? 2 : 4;
+    const size_t nq = (size_t)a.BH * a.S * a.D * es, nk = (size_t)a.BH * a.L * a.D * es;
+    const size_t nl = (size_t)a.BH * a.S * sizeof(float);
+    DevBuf dq_, dk_, dv_, do_, dl_;
+    TT_TRY(dq_.get(nq)); TT_TRY(dk_.get(nk)); TT_TRY(dv_.get(nk)); TT_TRY(do_.get(nq)); TT_TRY(dl_.get(nl));
+    cudaStream_t st = host_call_stream();
+    TT_CUDA(cudaMemcpyAsync(dq_.p, q, nq, cudaMemcpyHostToDevice, st), "upload q");
+    TT_CUDA(cudaMemcpyAsync(dk_.p, k, nk, cudaMemcpyHostToDevice, st), "upload k");
+    TT_CUDA(cudaMemcpyAsync(dv_.p, v, nk, cudaMemcpyHostToDevice, st), "upload v");
+    TT_TRY(tt_attn_fwd(d, dq_.p, dk_.p, dv_.p, do_.p, (float*)dl_.p, st));
+    TT_CUDA(cudaMemcpyAsync(out, do_.p, nq, cudaMemcpyDeviceToHost, st), "download out");
+    if (lse) TT_CUDA(cudaMemcpyAsync(lse, dl_.p, nl, cudaMemcpyDeviceToHost, st), "download lse");
+    return tt_check_device_status(st);
+}
+
+int tt_attn_bwd_host(const tt_attn_desc* d, const void* q, const void* k, const void* v, const void* out,
+                     const float* lse, const void* dout, void* dq, void* dk, void* dv) {
+    AttnArgs a;
+    TT_TRY(resolve(d, &a, "tt_attn_bwd_host"));
+    if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv)
+        return fail(TT_ERR_NULL, "tt_attn_bwd_host: all tensor pointers must be non-null");
+    TT_TRY(check_device());
+    const size_t es = a.bf16 ? 2 : 4;
+    const size_t nq = (size_t)a.BH * a.S * a.D * es, nk = (size_t)a.BH * a.L * a.D * es;
+    const size_t nl = (size_t)a.BH * a.S * sizeof(float);
+    const size_t nws = tt_attn_bwd_workspace_bytes(d);
+    DevBuf bq, bk, bv, bo, bl, bdo, bdq, bdk, bdv, bws;
+    TT_TRY(bq.get(nq)); TT_TRY(bk.get(nk)); TT_TRY(bv.get(nk)); TT_TRY(bo.get(nq)); TT_TRY(bl.get(nl));
+    TT_TRY(bdo.get(nq)); TT_TRY(bdq.get(nq)); TT_TRY(bdk.get(nk)); TT_TRY(bdv.get(nk)); TT_TRY(bws.get(nws));
+    cudaStream_t st = host_call_stream();
+    TT_CUDA(cudaMemcpyAsync(bq.p, q, nq, cudaMemcpyHostToDevice, st), "upload q");
+    TT_CUDA(cudaMemcpyAsync(bk.p, k, nk, cudaMemcpyHostToDevice, st), "upload k");
+    TT_CUDA(cudaMemcpyAsync(bv.p, v, nk, cudaMemcpyHostToDevice, st), "upload v");
+    TT_CUDA(cudaMemcpyAsync(bo.p, out, nq, cudaMemcpyHostToDevice, st), "upload out");
+    TT_CUDA(cudaMemcpyAsync(bl.p, lse, nl, cudaMemcpyHostToDevice, st), "upload lse");
+    TT_CUDA(cudaMemcpyAsync(bdo.p, dout, nq, cudaMemcpyHostToDevice, st), "upload dout");
+    TT_TRY(tt_attn_bwd(d, bq.p, bk.p, bv.p, bo.p, (const float*)bl.p, bdo.p, bdq.p, bdk.p, bdv.p, bws.p, nws, st));
+    TT_CUDA(cudaMemcpyAsync(dq, bdq.p, nq, cudaMemcpyDeviceToHost, st), "download dq");
+    TT_CUDA(cudaMemcpyAsync(dk, bdk.p, nk, cudaMemcpyDeviceToHost, st), "download dk");
+    TT_CUDA(cudaMemcpyAsync(dv, bdv.p, nk, cudaMemcpyDeviceToHost, st), "download dv");
+    return tt_check_device_status(st);
+}
+
+int tt_attn_decode_host(const tt_attn_desc* d, const void* q, const void* k, const void* v, void* out,
+                        float* lse) {
+    AttnArgs a;
+    TT_TRY(resolve(d, &a, "tt_attn_decode_host"));
+    if (a.S != 1) return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_host: S must be 1, got %d", a.S);
+    if (!q || !k || !v || !out) return fail(TT_ERR_NULL, "tt_attn_decode_host: q, k, v and out must be non-null");
+    TT_TRY(check_device());
+    const size_t es = a.bf16 ? 2 : 4;
+    const size_t nq = (size_t)a.BH * a.D * es, nk = (size_t)a.BH * a.L * a.D * es;
+    const size_t nl = (size_t)a.BH * sizeof(float);
+    const size_t nws = tt_attn_decode_workspace_bytes(d);
+    DevBuf bq, bk, bv, bo, bl, bws;
+    TT_TRY(bq.get(nq)); TT_TRY(bk.get(nk)); TT_TRY(bv.get(nk)); TT_TRY(bo.get(nq)); TT_TRY(bl.get(nl));
+    TT_TRY(bws.get(nws));
+    cudaStream_t st = host_call_stream();
+    TT_CUDA(cudaMemcpyAsync(bq.p, q, nq, cudaMemcpyHostToDevice, st), "upload q");
+    TT_CUDA(cudaMemcpyAsync(bk.p, k, nk, cudaMemcpyHostToDevice, st), "upload k");
+    TT_CUDA(cudaMemcpyAsync(bv.p, v, nk, cudaMemcpyHostToDevice, st), "upload v");
+    TT_TRY(tt_attn_decode(d, bq.p, bk.p, bv.p, bo.p, (float*)bl.p, bws.p, nws, st));
+    TT_CUDA(cudaMemcpyAsync(out, bo.p, nq, cudaMemcpyDeviceToHost, st), "download out");
+    if (lse) TT_CUDA(cudaMemcpyAsync(lse, bl.p, nl, cudaMemcpyDeviceToHost, st), "download lse");
+    return tt_check_device_status(st);
+}
+
+}  // extern "C"

@@ -1,0 +1,154 @@
+"""Attention calls over torch CUDA tensors.
+
+torch is used for device memory and streams only: every call hands raw device pointers
+to the C ABI (`capi.lib`).  Shapes follow the reference's row-major layout:
+q/out `[B,H,S,D]`, k/v `[B,H,L,D]`, lse `[B,H,S]` fp32.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import capi
+
+_DT = {torch.float32: capi.TT_F32, torch.bfloat16: capi.TT_BF16}
+
+
+def _check_inputs(q, k, v):
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not isinstance(t, torch.Tensor):
+            raise ValueError(f"{name} must be a torch.Tensor")
+        if t.dim() != 4:
+            raise ValueError(f"{name} must be 4-D [B,H,rows,D], got shape {tuple(t.shape)}")
+        if not t.is_cuda:
+            raise ValueError(f"{name} is on {t.device}; attention runs on CUDA tensors only (no CPU path)")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    if q.dtype not in _DT or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError(f"q, k, v must share dtype float32 or bfloat16, got {q.dtype}, {k.dtype}, {v.dtype}")
+    B, H, S, D = q.shape
+    if k.shape[0] != B or k.shape[1] != H or k.shape[3] != D or tuple(v.shape) != tuple(k.shape):
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)} k {tuple(k.shape)} v {tuple(v.shape)}")
+    return B, H, S, k.shape[2], D
+
+
+def _stream_ptr(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def attention_forward(q, k, v, causal=False, scale=None, out=None, lse=None, need_lse=True):
+    """`softmax(scale * q k^T [+causal]) v` -> (out, lse).  Asynchronous on the current stream."""
+    B, H, S, L, D = _check_inputs(q, k, v)
+    with torch.cuda.device(q.device):
+        if out is None:
+            out = torch.empty_like(q)
+        if lse is None and need_lse:
+            lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+        d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+        capi.check(capi.lib.tt_attn_fwd(ctypes.byref(d), _p(q), _p(k), _p(v), _p(out), _p(lse), _stream_ptr(q)))
+    return out, lse
+
+
+def attention_backward(q, k, v, out, lse, dout, causal=False, scale=None, workspace=None):
+    """(dq, dk, dv) for upstream gradient `dout`; `out`, `lse` from `attention_forward`."""
+    B, H, S, L, D = _check_inputs(q, k, v)
+    for name, t, shp in (("out", out, q.shape), ("dout", dout, q.shape)):
+        if tuple(t.shape) != tuple(shp) or t.dtype != q.dtype or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous CUDA tensor of shape {tuple(shp)} and dtype {q.dtype}")
+    if tuple(lse.shape) != (B, H, S) or lse.dtype != torch.float32 or not lse.is_contiguous():
+        raise ValueError("lse must be contiguous float32 [B,H,S]")
+    with torch.cuda.device(q.device):
+        d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+        need = int(capi.lib.tt_attn_bwd_workspace_bytes(ctypes.byref(d)))
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        capi.check(capi.lib.tt_attn_bwd(ctypes.byref(d), _p(q), _p(k), _p(v), _p(out), _p(lse), _p(dout),
+                                        _p(dq), _p(dk), _p(dv), _p(workspace),
+                                        workspace.numel() * workspace.element_size(), _stream_ptr(q)))
+    return dq, dk, dv
+
+
+def decode_workspace_bytes(B, H, L, D, dtype=torch.bfloat16) -> int:
+    d = capi.make_desc(B, H, 1, L, D, _DT[dtype], False, None)
+    return int(capi.lib.tt_attn_decode_workspace_bytes(ctypes.byref(d)))
+
+
+def attention_decode(q, k, v, scale=None, out=None, lse=None, workspace=None, need_lse=True):
+    """Single-query attention: q `[B,H,1,D]` against the whole cache k,v `[B,H,L,D]`."""
+    B, H, S, L, D = _check_inputs(q, k, v)
+    if S != 1:
+        raise ValueError(f"decode needs S == 1, got {S}")
+    with torch.cuda.device(q.device):
+        if out is None:
+            out = torch.empty_like(q)
+        if lse is None and need_lse:
+            lse = torch.empty((B, H, 1), dtype=torch.float32, device=q.device)
+        d = capi.make_desc(B, H, 1, L, D, _DT[q.dtype], False, scale)
+        need = int(capi.lib.tt_attn_decode_workspace_bytes(ctypes.byref(d)))
+        if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+            workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+        nbytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+        capi.check(capi.lib.tt_attn_decode(ctypes.byref(d), _p(q), _p(k), _p(v), _p(out), _p(lse),
+                                           _p(workspace), nbytes, _stream_ptr(q)))
+    return out, lse
+
+
+def check_device_status(device=None):
+    """Synchronises the current stream and raises if a bounded device-side wait expired."""
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        capi.check(capi.lib.tt_check_device_status(st))
+
+
+# ------------------------------------------------------------------ host-buffer calls
+def _host_ptr(t):
+    if t is None:
+        return None
+    if t.is_cuda or not t.is_contiguous():
+        raise ValueError("host-buffer calls take contiguous CPU tensors")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def attention_forward_host(q, k, v, causal=False, scale=None, out=None, lse=None):
+    """Same as `attention_forward` for CPU (ideally pinned) tensors: upload, run, download."""
+    B, H, S, D = q.shape
+    L = k.shape[2]
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((B, H, S), dtype=torch.float32)
+    d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+    capi.check(capi.lib.tt_attn_fwd_host(ctypes.byref(d), _host_ptr(q), _host_ptr(k), _host_ptr(v),
+                                         _host_ptr(out), _host_ptr(lse)))
+    return out, lse
+
+
+def attention_backward_host(q, k, v, out, lse, dout, causal=False, scale=None, dq=None, dk=None, dv=None):
+    B, H, S, D = q.shape
+    L = k.shape[2]
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(k) if dk is None else dk
+    dv = torch.empty_like(v) if dv is None else dv
+    d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+    capi.check(capi.lib.tt_attn_bwd_host(ctypes.byref(d), _host_ptr(q), _host_ptr(k), _host_ptr(v), _host_ptr(out),
+                                         _host_ptr(lse), _host_ptr(dout), _host_ptr(dq), _host_ptr(dk), _host_ptr(dv)))
+    return dq, dk, dv
+
+
+def attention_decode_host(q, k, v, scale=None, out=None, lse=None):
+    B, H, S, D = q.shape
+    L = k.shape[2]
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((B, H, 1), dtype=torch.float32)
+    d = capi.make_desc(B, H, 1, L, D, _DT[q.dtype], False, scale)
+    capi.check(capi.lib.tt_attn_decode_host(ctypes.byref(d), _host_ptr(q), _host_ptr(k), _host_ptr(v),
+                                            _host_ptr(out), _host_ptr(lse)))
+    return out, lse

@@ -1,0 +1,90 @@
+"""Generate the golden attention fixtures by EXECUTING the reference's own ops.
+
+Run where the reference checkout is available:
+
+    python tests/golden/make_golden.py --reference /path/to/reference
+
+It imports the reference's `operators.py` (NumPy-backed autograd ops and reverse sweep),
+composes attention exactly as `oracle/attention_oracle.py` documents, calls
+`O.backward(dO)` and stores inputs and outputs as `.npz` files next to this script.
+The reference's two pybind modules (`myTensor`, `myLayer`) are only *named* at import
+time by `operators.py`; none of the ops on this path calls into them, so inert
+stand-in modules are registered instead of building them.
+
+The fixtures travel with the repository; the reference checkout does not, so tests
+read only the `.npz` files.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+from oracle.attention_oracle import make_inputs, causal_mask, MASK_VALUE  # noqa: E402
+
+# name, B, H, S, L, D, causal, sigma, seed
+CASES = [
+    ("cfg1_f32_b2h4s64d32", 2, 4, 64, 64, 32, False, 1.0, 0),       # BASELINE config 1
+    ("causal_b1h2s48d32", 1, 2, 48, 48, 32, True, 1.0, 1),
+    ("causal_ragged_b1h2s40l72d64", 1, 2, 40, 72, 64, True, 0.5, 2),  # L != S, bottom-right aligned
+    ("cross_b1h3s17l33d16", 1, 3, 17, 33, 16, False, 1.0, 3),
+    ("decode_b2h2s1l96d64", 2, 2, 1, 96, 64, False, 1.0, 4),
+    ("causal_b1h1s130d128", 1, 1, 130, 130, 128, True, 0.5, 5),     # crosses a 128-row tile edge
+]
+
+
+def load_reference_ops(ref_root: str):
+    opt = os.path.join(ref_root, "Task3", "Tinytensor", "optimizer")
+    if not os.path.isdir(opt):
+        raise SystemExit(f"reference optimizer directory not found: {opt}")
+    mt = types.ModuleType("myTensor")
+    mt.Tensor_float = type("Tensor_float", (), {})
+    mt.Tensor_int = type("Tensor_int", (), {})
+    sys.modules["myTensor"] = mt
+    sys.modules["myLayer"] = types.ModuleType("myLayer")
+    sys.path.insert(0, opt)
+    import operators as ops  # the reference's module, unmodified
+    return ops
+
+
+def reference_attention(ops, q, k, v, do, causal, scale):
+    B, H, S, D = q.shape
+    L = k.shape[2]
+    Q = ops.Tensor(q); K = ops.Tensor(k); V = ops.Tensor(v)
+    s = (Q @ ops.transpose(K)) * float(scale)
+    if causal:
+        m = np.ascontiguousarray(np.broadcast_to(causal_mask(S, L), (B, H, S, L)))
+        s = s + ops.Tensor(m, requires_grad=False)
+    e = ops.exp(s)
+    den = ops.broadcast_to(ops.reshape(ops.summation(e, axes=(3,)), (B, H, S, 1)), (B, H, S, L))
+    O = (e / den) @ V
+    O.backward(ops.Tensor(do, requires_grad=False))
+    return O.numpy(), Q.grad.numpy(), K.grad.numpy(), V.grad.numpy()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    ops = load_reference_ops(args.reference)
+    for name, B, H, S, L, D, causal, sigma, seed in CASES:
+        q, k, v, do = make_inputs(seed, B, H, S, L, D, sigma=sigma)
+        scale = 1.0 / float(np.sqrt(float(D)))
+        o, dq, dk, dv = reference_attention(ops, q, k, v, do, causal, scale)
+        for t in (o, dq, dk, dv):
+            assert t.dtype == np.float32, t.dtype
+        path = os.path.join(HERE, name + ".npz")
+        np.savez(path, q=q, k=k, v=v, do=do, o=o, dq=dq, dk=dk, dv=dv,
+                 causal=np.int32(causal), scale=np.float32(scale), seed=np.int32(seed),
+                 sigma=np.float32(sigma))
+        print(f"{name}: wrote {os.path.getsize(path)/1024:.0f} KiB  |O|max={np.abs(o).max():.4f}")
+
+
+if __name__ == "__main__":
+    main()
