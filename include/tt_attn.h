@@ -128,6 +128,16 @@ const char* tt_attn_bwd_path(const tt_attn_desc* desc);
  * TT_OK, or TT_ERR_TIMEOUT with details in tt_last_error(). */
 int tt_check_device_status(void* stream);
 
+/* Optional per-kernel timing: while enabled, every kernel launch of this library is
+ * bracketed by CUDA events on its launching stream.  tt_profile_read() waits for the
+ * recorded events and returns the accumulated device time and launch count of one kernel
+ * family (ids 0 .. tt_profile_kernel_count()-1, names from tt_profile_kernel_name()). */
+int tt_profile_enable(int on);
+int tt_profile_reset(void);
+int tt_profile_kernel_count(void);
+const char* tt_profile_kernel_name(int kernel_id);
+int tt_profile_read(int kernel_id, double* total_ms, uint64_t* launches);
+
 /* Building-block self test of the tensor-core plumbing (TMA load -> tcgen05.mma from
  * shared memory -> tcgen05.ld, tcgen05.st -> tcgen05.mma with A in tensor memory and an
  * MN-major B).  a,b: bf16 [128,128] row-major; vt: bf16 [128,D] row-major (D = 64|128).

@@ -50,6 +50,11 @@ SIGNATURES = {
     "tt_attn_fwd_path": (c_char_p, [_DP]),
     "tt_attn_bwd_path": (c_char_p, [_DP]),
     "tt_check_device_status": (c_int, [_P]),
+    "tt_profile_enable": (c_int, [c_int]),
+    "tt_profile_reset": (c_int, []),
+    "tt_profile_kernel_count": (c_int, []),
+    "tt_profile_kernel_name": (c_char_p, [c_int]),
+    "tt_profile_read": (c_int, [c_int, POINTER(ctypes.c_double), POINTER(c_uint64)]),
     "tt_debug_umma_probe": (c_int, [_P, _P, _P, c_int32, _P, _P, _P]),
 }
 
@@ -107,3 +112,22 @@ def shard_range(n_slices: int, world: int, rank: int):
 
 def launch_count() -> int:
     return int(lib.tt_kernel_launch_count())
+
+
+def profile_enable(on: bool = True) -> None:
+    check(lib.tt_profile_enable(1 if on else 0))
+
+
+def profile_reset() -> None:
+    check(lib.tt_profile_reset())
+
+
+def profile_read() -> dict:
+    """{kernel name: (total device ms, timed launches)} for every kernel family with launches."""
+    res = {}
+    for i in range(int(lib.tt_profile_kernel_count())):
+        ms, n = ctypes.c_double(0.0), c_uint64(0)
+        check(lib.tt_profile_read(i, ctypes.byref(ms), ctypes.byref(n)))
+        if n.value:
+            res[lib.tt_profile_kernel_name(i).decode()] = (float(ms.value), int(n.value))
+    return res

@@ -387,9 +387,11 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     float* delta = reinterpret_cast<float*>(ws);
     float* lse2 = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(ws) + align256((size_t)a.BH * a.S * sizeof(float)));
     const long long n_rows = a.BH * (long long)a.S;
-    attn_bwd_prep_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>(
-        (const __nv_bfloat16*)a.out, (const __nv_bfloat16*)a.dout, a.lse, delta, lse2, n_rows, D);
-    count_launch();
+    {
+        LaunchScope ls(K_BWD_PREP, st);
+        attn_bwd_prep_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>(
+            (const __nv_bfloat16*)a.out, (const __nv_bfloat16*)a.dout, a.lse, delta, lse2, n_rows, D);
+    }
     TmapStorage tq, tk, tv, tdo;
     const char* why = nullptr;
     if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
@@ -416,16 +418,20 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.out0 = (__nv_bfloat16*)a.dv;
     p.out1 = (__nv_bfloat16*)a.dk;
     p.n_tiles = (a.L + 127) / 128;
-    attn_bwd_sm100_kernel<D, true><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
-        M(tk), M(tv), M(tq), M(tdo), p);
-    count_launch();
+    {
+        LaunchScope ls(K_BWD_DKV, st);
+        attn_bwd_sm100_kernel<D, true><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+            M(tk), M(tv), M(tq), M(tdo), p);
+    }
     // dQ: queries resident, stream (K, V)
     p.out0 = nullptr;
     p.out1 = (__nv_bfloat16*)a.dq;
     p.n_tiles = (a.S + 127) / 128;
-    attn_bwd_sm100_kernel<D, false><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
-        M(tq), M(tdo), M(tk), M(tv), p);
-    count_launch();
+    {
+        LaunchScope ls(K_BWD_DQ, st);
+        attn_bwd_sm100_kernel<D, false><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+            M(tq), M(tdo), M(tk), M(tv), p);
+    }
     return cudaGetLastError();
 }
 

@@ -234,14 +234,16 @@ DecodePlan attn_decode_plan(const AttnArgs& a) {
 template <int D>
 static cudaError_t launch_decode(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaStream_t st) {
     const long long units = a.BH * pl.splits;
-    attn_decode_bf16_kernel<D><<<(unsigned)units, kDecThreads, 0, st>>>(
-        (const __nv_bfloat16*)a.q, (const __nv_bfloat16*)a.k, (const __nv_bfloat16*)a.v, (__nv_bfloat16*)a.out, a.lse,
-        (float*)ws, a.L, pl.splits, pl.chunk, a.scale * 1.4426950408889634f);
-    count_launch();
+    {
+        LaunchScope ls(K_DECODE, st);
+        attn_decode_bf16_kernel<D><<<(unsigned)units, kDecThreads, 0, st>>>(
+            (const __nv_bfloat16*)a.q, (const __nv_bfloat16*)a.k, (const __nv_bfloat16*)a.v, (__nv_bfloat16*)a.out,
+            a.lse, (float*)ws, a.L, pl.splits, pl.chunk, a.scale * 1.4426950408889634f);
+    }
     if (pl.splits > 1) {
+        LaunchScope ls(K_DECODE_MERGE, st);
         attn_decode_merge_kernel<D><<<(unsigned)a.BH, D, 0, st>>>((const float*)ws, (__nv_bfloat16*)a.out, a.lse,
                                                                   pl.splits);
-        count_launch();
     }
     return cudaGetLastError();
 }

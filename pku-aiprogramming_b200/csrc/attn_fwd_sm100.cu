@@ -377,10 +377,12 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = device_status_word();
     unsigned grid = (unsigned)(a.BH * p.n_qblk);
-    attn_fwd_sm100_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
-        *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
-        *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
-    count_launch();
+    {
+        LaunchScope ls(K_FWD_TC, st);
+        attn_fwd_sm100_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+            *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
+            *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
+    }
     return cudaGetLastError();
 }
 
@@ -505,11 +507,13 @@ static cudaError_t launch_probe(const void* a, const void* b, const void* vt, fl
     const int smem = 6 * 128 * 128 + 1024 + 1024;
     cudaError_t e = cudaFuncSetAttribute(umma_probe_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    umma_probe_kernel<D><<<1, 128, smem, st>>>(*reinterpret_cast<CUtensorMap*>(ta.bytes),
-                                               *reinterpret_cast<CUtensorMap*>(tb.bytes),
-                                               *reinterpret_cast<CUtensorMap*>(tv.bytes), s_out, o_out,
-                                               device_status_word());
-    count_launch();
+    {
+        LaunchScope ls(K_PROBE, st);
+        umma_probe_kernel<D><<<1, 128, smem, st>>>(*reinterpret_cast<CUtensorMap*>(ta.bytes),
+                                                   *reinterpret_cast<CUtensorMap*>(tb.bytes),
+                                                   *reinterpret_cast<CUtensorMap*>(tv.bytes), s_out, o_out,
+                                                   device_status_word());
+    }
     return cudaGetLastError();
 }
 

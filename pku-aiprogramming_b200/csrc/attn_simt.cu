@@ -345,19 +345,23 @@ static cudaError_t launch_fwd_simt(const AttnArgs& a, cudaStream_t st) {
     cudaError_t e = set_smem(attn_fwd_simt_kernel<T, NV>, smem);
     if (e != cudaSuccess) return e;
     unsigned grid = (unsigned)(((a.S + kRowsPerBlock - 1) / kRowsPerBlock) * a.BH);
-    attn_fwd_simt_kernel<T, NV><<<grid, kSimtThreads, smem, st>>>((const T*)a.q, (const T*)a.k, (const T*)a.v,
-                                                                  (T*)a.out, a.lse, a.S, a.L, a.D, a.causal,
-                                                                  a.scale);
-    count_launch();
+    {
+        LaunchScope ls(K_FWD_SIMT, st);
+        attn_fwd_simt_kernel<T, NV><<<grid, kSimtThreads, smem, st>>>((const T*)a.q, (const T*)a.k, (const T*)a.v,
+                                                                      (T*)a.out, a.lse, a.S, a.L, a.D, a.causal,
+                                                                      a.scale);
+    }
     return cudaGetLastError();
 }
 
 template <typename T, int NV>
 static cudaError_t launch_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t st) {
     long long n_rows = a.BH * (long long)a.S;
-    attn_bwd_delta_kernel<T><<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>((const T*)a.out, (const T*)a.dout, delta,
-                                                                          n_rows, a.D);
-    count_launch();
+    {
+        LaunchScope ls(K_BWD_SIMT_DELTA, st);
+        attn_bwd_delta_kernel<T><<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>((const T*)a.out, (const T*)a.dout,
+                                                                              delta, n_rows, a.D);
+    }
     size_t smem_q = (size_t)4 * 32 * (a.D + 1) * sizeof(float);
     size_t smem_kv = smem_q + 64 * sizeof(float);
     cudaError_t e = set_smem(attn_bwd_dq_simt_kernel<T, NV>, smem_q);
@@ -365,15 +369,19 @@ static cudaError_t launch_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t
     e = set_smem(attn_bwd_dkv_simt_kernel<T, NV>, smem_kv);
     if (e != cudaSuccess) return e;
     unsigned gq = (unsigned)(((a.S + kRowsPerBlock - 1) / kRowsPerBlock) * a.BH);
-    attn_bwd_dq_simt_kernel<T, NV><<<gq, kSimtThreads, smem_q, st>>>(
-        (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dq, a.S, a.L, a.D,
-        a.causal, a.scale);
-    count_launch();
+    {
+        LaunchScope ls(K_BWD_SIMT_DQ, st);
+        attn_bwd_dq_simt_kernel<T, NV><<<gq, kSimtThreads, smem_q, st>>>(
+            (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dq, a.S, a.L, a.D,
+            a.causal, a.scale);
+    }
     unsigned gk = (unsigned)(((a.L + kRowsPerBlock - 1) / kRowsPerBlock) * a.BH);
-    attn_bwd_dkv_simt_kernel<T, NV><<<gk, kSimtThreads, smem_kv, st>>>(
-        (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dk, (T*)a.dv, a.S, a.L,
-        a.D, a.causal, a.scale);
-    count_launch();
+    {
+        LaunchScope ls(K_BWD_SIMT_DKV, st);
+        attn_bwd_dkv_simt_kernel<T, NV><<<gk, kSimtThreads, smem_kv, st>>>(
+            (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dk, (T*)a.dv, a.S,
+            a.L, a.D, a.causal, a.scale);
+    }
     return cudaGetLastError();
 }
 

@@ -22,7 +22,20 @@ struct AttnArgs {
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
-void count_launch();
+// Kernel families, for launch accounting and the optional per-kernel event timing.
+enum KernelId {
+    K_FWD_TC = 0, K_FWD_SIMT, K_BWD_PREP, K_BWD_DKV, K_BWD_DQ, K_BWD_SIMT_DELTA, K_BWD_SIMT_DQ, K_BWD_SIMT_DKV,
+    K_DECODE, K_DECODE_MERGE, K_PROBE, K_COUNT
+};
+// Scoped around ONE kernel launch: counts it and, when timing is enabled, brackets it with
+// CUDA events on the launching stream.
+struct LaunchScope {
+    LaunchScope(KernelId id, cudaStream_t st);
+    ~LaunchScope();
+    KernelId id;
+    cudaStream_t st;
+    void* rec;
+};
 unsigned int* device_status_word();  // 4 x uint32 in global memory of the current device (zeroed)
 
 // --- SIMT fp32-arithmetic kernels (any D <= 256, float or bf16 tensors)

@@ -30,7 +30,52 @@ static int cuda_fail(cudaError_t e, const char* what) {
 }
 
 static std::atomic<uint64_t> g_launches{0};
-void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// ------------------------------------------------------------------------------ per-kernel event timing
+static const char* const kKernelNames[K_COUNT] = {
+    "attn_fwd_sm100", "attn_fwd_simt", "attn_bwd_prep", "attn_bwd_sm100_dkv", "attn_bwd_sm100_dq",
+    "attn_bwd_simt_delta", "attn_bwd_simt_dq", "attn_bwd_simt_dkv", "attn_decode", "attn_decode_merge",
+    "umma_probe"};
+struct TimedLaunch {
+    KernelId id;
+    cudaEvent_t start, stop;
+};
+static std::atomic<int> g_timing_on{0};
+static std::mutex g_timing_mu;
+static std::vector<TimedLaunch*> g_pending;          // recorded, not yet read back
+static std::vector<TimedLaunch*> g_free_records;     // events are reused
+static double g_total_ms[K_COUNT];
+static uint64_t g_timed_launches[K_COUNT];
+
+LaunchScope::LaunchScope(KernelId id_, cudaStream_t st_) : id(id_), st(st_), rec(nullptr) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (!g_timing_on.load(std::memory_order_relaxed)) return;
+    TimedLaunch* r = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_timing_mu);
+        if (!g_free_records.empty()) {
+            r = g_free_records.back();
+            g_free_records.pop_back();
+        }
+    }
+    if (!r) {
+        r = new TimedLaunch();
+        if (cudaEventCreate(&r->start) != cudaSuccess || cudaEventCreate(&r->stop) != cudaSuccess) {
+            delete r;
+            return;
+        }
+    }
+    r->id = id;
+    cudaEventRecord(r->start, st);
+    rec = r;
+}
+LaunchScope::~LaunchScope() {
+    if (!rec) return;
+    TimedLaunch* r = static_cast<TimedLaunch*>(rec);
+    cudaEventRecord(r->stop, st);
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    g_pending.push_back(r);
+}
 
 // ------------------------------------------------------------------------------ device status word
 __device__ unsigned int g_device_status[4];
@@ -368,6 +413,44 @@ int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const
     a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
     cudaError_t e = attn_decode(a, pl, workspace, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "tt_attn_decode: launch");
+    return TT_OK;
+}
+
+int tt_profile_enable(int on) {
+    g_timing_on.store(on ? 1 : 0);
+    return TT_OK;
+}
+int tt_profile_reset(void) {
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    for (TimedLaunch* r : g_pending) {
+        cudaEventSynchronize(r->stop);
+        g_free_records.push_back(r);
+    }
+    g_pending.clear();
+    for (int i = 0; i < K_COUNT; ++i) {
+        g_total_ms[i] = 0.0;
+        g_timed_launches[i] = 0;
+    }
+    return TT_OK;
+}
+int tt_profile_kernel_count(void) { return K_COUNT; }
+const char* tt_profile_kernel_name(int kernel_id) {
+    return (kernel_id >= 0 && kernel_id < K_COUNT) ? kKernelNames[kernel_id] : "";
+}
+int tt_profile_read(int kernel_id, double* total_ms, uint64_t* launches) {
+    if (kernel_id < 0 || kernel_id >= K_COUNT) return fail(TT_ERR_BAD_SHAPE, "tt_profile_read: kernel id %d", kernel_id);
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    for (TimedLaunch* r : g_pending) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(r->stop) == cudaSuccess && cudaEventElapsedTime(&ms, r->start, r->stop) == cudaSuccess) {
+            g_total_ms[r->id] += ms;
+            g_timed_launches[r->id] += 1;
+        }
+        g_free_records.push_back(r);
+    }
+    g_pending.clear();
+    if (total_ms) *total_ms = g_total_ms[kernel_id];
+    if (launches) *launches = g_timed_launches[kernel_id];
     return TT_OK;
 }
 
