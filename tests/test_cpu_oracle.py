@@ -1,0 +1,99 @@
+"""CPU tests of the oracle: pinned against the golden fixtures (outputs of the reference's own
+ops, see tests/golden/make_golden.py), an independent float64 closed form, and finite
+differences -- the way the reference's course template validated its NumPy ops."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+
+
+def test_fixtures_present():
+    names = {os.path.basename(p) for p in GOLDEN}
+    assert "cfg1_f32_b2h4s64d32.npz" in names and len(GOLDEN) >= 6
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_oracle_reproduces_reference_outputs_bit_exactly(oracle, path):
+    """The restatement performs the same NumPy calls in the same order as the reference's
+    composed ops, so fp32 results are identical to the last bit."""
+    g = np.load(path)
+    o, lse, dq, dk, dv = oracle.attention_backward(g["q"], g["k"], g["v"], g["do"], bool(g["causal"]), float(g["scale"]))
+    for got, name in ((o, "o"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert got.dtype == np.float32
+        assert np.array_equal(got, g[name]), name
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_reference_outputs_match_float64_closed_form(oracle, path):
+    g = np.load(path)
+    ref = oracle.closed_form_f64(g["q"], g["k"], g["v"], g["do"], bool(g["causal"]), float(g["scale"]))
+    for got, want in zip((g["o"], g["dq"], g["dk"], g["dv"]), (ref[0], ref[2], ref[3], ref[4])):
+        assert oracle.rel_err(got, want) < 2e-6
+
+
+def test_config1_inputs_regenerate_from_seed(oracle):
+    """BASELINE config 1: Q/K/V/dO [2,4,64,32] ~ N(0,1) from seed 0; the fixture stores exactly
+    what `make_inputs` produces, so any rank can rebuild its shard."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "cfg1_f32_b2h4s64d32.npz"))
+    q, k, v, do = oracle.make_inputs(0, 2, 4, 64, 64, 32)
+    for a, n in ((q, "q"), (k, "k"), (v, "v"), (do, "do")):
+        assert np.array_equal(a, g[n])
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_finite_differences(oracle, causal):
+    """d/dx sum(O * dO) by central differences in float64 against the analytic gradients."""
+    rng = np.random.default_rng(0)
+    B, H, S, L, D = 1, 2, 5, 7, 4
+    q, k, v = (rng.standard_normal((B, H, n, D)) for n in (S, L, L))
+    do = rng.standard_normal((B, H, S, D))
+    _, _, dq, dk, dv = oracle.attention_backward(q, k, v, do, causal)
+
+    def f(q_, k_, v_):
+        return float((oracle.attention_forward(q_, k_, v_, causal)[0] * do).sum())
+
+    eps = 1e-6
+    for x, gx, idx in ((q, dq, 0), (k, dk, 1), (v, dv, 2)):
+        num = np.zeros_like(x)
+        it = np.nditer(x, flags=["multi_index"])
+        for _ in it:
+            i = it.multi_index
+            args = [q.copy(), k.copy(), v.copy()]
+            args[idx][i] += eps
+            fp = f(*args)
+            args[idx][i] -= 2 * eps
+            fm = f(*args)
+            num[i] = (fp - fm) / (2 * eps)
+        assert np.max(np.abs(num - gx)) < 1e-6
+
+
+def test_causal_first_row_and_alignment(oracle):
+    q, k, v, _ = oracle.make_inputs(3, 1, 1, 6, 9, 8, with_do=False)
+    o, lse = oracle.attention_forward(q, k, v, causal=True)
+    # bottom-right alignment: query 0 sees keys 0..3 (L - S = 3), the last query sees all 9
+    m = oracle.causal_mask(6, 9)
+    assert (m[0, :4] == 0).all() and (m[0, 4:] < -1e29).all() and (m[5] == 0).all()
+    o_rows, lse_rows = oracle.attention_rows(q[0, 0, 2:5], k[0, 0], v[0, 0], 2, 6, causal=True)
+    assert np.allclose(o_rows, o[0, 0, 2:5], atol=1e-6) and np.allclose(lse_rows, lse[0, 0, 2:5], atol=1e-6)
+    # square causal: the first row attends to one key only
+    o2, _ = oracle.attention_forward(q, k[:, :, :6], v[:, :, :6], causal=True)
+    assert np.allclose(o2[0, 0, 0], v[0, 0, 0], atol=1e-6)
+
+
+def test_bf16_rounding_matches_torch(oracle):
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal(100000) * np.exp(rng.uniform(-20, 20, 100000))).astype(np.float32)
+    want = torch.from_numpy(x).to(torch.bfloat16).float().numpy()
+    assert np.array_equal(oracle.bf16_round(x), want)
+    assert np.array_equal(oracle.bf16_bits_to_f32(oracle.bf16_bits(x)), want)
+
+
+def test_lse_is_log_of_denominator(oracle):
+    q, k, v, _ = oracle.make_inputs(5, 1, 2, 9, 9, 16, with_do=False)
+    _, lse = oracle.attention_forward(q, k, v, causal=True)
+    _, lse64 = oracle.closed_form_f64(q, k, v, None, True)
+    assert np.max(np.abs(lse - lse64)) < 1e-5
