@@ -92,6 +92,26 @@ size_t tt_attn_decode_workspace_bytes(const tt_attn_desc* desc);
 int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
                    void* out, float* lse, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Decode for callers that cannot allocate device memory.  No counterpart in the reference:
+ * it exists for hosts that run with a frozen memory map -- code inside a CUDA-graph capture
+ * or a real-time serving loop that pre-allocated everything, or a plugin sandbox whose policy
+ * forbids cudaMalloc -- and therefore cannot supply the partials workspace tt_attn_decode
+ * wants.  Same kernels and same results as tt_attn_decode; the split-KV partials go to an
+ * 8 MiB array built into the library's device image (each GPU that loads the library keeps
+ * those 8 MiB until the process exits).  The call itself performs no cudaMalloc/cudaFree and
+ * calls no allocating library routine; q, k, v, out (and lse) are still the caller's.
+ *   - bf16, D = 64 or 128, S = 1 only; problems whose partials exceed the array are refused
+ *     with TT_ERR_WORKSPACE and a message naming both sizes (B*H*(D+2)*4*splits bytes; e.g.
+ *     B*H up to ~4000 slices at D = 128 with 4 key ranges each).
+ *   - The first call on each device looks up the array's device address (one runtime query);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call
+ *     left; nothing in it needs clearing because each call overwrites every partial it
+ *     later reads.  Two calls that overlap on the GPU (different streams) race on it:
+ *     serialise them. */
+int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                          void* out, float* lse, void* stream);
+
 /* ---- host-buffer calls (what the reference's Python ops do around each native op:
  * upload NumPy -> run -> download, optimizer/operators.py:502-512) ----------------------
  * Pointers are HOST pointers (pinned memory gives the best copy rate).  Device buffers

@@ -37,6 +37,7 @@ SIGNATURES = {
     "tt_attn_bwd": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
     "tt_attn_decode_workspace_bytes": (c_size_t, [_DP]),
     "tt_attn_decode": (c_int, [_DP, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
+    "tt_attn_decode_static": (c_int, [_DP, _P, _P, _P, _P, _P, _P]),
     "tt_attn_fwd_host": (c_int, [_DP, _P, _P, _P, _P, _P]),
     "tt_attn_bwd_host": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "tt_attn_decode_host": (c_int, [_DP, _P, _P, _P, _P, _P]),

@@ -14,6 +14,7 @@
 //     per slice the unnormalised (max, sum, out) partials go to the workspace and a small
 //     second kernel merges them.
 #include "common.h"
+#include <atomic>
 
 namespace ttk {
 
@@ -232,16 +233,17 @@ DecodePlan attn_decode_plan(const AttnArgs& a) {
 }
 
 template <int D>
-static cudaError_t launch_decode(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaStream_t st) {
+static cudaError_t launch_decode(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaStream_t st,
+                                 bool allow_timing = true) {
     const long long units = a.BH * pl.splits;
     {
-        LaunchScope ls(K_DECODE, st);
+        LaunchScope ls(K_DECODE, st, allow_timing);
         attn_decode_bf16_kernel<D><<<(unsigned)units, kDecThreads, 0, st>>>(
             (const __nv_bfloat16*)a.q, (const __nv_bfloat16*)a.k, (const __nv_bfloat16*)a.v, (__nv_bfloat16*)a.out,
             a.lse, (float*)ws, a.L, pl.splits, pl.chunk, a.scale * 1.4426950408889634f);
     }
     if (pl.splits > 1) {
-        LaunchScope ls(K_DECODE_MERGE, st);
+        LaunchScope ls(K_DECODE_MERGE, st, allow_timing);
         attn_decode_merge_kernel<D><<<(unsigned)a.BH, D, 0, st>>>((const float*)ws, (__nv_bfloat16*)a.out, a.lse,
                                                                   pl.splits);
     }
@@ -252,6 +254,43 @@ cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaS
     if (a.bf16 && a.S == 1 && a.D == 128) return launch_decode<128>(a, pl, ws, st);
     if (a.bf16 && a.S == 1 && a.D == 64) return launch_decode<64>(a, pl, ws, st);
     return attn_fwd_simt(a, st);
+}
+
+// ------------------------------------------------------------------------------------------
+// Variant for callers that must not allocate device memory: the split-KV partials live in a
+// fixed array that is part of this library's device image.  Every context that loads the
+// library carries these bytes until it exits, whether or not this path is ever called.
+constexpr size_t kStaticScratchBytes = (size_t)8 << 20;   // 8 MiB
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, not a device address: the
+// address a kernel can use has to be asked for, per device, with that device current.
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices];
+static std::atomic<int> g_static_scratch_ready[kMaxDevices];
+
+size_t attn_decode_static_capacity() { return kStaticScratchBytes; }
+
+cudaError_t attn_decode_static(const AttnArgs& a, const DecodePlan& pl, cudaStream_t st, bool* too_big) {
+    *too_big = pl.ws_bytes > kStaticScratchBytes;
+    if (*too_big) return cudaSuccess;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!g_static_scratch_ready[dev].load(std::memory_order_acquire)) {
+        // first call on this device: resolve the device address of the array
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_static_scratch_addr[dev] = p;
+        g_static_scratch_ready[dev].store(1, std::memory_order_release);
+    }
+    void* scratch = g_static_scratch_addr[dev];
+    // Nothing in the array has to start at zero: every partial the merge kernel reads is
+    // written by the first kernel of the same call.
+    if (a.D == 128) return launch_decode<128>(a, pl, scratch, st, /*allow_timing=*/false);
+    return launch_decode<64>(a, pl, scratch, st, /*allow_timing=*/false);
 }
 
 }  // namespace ttk

@@ -30,7 +30,8 @@ enum KernelId {
 // Scoped around ONE kernel launch: counts it and, when timing is enabled, brackets it with
 // CUDA events on the launching stream.
 struct LaunchScope {
-    LaunchScope(KernelId id, cudaStream_t st);
+    // allow_timing = false: count only (creates no events, so nothing is allocated)
+    LaunchScope(KernelId id, cudaStream_t st, bool allow_timing = true);
     ~LaunchScope();
     KernelId id;
     cudaStream_t st;
@@ -60,6 +61,10 @@ struct DecodePlan {
 };
 DecodePlan attn_decode_plan(const AttnArgs& a);
 cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& plan, void* workspace, cudaStream_t st);
+// Same kernels, partials in the library's own fixed device array (no allocation anywhere).
+// *too_big is set when the plan needs more than the array holds (nothing is launched then).
+size_t attn_decode_static_capacity();
+cudaError_t attn_decode_static(const AttnArgs& a, const DecodePlan& plan, cudaStream_t st, bool* too_big);
 
 // Builds a 3-D bf16 tensor map over a dense [slices, rows, cols] array, box
 // [1, box_rows, 64] with 128-byte swizzle.  Returns false (and sets `why`) on failure.

@@ -47,9 +47,9 @@ static std::vector<TimedLaunch*> g_free_records;     // events are reused
 static double g_total_ms[K_COUNT];
 static uint64_t g_timed_launches[K_COUNT];
 
-LaunchScope::LaunchScope(KernelId id_, cudaStream_t st_) : id(id_), st(st_), rec(nullptr) {
+LaunchScope::LaunchScope(KernelId id_, cudaStream_t st_, bool allow_timing) : id(id_), st(st_), rec(nullptr) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (!g_timing_on.load(std::memory_order_relaxed)) return;
+    if (!allow_timing || !g_timing_on.load(std::memory_order_relaxed)) return;
     TimedLaunch* r = nullptr;
     {
         std::lock_guard<std::mutex> lk(g_timing_mu);
@@ -413,6 +413,33 @@ int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const
     a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
     cudaError_t e = attn_decode(a, pl, workspace, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "tt_attn_decode: launch");
+    return TT_OK;
+}
+
+int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k, const void* v, void* out,
+                          float* lse, void* stream) {
+    AttnArgs a;
+    int rc = resolve(desc, &a, "tt_attn_decode_static");
+    if (rc != TT_OK) return rc;
+    if (a.S != 1) return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_static: S must be 1, got %d", a.S);
+    if (!(a.bf16 && (a.D == 64 || a.D == 128)))
+        return fail(TT_ERR_UNSUPPORTED, "tt_attn_decode_static: bf16 with head dim 64 or 128 only (got dtype %d, D=%d)",
+                    desc->dtype, a.D);
+    if (!q || !k || !v || !out) return fail(TT_ERR_NULL, "tt_attn_decode_static: q, k, v and out must be non-null");
+    if (!(aligned16(q) && aligned16(k) && aligned16(v)))
+        return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_static: q, k, v must be 16-byte aligned");
+    if ((rc = check_device()) != TT_OK) return rc;
+    a.causal = 0;
+    DecodePlan pl = attn_decode_plan(a);
+    a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
+    bool too_big = false;
+    cudaError_t e = attn_decode_static(a, pl, (cudaStream_t)stream, &too_big);
+    if (too_big)
+        return fail(TT_ERR_WORKSPACE,
+                    "tt_attn_decode_static: this problem needs %zu bytes of partials but the built-in scratch array "
+                    "holds %zu; use tt_attn_decode with a caller-provided workspace", pl.ws_bytes,
+                    attn_decode_static_capacity());
+    if (e != cudaSuccess) return cuda_fail(e, "tt_attn_decode_static");
     return TT_OK;
 }
 
