@@ -40,7 +40,12 @@ WORKLOADS = {
 }
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
 # summaries under profiles/ ; None until a capture of that kernel exists.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # cfg3, one launch each: profiles/attn_fwd_bwd_sm100_cfg3.md
+    "attn_fwd_sm100": 520.8e6, "attn_bwd_sm100_dkv": 780.9e6, "attn_bwd_sm100_dq": 664.1e6,
+    # config 4 = 8 x the captured batch-8 launch: profiles/attn_decode_bf16_b8.md
+    "attn_decode": 8.637e9,
+}
 
 
 def fwd_flops(B, H, S, L, D, causal=True):
@@ -163,6 +168,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--decode-batch", type=int, default=64, help="batch of the decode leg (64 = BASELINE config 4)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
@@ -272,7 +278,8 @@ def main():
         if name in alg:
             ach = alg[name] * f_fwd / (per * 1e-3) / 1e12
             ent.update({"bound": "tensor", "achieved": ach, "peak": peaks["bf16"], "unit": "TFLOP/s",
-                        "frac": ach / peaks["bf16"], "traffic": NCU_TRAFFIC_BYTES.get(name)})
+                        "frac": ach / peaks["bf16"],
+                        "traffic": NCU_TRAFFIC_BYTES.get(name) if args.workload == "cfg3" else None})
         kernels[name] = ent
     dom = max((n for n in kernels if n in alg), key=lambda n: kernels[n]["share"], default=None)
     roofline = None
@@ -315,7 +322,7 @@ def main():
     decode = None
     if rank == 0 and not args.no_decode:
         try:
-            dB, dH, dL, dD = 64, 32, 8192, 128
+            dB, dH, dL, dD = args.decode_batch, 32, 8192, 128
             dq_ = torch.randn((dB, dH, 1, dD), device=dev).to(torch.bfloat16)
             dk_ = torch.randn((dB, dH, dL, dD), device=dev).to(torch.bfloat16)
             dv_ = torch.randn((dB, dH, dL, dD), device=dev).to(torch.bfloat16)
@@ -335,9 +342,9 @@ def main():
             ms = a.elapsed_time(b) / 20
             by = 2.0 * dB * dH * dL * dD * 2 + 2.0 * dB * dH * dD * 2
             kms = dprof["attn_decode"][0] / dprof["attn_decode"][1]
-            decode = {"workload": "bf16 decode Q [64,32,1,128], K/V [64,32,8192,128]", "ms": ms, "gbs": by / ms / 1e6,
+            decode = {"workload": f"bf16 decode Q [{dB},32,1,128], K/V [{dB},32,8192,128]", "ms": ms, "gbs": by / ms / 1e6,
                       "roofline": {"bound": "hbm", "achieved": by / kms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
-                                   "frac": by / kms / 1e6 / peaks["hbm"], "traffic": NCU_TRAFFIC_BYTES.get("attn_decode"),
+                                   "frac": by / kms / 1e6 / peaks["hbm"], "traffic": NCU_TRAFFIC_BYTES.get("attn_decode") if dB == 64 else None,
                                    "kernel": "attn_decode", "peak_source": f"hbm_gbs of {peaks['source']} MEASURED_PEAKS.json"}}
             del dq_, dk_, dv_
         except Exception as e:  # noqa: BLE001
