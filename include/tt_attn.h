@@ -158,6 +158,14 @@ int tt_profile_kernel_count(void);
 const char* tt_profile_kernel_name(int kernel_id);
 int tt_profile_read(int kernel_id, double* total_ms, uint64_t* launches);
 
+/* Debug aid for tuning the tensor-core forward: while `device_buf` (3*64*8 int64, device
+ * memory) is non-null, CTA number `block` of every forward launch records clock64() at its
+ * hand-off points (softmax warpgroups: wait for S, S loaded, max known, P half/whole written;
+ * MMA issuer: waits and issues).  Pass null to switch it off. */
+int tt_debug_fwd_trace(void* device_buf, int32_t block);
+/* Same for the tensor-core backward; pass = 1 traces the dK/dV launch, 2 the dQ launch. */
+int tt_debug_bwd_trace(void* device_buf, int32_t block, int32_t pass);
+
 /* Building-block self test of the tensor-core plumbing (TMA load -> tcgen05.mma from
  * shared memory -> tcgen05.ld, tcgen05.st -> tcgen05.mma with A in tensor memory and an
  * MN-major B).  a,b: bf16 [128,128] row-major; vt: bf16 [128,D] row-major (D = 64|128).

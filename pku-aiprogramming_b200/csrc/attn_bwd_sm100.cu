@@ -24,6 +24,7 @@
 // P / dS written by warpgroup w overlay columns [64w,64w+32) of S / dP.
 #include "common.h"
 #include "sm100_ptx.cuh"
+#include <stdlib.h>
 
 namespace ttk {
 using namespace sm100;
@@ -41,7 +42,7 @@ struct BwdCfg {
 };
 
 enum BwdBarId { BB_RES = 0, BB_STFULL = 10, BB_STEMPTY = 20, BB_SFULL = 30, BB_DPFULL = 31, BB_PFULL = 32,
-                BB_DSFULL = 33, BB_FINAL = 34 };
+                BB_DSFULL = 33, BB_FINAL = 34, BB_PREAD = 35 };
 
 struct BwdParams {
     __nv_bfloat16* out0;   // keys resident: dV ; else unused
@@ -53,13 +54,23 @@ struct BwdParams {
     int causal;
     float scale, scale_log2;
     unsigned int* status;
+    long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
+    int trace_block;
 };
+
+#define TT_BTRACE(role, iter, slot)                                                                 \
+    do {                                                                                           \
+        if (p.trace != nullptr && (int)blockIdx.x == p.trace_block && (iter) < 64)                 \
+            p.trace[((role) * 64 + (iter)) * 8 + (slot)] = clock64();                              \
+    } while (0)
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-template <int D, bool kKeysResident>
+// kPoly: of every 8 pairs of exponentials, kPoly are evaluated by a polynomial on the FMA pipes
+// instead of the special-function unit.
+template <int D, bool kKeysResident, int kPoly>
 __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_constant__ CUtensorMap tmR1,
                       const __grid_constant__ CUtensorMap tmT0, const __grid_constant__ CUtensorMap tmT1,
@@ -79,11 +90,12 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
     uint64_t* bar_p_full = bar_dp_full + 1;
     uint64_t* bar_ds_full = bar_p_full + 1;
     uint64_t* bar_final = bar_ds_full + 1;
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bar_final + 1);
+    uint64_t* bar_p_read = bar_final + 1;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bar_p_read + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     float* s_stat = reinterpret_cast<float*>(aux + 1024);     // [2 buffers][2: lse2, delta][128]
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = uniform_warp_idx();
     const int lane = threadIdx.x & 31;
     const int off = p.L - p.S;
     const int bh = blockIdx.x / p.n_tiles;
@@ -112,6 +124,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
         mbar_init(bar_dp_full, 1);
         mbar_init(bar_p_full, 256);
         mbar_init(bar_ds_full, 256);
+        mbar_init(bar_p_read, 1);
         mbar_init(bar_final, 1);
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -143,26 +156,38 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
         const uint32_t tS = tmem_base + lane_off + kColS + wg * 64;
         const uint32_t tDP = tmem_base + lane_off + kColDP + wg * 64;
         const int ctid = threadIdx.x;                          // 0..255 among compute threads
-        float row_lse2 = 0.f, row_delta = 0.f;
+        // row constants (queries resident) as packed pairs of the NEGATED values
+        uint64_t row_nlse2 = 0, row_ndelta2 = 0;
         if (!kKeysResident) {
             const bool ok = rrow < p.S;
-            row_lse2 = ok ? p.lse2[(long long)bh * p.S + rrow] : INFINITY;
-            row_delta = ok ? p.delta[(long long)bh * p.S + rrow] : 0.f;
+            const float nl = ok ? -p.lse2[(long long)bh * p.S + rrow] : -INFINITY;
+            const float nd = ok ? -p.delta[(long long)bh * p.S + rrow] : 0.f;
+            row_nlse2 = pack_f32x2(nl, nl);
+            row_ndelta2 = pack_f32x2(nd, nd);
         }
+        // per-column statistics (keys resident): thread ctid fetches -lse2 (ctid < 128) or -delta of
+        // streamed query (ctid & 127), one tile ahead of its use
+        const float* stat_src = (ctid < 128 ? p.lse2 : p.delta) + (long long)bh * p.S;
+        const float stat_oob = (ctid < 128) ? -INFINITY : 0.f;
+        float stat_next = stat_oob;
+        if (kKeysResident && t_begin < t_end) {
+            const int qrow = t_begin * 128 + (ctid & 127);
+            stat_next = qrow < p.S ? -stat_src[qrow] : stat_oob;
+        }
+        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
         for (int t = t_begin; t < t_end; ++t) {
             const int it = t - t_begin;
             const int c0 = t * 128;                            // first streamed row of this tile
-            const float* st_lse = s_stat + (it & 1) * 256;
-            const float* st_delta = st_lse + 128;
+            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 0);
+            const float* st_nlse = s_stat + (it & 1) * 256;    // -lse2 of the 128 streamed queries
+            const float* st_ndelta = st_nlse + 128;            // -delta
             if (kKeysResident) {
-                // stage lse2 / delta of the 128 streamed queries
-                const int qrow = c0 + (ctid & 127);
-                const bool ok = qrow < p.S;
-                float val;
-                if (ctid < 128) val = ok ? p.lse2[(long long)bh * p.S + qrow] : INFINITY;
-                else val = ok ? p.delta[(long long)bh * p.S + qrow] : 0.f;
-                s_stat[(it & 1) * 256 + ctid] = val;
+                s_stat[(it & 1) * 256 + ctid] = stat_next;
                 named_bar_sync(1, 256);
+                if (t + 1 < t_end) {
+                    const int qrow = (t + 1) * 128 + (ctid & 127);
+                    stat_next = qrow < p.S ? -stat_src[qrow] : stat_oob;
+                }
             }
             // visible columns of this thread's row inside the tile: [vis_lo, vis_hi)
             int vis_lo = 0, vis_hi = 128;
@@ -173,39 +198,65 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 if (p.causal) vis_hi = min(vis_hi, rrow + off + 1 - c0);  // key <= query + off
                 vis_hi = min(vis_hi, 128);
             }
-            const bool need_mask = (vis_lo > 0) || (vis_hi < 128);   // per thread; the selects below are cheap
+            const bool need_mask = (vis_lo > 0) || (vis_hi < 128);
             // ---------------- phase A: P = exp2(S*c - lse2)
+            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 1);
             mbar_wait(bar_s_full, it & 1, wctx, BB_SFULL, it);
             __syncwarp();
             tc_fence_after();
-            float pf[64];
+            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 2);
+            uint64_t pf2[32];     // this thread's 64 probabilities, fp32 pairs
+            uint32_t sr[2][32];
+            if (!kKeysResident) {
+                // nothing is written back into the S columns in this pass: release them as soon as
+                // they are in registers so that the next tile's scores overlap these exponentials
+                tmem_ld32(tS, sr[0]);
+                tmem_ld32(tS + 32, sr[1]);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(bar_p_full);
+            }
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
-                uint32_t sr[32];
-                tmem_ld32(tS + cc * 32, sr);
-                tmem_wait_ld();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int col = wg * 64 + cc * 32 + e;
-                    const float l2 = kKeysResident ? st_lse[col] : row_lse2;
-                    float pv = ex2_approx(fmaf(__uint_as_float(sr[e]), p.scale_log2, -l2));
-                    if (need_mask) pv = (col >= vis_lo && col < vis_hi) ? pv : 0.f;
-                    pf[cc * 32 + e] = pv;
-                }
                 if (kKeysResident) {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int e = 0; e < 32; e += 2) pk[e >> 1] = pack_bf16x2(pf[cc * 32 + e], pf[cc * 32 + e + 1]);
-                    tmem_st16(tS + cc * 16, pk);
+                    tmem_ld32(tS + cc * 32, sr[cc]);
+                    tmem_wait_ld();
                 }
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int col = wg * 64 + cc * 32 + e;
+                    const uint64_t nl = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_nlse + col) : row_nlse2;
+                    const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, nl);
+                    float p0, p1;
+                    if ((((e >> 1) * kPoly) % 8) < kPoly) {   // kPoly of every 8 pairs on the FMA pipes
+                        ex2_poly_x2(x, p0, p1);
+                    } else {
+                        float a0, a1;
+                        unpack_f32x2(x, a0, a1);
+                        p0 = ex2_approx(a0);
+                        p1 = ex2_approx(a1);
+                    }
+                    if (need_mask) {
+                        p0 = (col >= vis_lo && col < vis_hi) ? p0 : 0.f;
+                        p1 = (col + 1 >= vis_lo && col + 1 < vis_hi) ? p1 : 0.f;
+                    }
+                    pf2[cc * 16 + (e >> 1)] = pack_f32x2(p0, p1);
+                    if (kKeysResident) pk[e >> 1] = pack_bf16x2(p0, p1);
+                }
+                if (kKeysResident) tmem_st16(tS + cc * 16, pk);
             }
-            if (kKeysResident) tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar_p_full);
+            if (kKeysResident) {
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar_p_full);
+            }
+            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 3);
             // ---------------- phase B: dS = P * (dP - delta)
             mbar_wait(bar_dp_full, it & 1, wctx, BB_DPFULL, it);
             __syncwarp();
             tc_fence_after();
+            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 4);
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 uint32_t dr[32];
@@ -215,10 +266,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
                     const int col = wg * 64 + cc * 32 + e;
-                    const float d0 = kKeysResident ? st_delta[col] : row_delta;
-                    const float d1 = kKeysResident ? st_delta[col + 1] : row_delta;
-                    const float x0 = pf[cc * 32 + e] * (__uint_as_float(dr[e]) - d0);
-                    const float x1 = pf[cc * 32 + e + 1] * (__uint_as_float(dr[e + 1]) - d1);
+                    const uint64_t nd = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_ndelta + col) : row_ndelta2;
+                    const uint64_t tdiff = add_f32x2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd);
+                    const uint64_t ds = mul_f32x2(pf2[cc * 16 + (e >> 1)], tdiff);
+                    float x0, x1;
+                    unpack_f32x2(ds, x0, x1);
                     pk[e >> 1] = pack_bf16x2(x0, x1);
                 }
                 tmem_st16(tDP + cc * 16, pk);
@@ -226,6 +278,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar_ds_full);
+            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 5);
         }
         // ---------------- epilogue: accumulators -> bf16 -> global (warpgroup w: columns [w*D/2, +D/2))
         mbar_wait(bar_final, 0, wctx, BB_FINAL, 0);
@@ -260,55 +313,70 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
         }
     } else {
         setmaxnreg_dec<56>();
-        if (warp == 9 && lane == 0) {
-            // ============================================================ TMA loader
+        if (warp == 9) {
+            // ============================================================ TMA loader (whole warp runs the
+            // control flow, one elected lane issues)
             auto load_tile = [&](unsigned char* dst, const CUtensorMap* tm, uint64_t* bar, int row_start) {
 #pragma unroll
                 for (int sb = 0; sb < Cfg::kSub; ++sb) tma_load_3d(dst + sb * Cfg::kSubBytes, tm, bar, sb * 64, row_start, bh);
             };
-            mbar_arrive_expect_tx(bar_res, 2 * Cfg::kTileBytes);
-            load_tile(sR, &tmR0, bar_res, r0);
-            load_tile(sR + Cfg::kTileBytes, &tmR1, bar_res, r0);
+            if (elect_one()) {
+                mbar_arrive_expect_tx(bar_res, 2 * Cfg::kTileBytes);
+                load_tile(sR, &tmR0, bar_res, r0);
+                load_tile(sR + Cfg::kTileBytes, &tmR1, bar_res, r0);
+            }
+            __syncwarp();
             for (int t = t_begin; t < t_end; ++t) {
                 const int it = t - t_begin;
                 const int slot = it % kStages;
                 mbar_wait(&bar_st_empty[slot], ((it / kStages) & 1) ^ 1, wctx, BB_STEMPTY + slot, it);
-                mbar_arrive_expect_tx(&bar_st_full[slot], 2 * Cfg::kTileBytes);
-                unsigned char* dst = sT + slot * 2 * Cfg::kTileBytes;
-                load_tile(dst, &tmT0, &bar_st_full[slot], t * 128);
-                load_tile(dst + Cfg::kTileBytes, &tmT1, &bar_st_full[slot], t * 128);
+                __syncwarp();
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&bar_st_full[slot], 2 * Cfg::kTileBytes);
+                    unsigned char* dst = sT + slot * 2 * Cfg::kTileBytes;
+                    load_tile(dst, &tmT0, &bar_st_full[slot], t * 128);
+                    load_tile(dst + Cfg::kTileBytes, &tmT1, &bar_st_full[slot], t * 128);
+                }
+                __syncwarp();
             }
-        } else if (warp == 8 && lane == 0) {
-            // ============================================================ MMA issuer
+        } else if (warp == 8) {
+            // ============================================================ MMA issuer (whole warp runs the
+            // control flow; each tcgen05.mma / commit is issued by one elected lane, so descriptors and
+            // addresses stay on the uniform datapath)
             constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);
             constexpr uint32_t idesc_acc = umma_idesc_bf16(128, D, false, true);
-            const uint32_t sR_addr = smem_u32(sR);
-            const uint32_t sT_addr = smem_u32(sT);
+            const uint32_t sR_addr = __shfl_sync(0xffffffffu, smem_u32(sR), 0);
+            const uint32_t sT_addr = __shfl_sync(0xffffffffu, smem_u32(sT), 0);
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+            const uint64_t dR_base = umma_smem_desc(sR_addr, 16, 1024);                   // K-major
+            const uint64_t dT_base = umma_smem_desc(sT_addr, 16, 1024);                   // K-major
+            const uint64_t dT_mn_base = umma_smem_desc(sT_addr, Cfg::kSubBytes, 1024);    // MN-major
             // G1 / G2: tmem[col] = R_which T_which^T for the pair in `slot`
             auto issue_score = [&](int which, int slot, uint32_t col) {
-                const uint32_t a0 = sR_addr + which * Cfg::kTileBytes;
-                const uint32_t b0 = sT_addr + (slot * 2 + which) * Cfg::kTileBytes;
+                const uint64_t a0 = umma_desc_advance(dR_base, which * Cfg::kTileBytes);
+                const uint64_t b0 = umma_desc_advance(dT_base, (slot * 2 + which) * Cfg::kTileBytes);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t o = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
-                    umma_ss(tmem_base + col, umma_smem_desc(a0 + o, 16, 1024), umma_smem_desc(b0 + o, 16, 1024), idesc_s,
-                            kk > 0);
+                    umma_ss(tmem_u + col, umma_desc_advance(a0, o), umma_desc_advance(b0, o), idesc_s, kk > 0);
                 }
             };
             // G3 / G4: tmem[acc] (+)= bf16 A at tmem[a_col] (two 32-column halves) times T_which (MN-major)
             auto issue_acc = [&](int which, int slot, uint32_t a_col, uint32_t acc_col, bool accumulate) {
-                const uint32_t b0 = sT_addr + (slot * 2 + which) * Cfg::kTileBytes;
+                const uint64_t b0 = umma_desc_advance(dT_mn_base, (slot * 2 + which) * Cfg::kTileBytes);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t a = tmem_base + a_col + (kk >> 2) * 64 + (kk & 3) * 8;
-                    umma_ts(tmem_base + acc_col, a, umma_smem_desc(b0 + kk * 2048, Cfg::kSubBytes, 1024), idesc_acc,
+                    const uint32_t a = tmem_u + a_col + (kk >> 2) * 64 + (kk & 3) * 8;
+                    umma_ts(tmem_u + acc_col, a, umma_desc_advance(b0, kk * 2048), idesc_acc,
                             (accumulate || kk > 0) ? 1u : 0u);
                 }
             };
             const int n_it = t_end - t_begin;
             mbar_wait(bar_res, 0, wctx, BB_RES, 0);
+            __syncwarp();
             if (n_it > 0) {
                 mbar_wait(&bar_st_full[0], 0, wctx, BB_STFULL, 0);
+                __syncwarp();
                 tc_fence_after();
                 issue_score(0, 0, kColS);
                 tc_commit(bar_s_full);
@@ -319,23 +387,31 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 const int slot = it % kStages;
                 const bool has_next = it + 1 < n_it;
                 const int nslot = (it + 1) % kStages;
+                if (lane == 0) TT_BTRACE(2, it, 0);
                 mbar_wait(bar_p_full, it & 1, wctx, BB_PFULL, it);
+                __syncwarp();
                 tc_fence_after();
+                if (lane == 0) TT_BTRACE(2, it, 1);
                 if (kKeysResident) issue_acc(1, slot, kColS, kColAcc0, it > 0);     // dV += P^T dO
                 if (has_next) {
                     mbar_wait(&bar_st_full[nslot], ((it + 1) / kStages) & 1, wctx, BB_STFULL + nslot, it + 1);
+                    __syncwarp();
                     tc_fence_after();
                     issue_score(0, nslot, kColS);
                     tc_commit(bar_s_full);
                 }
+                if (lane == 0) TT_BTRACE(2, it, 2);
                 mbar_wait(bar_ds_full, it & 1, wctx, BB_DSFULL, it);
+                __syncwarp();
                 tc_fence_after();
+                if (lane == 0) TT_BTRACE(2, it, 3);
                 issue_acc(0, slot, kColDP, kColAcc1, it > 0);                        // dK += dS^T Q | dQ += dS K
                 tc_commit(&bar_st_empty[slot]);
                 if (has_next) {
                     issue_score(1, nslot, kColDP);
                     tc_commit(bar_dp_full);
                 }
+                if (lane == 0) TT_BTRACE(2, it, 4);
             }
             tc_commit(bar_final);
         }
@@ -381,7 +457,15 @@ bool attn_bwd_sm100_supported(const AttnArgs& a) {
 }
 size_t attn_bwd_sm100_workspace(const AttnArgs& a) { return 2 * align256((size_t)a.BH * a.S * sizeof(float)); }
 
-template <int D>
+static long long* g_bwd_trace = nullptr;
+static int g_bwd_trace_block = 0, g_bwd_trace_mode = 0;   // mode 1: dK/dV pass, 2: dQ pass
+void attn_bwd_set_trace(long long* device_buf, int block, int pass) {
+    g_bwd_trace = device_buf;
+    g_bwd_trace_block = block;
+    g_bwd_trace_mode = device_buf ? pass : 0;
+}
+
+template <int D, int kPoly>
 static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     using Cfg = BwdCfg<D>;
     float* delta = reinterpret_cast<float*>(ws);
@@ -399,10 +483,10 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tdo, a.dout, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
     auto M = [](TmapStorage& t) -> CUtensorMap& { return *reinterpret_cast<CUtensorMap*>(t.bytes); };
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, true, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, false, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     BwdParams p;
@@ -414,29 +498,50 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.scale = a.scale;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = device_status_word();
+    p.trace = g_bwd_trace_mode == 1 ? g_bwd_trace : nullptr;
+    p.trace_block = g_bwd_trace_block;
     // dK, dV: keys resident, stream (Q, dO)
     p.out0 = (__nv_bfloat16*)a.dv;
     p.out1 = (__nv_bfloat16*)a.dk;
     p.n_tiles = (a.L + 127) / 128;
     {
         LaunchScope ls(K_BWD_DKV, st);
-        attn_bwd_sm100_kernel<D, true><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, true, kPoly><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tk), M(tv), M(tq), M(tdo), p);
     }
     // dQ: queries resident, stream (K, V)
+    p.trace = g_bwd_trace_mode == 2 ? g_bwd_trace : nullptr;
     p.out0 = nullptr;
     p.out1 = (__nv_bfloat16*)a.dq;
     p.n_tiles = (a.S + 127) / 128;
     {
         LaunchScope ls(K_BWD_DQ, st);
-        attn_bwd_sm100_kernel<D, false><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, false, kPoly><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tq), M(tdo), M(tk), M(tv), p);
     }
     return cudaGetLastError();
 }
 
+static int bwd_poly_setting() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("TT_BWD_POLY");
+        v = (e && *e) ? atoi(e) : 0;
+        if (v != 0 && v != 2 && v != 4 && v != 6) v = 0;
+    }
+    return v;
+}
+template <int D>
+static cudaError_t launch_bwd_d(const AttnArgs& a, void* ws, cudaStream_t st) {
+    switch (bwd_poly_setting()) {
+        case 2: return launch_bwd<D, 2>(a, ws, st);
+        case 4: return launch_bwd<D, 4>(a, ws, st);
+        case 6: return launch_bwd<D, 6>(a, ws, st);
+        default: return launch_bwd<D, 0>(a, ws, st);
+    }
+}
 cudaError_t attn_bwd_sm100(const AttnArgs& a, void* ws, cudaStream_t st) {
-    return a.D == 128 ? launch_bwd<128>(a, ws, st) : launch_bwd<64>(a, ws, st);
+    return a.D == 128 ? launch_bwd_d<128>(a, ws, st) : launch_bwd_d<64>(a, ws, st);
 }
 
 }  // namespace ttk

@@ -25,6 +25,7 @@
 // sub-blocks of [128 rows x 128 bytes] with the 128-byte swizzle.
 #include "common.h"
 #include "sm100_ptx.cuh"
+#include <stdlib.h>
 
 namespace ttk {
 using namespace sm100;
@@ -52,9 +53,78 @@ struct FwdParams {
     int causal;
     float scale_log2; // scale * log2(e)
     unsigned int* status;
+    long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
+    int trace_block;
 };
 
-template <int D>
+#define TT_TRACE(role, iter, slot)                                                                  \
+    do {                                                                                           \
+        if (p.trace != nullptr && (int)blockIdx.x == p.trace_block && (iter) < 64)                 \
+            p.trace[((role) * 64 + (iter)) * 8 + (slot)] = clock64();                              \
+    } while (0)
+
+// This thread's row of S (128 fp32 columns) from tensor memory; columns >= lim become -inf.
+__device__ __forceinline__ void load_s_row(uint32_t tS, uint32_t (&sr)[4][32], bool need_mask, int lim) {
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, sr[cc]);
+    tmem_wait_ld();
+    if (need_mask) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+                if (cc * 32 + e >= lim) sr[cc][e] = 0xff800000u;   // -inf
+    }
+}
+__device__ __forceinline__ float row_max_raw(const uint32_t (&sr)[4][32]) {
+    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+        mx0 = fmax3(mx0, __uint_as_float(sr[0][e]), __uint_as_float(sr[0][e + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sr[1][e]), __uint_as_float(sr[1][e + 1]));
+        mx2 = fmax3(mx2, __uint_as_float(sr[2][e]), __uint_as_float(sr[2][e + 1]));
+        mx3 = fmax3(mx3, __uint_as_float(sr[3][e]), __uint_as_float(sr[3][e + 1]));
+    }
+    return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+}
+// P = exp2(S*c - m) for one half (64 keys) of this thread's row: packs P to bf16 pairs and
+// returns the two-lane partial row sum.
+template <int kPoly>
+__device__ __forceinline__ uint64_t softmax_exp_half(const uint32_t (&sr)[4][32], int h, float c, float m,
+                                                     uint32_t (&pk)[32]) {
+    const float nm = -m;
+    const uint64_t c2 = pack_f32x2(c, c), nm2 = pack_f32x2(nm, nm);
+    uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
+#pragma unroll
+    for (int cq = 0; cq < 2; ++cq) {
+        const int cc = h * 2 + cq;
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+            const uint64_t xa = fma_f32x2(pack_f32x2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, nm2);
+            const uint64_t xb = fma_f32x2(pack_f32x2(__uint_as_float(sr[cc][e + 2]), __uint_as_float(sr[cc][e + 3])), c2, nm2);
+            float a0, a1, p2, p3;
+            unpack_f32x2(xa, a0, a1);
+            const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
+            if ((((e >> 2) * kPoly) % 4) < kPoly) {
+                ex2_poly_x2(xb, p2, p3);
+            } else {
+                float b0, b1;
+                unpack_f32x2(xb, b0, b1);
+                p2 = ex2_approx(b0);
+                p3 = ex2_approx(b1);
+            }
+            acc0 = add_f32x2(acc0, pack_f32x2(p0, p1));
+            acc1 = add_f32x2(acc1, pack_f32x2(p2, p3));
+            pk[cq * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
+            pk[cq * 16 + (e >> 1) + 1] = pack_bf16x2(p2, p3);
+        }
+    }
+    return add_f32x2(acc0, acc1);
+}
+
+// kPoly: of every 8 exponentials, kPoly are evaluated by a polynomial on the FMA pipes instead
+// of the special-function unit (0..4), to balance the two pipes.
+template <int D, int kPoly>
 __global__ void __launch_bounds__(FwdCfg<D>::kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -70,12 +140,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     uint64_t* bar_kv_full = bars + 2;          // [kStages]
     uint64_t* bar_kv_empty = bars + 2 + kStages;
     uint64_t* bar_s_full = bars + 2 + 2 * kStages;   // [2]
-    uint64_t* bar_p_full = bar_s_full + 2;           // [2]
-    uint64_t* bar_o_final = bar_p_full + 2;          // [2]
+    uint64_t* bar_p_full = bar_s_full + 2;           // [2 tiles][2 halves of the key tile]
+    uint64_t* bar_o_final = bar_p_full + 4;          // [2]
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bar_o_final + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = uniform_warp_idx();
     const int lane = threadIdx.x & 31;
 
     // ---- which rows / how many key tiles
@@ -104,7 +174,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_q_full[i], 1);
             mbar_init(&bar_s_full[i], 1);
-            mbar_init(&bar_p_full[i], 128);
+            mbar_init(&bar_p_full[2 * i], 128);
+            mbar_init(&bar_p_full[2 * i + 1], 128);
             mbar_init(&bar_o_final[i], 1);
         }
         for (int s = 0; s < kStages; ++s) {
@@ -144,48 +215,37 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         float m2 = -INFINITY;   // running max in the scaled log2 domain
         float l = 0.f;          // running sum of exp2(s*c - m2)
         for (int j = 0; j < nt; ++j) {
+            if (wq == 0 && lane == 0) TT_TRACE(i, j, 0);
             mbar_wait(&bar_s_full[i], j & 1, wctx, BAR_SFULL + i, j);
             __syncwarp();
             tc_fence_after();
-            uint32_t sr[4][32];
-#pragma unroll
-            for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, sr[cc]);
-            tmem_wait_ld();
-            // mask: key index must be < L and (causal) <= row + off
+            if (wq == 0 && lane == 0) TT_TRACE(i, j, 1);
+            // visible columns of this row inside the tile: [0, lim)
             const int kv0 = j << 7;
             const bool need_mask = (kv0 + 128 > p.L) || (p.causal && (kv0 + 127 > (q0 + 128 * i) + off));
+            int lim = 128;
             if (need_mask) {
-                int lim = p.L;
+                lim = p.L;
                 if (p.causal) lim = min(lim, row + off + 1);
-                lim -= kv0;   // columns [0, lim) of this tile are visible
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc)
-#pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        if (cc * 32 + e >= lim) sr[cc][e] = 0xff800000u;  // -inf
+                lim -= kv0;
             }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                mx0 = fmaxf(mx0, __uint_as_float(sr[0][e]));
-                mx1 = fmaxf(mx1, __uint_as_float(sr[1][e]));
-                mx2 = fmaxf(mx2, __uint_as_float(sr[2][e]));
-                mx3 = fmaxf(mx3, __uint_as_float(sr[3][e]));
-            }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
+            uint32_t sr[4][32];
+            load_s_row(tS, sr, need_mask, lim);
+            if (wq == 0 && lane == 0) TT_TRACE(i, j, 2);
+            const float mx = row_max_raw(sr) * c;
             float resc = 1.0f;
             bool grow = false;
             if (j == 0) {
                 m2 = mx;
-            } else if (mx > m2 + 8.0f) {   // lazy rescale: only when the max grew by > 2^8
+            } else if (mx > m2 + 8.0f) {   // lazy rescale: only when the max grew by more than 2^8
                 resc = ex2_approx(m2 - mx);
                 m2 = mx;
                 l *= resc;
                 grow = true;
             }
             if (__any_sync(0xffffffffu, grow)) {
-                // O_i *= resc  (the previous P V of this tile has completed: its commit precedes
-                // the S commit just waited on)
+                // O_i *= resc (the previous P V of this tile has completed: its commit precedes the
+                // S commit waited on above)
 #pragma unroll
                 for (int cc = 0; cc < D / 32; ++cc) {
                     uint32_t orr[32];
@@ -196,25 +256,31 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     tmem_st32(tO + cc * 32, orr);
                 }
             }
-            const float nm = -m2;
-            float sum0 = 0.f, sum1 = 0.f;
+            if (wq == 0 && lane == 0) TT_TRACE(i, j, 3);
+            // P = exp2(S*c - m2) in two halves of 64 keys; the P V MMAs of a half start as soon as
+            // that half is in tensor memory
+            uint64_t acc = pack_f32x2(0.f, 0.f);
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                uint32_t pk[16];
+            for (int h = 0; h < 2; ++h) {
+                uint32_t pk[32];
+                acc = add_f32x2(acc, softmax_exp_half<kPoly>(sr, h, c, m2, pk));
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    float p0 = ex2_approx(fmaf(__uint_as_float(sr[cc][e]), c, nm));
-                    float p1 = ex2_approx(fmaf(__uint_as_float(sr[cc][e + 1]), c, nm));
-                    sum0 += p0;
-                    sum1 += p1;
-                    pk[e >> 1] = pack_bf16x2(p0, p1);
+                for (int q4 = 0; q4 < 2; ++q4) {
+                    uint32_t t16[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) t16[e] = pk[q4 * 16 + e];
+                    tmem_st16(tP + h * 32 + q4 * 16, t16);
                 }
-                tmem_st16(tP + cc * 16, pk);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&bar_p_full[2 * i + h]);
+                if (wq == 0 && lane == 0) TT_TRACE(i, j, 4 + h);
             }
-            l += sum0 + sum1;
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&bar_p_full[i]);
+            {
+                float t0, t1;
+                unpack_f32x2(acc, t0, t1);
+                l += t0 + t1;
+            }
         }
         if (nt > 0) {
             // ---- epilogue: O_i / l -> bf16 -> global, LSE
@@ -247,19 +313,24 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
     } else {
         setmaxnreg_dec<56>();
-        if (warp == 9 && lane == 0) {
-            // ======================================================= TMA loader
+        if (warp == 9) {
+            // ======================================================= TMA loader (whole warp, one lane issues)
             // ring order: K_0, V_0, K_1, V_1, ...
             auto load_tile = [&](unsigned char* dst, const CUtensorMap* tm, uint64_t* bar, int row_start) {
-                mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
 #pragma unroll
-                for (int sb = 0; sb < Cfg::kSub; ++sb) tma_load_3d(dst + sb * Cfg::kSubBytes, tm, bar, sb * 64, row_start, bh);
+                    for (int sb = 0; sb < Cfg::kSub; ++sb)
+                        tma_load_3d(dst + sb * Cfg::kSubBytes, tm, bar, sb * 64, row_start, bh);
+                }
+                __syncwarp();
             };
             if (n_tiles[0] > 0) load_tile(sQ, &tmQ, &bar_q_full[0], q0);
             int t = 0;   // ring item counter
             auto load_kv = [&](const CUtensorMap* tm, int j) {
                 const int slot = t % kStages;
                 mbar_wait(&bar_kv_empty[slot], ((t / kStages) & 1) ^ 1, wctx, BAR_KVEMPTY + slot, t);
+                __syncwarp();
                 load_tile(sKV + slot * Cfg::kTileBytes, tm, &bar_kv_full[slot], j * 128);
                 ++t;
             };
@@ -269,38 +340,46 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 load_kv(&tmV, j);
                 if (j + 1 < n_max) load_kv(&tmK, j + 1);
             }
-        } else if (warp == 8 && lane == 0) {
-            // ======================================================= MMA issuer
+        } else if (warp == 8) {
+            // ======================================================= MMA issuer (whole warp runs the
+            // control flow; each tcgen05.mma / commit is issued by one elected lane)
             constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);
             constexpr uint32_t idesc_pv = umma_idesc_bf16(128, D, false, true);
-            const uint32_t sQ_addr = smem_u32(sQ);
-            const uint32_t sKV_addr = smem_u32(sKV);
+            const uint32_t sQ_addr = __shfl_sync(0xffffffffu, smem_u32(sQ), 0);
+            const uint32_t sKV_addr = __shfl_sync(0xffffffffu, smem_u32(sKV), 0);
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);   // warp-uniform copy
             int t = 0;   // ring item counter (consumer side)
             auto wait_item = [&](int item) {
                 const int slot = item % kStages;
                 mbar_wait(&bar_kv_full[slot], (item / kStages) & 1, wctx, BAR_KVFULL + slot, item);
+                __syncwarp();
             };
             auto release_item = [&](int item) { tc_commit(&bar_kv_empty[item % kStages]); };
+            // descriptor templates; per MMA only the 14-bit start-address field moves
+            const uint64_t dq_base = umma_smem_desc(sQ_addr, 16, 1024);
+            const uint64_t dk_base = umma_smem_desc(sKV_addr, 16, 1024);                 // K-major (S = Q K^T)
+            const uint64_t dv_base = umma_smem_desc(sKV_addr, Cfg::kSubBytes, 1024);     // MN-major (O += P V)
             // S_i = Q_i K^T with K in ring item `item`
             auto issue_s = [&](int i, int item) {
-                const uint32_t a0 = sQ_addr + i * Cfg::kTileBytes;
-                const uint32_t b0 = sKV_addr + (item % kStages) * Cfg::kTileBytes;
-                const uint32_t d = tmem_base + (uint32_t)(i * 128);
+                const uint64_t a0 = umma_desc_advance(dq_base, i * Cfg::kTileBytes);
+                const uint64_t b0 = umma_desc_advance(dk_base, (item % kStages) * Cfg::kTileBytes);
+                const uint32_t d = tmem_u + (uint32_t)(i * 128);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t o = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
-                    umma_ss(d, umma_smem_desc(a0 + o, 16, 1024), umma_smem_desc(b0 + o, 16, 1024), idesc_s, kk > 0);
+                    umma_ss(d, umma_desc_advance(a0, o), umma_desc_advance(b0, o), idesc_s, kk > 0);
                 }
             };
             // O_i (+)= P_i V with V in ring item `item`
-            auto issue_pv = [&](int i, int item, bool accumulate) {
-                const uint32_t b0 = sKV_addr + (item % kStages) * Cfg::kTileBytes;
-                const uint32_t d = tmem_base + (uint32_t)(256 + i * D);
-                const uint32_t a = tmem_base + (uint32_t)(i * 128);
+            auto issue_pv = [&](int i, int item, bool accumulate, int half) {
+                const uint64_t b0 = umma_desc_advance(dv_base, (item % kStages) * Cfg::kTileBytes);
+                const uint32_t d = tmem_u + (uint32_t)(256 + i * D);
+                const uint32_t a = tmem_u + (uint32_t)(i * 128);
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    umma_ts(d, a + kk * 8, umma_smem_desc(b0 + kk * 2048, Cfg::kSubBytes, 1024), idesc_pv,
-                            (accumulate || kk > 0) ? 1u : 0u);
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const int kk = half * 4 + k4;
+                    umma_ts(d, a + kk * 8, umma_desc_advance(b0, kk * 2048), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+                }
             };
             if (n_max > 0) {
                 wait_item(0);   // K_0
@@ -308,6 +387,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 for (int i = 0; i < 2; ++i) {
                     if (n_tiles[i] > 0) {
                         mbar_wait(&bar_q_full[i], 0, wctx, BAR_QFULL + i, 0);
+                        __syncwarp();
                         tc_fence_after();
                         issue_s(i, 0);
                         tc_commit(&bar_s_full[i]);
@@ -321,9 +401,17 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 bool k_waited = false;
                 for (int i = 0; i < 2; ++i) {
                     if (j < n_tiles[i]) {
-                        mbar_wait(&bar_p_full[i], j & 1, wctx, BAR_PFULL + i, j);
+                        if (lane == 0) TT_TRACE(2, j, 4 * i + 0);
+                        mbar_wait(&bar_p_full[2 * i], j & 1, wctx, BAR_PFULL + 2 * i, j);
+                        __syncwarp();
                         tc_fence_after();
-                        issue_pv(i, item_v, j > 0);
+                        if (lane == 0) TT_TRACE(2, j, 4 * i + 1);
+                        issue_pv(i, item_v, j > 0, 0);
+                        mbar_wait(&bar_p_full[2 * i + 1], j & 1, wctx, BAR_PFULL + 2 * i + 1, j);
+                        __syncwarp();
+                        tc_fence_after();
+                        if (lane == 0) TT_TRACE(2, j, 4 * i + 2);
+                        issue_pv(i, item_v, j > 0, 1);
                         if (j + 1 < n_tiles[i]) {
                             if (!k_waited) {
                                 wait_item(item_k);
@@ -332,6 +420,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                             }
                             issue_s(i, item_k);
                             tc_commit(&bar_s_full[i]);
+                            if (lane == 0) TT_TRACE(2, j, 4 * i + 3);
                         } else {
                             tc_commit(&bar_o_final[i]);
                         }
@@ -356,7 +445,24 @@ bool attn_fwd_sm100_supported(const AttnArgs& a) {
     return a.bf16 && (a.D == 64 || a.D == 128) && a.S >= 1 && a.L >= 1 && a.BH * (long long)((a.S + 255) / 256) < (1LL << 31);
 }
 
-template <int D>
+static long long* g_fwd_trace = nullptr;
+static int g_fwd_trace_block = 0;
+void attn_fwd_set_trace(long long* device_buf, int block) {
+    g_fwd_trace = device_buf;
+    g_fwd_trace_block = block;
+}
+
+static int fwd_poly_setting() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("TT_FWD_POLY");
+        v = (e && *e) ? atoi(e) : 0;
+        if (v < 0 || v > 4) v = 0;
+    }
+    return v;
+}
+
+template <int D, int kPoly>
 static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     using Cfg = FwdCfg<D>;
     TmapStorage tq, tk, tv;
@@ -364,7 +470,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH, 128, &why)) return cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     FwdParams p;
@@ -376,18 +482,30 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.causal = a.causal;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = device_status_word();
+    p.trace = g_fwd_trace;
+    p.trace_block = g_fwd_trace_block;
     unsigned grid = (unsigned)(a.BH * p.n_qblk);
     {
         LaunchScope ls(K_FWD_TC, st);
-        attn_fwd_sm100_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_fwd_sm100_kernel<D, kPoly><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
             *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
     }
     return cudaGetLastError();
 }
 
+template <int D>
+static cudaError_t launch_fwd_d(const AttnArgs& a, cudaStream_t st) {
+    switch (fwd_poly_setting()) {
+        case 1: return launch_fwd<D, 1>(a, st);
+        case 3: return launch_fwd<D, 3>(a, st);
+        case 4: return launch_fwd<D, 4>(a, st);
+        case 2: return launch_fwd<D, 2>(a, st);
+        default: return launch_fwd<D, 0>(a, st);
+    }
+}
 cudaError_t attn_fwd_sm100(const AttnArgs& a, cudaStream_t st) {
-    return a.D == 128 ? launch_fwd<128>(a, st) : launch_fwd<64>(a, st);
+    return a.D == 128 ? launch_fwd_d<128>(a, st) : launch_fwd_d<64>(a, st);
 }
 
 // ------------------------------------------------------------------------------ self test
@@ -406,7 +524,8 @@ umma_probe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kSubBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
+    (void)lane;
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(&bars[0], 1);
@@ -425,14 +544,18 @@ umma_probe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     WaitCtx wctx{status, abort_flag, warp};
-    if (threadIdx.x == 0) {
-        mbar_arrive_expect_tx(&bars[0], (4 + D / 64) * kSubBytes);
-        for (int sb = 0; sb < 2; ++sb) {
-            tma_load_3d(sA + sb * kSubBytes, &tmA, &bars[0], sb * 64, 0, 0);
-            tma_load_3d(sB + sb * kSubBytes, &tmB, &bars[0], sb * 64, 0, 0);
+    if (warp == 0) {
+        if (elect_one()) {
+            mbar_arrive_expect_tx(&bars[0], (4 + D / 64) * kSubBytes);
+            for (int sb = 0; sb < 2; ++sb) {
+                tma_load_3d(sA + sb * kSubBytes, &tmA, &bars[0], sb * 64, 0, 0);
+                tma_load_3d(sB + sb * kSubBytes, &tmB, &bars[0], sb * 64, 0, 0);
+            }
+            for (int sb = 0; sb < D / 64; ++sb) tma_load_3d(sV + sb * kSubBytes, &tmV, &bars[0], sb * 64, 0, 0);
         }
-        for (int sb = 0; sb < D / 64; ++sb) tma_load_3d(sV + sb * kSubBytes, &tmV, &bars[0], sb * 64, 0, 0);
+        __syncwarp();
         mbar_wait(&bars[0], 0, wctx, 0, 0);
+        __syncwarp();
         tc_fence_after();
         constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);
         for (int kk = 0; kk < 8; ++kk) {
@@ -468,7 +591,7 @@ umma_probe_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (warp == 0) {
         tc_fence_after();
         constexpr uint32_t idesc_pv = umma_idesc_bf16(128, D, false, true);
         for (int kk = 0; kk < 8; ++kk)

@@ -47,6 +47,10 @@ size_t attn_bwd_simt_workspace(const AttnArgs& a);
 // --- tcgen05 / TMA kernels (bf16, D in {64,128})
 bool attn_fwd_sm100_supported(const AttnArgs& a);
 cudaError_t attn_fwd_sm100(const AttnArgs& a, cudaStream_t st);
+// Debug aid: when device_buf is non-null, CTA `block` of every later forward launch stamps
+// clock64() at its hand-off points into device_buf ([3 roles][64 iterations][8 stamps]).
+void attn_fwd_set_trace(long long* device_buf, int block);
+void attn_bwd_set_trace(long long* device_buf, int block, int pass);   // pass 1: dK/dV, 2: dQ
 bool attn_bwd_sm100_supported(const AttnArgs& a);
 size_t attn_bwd_sm100_workspace(const AttnArgs& a);
 cudaError_t attn_bwd_sm100(const AttnArgs& a, void* workspace, cudaStream_t st);

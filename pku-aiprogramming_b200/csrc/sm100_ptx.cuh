@@ -14,6 +14,21 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of a converged warp (all 32 lanes must execute this together).  Issuing the
+// single-thread instructions (tcgen05.mma, tcgen05.commit, TMA) under this predicate inside
+// otherwise warp-uniform code keeps descriptors and addresses on the uniform datapath.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+// Warp index as a value the compiler knows to be warp-uniform.
+__device__ __forceinline__ int uniform_warp_idx() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
+
 // ------------------------------------------------------------------ status / bounded waits
 // Device status word layout (one per device, in global memory):
 //   [0] nonzero once any wait expired; value = (code << 16) | (block & 0xffff)
@@ -122,9 +137,10 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 
 // Arrives (count 1) on the mbarrier once every tcgen05.mma this thread issued so far has
 // completed.  Implies tcgen05.fence::before_thread_sync.
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {   // whole warp calls, one lane issues
+    if (elect_one())
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                     : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of warp w reads lane 32*(w%4)+t.
@@ -189,6 +205,12 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_
     return d;
 }
 
+// Descriptor of the same layout `bytes` further into shared memory (bytes % 16 == 0; the
+// 14-bit start-address field cannot overflow inside the 227 KB window).
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+    return desc + (uint64_t)(bytes >> 4);
+}
+
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 //   bits [4,6) D format (1 = f32), [7,10) A format (1 = bf16), [10,13) B format (1 = bf16),
 //   bit 15 A major (0 = K), bit 16 B major (0 = K, 1 = MN), [17,23) N>>3, [24,29) M>>4
@@ -197,9 +219,10 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, bool a_mn_m
            ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
+// D[tmem] (+)= A[smem] * B[smem].  Called by a whole converged warp; one elected lane issues.
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate) {
+    if (elect_one())
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
@@ -211,6 +234,7 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
 // column holds two consecutive-K bf16 values).
 __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate) {
+    if (elect_one())
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
@@ -228,11 +252,67 @@ __device__ __forceinline__ void setmaxnreg_dec() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
+// 3-input max and packed two-lane fp32 arithmetic (sm_100): halve the instruction count of
+// the softmax inner loops.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// 2^x for two packed floats WITHOUT the special-function unit: split x = floor(x) + f with a
+// round-down add of 1.5*2^23 (the integer lands in the low mantissa bits), evaluate a degree-3
+// minimax polynomial of 2^f on [0,1) (relative error < 9e-5, far below bf16 rounding), then add
+// floor(x) into the exponent field.  Inputs are clamped to >= -126 (so -inf gives ~1e-38).
+__device__ __forceinline__ void ex2_poly_x2(uint64_t x, float& r0, float& r1) {
+    float x0, x1;
+    unpack_f32x2(x, x0, x1);
+    const uint64_t xc = pack_f32x2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t magic = pack_f32x2(12582912.0f, 12582912.0f);
+    uint64_t xf;
+    asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(xf) : "l"(xc), "l"(magic));
+    uint64_t fl, fr;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(fl) : "l"(xf), "l"(magic));
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(fr) : "l"(xc), "l"(fl));
+    uint64_t r = fma_f32x2(pack_f32x2(0.07706617563962936f, 0.07706617563962936f), fr,
+                           pack_f32x2(0.22764593362808228f, 0.22764593362808228f));
+    r = fma_f32x2(r, fr, pack_f32x2(0.6951165795326233f, 0.6951165795326233f));
+    r = fma_f32x2(r, fr, pack_f32x2(1.0f, 1.0f));
+    float a0, a1, i0, i1;
+    unpack_f32x2(r, a0, a1);
+    unpack_f32x2(xf, i0, i1);
+    r0 = __uint_as_float(__float_as_uint(a0) + (__float_as_uint(i0) << 23));
+    r1 = __uint_as_float(__float_as_uint(a1) + (__float_as_uint(i1) << 23));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

@@ -443,6 +443,16 @@ int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k
     return TT_OK;
 }
 
+int tt_debug_fwd_trace(void* device_buf, int32_t block) {
+    attn_fwd_set_trace(reinterpret_cast<long long*>(device_buf), block);
+    return TT_OK;
+}
+
+int tt_debug_bwd_trace(void* device_buf, int32_t block, int32_t pass) {
+    attn_bwd_set_trace(reinterpret_cast<long long*>(device_buf), block, pass);
+    return TT_OK;
+}
+
 int tt_profile_enable(int on) {
     g_timing_on.store(on ? 1 : 0);
     return TT_OK;
