@@ -74,6 +74,55 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST = os.path.join(CSRC, "host")
+HOST_DIR = os.path.join(PKG, "host_modules")   # myTensor*.so and myLayer*.so land here
+
+
+def build_host_modules(force: bool = False, verbose: bool = False):
+    """The reference-style pybind11 modules `myTensor` and `myLayer` (they link libtt_attn.so)."""
+    import sysconfig
+    import pybind11
+    build_library(force=False, verbose=verbose)
+    os.makedirs(HOST_DIR, exist_ok=True)
+    suffix = sysconfig.get_config_var("EXT_SUFFIX")
+    inc = ["-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"], "-I" + HOST]
+    flags = [f for f in NVCC_FLAGS if f != "-fvisibility=hidden"]
+    # drop the "-Xcompiler" that preceded the removed visibility flag
+    cleaned, skip = [], False
+    for i, f in enumerate(NVCC_FLAGS):
+        if f == "-Xcompiler" and i + 1 < len(NVCC_FLAGS) and NVCC_FLAGS[i + 1] == "-fvisibility=hidden":
+            skip = True
+            continue
+        if skip:
+            skip = False
+            continue
+        cleaned.append(f)
+    hdr_t = max(_newest_header(), max(os.path.getmtime(os.path.join(HOST, f)) for f in os.listdir(HOST) if f.endswith(".h")))
+    objs, jobs = {}, []
+    for src in ("TinyTensor.cu", "Layers.cu", "bind_Tensor.cu", "bind_Layer.cu"):
+        s_ = os.path.join(HOST, src)
+        o = os.path.join(OBJ, "host_" + src[:-3] + ".o")
+        objs[src] = o
+        if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s_), hdr_t):
+            jobs.append([_nvcc(), *cleaned, *inc, "-c", s_, "-o", o])
+    if jobs:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=len(jobs)) as ex:
+            list(ex.map(lambda c: _run(c, verbose), jobs))
+    link = ["-shared", "-Wno-deprecated-gpu-targets", "-L" + LIB_DIR, "-ltt_attn", "-Xlinker", "-rpath", "-Xlinker",
+            "$ORIGIN/../lib", "-cudart", "static"]
+    outs = []
+    for name, parts in (("myTensor", ["bind_Tensor.cu", "TinyTensor.cu"]),
+                        ("myLayer", ["bind_Layer.cu", "Layers.cu", "TinyTensor.cu"])):
+        out = os.path.join(HOST_DIR, name + suffix)
+        if jobs or not os.path.exists(out):
+            _run([_nvcc(), *link, "-o", out, *[objs[p_] for p_ in parts]], verbose)
+        outs.append(out)
+    return outs
+
+
 if __name__ == "__main__":
     path = build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
+    for m_ in build_host_modules(force="--force" in sys.argv, verbose="--verbose" in sys.argv):
+        print(m_)

@@ -1,0 +1,147 @@
+#include "Layers.h"
+
+#include <stdexcept>
+#include <type_traits>
+
+#include "tt_attn.h"
+
+namespace {
+
+void raise(int rc, const char* who) {
+    if (rc == TT_OK) return;
+    std::string msg = std::string(who) + ": " + tt_last_error();
+    if (rc == TT_ERR_NULL || rc == TT_ERR_BAD_SHAPE || rc == TT_ERR_BAD_DTYPE || rc == TT_ERR_WORKSPACE)
+        throw std::invalid_argument(msg);
+    throw std::runtime_error(msg);
+}
+
+template <typename T>
+void require_gpu(const TinyTensor<T>& t, const char* who, const char* name) {
+    if (t.device != "gpu")
+        throw std::invalid_argument(std::string(who) + ": tensor '" + name + "' is on '" + t.device +
+                                    "'; attention runs on gpu tensors only");
+}
+
+template <typename T>
+tt_attn_desc describe(const TinyTensor<T>& q, const TinyTensor<T>& k, const TinyTensor<T>& v, bool causal, float scale,
+                      const char* who) {
+    if (q.shape.size() != 4 || k.shape.size() != 4 || v.shape.size() != 4)
+        throw std::invalid_argument(std::string(who) + ": q, k, v must be 4-D [B,H,rows,D]");
+    if (k.shape != v.shape || q.shape[0] != k.shape[0] || q.shape[1] != k.shape[1] || q.shape[3] != k.shape[3])
+        throw std::invalid_argument(std::string(who) + ": q, k, v shapes do not agree");
+    tt_attn_desc d;
+    d.B = q.shape[0];
+    d.H = q.shape[1];
+    d.S = q.shape[2];
+    d.L = k.shape[2];
+    d.D = q.shape[3];
+    d.dtype = std::is_same<T, float>::value ? TT_F32 : TT_BF16;
+    d.causal = causal ? 1 : 0;
+    d.scale = scale;
+    return d;
+}
+
+struct PoolBuffer {   // workspace taken from the pooled allocator for the duration of a call
+    void* p = nullptr;
+    size_t bytes = 0;
+    explicit PoolBuffer(size_t n) : bytes(n) {
+        if (n) raise(tt_alloc(n, &p), "workspace");
+    }
+    ~PoolBuffer() { tt_free(p); }
+};
+
+template <typename T>
+__global__ void softmax_rows_kernel(const T* in, T* out, long long rows, int cols) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= rows) return;
+    const T* x = in + row * cols;
+    T* y = out + row * cols;
+    float m = -INFINITY;
+    for (int c = lane; c < cols; c += 32) m = fmaxf(m, (float)x[c]);
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.f;
+    for (int c = lane; c < cols; c += 32) s += expf((float)x[c] - m);
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float inv = 1.0f / s;
+    for (int c = lane; c < cols; c += 32) y[c] = (T)(expf((float)x[c] - m) * inv);
+}
+
+}  // namespace
+
+template <typename T>
+void AttentionForward(const TinyTensor<T>& q, const TinyTensor<T>& k, const TinyTensor<T>& v, TinyTensor<T>& out,
+                      TinyTensor<float>& lse, bool causal, float scale) {
+    const char* who = "AttentionForward";
+    require_gpu(q, who, "q"); require_gpu(k, who, "k"); require_gpu(v, who, "v");
+    tt_attn_desc d = describe(q, k, v, causal, scale, who);
+    if (out.device != "gpu") out.gpu();
+    if (lse.device != "gpu") lse.gpu();
+    out.resize(q.shape);
+    lse.resize({d.B, d.H, d.S});
+    int rc;
+    if (d.S == 1 && d.dtype == TT_BF16) {
+        tt_attn_desc dd = d;
+        dd.causal = 0;
+        PoolBuffer ws(tt_attn_decode_workspace_bytes(&dd));
+        rc = tt_attn_decode(&dd, q.p_data, k.p_data, v.p_data, out.p_data, lse.p_data, ws.p, ws.bytes, nullptr);
+        if (rc == TT_OK) rc = tt_check_device_status(nullptr);   // synchronises before the workspace is returned
+    } else {
+        rc = tt_attn_fwd(&d, q.p_data, k.p_data, v.p_data, out.p_data, lse.p_data, nullptr);
+        if (rc == TT_OK) rc = tt_check_device_status(nullptr);   // "returns when done", like the reference's ops
+    }
+    raise(rc, who);
+}
+
+template <typename T>
+void AttentionBackward(const TinyTensor<T>& q, const TinyTensor<T>& k, const TinyTensor<T>& v,
+                       const TinyTensor<T>& out, const TinyTensor<float>& lse, TinyTensor<T>& grad_q,
+                       TinyTensor<T>& grad_k, TinyTensor<T>& grad_v, const TinyTensor<T>& grad_out, bool causal,
+                       float scale) {
+    const char* who = "AttentionBackward";
+    require_gpu(q, who, "q"); require_gpu(k, who, "k"); require_gpu(v, who, "v");
+    require_gpu(out, who, "out"); require_gpu(lse, who, "lse"); require_gpu(grad_out, who, "grad_out");
+    tt_attn_desc d = describe(q, k, v, causal, scale, who);
+    if (out.shape != q.shape || grad_out.shape != q.shape)
+        throw std::invalid_argument(std::string(who) + ": out and grad_out must have q's shape");
+    if (lse.size != (size_t)d.B * d.H * d.S) throw std::invalid_argument(std::string(who) + ": lse must be [B,H,S]");
+    for (TinyTensor<T>* g : {&grad_q, &grad_k, &grad_v})
+        if (g->device != "gpu") g->gpu();
+    grad_q.resize(q.shape);
+    grad_k.resize(k.shape);
+    grad_v.resize(v.shape);
+    PoolBuffer ws(tt_attn_bwd_workspace_bytes(&d));
+    int rc = tt_attn_bwd(&d, q.p_data, k.p_data, v.p_data, out.p_data, lse.p_data, grad_out.p_data, grad_q.p_data,
+                         grad_k.p_data, grad_v.p_data, ws.p, ws.bytes, nullptr);
+    if (rc == TT_OK) rc = tt_check_device_status(nullptr);
+    raise(rc, who);
+}
+
+template <typename T>
+void SoftmaxForward(const TinyTensor<T>& input, TinyTensor<T>& output) {
+    require_gpu(input, "SoftmaxForward", "input");
+    if (input.shape.empty()) throw std::invalid_argument("SoftmaxForward: empty shape");
+    if (output.device != "gpu") output.gpu();
+    output.resize(input.shape);
+    const int cols = input.shape.back();
+    const long long rows = cols ? (long long)(input.size / (size_t)cols) : 0;
+    if (rows == 0) return;
+    softmax_rows_kernel<T><<<(unsigned)((rows + 7) / 8), 256>>>(input.p_data, output.p_data, rows, cols);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) throw std::runtime_error(std::string("SoftmaxForward: ") + cudaGetErrorString(e));
+}
+
+template void AttentionForward<float>(const TinyTensor<float>&, const TinyTensor<float>&, const TinyTensor<float>&,
+                                      TinyTensor<float>&, TinyTensor<float>&, bool, float);
+template void AttentionForward<__nv_bfloat16>(const TinyTensor<__nv_bfloat16>&, const TinyTensor<__nv_bfloat16>&,
+                                              const TinyTensor<__nv_bfloat16>&, TinyTensor<__nv_bfloat16>&,
+                                              TinyTensor<float>&, bool, float);
+template void AttentionBackward<float>(const TinyTensor<float>&, const TinyTensor<float>&, const TinyTensor<float>&,
+                                       const TinyTensor<float>&, const TinyTensor<float>&, TinyTensor<float>&,
+                                       TinyTensor<float>&, TinyTensor<float>&, const TinyTensor<float>&, bool, float);
+template void AttentionBackward<__nv_bfloat16>(const TinyTensor<__nv_bfloat16>&, const TinyTensor<__nv_bfloat16>&,
+                                               const TinyTensor<__nv_bfloat16>&, const TinyTensor<__nv_bfloat16>&,
+                                               const TinyTensor<float>&, TinyTensor<__nv_bfloat16>&,
+                                               TinyTensor<__nv_bfloat16>&, TinyTensor<__nv_bfloat16>&,
+                                               const TinyTensor<__nv_bfloat16>&, bool, float);
+template void SoftmaxForward<float>(const TinyTensor<float>&, TinyTensor<float>&);

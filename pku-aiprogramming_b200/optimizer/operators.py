@@ -1,0 +1,386 @@
+"""`Tensor`, the NumPy-backed differentiable ops, and the GPU-backed `Attention` op.
+
+Interface and semantics follow the reference's `optimizer/operators.py` (Tensor :14-187,
+TensorOp :189-191, NumPy ops :194-475, GPU-backed op pattern `FC` :498-532): node data is
+always a NumPy array; an op that uses the GPU uploads its inputs into `myTensor` tensors,
+calls a `myLayer` function, and downloads the result.  `Attention` is the op the reference
+lacks; composing MatMul/Transpose/MulScalar/EWiseAdd/Exp/Summation/Reshape/BroadcastTo/EWiseDiv
+from this module gives the same numbers on the CPU (that composition is what the tests check
+the kernels against).
+"""
+from __future__ import annotations
+
+import math
+import os
+import sys
+from typing import Optional
+
+import numpy as np
+
+from .engine import Op, Value, backward_pass
+
+_HOST = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "host_modules")
+
+
+def _native():
+    """The pybind modules (built by `build.py`); imported on first GPU op."""
+    if _HOST not in sys.path:
+        sys.path.insert(0, _HOST)
+    try:
+        import myTensor
+        import myLayer
+    except ImportError as e:  # no silent substitute: the op has no CPU implementation
+        raise ImportError("myTensor/myLayer are not built; run `python pku-aiprogramming_b200/build.py`") from e
+    return myTensor, myLayer
+
+
+class Tensor(Value):
+    grad: "Tensor"
+
+    def __init__(self, array, *, device=None, dtype=None, requires_grad=True, **kwargs):
+        if isinstance(array, Tensor):
+            data = array.realize_cached_data()
+            data = data if dtype is None else np.asarray(data, dtype=dtype)
+        elif isinstance(array, np.ndarray):
+            data = np.array(array, dtype=dtype)
+        elif hasattr(array, "get_data") and hasattr(array, "get_shape"):   # a myTensor tensor
+            data = np.array(array.get_data(), dtype=dtype).reshape(array.get_shape())
+        else:
+            data = np.array(array, dtype=dtype)
+        self._init(None, [], cached_data=data, requires_grad=requires_grad)
+
+    @staticmethod
+    def make_from_op(op: Op, inputs):
+        t = Tensor.__new__(Tensor)
+        t._init(op, inputs)
+        if not t.requires_grad:
+            return t.detach()
+        t.realize_cached_data()
+        return t
+
+    @staticmethod
+    def make_const(data, requires_grad=False):
+        t = Tensor.__new__(Tensor)
+        t._init(None, [], cached_data=data.realize_cached_data() if isinstance(data, Tensor) else data,
+                requires_grad=requires_grad)
+        return t
+
+    def detach(self):
+        return Tensor.make_const(self.realize_cached_data())
+
+    @property
+    def data(self):
+        return self.detach()
+
+    @data.setter
+    def data(self, value):
+        assert isinstance(value, Tensor) and value.dtype == self.dtype
+        self.cached_data = value.realize_cached_data()
+
+    @property
+    def shape(self):
+        return self.realize_cached_data().shape
+
+    @property
+    def dtype(self):
+        return self.realize_cached_data().dtype
+
+    def numpy(self):
+        return self.realize_cached_data()
+
+    def backward(self, out_grad=None):
+        if out_grad is None:
+            out_grad = Tensor(np.ones(self.shape, dtype=self.dtype), requires_grad=False)
+        backward_pass(self, out_grad)
+
+    def __repr__(self):
+        return "Tensor(" + str(self.realize_cached_data()) + ")"
+
+    __str__ = lambda self: str(self.realize_cached_data())
+
+    def __add__(self, other):
+        return EWiseAdd()(self, other) if isinstance(other, Tensor) else AddScalar(other)(self)
+
+    def __mul__(self, other):
+        return EWiseMul()(self, other) if isinstance(other, Tensor) else MulScalar(other)(self)
+
+    def __sub__(self, other):
+        return EWiseAdd()(self, Negate()(other)) if isinstance(other, Tensor) else AddScalar(-other)(self)
+
+    def __truediv__(self, other):
+        return EWiseDiv()(self, other) if isinstance(other, Tensor) else DivScalar(other)(self)
+
+    def __pow__(self, other):
+        return PowerScalar(other)(self)
+
+    def __neg__(self):
+        return Negate()(self)
+
+    def __matmul__(self, other):
+        return MatMul()(self, other)
+
+    matmul = __matmul__
+    __radd__ = __add__
+    __rmul__ = __mul__
+
+    def sum(self, axes=None):
+        return Summation(axes)(self)
+
+    def reshape(self, shape):
+        return Reshape(shape)(self)
+
+    def broadcast_to(self, shape):
+        return BroadcastTo(shape)(self)
+
+    def transpose(self, axes=None):
+        return Transpose(axes)(self)
+
+
+class TensorOp(Op):
+    def __call__(self, *args):
+        return Tensor.make_from_op(self, args)
+
+
+# ----------------------------------------------------------------------------- NumPy ops
+class EWiseAdd(TensorOp):
+    def compute(self, a, b):
+        return a + b
+
+    def gradient(self, g, node):
+        return g, g
+
+
+class AddScalar(TensorOp):
+    def __init__(self, scalar):
+        self.scalar = scalar
+
+    def compute(self, a):
+        return a + self.scalar
+
+    def gradient(self, g, node):
+        return g
+
+
+class EWiseMul(TensorOp):
+    def compute(self, a, b):
+        return a * b
+
+    def gradient(self, g, node):
+        a, b = node.inputs
+        return g * b, g * a
+
+
+class MulScalar(TensorOp):
+    def __init__(self, scalar):
+        self.scalar = scalar
+
+    def compute(self, a):
+        return a * self.scalar
+
+    def gradient(self, g, node):
+        return g * self.scalar
+
+
+class PowerScalar(TensorOp):
+    def __init__(self, scalar):
+        self.scalar = scalar
+
+    def compute(self, a):
+        return np.power(a, self.scalar)
+
+    def gradient(self, g, node):
+        (a,) = node.inputs
+        return g * self.scalar * (a ** (self.scalar - 1))
+
+
+class EWiseDiv(TensorOp):
+    def compute(self, a, b):
+        return a / b
+
+    def gradient(self, g, node):
+        a, b = node.inputs
+        return g / b, -g * a / (b ** 2)
+
+
+class DivScalar(TensorOp):
+    def __init__(self, scalar):
+        self.scalar = scalar
+
+    def compute(self, a):
+        return a / self.scalar
+
+    def gradient(self, g, node):
+        return g / self.scalar
+
+
+class Negate(TensorOp):
+    def compute(self, a):
+        return -a
+
+    def gradient(self, g, node):
+        return -g
+
+
+class Log(TensorOp):
+    def compute(self, a):
+        return np.log(a)
+
+    def gradient(self, g, node):
+        return g / node.inputs[0]
+
+
+class Exp(TensorOp):
+    def compute(self, a):
+        return np.exp(a)
+
+    def gradient(self, g, node):
+        return g * Tensor(np.exp(node.inputs[0].realize_cached_data()), requires_grad=False)
+
+
+class Transpose(TensorOp):
+    """Swaps two axes; the last two when `axes` is None."""
+
+    def __init__(self, axes: Optional[tuple] = None):
+        self.axes = axes
+
+    def compute(self, a):
+        i, j = (a.ndim - 2, a.ndim - 1) if self.axes is None else self.axes
+        return np.swapaxes(a, i, j)
+
+    def gradient(self, g, node):
+        return Transpose(self.axes)(g)
+
+
+class Reshape(TensorOp):
+    def __init__(self, shape):
+        self.shape = shape
+
+    def compute(self, a):
+        return np.reshape(a, self.shape)
+
+    def gradient(self, g, node):
+        return Reshape(node.inputs[0].shape)(g)
+
+
+class BroadcastTo(TensorOp):
+    def __init__(self, shape):
+        self.shape = tuple(shape)
+
+    def compute(self, a):
+        return np.broadcast_to(a, self.shape)
+
+    def gradient(self, g, node):
+        src = tuple(node.inputs[0].shape)
+        padded = (1,) * (len(self.shape) - len(src)) + src
+        axes = tuple(i for i, (s, t) in enumerate(zip(padded, self.shape)) if s != t)
+        return Reshape(src)(Summation(axes)(g))
+
+
+class Summation(TensorOp):
+    def __init__(self, axes=None):
+        self.axes = axes if axes is None or isinstance(axes, (tuple, list)) else (axes,)
+
+    def compute(self, a):
+        return np.sum(a) if self.axes is None else np.sum(a, axis=tuple(self.axes))
+
+    def gradient(self, g, node):
+        shape = node.inputs[0].shape
+        axes = range(len(shape)) if self.axes is None else self.axes
+        kept = [1 if i in axes else s for i, s in enumerate(shape)]
+        return BroadcastTo(shape)(Reshape(kept)(g))
+
+
+class MatMul(TensorOp):
+    def compute(self, a, b):
+        return np.matmul(a, b)
+
+    def gradient(self, g, node):
+        a, b = node.inputs
+        ga, gb = MatMul()(g, Transpose()(b)), MatMul()(Transpose()(a), g)
+        if len(ga.shape) > len(a.shape):
+            ga = Summation(tuple(range(len(ga.shape) - len(a.shape))))(ga)
+        if len(gb.shape) > len(b.shape):
+            gb = Summation(tuple(range(len(gb.shape) - len(b.shape))))(gb)
+        return ga, gb
+
+
+def add(a, b): return EWiseAdd()(a, b)
+def add_scalar(a, s): return AddScalar(s)(a)
+def multiply(a, b): return EWiseMul()(a, b)
+def mul_scalar(a, s): return MulScalar(s)(a)
+def power_scalar(a, s): return PowerScalar(s)(a)
+def divide(a, b): return EWiseDiv()(a, b)
+def divide_scalar(a, s): return DivScalar(s)(a)
+def negate(a): return Negate()(a)
+def log(a): return Log()(a)
+def exp(a): return Exp()(a)
+def transpose(a, axes=None): return Transpose(axes)(a)
+def reshape(a, shape): return Reshape(shape)(a)
+def broadcast_to(a, shape): return BroadcastTo(shape)(a)
+def summation(a, axes=None): return Summation(axes)(a)
+def matmul(a, b): return MatMul()(a, b)
+
+
+# ----------------------------------------------------------------------------- attention
+class Attention(TensorOp):
+    """`softmax(scale * q k^T [+ causal mask]) v` on the GPU.
+
+    q `[B,H,S,D]`, k and v `[B,H,L,D]`.  `dtype="float32"` runs the exact fp32 kernels,
+    `dtype="bfloat16"` rounds the inputs to bf16 (nearest even) and runs the tensor-core
+    kernels; node data stays NumPy float32 either way.  The forward keeps `out` and `lse` on
+    the op instance for the backward, like the reference's ops keep their masks
+    (operators.py:577-586 of the reference).
+    """
+
+    def __init__(self, causal: bool = False, scale: Optional[float] = None, dtype: str = "float32"):
+        if dtype not in ("float32", "bfloat16"):
+            raise ValueError("dtype must be 'float32' or 'bfloat16'")
+        self.causal, self.scale, self.dtype = bool(causal), 0.0 if scale is None else float(scale), dtype
+        self._saved = None
+
+    def _names(self):
+        mt, ml = _native()
+        if self.dtype == "float32":
+            return mt.Tensor_float, ml.AttentionForward, ml.AttentionBackward, mt.Tensor_float
+        return mt.Tensor_bf16, ml.AttentionForward_bf16, ml.AttentionBackward_bf16, mt.Tensor_float
+
+    def compute(self, q, k, v):
+        T, fwd, _, F = self._names()
+        up = lambda a: T(np.ascontiguousarray(a, dtype=np.float32), "gpu")
+        tq, tk, tv = up(q), up(k), up(v)
+        out, lse = T(list(q.shape), "gpu"), F(list(q.shape[:3]), "gpu")
+        fwd(tq, tk, tv, out, lse, self.causal, self.scale)
+        self._saved = (tq, tk, tv, out, lse)
+        return out.numpy().astype(q.dtype, copy=False)
+
+    def gradient(self, out_grad, node):
+        T, _, bwd, _ = self._names()
+        if self._saved is None:
+            node.realize_cached_data()
+        tq, tk, tv, out, lse = self._saved
+        go = T(np.ascontiguousarray(out_grad.realize_cached_data(), dtype=np.float32), "gpu")
+        gq, gk, gv = T(tq.get_shape(), "gpu"), T(tk.get_shape(), "gpu"), T(tv.get_shape(), "gpu")
+        bwd(tq, tk, tv, out, lse, gq, gk, gv, go, self.causal, self.scale)
+        dt = node.inputs[0].dtype
+        mk = lambda t: Tensor(t.numpy().astype(dt, copy=False), requires_grad=False)
+        return mk(gq), mk(gk), mk(gv)
+
+
+def attention(q, k, v, causal: bool = False, scale: Optional[float] = None, dtype: str = "float32"):
+    return Attention(causal, scale, dtype)(q, k, v)
+
+
+def attention_composed(q, k, v, causal: bool = False, scale: Optional[float] = None):
+    """The same function built from the NumPy ops above (CPU): the reference's way of writing
+    attention with what it ships.  Used as the cross-check of the fused op."""
+    B, H, S, D = q.shape
+    L = k.shape[2]
+    sc = 1.0 / math.sqrt(D) if not scale or scale <= 0 else float(scale)
+    s = (q @ transpose(k)) * sc
+    if causal:
+        i, j = np.arange(S)[:, None], np.arange(L)[None, :]
+        mask = np.where(j <= i + (L - S), 0.0, -1e30).astype(q.dtype)
+        s = s + Tensor(np.ascontiguousarray(np.broadcast_to(mask, (B, H, S, L))), requires_grad=False)
+    e = exp(s)
+    den = broadcast_to(reshape(summation(e, axes=(3,)), (B, H, S, 1)), (B, H, S, L))
+    return (e / den) @ v
