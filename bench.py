@@ -3,11 +3,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg5]
 
-One step = causal bf16 attention forward + backward over one batch of synthetic input
-(workload `cfg3`: Q,K,V,dO [B=4,H=32,S=4096,D=128] per GPU, Q/K/V ~ 0.5*N(0,1), dO ~ N(0,1)).
-With N > 1 (launched under torchrun, one process per GPU) every rank owns its own 128
-(batch, head) slices -- weak scaling -- and the step also all-gathers O over NCCL on a side
-stream, overlapped with the backward.  FLOPs are counted as the task defines them: 2 per MAC,
+One step = causal bf16 attention forward + backward over one batch of synthetic input.
+Default workload `cfg5` (BASELINE config 5): Q,K,V,dO [B=1,H=64,S=32768,D=128], Q/K/V ~
+0.5*N(0,1), dO ~ N(0,1).  With N > 1 (launched under torchrun, one process per GPU) the 64
+heads are sharded over the ranks in contiguous ranges -- strong scaling, no collective on the
+data path -- and the step all-gathers O over NCCL on a side stream, overlapped with the
+backward.  At N = 1 the line also carries `cfg3` (BASELINE config 3, [4,32,4096,128]: the shape
+the forward target is stated on) and `decode` (config 4).  `--workload cfg3` makes config 3 the
+main workload (weak scaling: every rank owns its own 128 slices).  FLOPs are counted as the task defines them: 2 per MAC,
 forward = 2 GEMMs, backward = 5 GEMMs (2.5x forward), causal = half of dense.
 
 Prints ONE JSON line (rank 0).  `value` is device-timed with inputs resident in HBM;
@@ -35,7 +38,7 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     # name: (B, H, S, D) per rank
     "cfg3": dict(B=4, H=32, S=4096, D=128, desc="bf16 causal fwd+bwd, Q/K/V [4,32,4096,128] per GPU"),
-    "cfg5": dict(B=1, H=64, S=32768, D=128, desc="bf16 causal fwd+bwd, Q/K/V [1,64,32768,128], heads sharded (strong)"),
+    "cfg5": dict(B=1, H=64, S=32768, D=128, desc="bf16 causal fwd+bwd, Q/K/V [1,64,32768,128], heads sharded over the GPUs"),
     "cfg2": dict(B=8, H=16, S=1024, D=64, desc="bf16 causal fwd+bwd, Q/K/V [8,16,1024,64] per GPU"),
 }
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
@@ -144,12 +147,13 @@ def run_reference_arm(args, w, rank):
     fl = 3.5 * fwd_flops(1, 1, S_cpu, S_cpu, D, True)
     sec = float(np.mean(ts))
     val = fl / sec / 1e12
-    sample = f"one (batch,head) slice per step, causal fwd+bwd, S=L={S_cpu}, D={D}, fp32 NumPy"
+    what = "one (batch,head) slice" if S_cpu == S else f"the S=L={S_cpu} prefix of one (batch,head) slice"
+    sample = f"{what} per step, causal fwd+bwd, D={D}, fp32 NumPy, all BLAS threads"
     line = {
         "impl": "reference", "metric": "attention fwd+bwd TFLOP/s", "value": val, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["desc"], "sampled": sample},
+        "higher_is_better": True, "scaling": "strong" if args.workload == "cfg5" else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": w["desc"], "sampled": sample},
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -158,16 +162,198 @@ def run_reference_arm(args, w, rank):
 
 
 # ------------------------------------------------------------------------------------ GPU arm
+ALG_FWD_UNITS = {  # algorithmic FLOPs per launch, in units of the forward's count
+    "attn_fwd_sm100": 1.0,        # QK^T, PV
+    "attn_bwd_sm100_dkv": 2.0,    # S recompute, dP, dV, dK  (4 of the 5 backward GEMMs)
+    "attn_bwd_sm100_dq": 0.5,     # dQ (its S and dP recompute is overhead of the two-pass design)
+}
+
+
+def run_workload(tt, name, steps, warmup, world, rank, dev, peaks, e2e_steps, sample_clocks):
+    """Times `steps` forward+backward steps of workload `name`; returns the fields of the JSON line."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    capi = tt.capi
+    w = WORKLOADS[name]
+    B, H, S, D = w["B"], w["H"], w["S"], w["D"]
+    strong = name == "cfg5"
+    if strong:
+        _, cnt = capi.shard_range(B * H, world, rank)
+        Bl, Hl = 1, cnt
+    else:
+        Bl, Hl = B, H
+    n_local = Bl * Hl
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    mk = lambda sig: (torch.randn((Bl, Hl, S, D), generator=g, device=dev) * sig).to(torch.bfloat16)
+    q, k, v, do = mk(0.5), mk(0.5), mk(0.5), mk(1.0)
+    out = torch.empty_like(q)
+    lse = torch.empty((Bl, Hl, S), dtype=torch.float32, device=dev)
+    desc = capi.make_desc(Bl, Hl, S, S, D, capi.TT_BF16, True, None)
+    ws = torch.empty(max(int(capi.lib.tt_attn_bwd_workspace_bytes(ctypes.byref(desc))), 256), dtype=torch.uint8, device=dev)
+    grads = {}
+    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    out_full = torch.empty((world * n_local, S, D), dtype=torch.bfloat16, device=dev) if world > 1 else None
+
+    def step():
+        tt.attention_forward(q, k, v, causal=True, out=out, lse=lse)
+        if world > 1:
+            ev = torch.cuda.Event()
+            ev.record()
+            with torch.cuda.stream(comm_stream):
+                comm_stream.wait_event(ev)
+                dist.all_gather_into_tensor(out_full, out.view(n_local, S, D))
+        grads["g"] = tt.attention_backward(q, k, v, out, lse, do, causal=True, workspace=ws)
+        if world > 1:
+            torch.cuda.current_stream().wait_stream(comm_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    tt.check_device_status()
+    barrier()
+    sampler = ClockSampler(dev.index)
+    if sample_clocks:
+        sampler.start()
+        time.sleep(0.25)
+    capi.profile_reset()
+    capi.profile_enable(True)
+    launches0 = capi.launch_count()
+    torch.cuda.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = capi.launch_count() - launches0
+    capi.profile_enable(False)
+    prof = capi.profile_read()
+    clocks = sampler.stop() if sample_clocks else None
+    tt.check_device_status()
+    if world > 1:
+        t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / steps
+    f_fwd = fwd_flops(Bl, Hl, S, S, D, True)                       # this rank's forward count per step
+    f_step_all = 3.5 * fwd_flops(B, H, S, S, D, True) if strong else 3.5 * f_fwd * world
+    value = f_step_all / (ms_step * 1e-3) / 1e12
+
+    # per-kernel rooflines from the events recorded inside the timed region
+    traffic_scale = {"cfg3": 1.0, "cfg5": 4.0}.get(name)           # tensor bytes relative to the ncu capture (cfg3)
+    if strong and world > 1:
+        traffic_scale = None
+    kernels = {}
+    total_ms = max(sum(x[0] for x in prof.values()), 1e-9)
+    for kname, (ms, n) in prof.items():
+        per = ms / n
+        ent = {"launches": n, "ms_per_launch": per, "share": ms / total_ms}
+        if kname in ALG_FWD_UNITS:
+            ach = ALG_FWD_UNITS[kname] * f_fwd / (per * 1e-3) / 1e12
+            tr = NCU_TRAFFIC_BYTES.get(kname)
+            ent.update({"bound": "tensor", "achieved": ach, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                        "frac": ach / peaks["bf16"],
+                        "traffic": tr * traffic_scale if (tr and traffic_scale) else None})
+        kernels[kname] = ent
+    dom = max((n for n in kernels if n in ALG_FWD_UNITS), key=lambda n: kernels[n]["share"], default=None)
+    roofline = None
+    if dom:
+        roofline = {k_: kernels[dom][k_] for k_ in ("bound", "achieved", "peak", "unit", "frac", "traffic")}
+        roofline["kernel"] = dom
+        roofline["peak_source"] = f"bf16_tflops (burst) of {peaks['source']} MEASURED_PEAKS.json"
+        if traffic_scale and traffic_scale != 1.0:
+            roofline["traffic_note"] = "ncu capture of the cfg3 launch scaled by tensor bytes (x4)"
+    fwd_tf = kernels.get("attn_fwd_sm100", {}).get("achieved")
+
+    # end to end through the host-buffer C ABI (pinned host memory)
+    e2e = None
+    if e2e_steps > 0:
+        hq, hk, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, do))
+        ho, hl = torch.empty_like(hq).pin_memory(), torch.empty((Bl, Hl, S), dtype=torch.float32).pin_memory()
+        hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(3))
+
+        def e2e_step():
+            tt.attention_forward_host(hq, hk, hv, causal=True, out=ho, lse=hl)
+            tt.attention_backward_host(hq, hk, hv, ho, hl, hdo, causal=True, dq=hdq, dk=hdk, dv=hdv)
+
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        sec = (time.perf_counter() - t0) / e2e_steps
+        if world > 1:
+            t = torch.tensor([sec], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        nb = hq.numel() * 2
+        nl = hl.numel() * 4
+        e2e = {"value": f_step_all / sec / 1e12, "unit": "TFLOP/s", "ms_per_step": sec * 1e3,
+               "h2d_bytes_per_step": int((3 * nb) + (5 * nb + nl)), "d2h_bytes_per_step": int((nb + nl) + 3 * nb),
+               "steps": e2e_steps, "api": "tt_attn_fwd_host + tt_attn_bwd_host (upload, run, download per op)"}
+        del hq, hk, hv, hdo, ho, hl, hdq, hdk, hdv
+        tt.capi.lib.tt_pool_trim()
+    return dict(value=value, ms_per_step=ms_step, scaling="strong" if strong else "weak", kernels=kernels,
+                roofline=roofline, fwd_tflops=fwd_tf, e2e=e2e, clocks=clocks, gpu_launches=int(launches),
+                n_local=n_local, desc=w["desc"], S=S, D=D,
+                pct_of_bf16_peak={"fwd": (fwd_tf / peaks["bf16"] * 100) if fwd_tf else None,
+                                  "fwd_bwd": value / world / peaks["bf16"] * 100})
+
+
+def run_decode(tt, dev, peaks, batch):
+    """BASELINE config 4 (HBM-bound): reported beside the step metric, not part of it."""
+    import torch
+    capi = tt.capi
+    try:
+        dB, dH, dL, dD = batch, 32, 8192, 128
+        dq_ = torch.randn((dB, dH, 1, dD), device=dev).to(torch.bfloat16)
+        dk_ = torch.randn((dB, dH, dL, dD), device=dev).to(torch.bfloat16)
+        dv_ = torch.randn((dB, dH, dL, dD), device=dev).to(torch.bfloat16)
+        dout_ = torch.empty_like(dq_)
+        dws = torch.empty(max(tt.decode_workspace_bytes(dB, dH, dL, dD), 256), dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            tt.attention_decode(dq_, dk_, dv_, out=dout_, workspace=dws, need_lse=False)
+        torch.cuda.synchronize()
+        capi.profile_reset(); capi.profile_enable(True)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(20):
+            tt.attention_decode(dq_, dk_, dv_, out=dout_, workspace=dws, need_lse=False)
+        b.record(); torch.cuda.synchronize()
+        capi.profile_enable(False)
+        dprof = capi.profile_read()
+        ms = a.elapsed_time(b) / 20
+        by = 2.0 * dB * dH * dL * dD * 2 + 2.0 * dB * dH * dD * 2
+        kms = dprof["attn_decode"][0] / dprof["attn_decode"][1]
+        return {"workload": f"bf16 decode Q [{dB},32,1,128], K/V [{dB},32,8192,128]", "ms": ms, "gbs": by / ms / 1e6,
+                "roofline": {"bound": "hbm", "achieved": by / kms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
+                             "frac": by / kms / 1e6 / peaks["hbm"],
+                             "traffic": NCU_TRAFFIC_BYTES.get("attn_decode") if dB == 64 else None,
+                             "kernel": "attn_decode", "peak_source": f"hbm_gbs of {peaks['source']} MEASURED_PEAKS.json"}}
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
-    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cfg3", action="store_true", help="skip the S=4096 side measurement at N=1")
+    ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--decode-batch", type=int, default=64, help="batch of the decode leg (64 = BASELINE config 4)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -190,190 +376,46 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     tt = importlib.import_module("pku-aiprogramming_b200")
-    capi = tt.capi
     peaks = load_peaks()
 
-    B, H, S, D = w["B"], w["H"], w["S"], w["D"]
-    strong = args.workload == "cfg5"
-    if strong:
-        b0, cnt = capi.shard_range(B * H, world, rank)
-        Bl, Hl = 1, cnt
-    else:
-        Bl, Hl = B, H
-    n_local = Bl * Hl
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    mk = lambda sig: (torch.randn((Bl, Hl, S, D), generator=g, device=dev) * sig).to(torch.bfloat16)
-    q, k, v, do = mk(0.5), mk(0.5), mk(0.5), mk(1.0)
-    out = torch.empty_like(q)
-    lse = torch.empty((Bl, Hl, S), dtype=torch.float32, device=dev)
-    desc = capi.make_desc(Bl, Hl, S, S, D, capi.TT_BF16, True, None)
-    import ctypes
-    ws = torch.empty(max(int(capi.lib.tt_attn_bwd_workspace_bytes(ctypes.byref(desc))), 256), dtype=torch.uint8, device=dev)
-    grads = {}
-    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-    out_full = torch.empty((world * n_local, S, D), dtype=torch.bfloat16, device=dev) if world > 1 else None
+    main_res = run_workload(tt, args.workload, args.steps, args.warmup, world, rank, dev, peaks, args.e2e_steps,
+                            sample_clocks=(rank == 0))
+    side = None
+    if rank == 0 and world == 1 and args.workload != "cfg3" and not args.no_cfg3:
+        # the S=4096/D=128 shape the forward target (>= 60 % of bf16 peak) is stated on
+        r3 = run_workload(tt, "cfg3", 20, 5, 1, 0, dev, peaks, 0, sample_clocks=False)
+        side = {"workload": r3["desc"], "fwd_bwd_tflops": r3["value"], "ms_per_step": r3["ms_per_step"],
+                "fwd_tflops": r3["fwd_tflops"], "pct_of_bf16_peak": r3["pct_of_bf16_peak"], "kernels": r3["kernels"]}
+    decode = run_decode(tt, dev, peaks, args.decode_batch) if (rank == 0 and not args.no_decode) else None
 
-    def step():
-        tt.attention_forward(q, k, v, causal=True, out=out, lse=lse)
-        if world > 1:
-            ev = torch.cuda.Event()
-            ev.record()
-            with torch.cuda.stream(comm_stream):
-                comm_stream.wait_event(ev)
-                dist.all_gather_into_tensor(out_full, out.view(n_local, S, D))
-        grads["g"] = tt.attention_backward(q, k, v, out, lse, do, causal=True, workspace=ws)
-        if world > 1:
-            torch.cuda.current_stream().wait_stream(comm_stream)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-
-    for _ in range(args.warmup):
-        step()
-    torch.cuda.synchronize()
-    tt.check_device_status()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.25)
-    capi.profile_reset()
-    capi.profile_enable(True)
-    launches0 = capi.launch_count()
-    torch.cuda.synchronize()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    launches = capi.launch_count() - launches0
-    capi.profile_enable(False)
-    prof = capi.profile_read()
-    clocks = sampler.stop() if rank == 0 else None
-    tt.check_device_status()
-    if world > 1:
-        t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-    f_fwd = fwd_flops(Bl, Hl, S, S, D, True)
-    f_step_all = 3.5 * fwd_flops(B, H, S, S, D, True) if strong else 3.5 * f_fwd * world
-    value = f_step_all / (ms_step * 1e-3) / 1e12
-
-    # ---- per-kernel rooflines from the events recorded inside the timed region
-    alg = {  # algorithmic FLOPs per launch, in units of the forward's count
-        "attn_fwd_sm100": 1.0,        # QK^T, PV
-        "attn_bwd_sm100_dkv": 2.0,    # S recompute, dP, dV, dK  (4 of the 5 backward GEMMs)
-        "attn_bwd_sm100_dq": 0.5,     # dQ (its S and dP recompute is overhead of the two-pass design)
-    }
-    kernels = {}
-    for name, (ms, n) in prof.items():
-        per = ms / n
-        ent = {"launches": n, "ms_per_launch": per, "share": ms / max(sum(x[0] for x in prof.values()), 1e-9)}
-        if name in alg:
-            ach = alg[name] * f_fwd / (per * 1e-3) / 1e12
-            ent.update({"bound": "tensor", "achieved": ach, "peak": peaks["bf16"], "unit": "TFLOP/s",
-                        "frac": ach / peaks["bf16"],
-                        "traffic": NCU_TRAFFIC_BYTES.get(name) if args.workload == "cfg3" else None})
-        kernels[name] = ent
-    dom = max((n for n in kernels if n in alg), key=lambda n: kernels[n]["share"], default=None)
-    roofline = None
-    if dom:
-        roofline = {k_: kernels[dom][k_] for k_ in ("bound", "achieved", "peak", "unit", "frac", "traffic")}
-        roofline["kernel"] = dom
-        roofline["peak_source"] = f"bf16_tflops (burst) of {peaks['source']} MEASURED_PEAKS.json"
-    fwd_tf = kernels.get("attn_fwd_sm100", {}).get("achieved")
-
-    # ---- end to end through the host-buffer C ABI (pinned host memory)
-    e2e = None
-    if args.e2e_steps > 0:
-        hq, hk, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, do))
-        ho, hl = torch.empty_like(hq).pin_memory(), torch.empty((Bl, Hl, S), dtype=torch.float32).pin_memory()
-        hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(3))
-
-        def e2e_step():
-            tt.attention_forward_host(hq, hk, hv, causal=True, out=ho, lse=hl)
-            tt.attention_backward_host(hq, hk, hv, ho, hl, hdo, causal=True, dq=hdq, dk=hdk, dv=hdv)
-
-        e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.e2e_steps):
-            e2e_step()
-        torch.cuda.synchronize()
-        sec = (time.perf_counter() - t0) / args.e2e_steps
-        if world > 1:
-            t = torch.tensor([sec], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            sec = float(t.item())
-        nb = hq.numel() * 2
-        nl = hl.numel() * 4
-        e2e = {"value": f_step_all / sec / 1e12, "unit": "TFLOP/s", "ms_per_step": sec * 1e3,
-               "h2d_bytes_per_step": int((3 * nb) + (5 * nb + nl)), "d2h_bytes_per_step": int((nb + nl) + 3 * nb),
-               "steps": args.e2e_steps, "api": "tt_attn_fwd_host + tt_attn_bwd_host (upload, run, download per op)"}
-        del hq, hk, hv, hdo, ho, hl, hdq, hdk, hdv
-
-    # ---- decode (BASELINE config 4): HBM-bound, reported beside the step metric, not part of it
-    decode = None
-    if rank == 0 and not args.no_decode:
-        try:
-            dB, dH, dL, dD = args.decode_batch, 32, 8192, 128
-            dq_ = torch.randn((dB, dH, 1, dD), device=dev).to(torch.bfloat16)
-            dk_ = torch.randn((dB, dH, dL, dD), device=dev).to(torch.bfloat16)
-            dv_ = torch.randn((dB, dH, dL, dD), device=dev).to(torch.bfloat16)
-            dout_ = torch.empty_like(dq_)
-            dws = torch.empty(max(tt.decode_workspace_bytes(dB, dH, dL, dD), 256), dtype=torch.uint8, device=dev)
-            for _ in range(3):
-                tt.attention_decode(dq_, dk_, dv_, out=dout_, workspace=dws, need_lse=False)
-            torch.cuda.synchronize()
-            capi.profile_reset(); capi.profile_enable(True)
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            for _ in range(20):
-                tt.attention_decode(dq_, dk_, dv_, out=dout_, workspace=dws, need_lse=False)
-            b.record(); torch.cuda.synchronize()
-            capi.profile_enable(False)
-            dprof = capi.profile_read()
-            ms = a.elapsed_time(b) / 20
-            by = 2.0 * dB * dH * dL * dD * 2 + 2.0 * dB * dH * dD * 2
-            kms = dprof["attn_decode"][0] / dprof["attn_decode"][1]
-            decode = {"workload": f"bf16 decode Q [{dB},32,1,128], K/V [{dB},32,8192,128]", "ms": ms, "gbs": by / ms / 1e6,
-                      "roofline": {"bound": "hbm", "achieved": by / kms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
-                                   "frac": by / kms / 1e6 / peaks["hbm"], "traffic": NCU_TRAFFIC_BYTES.get("attn_decode") if dB == 64 else None,
-                                   "kernel": "attn_decode", "peak_source": f"hbm_gbs of {peaks['source']} MEASURED_PEAKS.json"}}
-            del dq_, dk_, dv_
-        except Exception as e:  # noqa: BLE001
-            decode = {"error": str(e)}
-
-    # ---- CPU baseline: the oracle on a bounded sample of the same workload (rank 0, N = 1)
+    # CPU baseline: the oracle on a bounded sample of the same workload (rank 0, N = 1)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        S, D = main_res["S"], main_res["D"]
         S_cpu = min(S, 4096)
         t1 = cpu_sample_seconds(S_cpu, D, 7)
         n = int(min(16, max(2, round(12.0 / max(t1, 1e-3)))))
         ts = [cpu_sample_seconds(S_cpu, D, 8 + i) for i in range(n)]
         fl = 3.5 * fwd_flops(1, 1, S_cpu, S_cpu, D, True)
+        what = "whole (batch,head) slices" if S_cpu == S else f"the S=L={S_cpu} prefix of (batch,head) slices"
         cpu = {"value": fl / float(np.mean(ts)) / 1e12, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
-               "sample": f"{n} of {n_local} (batch,head) slices, causal fwd+bwd S=L={S_cpu} D={D}, fp32 NumPy oracle, "
-                         f"{float(np.mean(ts)):.2f} s per slice"}
+               "sample": f"{n} samples of {what}, causal fwd+bwd, D={D}, fp32 NumPy oracle, "
+                         f"{float(np.mean(ts)):.2f} s per sample"}
 
     if rank == 0:
         line = {
-            "metric": "attention fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": w["desc"], "causal": True, "flop_count": "2/MAC, fwd 2 GEMMs, bwd 5 GEMMs, causal = half",
-                       "l2": "inputs (0.5 GB) exceed the 126 MB L2", "collective": "all-gather of O over NCCL, overlapped with backward" if world > 1 else "none",
-                       "parallelism": f"{world} x (batch,head) shards"},
-            "fwd_tflops": fwd_tf, "pct_of_bf16_peak": {"fwd": (fwd_tf / peaks["bf16"] * 100) if fwd_tf else None,
-                                                       "fwd_bwd": value / world / peaks["bf16"] * 100},
-            "roofline": roofline, "kernels": kernels, "decode": decode, "cpu_baseline": cpu, "e2e": e2e,
-            "clocks": clocks, "gpu_launches": int(launches),
+            "metric": "attention fwd+bwd TFLOP/s", "value": main_res["value"], "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"], "higher_is_better": True,
+            "scaling": main_res["scaling"], "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": main_res["desc"], "causal": True,
+                       "flop_count": "2/MAC, fwd 2 GEMMs, bwd 5 GEMMs, causal = half",
+                       "l2": "inputs per step (>= 0.5 GB) exceed the 126 MB L2",
+                       "collective": "all-gather of O over NCCL, overlapped with backward" if world > 1 else "none",
+                       "parallelism": f"{world} x contiguous (batch,head) shards"},
+            "fwd_tflops": main_res["fwd_tflops"], "pct_of_bf16_peak": main_res["pct_of_bf16_peak"],
+            "roofline": main_res["roofline"], "kernels": main_res["kernels"], "cfg3": side, "decode": decode,
+            "cpu_baseline": cpu, "e2e": main_res["e2e"], "clocks": main_res["clocks"],
+            "gpu_launches": main_res["gpu_launches"],
         }
         print(json.dumps(line), flush=True)
     if world > 1:
