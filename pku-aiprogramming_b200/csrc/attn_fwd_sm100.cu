@@ -26,6 +26,8 @@
 #include "common.h"
 #include "sm100_ptx.cuh"
 #include <stdlib.h>
+#include <algorithm>
+#include <atomic>
 
 namespace ttk {
 using namespace sm100;
@@ -53,6 +55,8 @@ struct FwdParams {
     int causal;
     float scale_log2; // scale * log2(e)
     unsigned int* status;
+    unsigned int* sched_counter;   // zero at launch; work items are taken with atomicAdd
+    int n_items;                   // slices * n_qblk
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
 };
@@ -124,6 +128,38 @@ __device__ __forceinline__ uint64_t softmax_exp_half(const uint32_t (&sr)[4][32]
 
 // kPoly: of every 8 exponentials, kPoly are evaluated by a polynomial on the FMA pipes instead
 // of the special-function unit (0..4), to balance the two pipes.
+//
+// The kernel is persistent: one CTA per SM takes work items (slice, 256-row query block) from a
+// global counter until none are left.  Items are numbered slice-major with the heavy (late)
+// query blocks of a slice first, so that concurrently running CTAs share a slice's K/V in L2 and
+// the tail of the launch consists of light items.  The loader runs up to two items ahead; the
+// first MMAs of item n+1 overlap the epilogue (normalise, store O) of item n.
+struct FwdItem {
+    int bh, q0, n_tiles[2], n_max;
+};
+__device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p) {
+    FwdItem w;
+    w.bh = item / p.n_qblk;
+    const int qb = p.n_qblk - 1 - (item % p.n_qblk);
+    w.q0 = qb * 256;
+    const int off = p.L - p.S;
+    const int n_kv_total = (p.L + 127) >> 7;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r0 = w.q0 + 128 * i;
+        if (r0 >= p.S) {
+            w.n_tiles[i] = 0;
+        } else if (p.causal) {
+            const int last_row = min(r0 + 127, p.S - 1);
+            w.n_tiles[i] = min(n_kv_total, ((last_row + off) >> 7) + 1);
+        } else {
+            w.n_tiles[i] = n_kv_total;
+        }
+    }
+    w.n_max = max(w.n_tiles[0], w.n_tiles[1]);
+    return w;
+}
+
 template <int D, int kPoly>
 __global__ void __launch_bounds__(FwdCfg<D>::kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -136,47 +172,36 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     unsigned char* sQ = smem;                                  // 2 tiles
     unsigned char* sKV = smem + 2 * Cfg::kTileBytes;           // kStages tiles
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + kStages) * Cfg::kTileBytes);
-    uint64_t* bar_q_full = bars;               // [2]
-    uint64_t* bar_kv_full = bars + 2;          // [kStages]
-    uint64_t* bar_kv_empty = bars + 2 + kStages;
-    uint64_t* bar_s_full = bars + 2 + 2 * kStages;   // [2]
-    uint64_t* bar_p_full = bar_s_full + 2;           // [2 tiles][2 halves of the key tile]
-    uint64_t* bar_o_final = bar_p_full + 4;          // [2]
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bar_o_final + 2);
+    uint64_t* bar_q_full = bars;                     // [2]  TMA -> MMA
+    uint64_t* bar_q_empty = bar_q_full + 2;          // [2]  MMA (last S of the item) -> TMA
+    uint64_t* bar_kv_full = bar_q_empty + 2;         // [kStages]
+    uint64_t* bar_kv_empty = bar_kv_full + kStages;  // [kStages]
+    uint64_t* bar_s_full = bar_kv_empty + kStages;   // [2]  MMA -> softmax
+    uint64_t* bar_p_full = bar_s_full + 2;           // [2 tiles][2 halves of the key tile] softmax -> MMA
+    uint64_t* bar_o_final = bar_p_full + 4;          // [2]  MMA -> softmax (epilogue)
+    uint64_t* bar_o_free = bar_o_final + 2;          // [2]  softmax (O read out) -> MMA
+    uint64_t* bar_sched_full = bar_o_free + 2;       // [2]  loader -> MMA + softmax
+    uint64_t* bar_sched_empty = bar_sched_full + 2;  // [2]
+    int* sched_item = reinterpret_cast<int*>(bar_sched_empty + 2);   // [2]
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sched_item + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
     const int warp = uniform_warp_idx();
     const int lane = threadIdx.x & 31;
-
-    // ---- which rows / how many key tiles
-    const int bh = blockIdx.x / p.n_qblk;
-    const int qb = p.n_qblk - 1 - (int)(blockIdx.x % p.n_qblk);   // heavy (late) query blocks first
-    const int q0 = qb * 256;
     const int off = p.L - p.S;
-    const int n_kv_total = (p.L + 127) >> 7;
-    int n_tiles[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        int r0 = q0 + 128 * i;
-        if (r0 >= p.S) {
-            n_tiles[i] = 0;
-        } else if (p.causal) {
-            int last_row = min(r0 + 127, p.S - 1);
-            n_tiles[i] = min(n_kv_total, ((last_row + off) >> 7) + 1);
-        } else {
-            n_tiles[i] = n_kv_total;
-        }
-    }
-    const int n_max = max(n_tiles[0], n_tiles[1]);
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_q_full[i], 1);
+            mbar_init(&bar_q_empty[i], 1);
             mbar_init(&bar_s_full[i], 1);
             mbar_init(&bar_p_full[2 * i], 128);
             mbar_init(&bar_p_full[2 * i + 1], 128);
             mbar_init(&bar_o_final[i], 1);
+            mbar_init(&bar_o_free[i], 128);
+            mbar_init(&bar_sched_full[i], 1);
+            mbar_init(&bar_sched_empty[i], 257);   // MMA warp (1) + 256 softmax threads
         }
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&bar_kv_full[s], 1);
@@ -200,123 +225,144 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t tmem_base = *tmem_base_slot;
     WaitCtx wctx{p.status, abort_flag, warp};
 
+    // Every role walks the same item sequence.  Items are published by the loader in a two-slot
+    // ring; a negative value ends the sequence.
+    auto next_item = [&](int k) -> int {
+        const int slot = k & 1;
+        mbar_wait(&bar_sched_full[slot], (k >> 1) & 1, wctx, 80 + slot, k);
+        const int item = sched_item[slot];
+        return item;
+    };
+
     if (warp < 8) {
         // =========================================================== softmax warpgroups
         setmaxnreg_inc<224>();
         const int i = warp >> 2;                    // query tile
-        const int nt = n_tiles[i];
         const int wq = warp & 3;                    // TMEM lane quarter of this warp
-        const int row = q0 + 128 * i + wq * 32 + lane;
         const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
         const uint32_t tS = tmem_base + lane_off + (uint32_t)(i * 128);
         const uint32_t tP = tS;
         const uint32_t tO = tmem_base + lane_off + (uint32_t)(256 + i * D);
         const float c = p.scale_log2;
-        float m2 = -INFINITY;   // running max in the scaled log2 domain
-        float l = 0.f;          // running sum of exp2(s*c - m2)
-        for (int j = 0; j < nt; ++j) {
-            if (wq == 0 && lane == 0) TT_TRACE(i, j, 0);
-            mbar_wait(&bar_s_full[i], j & 1, wctx, BAR_SFULL + i, j);
+        uint32_t s_cnt = 0;    // S tiles of this query-tile slot consumed so far (barrier phase)
+        uint32_t o_cnt = 0;    // items in which this slot was active
+        for (int k = 0;; ++k) {
+            const int item = next_item(k);
             __syncwarp();
-            tc_fence_after();
-            if (wq == 0 && lane == 0) TT_TRACE(i, j, 1);
-            // visible columns of this row inside the tile: [0, lim)
-            const int kv0 = j << 7;
-            const bool need_mask = (kv0 + 128 > p.L) || (p.causal && (kv0 + 127 > (q0 + 128 * i) + off));
-            int lim = 128;
-            if (need_mask) {
-                lim = p.L;
-                if (p.causal) lim = min(lim, row + off + 1);
-                lim -= kv0;
-            }
-            uint32_t sr[4][32];
-            load_s_row(tS, sr, need_mask, lim);
-            if (wq == 0 && lane == 0) TT_TRACE(i, j, 2);
-            const float mx = row_max_raw(sr) * c;
-            float resc = 1.0f;
-            bool grow = false;
-            if (j == 0) {
-                m2 = mx;
-            } else if (mx > m2 + 8.0f) {   // lazy rescale: only when the max grew by more than 2^8
-                resc = ex2_approx(m2 - mx);
-                m2 = mx;
-                l *= resc;
-                grow = true;
-            }
-            if (__any_sync(0xffffffffu, grow)) {
-                // O_i *= resc (the previous P V of this tile has completed: its commit precedes the
-                // S commit waited on above)
-#pragma unroll
-                for (int cc = 0; cc < D / 32; ++cc) {
-                    uint32_t orr[32];
-                    tmem_ld32(tO + cc * 32, orr);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * resc);
-                    tmem_st32(tO + cc * 32, orr);
-                }
-            }
-            if (wq == 0 && lane == 0) TT_TRACE(i, j, 3);
-            // P = exp2(S*c - m2) in two halves of 64 keys; the P V MMAs of a half start as soon as
-            // that half is in tensor memory
-            uint64_t acc = pack_f32x2(0.f, 0.f);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t pk[32];
-                acc = add_f32x2(acc, softmax_exp_half<kPoly>(sr, h, c, m2, pk));
-#pragma unroll
-                for (int q4 = 0; q4 < 2; ++q4) {
-                    uint32_t t16[16];
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) t16[e] = pk[q4 * 16 + e];
-                    tmem_st16(tP + h * 32 + q4 * 16, t16);
-                }
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(&bar_p_full[2 * i + h]);
-                if (wq == 0 && lane == 0) TT_TRACE(i, j, 4 + h);
-            }
-            {
-                float t0, t1;
-                unpack_f32x2(acc, t0, t1);
-                l += t0 + t1;
-            }
-        }
-        if (nt > 0) {
-            // ---- epilogue: O_i / l -> bf16 -> global, LSE
-            mbar_wait(&bar_o_final[i], 0, wctx, BAR_OFINAL + i, 0);
-            __syncwarp();
-            tc_fence_after();
-            const float inv = 1.0f / l;
-            const bool row_ok = row < p.S;
-            __nv_bfloat16* orow = p.out + ((long long)bh * p.S + row) * D;
-#pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc) {
-                uint32_t orr[32];
+            mbar_arrive(&bar_sched_empty[k & 1]);
+            if (item < 0) break;
+            const FwdItem w = fwd_decode_item(item, p);
+            const int nt = w.n_tiles[i];
+            if (nt == 0) continue;
+            const int row = w.q0 + 128 * i + wq * 32 + lane;
+            float m2 = -INFINITY;   // running max in the scaled log2 domain
+            float l = 0.f;          // running sum of exp2(s*c - m2)
+            for (int j = 0; j < nt; ++j, ++s_cnt) {
+                const bool tr = (k == 0 && wq == 0 && lane == 0);
+                if (tr) TT_TRACE(i, j, 0);
+                mbar_wait(&bar_s_full[i], s_cnt & 1, wctx, BAR_SFULL + i, j);
                 __syncwarp();
-                tmem_ld32(tO + cc * 32, orr);
-                tmem_wait_ld();
-                if (row_ok) {
+                tc_fence_after();
+                if (tr) TT_TRACE(i, j, 1);
+                // visible columns of this row inside the tile: [0, lim)
+                const int kv0 = j << 7;
+                const bool need_mask = (kv0 + 128 > p.L) || (p.causal && (kv0 + 127 > (w.q0 + 128 * i) + off));
+                int lim = 128;
+                if (need_mask) {
+                    lim = p.L;
+                    if (p.causal) lim = min(lim, row + off + 1);
+                    lim -= kv0;
+                }
+                uint32_t sr[4][32];
+                load_s_row(tS, sr, need_mask, lim);
+                if (tr) TT_TRACE(i, j, 2);
+                const float mx = row_max_raw(sr) * c;
+                float resc = 1.0f;
+                bool grow = false;
+                if (j == 0) {
+                    m2 = mx;
+                } else if (mx > m2 + 8.0f) {   // lazy rescale: only when the max grew by more than 2^8
+                    resc = ex2_approx(m2 - mx);
+                    m2 = mx;
+                    l *= resc;
+                    grow = true;
+                }
+                if (__any_sync(0xffffffffu, grow)) {
+                    // O_i *= resc (the previous P V of this tile has completed: its commit precedes the
+                    // S commit waited on above)
 #pragma unroll
-                    for (int e = 0; e < 32; e += 8) {
-                        uint4 w;
-                        w.x = pack_bf16x2(__uint_as_float(orr[e + 0]) * inv, __uint_as_float(orr[e + 1]) * inv);
-                        w.y = pack_bf16x2(__uint_as_float(orr[e + 2]) * inv, __uint_as_float(orr[e + 3]) * inv);
-                        w.z = pack_bf16x2(__uint_as_float(orr[e + 4]) * inv, __uint_as_float(orr[e + 5]) * inv);
-                        w.w = pack_bf16x2(__uint_as_float(orr[e + 6]) * inv, __uint_as_float(orr[e + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + cc * 32 + e) = w;
+                    for (int cc = 0; cc < D / 32; ++cc) {
+                        uint32_t orr[32];
+                        tmem_ld32(tO + cc * 32, orr);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * resc);
+                        tmem_st32(tO + cc * 32, orr);
                     }
                 }
+                if (tr) TT_TRACE(i, j, 3);
+                // P = exp2(S*c - m2) in two halves of 64 keys; the P V MMAs of a half start as soon as
+                // that half is in tensor memory
+                uint64_t acc = pack_f32x2(0.f, 0.f);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t pk[32];
+                    acc = add_f32x2(acc, softmax_exp_half<kPoly>(sr, h, c, m2, pk));
+#pragma unroll
+                    for (int q4 = 0; q4 < 2; ++q4) {
+                        uint32_t t16[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) t16[e] = pk[q4 * 16 + e];
+                        tmem_st16(tP + h * 32 + q4 * 16, t16);
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&bar_p_full[2 * i + h]);
+                    if (tr) TT_TRACE(i, j, 4 + h);
+                }
+                {
+                    float t0, t1;
+                    unpack_f32x2(acc, t0, t1);
+                    l += t0 + t1;
+                }
             }
-            if (row_ok && p.lse != nullptr)
-                p.lse[(long long)bh * p.S + row] = (m2 + log2f(l)) * 0.6931471805599453f;
+            // ---- epilogue: O_i out of tensor memory (then the MMA warp may start the next item's
+            // accumulation in it), O_i / l -> bf16 -> global, LSE
+            mbar_wait(&bar_o_final[i], o_cnt & 1, wctx, BAR_OFINAL + i, k);
+            ++o_cnt;
+            __syncwarp();
+            tc_fence_after();
+            uint32_t orr[D / 32][32];
+#pragma unroll
+            for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tO + cc * 32, orr[cc]);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&bar_o_free[i]);
+            const float inv = 1.0f / l;
+            if (row < p.S) {
+                __nv_bfloat16* orow = p.out + ((long long)w.bh * p.S + row) * D;
+#pragma unroll
+                for (int cc = 0; cc < D / 32; ++cc) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 o4;
+                        o4.x = pack_bf16x2(__uint_as_float(orr[cc][e + 0]) * inv, __uint_as_float(orr[cc][e + 1]) * inv);
+                        o4.y = pack_bf16x2(__uint_as_float(orr[cc][e + 2]) * inv, __uint_as_float(orr[cc][e + 3]) * inv);
+                        o4.z = pack_bf16x2(__uint_as_float(orr[cc][e + 4]) * inv, __uint_as_float(orr[cc][e + 5]) * inv);
+                        o4.w = pack_bf16x2(__uint_as_float(orr[cc][e + 6]) * inv, __uint_as_float(orr[cc][e + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + cc * 32 + e) = o4;
+                    }
+                }
+                if (p.lse != nullptr) p.lse[(long long)w.bh * p.S + row] = (m2 + log2f(l)) * 0.6931471805599453f;
+            }
+            __syncwarp();
         }
     } else {
         setmaxnreg_dec<56>();
         if (warp == 9) {
-            // ======================================================= TMA loader (whole warp, one lane issues)
-            // ring order: K_0, V_0, K_1, V_1, ...
-            auto load_tile = [&](unsigned char* dst, const CUtensorMap* tm, uint64_t* bar, int row_start) {
+            // ======================================================= TMA loader + scheduler (whole warp
+            // runs the control flow, one elected lane issues)
+            auto load_tile = [&](unsigned char* dst, const CUtensorMap* tm, uint64_t* bar, int row_start, int bh) {
                 if (elect_one()) {
                     mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
 #pragma unroll
@@ -325,20 +371,43 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
                 __syncwarp();
             };
-            if (n_tiles[0] > 0) load_tile(sQ, &tmQ, &bar_q_full[0], q0);
-            int t = 0;   // ring item counter
-            auto load_kv = [&](const CUtensorMap* tm, int j) {
-                const int slot = t % kStages;
-                mbar_wait(&bar_kv_empty[slot], ((t / kStages) & 1) ^ 1, wctx, BAR_KVEMPTY + slot, t);
+            uint32_t t = 0;                    // K/V ring item counter (runs across work items)
+            uint32_t q_uses[2] = {0, 0};       // how often each Q buffer has been filled
+            for (int k = 0;; ++k) {
+                int item = 0;
+                if (lane == 0) item = (int)atomicAdd(p.sched_counter, 1u);
+                item = __shfl_sync(0xffffffffu, item, 0);
+                if (item >= p.n_items) item = -1;
+                const int slot = k & 1;
+                mbar_wait(&bar_sched_empty[slot], ((k >> 1) & 1) ^ 1, wctx, 90 + slot, k);
                 __syncwarp();
-                load_tile(sKV + slot * Cfg::kTileBytes, tm, &bar_kv_full[slot], j * 128);
-                ++t;
-            };
-            if (n_max > 0) load_kv(&tmK, 0);
-            if (n_tiles[1] > 0) load_tile(sQ + Cfg::kTileBytes, &tmQ, &bar_q_full[1], q0 + 128);
-            for (int j = 0; j < n_max; ++j) {
-                load_kv(&tmV, j);
-                if (j + 1 < n_max) load_kv(&tmK, j + 1);
+                if (lane == 0) {
+                    sched_item[slot] = item;
+                    mbar_arrive(&bar_sched_full[slot]);
+                }
+                __syncwarp();
+                if (item < 0) break;
+                const FwdItem w = fwd_decode_item(item, p);
+                auto load_q = [&](int i) {
+                    mbar_wait(&bar_q_empty[i], (q_uses[i] & 1) ^ 1, wctx, 5 + i, k);
+                    __syncwarp();
+                    load_tile(sQ + i * Cfg::kTileBytes, &tmQ, &bar_q_full[i], w.q0 + 128 * i, w.bh);
+                    ++q_uses[i];
+                };
+                auto load_kv = [&](const CUtensorMap* tm, int j) {   // ring order: K_0, V_0, K_1, V_1, ...
+                    const int st = t % kStages;
+                    mbar_wait(&bar_kv_empty[st], ((t / kStages) & 1) ^ 1, wctx, BAR_KVEMPTY + st, (int)t);
+                    __syncwarp();
+                    load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], j * 128, w.bh);
+                    ++t;
+                };
+                if (w.n_tiles[0] > 0) load_q(0);
+                if (w.n_max > 0) load_kv(&tmK, 0);
+                if (w.n_tiles[1] > 0) load_q(1);
+                for (int j = 0; j < w.n_max; ++j) {
+                    load_kv(&tmV, j);
+                    if (j + 1 < w.n_max) load_kv(&tmK, j + 1);
+                }
             }
         } else if (warp == 8) {
             // ======================================================= MMA issuer (whole warp runs the
@@ -348,21 +417,21 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const uint32_t sQ_addr = __shfl_sync(0xffffffffu, smem_u32(sQ), 0);
             const uint32_t sKV_addr = __shfl_sync(0xffffffffu, smem_u32(sKV), 0);
             const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);   // warp-uniform copy
-            int t = 0;   // ring item counter (consumer side)
-            auto wait_item = [&](int item) {
-                const int slot = item % kStages;
-                mbar_wait(&bar_kv_full[slot], (item / kStages) & 1, wctx, BAR_KVFULL + slot, item);
-                __syncwarp();
-            };
-            auto release_item = [&](int item) { tc_commit(&bar_kv_empty[item % kStages]); };
             // descriptor templates; per MMA only the 14-bit start-address field moves
             const uint64_t dq_base = umma_smem_desc(sQ_addr, 16, 1024);
             const uint64_t dk_base = umma_smem_desc(sKV_addr, 16, 1024);                 // K-major (S = Q K^T)
             const uint64_t dv_base = umma_smem_desc(sKV_addr, Cfg::kSubBytes, 1024);     // MN-major (O += P V)
-            // S_i = Q_i K^T with K in ring item `item`
-            auto issue_s = [&](int i, int item) {
+            uint32_t t = 0;                  // K/V ring items consumed before the current work item
+            uint32_t q_uses[2] = {0, 0}, p_cnt[2] = {0, 0}, o_uses[2] = {0, 0};
+            auto wait_item = [&](uint32_t ri) {
+                const int st = ri % kStages;
+                mbar_wait(&bar_kv_full[st], (ri / kStages) & 1, wctx, BAR_KVFULL + st, (int)ri);
+                __syncwarp();
+            };
+            auto release_item = [&](uint32_t ri) { tc_commit(&bar_kv_empty[ri % kStages]); };
+            auto issue_s = [&](int i, uint32_t ri) {   // S_i = Q_i K^T with K in ring item ri
                 const uint64_t a0 = umma_desc_advance(dq_base, i * Cfg::kTileBytes);
-                const uint64_t b0 = umma_desc_advance(dk_base, (item % kStages) * Cfg::kTileBytes);
+                const uint64_t b0 = umma_desc_advance(dk_base, (ri % kStages) * Cfg::kTileBytes);
                 const uint32_t d = tmem_u + (uint32_t)(i * 128);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -370,9 +439,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     umma_ss(d, umma_desc_advance(a0, o), umma_desc_advance(b0, o), idesc_s, kk > 0);
                 }
             };
-            // O_i (+)= P_i V with V in ring item `item`
-            auto issue_pv = [&](int i, int item, bool accumulate, int half) {
-                const uint64_t b0 = umma_desc_advance(dv_base, (item % kStages) * Cfg::kTileBytes);
+            auto issue_pv = [&](int i, uint32_t ri, bool accumulate, int half) {   // O_i (+)= P_i V
+                const uint64_t b0 = umma_desc_advance(dv_base, (ri % kStages) * Cfg::kTileBytes);
                 const uint32_t d = tmem_u + (uint32_t)(256 + i * D);
                 const uint32_t a = tmem_u + (uint32_t)(i * 128);
 #pragma unroll
@@ -381,55 +449,76 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     umma_ts(d, a + kk * 8, umma_desc_advance(b0, kk * 2048), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
                 }
             };
-            if (n_max > 0) {
-                wait_item(0);   // K_0
-                tc_fence_after();
-                for (int i = 0; i < 2; ++i) {
-                    if (n_tiles[i] > 0) {
-                        mbar_wait(&bar_q_full[i], 0, wctx, BAR_QFULL + i, 0);
-                        __syncwarp();
-                        tc_fence_after();
-                        issue_s(i, 0);
-                        tc_commit(&bar_s_full[i]);
-                    }
-                }
-                release_item(0);
-            }
-            for (int j = 0; j < n_max; ++j) {
-                const int item_v = 2 * j + 1, item_k = 2 * j + 2;
-                wait_item(item_v);
-                bool k_waited = false;
-                for (int i = 0; i < 2; ++i) {
-                    if (j < n_tiles[i]) {
-                        if (lane == 0) TT_TRACE(2, j, 4 * i + 0);
-                        mbar_wait(&bar_p_full[2 * i], j & 1, wctx, BAR_PFULL + 2 * i, j);
-                        __syncwarp();
-                        tc_fence_after();
-                        if (lane == 0) TT_TRACE(2, j, 4 * i + 1);
-                        issue_pv(i, item_v, j > 0, 0);
-                        mbar_wait(&bar_p_full[2 * i + 1], j & 1, wctx, BAR_PFULL + 2 * i + 1, j);
-                        __syncwarp();
-                        tc_fence_after();
-                        if (lane == 0) TT_TRACE(2, j, 4 * i + 2);
-                        issue_pv(i, item_v, j > 0, 1);
-                        if (j + 1 < n_tiles[i]) {
-                            if (!k_waited) {
-                                wait_item(item_k);
-                                tc_fence_after();
-                                k_waited = true;
-                            }
-                            issue_s(i, item_k);
+            for (int k = 0;; ++k) {
+                const int item = next_item(k);
+                __syncwarp();
+                if (elect_one()) mbar_arrive(&bar_sched_empty[k & 1]);
+                __syncwarp();
+                if (item < 0) break;
+                const FwdItem w = fwd_decode_item(item, p);
+                // S_i(0) for both tiles.  The S/P columns are free: the P V MMAs of the previous item
+                // were issued earlier by this warp and execute in order.
+                if (w.n_max > 0) {
+                    wait_item(t);   // K_0
+                    tc_fence_after();
+                    for (int i = 0; i < 2; ++i) {
+                        if (w.n_tiles[i] > 0) {
+                            mbar_wait(&bar_q_full[i], q_uses[i] & 1, wctx, BAR_QFULL + i, k);
+                            ++q_uses[i];
+                            __syncwarp();
+                            tc_fence_after();
+                            issue_s(i, t);
                             tc_commit(&bar_s_full[i]);
-                            if (lane == 0) TT_TRACE(2, j, 4 * i + 3);
-                        } else {
-                            tc_commit(&bar_o_final[i]);
+                            if (w.n_tiles[i] == 1) tc_commit(&bar_q_empty[i]);   // that was this tile's last S
                         }
                     }
+                    release_item(t);
                 }
-                release_item(item_v);
-                if (j + 1 < n_max) release_item(item_k);
+                for (int j = 0; j < w.n_max; ++j) {
+                    const uint32_t item_v = t + 2 * j + 1, item_k = t + 2 * j + 2;
+                    wait_item(item_v);
+                    bool k_waited = false;
+                    for (int i = 0; i < 2; ++i) {
+                        if (j < w.n_tiles[i]) {
+                            if (j == 0) {
+                                // the accumulator columns must have been read out by the previous item's epilogue
+                                mbar_wait(&bar_o_free[i], (o_uses[i] & 1) ^ 1, wctx, 75 + i, k);
+                                ++o_uses[i];
+                                __syncwarp();
+                            }
+                            const bool tr = (k == 0 && lane == 0);
+                            if (tr) TT_TRACE(2, j, 4 * i + 0);
+                            mbar_wait(&bar_p_full[2 * i], p_cnt[i] & 1, wctx, BAR_PFULL + 2 * i, j);
+                            __syncwarp();
+                            tc_fence_after();
+                            if (tr) TT_TRACE(2, j, 4 * i + 1);
+                            issue_pv(i, item_v, j > 0, 0);
+                            mbar_wait(&bar_p_full[2 * i + 1], p_cnt[i] & 1, wctx, BAR_PFULL + 2 * i + 1, j);
+                            ++p_cnt[i];
+                            __syncwarp();
+                            tc_fence_after();
+                            if (tr) TT_TRACE(2, j, 4 * i + 2);
+                            issue_pv(i, item_v, j > 0, 1);
+                            if (j + 1 < w.n_tiles[i]) {
+                                if (!k_waited) {
+                                    wait_item(item_k);
+                                    tc_fence_after();
+                                    k_waited = true;
+                                }
+                                issue_s(i, item_k);
+                                tc_commit(&bar_s_full[i]);
+                                if (j + 2 == w.n_tiles[i]) tc_commit(&bar_q_empty[i]);   // this tile's last S
+                                if (tr) TT_TRACE(2, j, 4 * i + 3);
+                            } else {
+                                tc_commit(&bar_o_final[i]);
+                            }
+                        }
+                    }
+                    release_item(item_v);
+                    if (j + 1 < w.n_max) release_item(item_k);
+                }
+                t += 2 * (uint32_t)w.n_max;
             }
-            (void)t;
         }
     }
     tc_fence_before();
@@ -450,6 +539,21 @@ static int g_fwd_trace_block = 0;
 void attn_fwd_set_trace(long long* device_buf, int block) {
     g_fwd_trace = device_buf;
     g_fwd_trace_block = block;
+}
+
+// Work-item counters for the persistent forward: a small rotating set in device memory, so that
+// launches that overlap on different streams do not share one.  The chosen counter is cleared on
+// the launch stream right before the kernel.
+constexpr int kSchedCounters = 64;
+__device__ unsigned int g_fwd_sched_counters[kSchedCounters];
+static unsigned int* next_sched_counter(cudaStream_t st, cudaError_t* err) {
+    static std::atomic<unsigned> rr{0};
+    unsigned int* base = nullptr;
+    *err = cudaGetSymbolAddress((void**)&base, g_fwd_sched_counters);
+    if (*err != cudaSuccess) return nullptr;
+    unsigned int* c = base + (rr.fetch_add(1) % kSchedCounters);
+    *err = cudaMemsetAsync(c, 0, sizeof(unsigned int), st);
+    return c;
 }
 
 static int fwd_poly_setting() {
@@ -484,7 +588,12 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.status = device_status_word();
     p.trace = g_fwd_trace;
     p.trace_block = g_fwd_trace_block;
-    unsigned grid = (unsigned)(a.BH * p.n_qblk);
+    p.n_items = (int)(a.BH * p.n_qblk);
+    p.sched_counter = next_sched_counter(st, &e);
+    if (e != cudaSuccess) return e;
+    int dev = 0, n_sm = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    unsigned grid = (unsigned)std::min<long long>(p.n_items, n_sm);
     {
         LaunchScope ls(K_FWD_TC, st);
         attn_fwd_sm100_kernel<D, kPoly><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
