@@ -25,6 +25,8 @@
 #include "common.h"
 #include "sm100_ptx.cuh"
 #include <stdlib.h>
+#include <algorithm>
+#include <atomic>
 
 namespace ttk {
 using namespace sm100;
@@ -54,6 +56,8 @@ struct BwdParams {
     int causal;
     float scale, scale_log2;
     unsigned int* status;
+    unsigned int* sched_counter;   // zero at launch; work items are taken with atomicAdd
+    int n_items;                   // slices * n_tiles
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
 };
@@ -70,6 +74,33 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 
 // kPoly: of every 8 pairs of exponentials, kPoly are evaluated by a polynomial on the FMA pipes
 // instead of the special-function unit.
+//
+// Persistent like the forward: one CTA per SM takes (slice, resident tile) items from a global
+// counter, heavy items of a slice first; the loader runs up to two items ahead and the first
+// MMAs of the next item overlap the write-out of the accumulators of the current one.
+struct BwdItem {
+    int bh, r0, t_begin, t_end;
+};
+template <bool kKeysResident>
+__device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p) {
+    BwdItem w;
+    const int off = p.L - p.S;
+    w.bh = item / p.n_tiles;
+    int rt;
+    if (kKeysResident) {
+        rt = item % p.n_tiles;                                        // early key tiles are the heavy ones
+        w.t_end = (p.S + 127) >> 7;
+        w.t_begin = p.causal ? (max(0, rt * 128 - off) >> 7) : 0;
+    } else {
+        rt = p.n_tiles - 1 - (item % p.n_tiles);                      // late query tiles are the heavy ones
+        const int n_kv = (p.L + 127) >> 7;
+        w.t_begin = 0;
+        w.t_end = p.causal ? min(n_kv, ((min(rt * 128 + 127, p.S - 1) + off) >> 7) + 1) : n_kv;
+    }
+    w.r0 = rt * 128;   // first resident row (key or query index)
+    return w;
+}
+
 template <int D, bool kKeysResident, int kPoly>
 __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_constant__ CUtensorMap tmR1,
@@ -82,40 +113,31 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
     unsigned char* sR = smem;                                 // R0, R1
     unsigned char* sT = smem + 2 * Cfg::kTileBytes;           // kStages x (T0, T1)
     unsigned char* aux = smem + (2 + 2 * kStages) * Cfg::kTileBytes;
-    uint64_t* bar_res = reinterpret_cast<uint64_t*>(aux);     // [1]
-    uint64_t* bar_st_full = bar_res + 1;                      // [kStages]
-    uint64_t* bar_st_empty = bar_st_full + kStages;           // [kStages]
+    uint64_t* bar_res_full = reinterpret_cast<uint64_t*>(aux);   // TMA -> MMA (resident pair)
+    uint64_t* bar_res_empty = bar_res_full + 1;                  // MMA (last score GEMMs of the item) -> TMA
+    uint64_t* bar_st_full = bar_res_empty + 1;                   // [kStages]
+    uint64_t* bar_st_empty = bar_st_full + kStages;              // [kStages]
     uint64_t* bar_s_full = bar_st_empty + kStages;
     uint64_t* bar_dp_full = bar_s_full + 1;
     uint64_t* bar_p_full = bar_dp_full + 1;
     uint64_t* bar_ds_full = bar_p_full + 1;
     uint64_t* bar_final = bar_ds_full + 1;
-    uint64_t* bar_p_read = bar_final + 1;
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bar_p_read + 1);
+    uint64_t* bar_acc_free = bar_final + 1;                      // compute (accumulators read out) -> MMA
+    uint64_t* bar_sched_full = bar_acc_free + 1;                 // [2]
+    uint64_t* bar_sched_empty = bar_sched_full + 2;              // [2]
+    int* sched_item = reinterpret_cast<int*>(bar_sched_empty + 2);   // [2]
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sched_item + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-    float* s_stat = reinterpret_cast<float*>(aux + 1024);     // [2 buffers][2: lse2, delta][128]
+    float* s_stat = reinterpret_cast<float*>(aux + 1024);     // [2 buffers][2: -lse2, -delta][128]
 
     const int warp = uniform_warp_idx();
     const int lane = threadIdx.x & 31;
     const int off = p.L - p.S;
-    const int bh = blockIdx.x / p.n_tiles;
-    int rt;            // resident tile index
-    int t_begin, t_end;  // streamed tile range [t_begin, t_end)
-    if (kKeysResident) {
-        rt = (int)(blockIdx.x % p.n_tiles);                           // early key tiles are the heavy ones
-        t_end = (p.S + 127) >> 7;
-        t_begin = p.causal ? (max(0, rt * 128 - off) >> 7) : 0;
-    } else {
-        rt = p.n_tiles - 1 - (int)(blockIdx.x % p.n_tiles);           // late query tiles are the heavy ones
-        const int n_kv = (p.L + 127) >> 7;
-        t_begin = 0;
-        t_end = p.causal ? min(n_kv, ((min(rt * 128 + 127, p.S - 1) + off) >> 7) + 1) : n_kv;
-    }
-    const int r0 = rt * 128;   // first resident row (key or query index)
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        mbar_init(bar_res, 1);
+        mbar_init(bar_res_full, 1);
+        mbar_init(bar_res_empty, 1);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&bar_st_full[s], 1);
             mbar_init(&bar_st_empty[s], 1);
@@ -124,8 +146,12 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
         mbar_init(bar_dp_full, 1);
         mbar_init(bar_p_full, 256);
         mbar_init(bar_ds_full, 256);
-        mbar_init(bar_p_read, 1);
         mbar_init(bar_final, 1);
+        mbar_init(bar_acc_free, 256);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_sched_full[i], 1);
+            mbar_init(&bar_sched_empty[i], 257);   // MMA warp (1) + 256 compute threads
+        }
         fence_barrier_init();
         fence_proxy_async_smem();
     }
@@ -146,198 +172,240 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
     WaitCtx wctx{p.status, abort_flag, warp};
     constexpr uint32_t kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 256 + D;
 
+    auto next_item = [&](int k) -> int {
+        const int slot = k & 1;
+        mbar_wait(&bar_sched_full[slot], (k >> 1) & 1, wctx, 80 + slot, k);
+        return sched_item[slot];
+    };
+
     if (warp < 8) {
         // ============================================================ compute warpgroups
         setmaxnreg_inc<224>();
         const int wg = warp >> 2;
         const int wq = warp & 3;
-        const int rrow = r0 + wq * 32 + lane;                  // this thread's resident row
         const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
         const uint32_t tS = tmem_base + lane_off + kColS + wg * 64;
         const uint32_t tDP = tmem_base + lane_off + kColDP + wg * 64;
         const int ctid = threadIdx.x;                          // 0..255 among compute threads
-        // row constants (queries resident) as packed pairs of the NEGATED values
-        uint64_t row_nlse2 = 0, row_ndelta2 = 0;
-        if (!kKeysResident) {
-            const bool ok = rrow < p.S;
-            const float nl = ok ? -p.lse2[(long long)bh * p.S + rrow] : -INFINITY;
-            const float nd = ok ? -p.delta[(long long)bh * p.S + rrow] : 0.f;
-            row_nlse2 = pack_f32x2(nl, nl);
-            row_ndelta2 = pack_f32x2(nd, nd);
-        }
-        // per-column statistics (keys resident): thread ctid fetches -lse2 (ctid < 128) or -delta of
-        // streamed query (ctid & 127), one tile ahead of its use
-        const float* stat_src = (ctid < 128 ? p.lse2 : p.delta) + (long long)bh * p.S;
-        const float stat_oob = (ctid < 128) ? -INFINITY : 0.f;
-        float stat_next = stat_oob;
-        if (kKeysResident && t_begin < t_end) {
-            const int qrow = t_begin * 128 + (ctid & 127);
-            stat_next = qrow < p.S ? -stat_src[qrow] : stat_oob;
-        }
         const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
-        for (int t = t_begin; t < t_end; ++t) {
-            const int it = t - t_begin;
-            const int c0 = t * 128;                            // first streamed row of this tile
-            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 0);
-            const float* st_nlse = s_stat + (it & 1) * 256;    // -lse2 of the 128 streamed queries
-            const float* st_ndelta = st_nlse + 128;            // -delta
-            if (kKeysResident) {
-                s_stat[(it & 1) * 256 + ctid] = stat_next;
-                named_bar_sync(1, 256);
-                if (t + 1 < t_end) {
-                    const int qrow = (t + 1) * 128 + (ctid & 127);
-                    stat_next = qrow < p.S ? -stat_src[qrow] : stat_oob;
-                }
-            }
-            // visible columns of this thread's row inside the tile: [vis_lo, vis_hi)
-            int vis_lo = 0, vis_hi = 128;
-            if (kKeysResident) {
-                if (p.causal) vis_lo = max(0, rrow - off - c0);           // query >= key - off
-            } else {
-                vis_hi = p.L - c0;
-                if (p.causal) vis_hi = min(vis_hi, rrow + off + 1 - c0);  // key <= query + off
-                vis_hi = min(vis_hi, 128);
-            }
-            const bool need_mask = (vis_lo > 0) || (vis_hi < 128);
-            // ---------------- phase A: P = exp2(S*c - lse2)
-            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 1);
-            mbar_wait(bar_s_full, it & 1, wctx, BB_SFULL, it);
+        uint32_t git = 0;      // streamed tiles processed so far, over all items (barrier phases)
+        for (int k = 0;; ++k) {
+            const int item = next_item(k);
             __syncwarp();
-            tc_fence_after();
-            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 2);
-            uint64_t pf2[32];     // this thread's 64 probabilities, fp32 pairs
-            uint32_t sr[2][32];
+            mbar_arrive(&bar_sched_empty[k & 1]);
+            if (item < 0) break;
+            const BwdItem w = bwd_decode_item<kKeysResident>(item, p);
+            const int bh = w.bh;
+            const int rrow = w.r0 + wq * 32 + lane;            // this thread's resident row
+            // row constants (queries resident) as packed pairs of the NEGATED values
+            uint64_t row_nlse2 = 0, row_ndelta2 = 0;
             if (!kKeysResident) {
-                // nothing is written back into the S columns in this pass: release them as soon as
-                // they are in registers so that the next tile's scores overlap these exponentials
-                tmem_ld32(tS, sr[0]);
-                tmem_ld32(tS + 32, sr[1]);
-                tmem_wait_ld();
-                tc_fence_before();
-                mbar_arrive(bar_p_full);
+                const bool ok = rrow < p.S;
+                const float nl = ok ? -p.lse2[(long long)bh * p.S + rrow] : -INFINITY;
+                const float nd = ok ? -p.delta[(long long)bh * p.S + rrow] : 0.f;
+                row_nlse2 = pack_f32x2(nl, nl);
+                row_ndelta2 = pack_f32x2(nd, nd);
             }
-#pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                if (kKeysResident) {
-                    tmem_ld32(tS + cc * 32, sr[cc]);
-                    tmem_wait_ld();
-                }
-                uint32_t pk[16];
-#pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int col = wg * 64 + cc * 32 + e;
-                    const uint64_t nl = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_nlse + col) : row_nlse2;
-                    const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, nl);
-                    float p0, p1;
-                    if ((((e >> 1) * kPoly) % 8) < kPoly) {   // kPoly of every 8 pairs on the FMA pipes
-                        ex2_poly_x2(x, p0, p1);
-                    } else {
-                        float a0, a1;
-                        unpack_f32x2(x, a0, a1);
-                        p0 = ex2_approx(a0);
-                        p1 = ex2_approx(a1);
-                    }
-                    if (need_mask) {
-                        p0 = (col >= vis_lo && col < vis_hi) ? p0 : 0.f;
-                        p1 = (col + 1 >= vis_lo && col + 1 < vis_hi) ? p1 : 0.f;
-                    }
-                    pf2[cc * 16 + (e >> 1)] = pack_f32x2(p0, p1);
-                    if (kKeysResident) pk[e >> 1] = pack_bf16x2(p0, p1);
-                }
-                if (kKeysResident) tmem_st16(tS + cc * 16, pk);
-            }
+            // per-column statistics (keys resident): thread ctid fetches -lse2 (ctid < 128) or -delta
+            // of streamed query (ctid & 127), one tile ahead of its use
+            const float* stat_src = (ctid < 128 ? p.lse2 : p.delta) + (long long)bh * p.S;
+            const float stat_oob = (ctid < 128) ? -INFINITY : 0.f;
+            float stat_next = stat_oob;
             if (kKeysResident) {
+                const int qrow = w.t_begin * 128 + (ctid & 127);
+                stat_next = qrow < p.S ? -stat_src[qrow] : stat_oob;
+            }
+            for (int t = w.t_begin; t < w.t_end; ++t, ++git) {
+                const int it = t - w.t_begin;
+                const bool tr = (k == 0 && wq == 0 && lane == 0);
+                const int c0 = t * 128;                            // first streamed row of this tile
+                if (tr) TT_BTRACE(wg, it, 0);
+                const float* st_nlse = s_stat + (git & 1) * 256;   // -lse2 of the 128 streamed queries
+                const float* st_ndelta = st_nlse + 128;            // -delta
+                if (kKeysResident) {
+                    s_stat[(git & 1) * 256 + ctid] = stat_next;
+                    named_bar_sync(1, 256);
+                    if (t + 1 < w.t_end) {
+                        const int qrow = (t + 1) * 128 + (ctid & 127);
+                        stat_next = qrow < p.S ? -stat_src[qrow] : stat_oob;
+                    }
+                }
+                // visible columns of this thread's row inside the tile: [vis_lo, vis_hi)
+                int vis_lo = 0, vis_hi = 128;
+                if (kKeysResident) {
+                    if (p.causal) vis_lo = max(0, rrow - off - c0);           // query >= key - off
+                } else {
+                    vis_hi = p.L - c0;
+                    if (p.causal) vis_hi = min(vis_hi, rrow + off + 1 - c0);  // key <= query + off
+                    vis_hi = min(vis_hi, 128);
+                }
+                const bool need_mask = (vis_lo > 0) || (vis_hi < 128);
+                // ---------------- phase A: P = exp2(S*c - lse2)
+                if (tr) TT_BTRACE(wg, it, 1);
+                mbar_wait(bar_s_full, git & 1, wctx, BB_SFULL, it);
+                __syncwarp();
+                tc_fence_after();
+                if (tr) TT_BTRACE(wg, it, 2);
+                uint64_t pf2[32];     // this thread's 64 probabilities, fp32 pairs
+                uint32_t sr[2][32];
+                if (!kKeysResident) {
+                    // nothing is written back into the S columns in this pass: release them as soon as
+                    // they are in registers so that the next tile's scores overlap these exponentials
+                    tmem_ld32(tS, sr[0]);
+                    tmem_ld32(tS + 32, sr[1]);
+                    tmem_wait_ld();
+                    tc_fence_before();
+                    mbar_arrive(bar_p_full);
+                }
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    if (kKeysResident) {
+                        tmem_ld32(tS + cc * 32, sr[cc]);
+                        tmem_wait_ld();
+                    }
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const int col = wg * 64 + cc * 32 + e;
+                        const uint64_t nl = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_nlse + col) : row_nlse2;
+                        const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, nl);
+                        float p0, p1;
+                        if ((((e >> 1) * kPoly) % 8) < kPoly) {   // kPoly of every 8 pairs on the FMA pipes
+                            ex2_poly_x2(x, p0, p1);
+                        } else {
+                            float a0, a1;
+                            unpack_f32x2(x, a0, a1);
+                            p0 = ex2_approx(a0);
+                            p1 = ex2_approx(a1);
+                        }
+                        if (need_mask) {
+                            p0 = (col >= vis_lo && col < vis_hi) ? p0 : 0.f;
+                            p1 = (col + 1 >= vis_lo && col + 1 < vis_hi) ? p1 : 0.f;
+                        }
+                        pf2[cc * 16 + (e >> 1)] = pack_f32x2(p0, p1);
+                        if (kKeysResident) pk[e >> 1] = pack_bf16x2(p0, p1);
+                    }
+                    if (kKeysResident) tmem_st16(tS + cc * 16, pk);
+                }
+                if (kKeysResident) {
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(bar_p_full);
+                }
+                if (tr) TT_BTRACE(wg, it, 3);
+                // ---------------- phase B: dS = P * (dP - delta)
+                mbar_wait(bar_dp_full, git & 1, wctx, BB_DPFULL, it);
+                __syncwarp();
+                tc_fence_after();
+                if (tr) TT_BTRACE(wg, it, 4);
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t dr[32];
+                    tmem_ld32(tDP + cc * 32, dr);
+                    tmem_wait_ld();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const int col = wg * 64 + cc * 32 + e;
+                        const uint64_t nd = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_ndelta + col) : row_ndelta2;
+                        const uint64_t tdiff = add_f32x2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd);
+                        const uint64_t ds = mul_f32x2(pf2[cc * 16 + (e >> 1)], tdiff);
+                        float x0, x1;
+                        unpack_f32x2(ds, x0, x1);
+                        pk[e >> 1] = pack_bf16x2(x0, x1);
+                    }
+                    tmem_st16(tDP + cc * 16, pk);
+                }
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(bar_p_full);
+                mbar_arrive(bar_ds_full);
+                if (tr) TT_BTRACE(wg, it, 5);
             }
-            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 3);
-            // ---------------- phase B: dS = P * (dP - delta)
-            mbar_wait(bar_dp_full, it & 1, wctx, BB_DPFULL, it);
+            // ---------------- epilogue: accumulators out of tensor memory (then the MMA warp may start
+            // the next item in them) -> bf16 -> global; warpgroup w owns columns [w*D/2, +D/2)
+            mbar_wait(bar_final, k & 1, wctx, BB_FINAL, k);
             __syncwarp();
             tc_fence_after();
-            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 4);
+            const int n_rows = kKeysResident ? p.L : p.S;
+            constexpr int kHalf = D / 2;
+            constexpr int kAccs = kKeysResident ? 2 : 1;
+            uint32_t acc[kAccs][kHalf / 32][32];
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                uint32_t dr[32];
-                tmem_ld32(tDP + cc * 32, dr);
-                tmem_wait_ld();
-                uint32_t pk[16];
+            for (int a = 0; a < kAccs; ++a) {
+                const uint32_t tA = tmem_base + lane_off + ((kKeysResident && a == 0) ? kColAcc0 : kColAcc1) + wg * kHalf;
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int col = wg * 64 + cc * 32 + e;
-                    const uint64_t nd = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_ndelta + col) : row_ndelta2;
-                    const uint64_t tdiff = add_f32x2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd);
-                    const uint64_t ds = mul_f32x2(pf2[cc * 16 + (e >> 1)], tdiff);
-                    float x0, x1;
-                    unpack_f32x2(ds, x0, x1);
-                    pk[e >> 1] = pack_bf16x2(x0, x1);
-                }
-                tmem_st16(tDP + cc * 16, pk);
+                for (int cc = 0; cc < kHalf / 32; ++cc) tmem_ld32(tA + cc * 32, acc[a][cc]);
             }
-            tmem_wait_st();
+            tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(bar_ds_full);
-            if (wq == 0 && lane == 0) TT_BTRACE(wg, it, 5);
-        }
-        // ---------------- epilogue: accumulators -> bf16 -> global (warpgroup w: columns [w*D/2, +D/2))
-        mbar_wait(bar_final, 0, wctx, BB_FINAL, 0);
-        __syncwarp();
-        tc_fence_after();
-        const int n_rows = kKeysResident ? p.L : p.S;
-        const bool row_ok = rrow < n_rows;
-        constexpr int kHalf = D / 2;
+            mbar_arrive(bar_acc_free);
+            if (rrow < n_rows) {
 #pragma unroll
-        for (int a = (kKeysResident ? 0 : 1); a < 2; ++a) {
-            __nv_bfloat16* dst = (a == 0 ? p.out0 : p.out1) + ((long long)bh * n_rows + rrow) * D + wg * kHalf;
-            const float mul = (a == 0) ? 1.0f : p.scale;
-            const uint32_t tA = tmem_base + lane_off + (a == 0 ? kColAcc0 : kColAcc1) + wg * kHalf;
+                for (int a = 0; a < kAccs; ++a) {
+                    const bool is_acc0 = kKeysResident && a == 0;
+                    __nv_bfloat16* dst = (is_acc0 ? p.out0 : p.out1) + ((long long)bh * n_rows + rrow) * D + wg * kHalf;
+                    const float mul = is_acc0 ? 1.0f : p.scale;
 #pragma unroll
-            for (int cc = 0; cc < kHalf / 32; ++cc) {
-                uint32_t orr[32];
-                __syncwarp();
-                tmem_ld32(tA + cc * 32, orr);
-                tmem_wait_ld();
-                if (row_ok) {
+                    for (int cc = 0; cc < kHalf / 32; ++cc) {
 #pragma unroll
-                    for (int e = 0; e < 32; e += 8) {
-                        uint4 w;
-                        w.x = pack_bf16x2(__uint_as_float(orr[e + 0]) * mul, __uint_as_float(orr[e + 1]) * mul);
-                        w.y = pack_bf16x2(__uint_as_float(orr[e + 2]) * mul, __uint_as_float(orr[e + 3]) * mul);
-                        w.z = pack_bf16x2(__uint_as_float(orr[e + 4]) * mul, __uint_as_float(orr[e + 5]) * mul);
-                        w.w = pack_bf16x2(__uint_as_float(orr[e + 6]) * mul, __uint_as_float(orr[e + 7]) * mul);
-                        *reinterpret_cast<uint4*>(dst + cc * 32 + e) = w;
+                        for (int e = 0; e < 32; e += 8) {
+                            uint4 o4;
+                            o4.x = pack_bf16x2(__uint_as_float(acc[a][cc][e + 0]) * mul, __uint_as_float(acc[a][cc][e + 1]) * mul);
+                            o4.y = pack_bf16x2(__uint_as_float(acc[a][cc][e + 2]) * mul, __uint_as_float(acc[a][cc][e + 3]) * mul);
+                            o4.z = pack_bf16x2(__uint_as_float(acc[a][cc][e + 4]) * mul, __uint_as_float(acc[a][cc][e + 5]) * mul);
+                            o4.w = pack_bf16x2(__uint_as_float(acc[a][cc][e + 6]) * mul, __uint_as_float(acc[a][cc][e + 7]) * mul);
+                            *reinterpret_cast<uint4*>(dst + cc * 32 + e) = o4;
+                        }
                     }
                 }
             }
+            __syncwarp();
         }
     } else {
         setmaxnreg_dec<56>();
         if (warp == 9) {
-            // ============================================================ TMA loader (whole warp runs the
-            // control flow, one elected lane issues)
-            auto load_tile = [&](unsigned char* dst, const CUtensorMap* tm, uint64_t* bar, int row_start) {
+            // ============================================================ TMA loader + scheduler (whole
+            // warp runs the control flow, one elected lane issues)
+            auto load_tile = [&](unsigned char* dst, const CUtensorMap* tm, uint64_t* bar, int row_start, int bh) {
 #pragma unroll
                 for (int sb = 0; sb < Cfg::kSub; ++sb) tma_load_3d(dst + sb * Cfg::kSubBytes, tm, bar, sb * 64, row_start, bh);
             };
-            if (elect_one()) {
-                mbar_arrive_expect_tx(bar_res, 2 * Cfg::kTileBytes);
-                load_tile(sR, &tmR0, bar_res, r0);
-                load_tile(sR + Cfg::kTileBytes, &tmR1, bar_res, r0);
-            }
-            __syncwarp();
-            for (int t = t_begin; t < t_end; ++t) {
-                const int it = t - t_begin;
-                const int slot = it % kStages;
-                mbar_wait(&bar_st_empty[slot], ((it / kStages) & 1) ^ 1, wctx, BB_STEMPTY + slot, it);
+            uint32_t git = 0;
+            for (int k = 0;; ++k) {
+                int item = 0;
+                if (lane == 0) item = (int)atomicAdd(p.sched_counter, 1u);
+                item = __shfl_sync(0xffffffffu, item, 0);
+                if (item >= p.n_items) item = -1;
+                const int slot = k & 1;
+                mbar_wait(&bar_sched_empty[slot], ((k >> 1) & 1) ^ 1, wctx, 90 + slot, k);
                 __syncwarp();
-                if (elect_one()) {
-                    mbar_arrive_expect_tx(&bar_st_full[slot], 2 * Cfg::kTileBytes);
-                    unsigned char* dst = sT + slot * 2 * Cfg::kTileBytes;
-                    load_tile(dst, &tmT0, &bar_st_full[slot], t * 128);
-                    load_tile(dst + Cfg::kTileBytes, &tmT1, &bar_st_full[slot], t * 128);
+                if (lane == 0) {
+                    sched_item[slot] = item;
+                    mbar_arrive(&bar_sched_full[slot]);
                 }
                 __syncwarp();
+                if (item < 0) break;
+                const BwdItem w = bwd_decode_item<kKeysResident>(item, p);
+                mbar_wait(bar_res_empty, (k & 1) ^ 1, wctx, BB_RES + 1, k);
+                __syncwarp();
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(bar_res_full, 2 * Cfg::kTileBytes);
+                    load_tile(sR, &tmR0, bar_res_full, w.r0, w.bh);
+                    load_tile(sR + Cfg::kTileBytes, &tmR1, bar_res_full, w.r0, w.bh);
+                }
+                __syncwarp();
+                for (int t = w.t_begin; t < w.t_end; ++t, ++git) {
+                    const int st = git % kStages;
+                    mbar_wait(&bar_st_empty[st], ((git / kStages) & 1) ^ 1, wctx, BB_STEMPTY + st, (int)git);
+                    __syncwarp();
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&bar_st_full[st], 2 * Cfg::kTileBytes);
+                        unsigned char* dst = sT + st * 2 * Cfg::kTileBytes;
+                        load_tile(dst, &tmT0, &bar_st_full[st], t * 128, w.bh);
+                        load_tile(dst + Cfg::kTileBytes, &tmT1, &bar_st_full[st], t * 128, w.bh);
+                    }
+                    __syncwarp();
+                }
             }
         } else if (warp == 8) {
             // ============================================================ MMA issuer (whole warp runs the
@@ -371,49 +439,71 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                             (accumulate || kk > 0) ? 1u : 0u);
                 }
             };
-            const int n_it = t_end - t_begin;
-            mbar_wait(bar_res, 0, wctx, BB_RES, 0);
-            __syncwarp();
-            if (n_it > 0) {
-                mbar_wait(&bar_st_full[0], 0, wctx, BB_STFULL, 0);
+            uint32_t git = 0;      // streamed tiles issued before the current item
+            for (int k = 0;; ++k) {
+                const int item = next_item(k);
                 __syncwarp();
-                tc_fence_after();
-                issue_score(0, 0, kColS);
-                tc_commit(bar_s_full);
-                issue_score(1, 0, kColDP);
-                tc_commit(bar_dp_full);
-            }
-            for (int it = 0; it < n_it; ++it) {
-                const int slot = it % kStages;
-                const bool has_next = it + 1 < n_it;
-                const int nslot = (it + 1) % kStages;
-                if (lane == 0) TT_BTRACE(2, it, 0);
-                mbar_wait(bar_p_full, it & 1, wctx, BB_PFULL, it);
+                if (elect_one()) mbar_arrive(&bar_sched_empty[k & 1]);
                 __syncwarp();
-                tc_fence_after();
-                if (lane == 0) TT_BTRACE(2, it, 1);
-                if (kKeysResident) issue_acc(1, slot, kColS, kColAcc0, it > 0);     // dV += P^T dO
-                if (has_next) {
-                    mbar_wait(&bar_st_full[nslot], ((it + 1) / kStages) & 1, wctx, BB_STFULL + nslot, it + 1);
+                if (item < 0) break;
+                const BwdItem w = bwd_decode_item<kKeysResident>(item, p);
+                const int n_it = w.t_end - w.t_begin;
+                mbar_wait(bar_res_full, k & 1, wctx, BB_RES, k);
+                __syncwarp();
+                if (n_it > 0) {
+                    // first scores of the item; the S / dP columns are free because the G3 / G4 of the
+                    // previous item were issued earlier by this warp and execute in order
+                    const int st0 = git % kStages;
+                    mbar_wait(&bar_st_full[st0], (git / kStages) & 1, wctx, BB_STFULL + st0, (int)git);
                     __syncwarp();
                     tc_fence_after();
-                    issue_score(0, nslot, kColS);
+                    issue_score(0, st0, kColS);
                     tc_commit(bar_s_full);
-                }
-                if (lane == 0) TT_BTRACE(2, it, 2);
-                mbar_wait(bar_ds_full, it & 1, wctx, BB_DSFULL, it);
-                __syncwarp();
-                tc_fence_after();
-                if (lane == 0) TT_BTRACE(2, it, 3);
-                issue_acc(0, slot, kColDP, kColAcc1, it > 0);                        // dK += dS^T Q | dQ += dS K
-                tc_commit(&bar_st_empty[slot]);
-                if (has_next) {
-                    issue_score(1, nslot, kColDP);
+                    issue_score(1, st0, kColDP);
                     tc_commit(bar_dp_full);
+                    if (n_it == 1) tc_commit(bar_res_empty);   // those were the item's last reads of the resident pair
                 }
-                if (lane == 0) TT_BTRACE(2, it, 4);
+                for (int it = 0; it < n_it; ++it) {
+                    const uint32_t g = git + it;
+                    const int slot = g % kStages;
+                    const bool has_next = it + 1 < n_it;
+                    const int nslot = (g + 1) % kStages;
+                    const bool tr = (k == 0 && lane == 0);
+                    if (tr) TT_BTRACE(2, it, 0);
+                    mbar_wait(bar_p_full, g & 1, wctx, BB_PFULL, it);
+                    __syncwarp();
+                    tc_fence_after();
+                    if (tr) TT_BTRACE(2, it, 1);
+                    if (it == 0) {
+                        // the accumulator columns must have been read out by the previous item's epilogue
+                        mbar_wait(bar_acc_free, (k & 1) ^ 1, wctx, BB_FINAL + 1, k);
+                        __syncwarp();
+                    }
+                    if (kKeysResident) issue_acc(1, slot, kColS, kColAcc0, it > 0);     // dV += P^T dO
+                    if (has_next) {
+                        mbar_wait(&bar_st_full[nslot], ((g + 1) / kStages) & 1, wctx, BB_STFULL + nslot, it + 1);
+                        __syncwarp();
+                        tc_fence_after();
+                        issue_score(0, nslot, kColS);
+                        tc_commit(bar_s_full);
+                    }
+                    if (tr) TT_BTRACE(2, it, 2);
+                    mbar_wait(bar_ds_full, g & 1, wctx, BB_DSFULL, it);
+                    __syncwarp();
+                    tc_fence_after();
+                    if (tr) TT_BTRACE(2, it, 3);
+                    issue_acc(0, slot, kColDP, kColAcc1, it > 0);                        // dK += dS^T Q | dQ += dS K
+                    tc_commit(&bar_st_empty[slot]);
+                    if (has_next) {
+                        issue_score(1, nslot, kColDP);
+                        tc_commit(bar_dp_full);
+                        if (it + 2 == n_it) tc_commit(bar_res_empty);   // last reads of the resident pair
+                    }
+                    if (tr) TT_BTRACE(2, it, 4);
+                }
+                tc_commit(bar_final);
+                git += (uint32_t)n_it;
             }
-            tc_commit(bar_final);
         }
     }
     tc_fence_before();
@@ -456,6 +546,20 @@ bool attn_bwd_sm100_supported(const AttnArgs& a) {
     return a.bf16 && (a.D == 64 || a.D == 128) && a.BH * tiles < (1LL << 31);
 }
 size_t attn_bwd_sm100_workspace(const AttnArgs& a) { return 2 * align256((size_t)a.BH * a.S * sizeof(float)); }
+
+// Work-item counters of the persistent launches (see the forward): a rotating set, cleared on the
+// launch stream right before each kernel.
+constexpr int kBwdSchedCounters = 64;
+__device__ unsigned int g_bwd_sched_counters[kBwdSchedCounters];
+static unsigned int* next_bwd_sched_counter(cudaStream_t st, cudaError_t* err) {
+    static std::atomic<unsigned> rr{0};
+    unsigned int* base = nullptr;
+    *err = cudaGetSymbolAddress((void**)&base, g_bwd_sched_counters);
+    if (*err != cudaSuccess) return nullptr;
+    unsigned int* c = base + (rr.fetch_add(1) % kBwdSchedCounters);
+    *err = cudaMemsetAsync(c, 0, sizeof(unsigned int), st);
+    return c;
+}
 
 static long long* g_bwd_trace = nullptr;
 static int g_bwd_trace_block = 0, g_bwd_trace_mode = 0;   // mode 1: dK/dV pass, 2: dQ pass
@@ -501,12 +605,17 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.trace = g_bwd_trace_mode == 1 ? g_bwd_trace : nullptr;
     p.trace_block = g_bwd_trace_block;
     // dK, dV: keys resident, stream (Q, dO)
+    int dev = 0, n_sm = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     p.out0 = (__nv_bfloat16*)a.dv;
     p.out1 = (__nv_bfloat16*)a.dk;
     p.n_tiles = (a.L + 127) / 128;
+    p.n_items = (int)(a.BH * p.n_tiles);
+    p.sched_counter = next_bwd_sched_counter(st, &e);
+    if (e != cudaSuccess) return e;
     {
         LaunchScope ls(K_BWD_DKV, st);
-        attn_bwd_sm100_kernel<D, true, kPoly><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, true, kPoly><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tk), M(tv), M(tq), M(tdo), p);
     }
     // dQ: queries resident, stream (K, V)
@@ -514,9 +623,12 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.out0 = nullptr;
     p.out1 = (__nv_bfloat16*)a.dq;
     p.n_tiles = (a.S + 127) / 128;
+    p.n_items = (int)(a.BH * p.n_tiles);
+    p.sched_counter = next_bwd_sched_counter(st, &e);
+    if (e != cudaSuccess) return e;
     {
         LaunchScope ls(K_BWD_DQ, st);
-        attn_bwd_sm100_kernel<D, false, kPoly><<<(unsigned)(a.BH * p.n_tiles), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, false, kPoly><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tq), M(tdo), M(tk), M(tv), p);
     }
     return cudaGetLastError();
