@@ -158,6 +158,12 @@ int tt_profile_kernel_count(void);
 const char* tt_profile_kernel_name(int kernel_id);
 int tt_profile_read(int kernel_id, double* total_ms, uint64_t* launches);
 
+/* Launches a one-warp kernel whose only wait can never be satisfied and whose wait budget is
+ * `budget_cycles` SM cycles (at most 4e9).  The wait expires, the kernel returns normally, and the
+ * next tt_check_device_status() reports TT_ERR_TIMEOUT (barrier id 99, iteration 7) and clears
+ * the status word: a way to test the failure-reporting path without faulting or hanging a GPU. */
+int tt_debug_wait_timeout(int64_t budget_cycles, void* stream);
+
 /* Debug aid for tuning the tensor-core forward: while `device_buf` (3*64*8 int64, device
  * memory) is non-null, CTA number `block` of every forward launch records clock64() at its
  * hand-off points (softmax warpgroups: wait for S, S loaded, max known, P half/whole written;

@@ -56,6 +56,7 @@ SIGNATURES = {
     "tt_profile_kernel_count": (c_int, []),
     "tt_profile_kernel_name": (c_char_p, [c_int]),
     "tt_profile_read": (c_int, [c_int, POINTER(ctypes.c_double), POINTER(c_uint64)]),
+    "tt_debug_wait_timeout": (c_int, [c_int64, _P]),
     "tt_debug_fwd_trace": (c_int, [_P, c_int32]),
     "tt_debug_bwd_trace": (c_int, [_P, c_int32, c_int32]),
     "tt_debug_umma_probe": (c_int, [_P, _P, _P, c_int32, _P, _P, _P]),

@@ -749,6 +749,27 @@ static cudaError_t launch_probe(const void* a, const void* b, const void* vt, fl
     return cudaGetLastError();
 }
 
+// Exercises the bounded-wait path: one warp waits on an mbarrier that nothing ever arrives on.
+// The wait gives up after `budget_cycles`, records itself in the status word and the kernel
+// returns normally (no trap, no hang); the host then sees TT_ERR_TIMEOUT.
+__global__ void wait_timeout_kernel(unsigned int* status, long long budget_cycles) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    WaitCtx ctx{status, &abort_flag, 0, budget_cycles};
+    mbar_wait(&bar, 0, ctx, 99, 7);
+}
+cudaError_t wait_timeout_probe(long long budget_cycles, cudaStream_t st) {
+    LaunchScope ls(K_PROBE, st);
+    wait_timeout_kernel<<<1, 32, 0, st>>>(device_status_word(), budget_cycles);
+    return cudaGetLastError();
+}
+
 cudaError_t umma_probe(const void* a, const void* b, const void* vt, int D, float* s_out, float* o_out,
                        cudaStream_t st) {
     if (D == 128) return launch_probe<128>(a, b, vt, s_out, o_out, st);

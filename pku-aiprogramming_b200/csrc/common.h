@@ -54,6 +54,7 @@ void attn_bwd_set_trace(long long* device_buf, int block, int pass);   // pass 1
 bool attn_bwd_sm100_supported(const AttnArgs& a);
 size_t attn_bwd_sm100_workspace(const AttnArgs& a);
 cudaError_t attn_bwd_sm100(const AttnArgs& a, void* workspace, cudaStream_t st);
+cudaError_t wait_timeout_probe(long long budget_cycles, cudaStream_t st);
 cudaError_t umma_probe(const void* a, const void* b, const void* vt, int D, float* s_out, float* o_out,
                        cudaStream_t st);
 

@@ -37,9 +37,9 @@ struct WaitCtx {
     unsigned int* gstatus;      // global status word (4 uints)
     volatile int* abort_flag;   // shared-memory flag of this CTA
     int role;
+    long long budget = 2000000000LL;   // cycles a single wait may take: about one second at 2 GHz
 };
 
-constexpr long long kWaitCycleBudget = 2000000000LL;  // about one second at 2 GHz
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -82,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*ctx.abort_flag) return false;
-        if (clock64() - t0 > kWaitCycleBudget) break;
+        if (clock64() - t0 > ctx.budget) break;
     }
     *ctx.abort_flag = 1;
     if (atomicCAS(ctx.gstatus, 0u, (7u << 16) | (blockIdx.x & 0xffffu)) == 0u) {

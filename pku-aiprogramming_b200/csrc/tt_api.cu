@@ -443,6 +443,16 @@ int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k
     return TT_OK;
 }
 
+int tt_debug_wait_timeout(int64_t budget_cycles, void* stream) {
+    if (budget_cycles < 1 || budget_cycles > 4000000000LL)
+        return fail(TT_ERR_BAD_SHAPE, "tt_debug_wait_timeout: budget of %lld cycles outside 1..4e9", (long long)budget_cycles);
+    int rc = check_device();
+    if (rc != TT_OK) return rc;
+    cudaError_t e = wait_timeout_probe(budget_cycles, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "tt_debug_wait_timeout: launch");
+    return TT_OK;
+}
+
 int tt_debug_fwd_trace(void* device_buf, int32_t block) {
     attn_fwd_set_trace(reinterpret_cast<long long*>(device_buf), block);
     return TT_OK;

@@ -292,3 +292,109 @@ def test_pool_reuses_blocks(tt):
     assert p1.value == p2.value and n0.value == n1.value   # second request served from the free list
     tt.capi.check(lib.tt_free(p2))
     assert lib.tt_free(ctypes.c_void_p(12345)) != 0       # foreign pointer is refused, not freed
+
+
+# ----------------------------------------------------------------------------- failure reporting
+def test_bounded_wait_reports_timeout_and_context_survives(tt, oracle):
+    """A device-side wait that can never be satisfied expires after its cycle budget, the kernel
+    returns normally, the host reads TT_ERR_TIMEOUT, and the next call works."""
+    tt.check_device_status()                                    # clean slate
+    tt.capi.check(tt.capi.lib.tt_debug_wait_timeout(20_000_000, None))   # ~10 ms budget
+    with pytest.raises(tt.TTError) as err:
+        tt.check_device_status()
+    assert err.value.code == tt.capi.TT_ERR_TIMEOUT and "barrier id 99" in str(err.value) and "iteration 7" in str(err.value)
+    tt.check_device_status()                                    # the word was cleared
+    q, k, v, _ = oracle.make_inputs(61, 1, 1, 128, 128, 64, sigma=0.5, with_do=False)
+    tq, tk, tv = (_dev(oracle.bf16_round(x), torch.bfloat16) for x in (q, k, v))
+    out, _ = tt.attention_forward(tq, tk, tv)
+    tt.check_device_status()
+    o_ref, _ = oracle.attention_forward(oracle.bf16_round(q), oracle.bf16_round(k), oracle.bf16_round(v), False)
+    assert oracle.max_abs_err(_np(out), o_ref) <= BF16_TOL
+
+
+# ----------------------------------------------------------------------------- explicit scale, random shapes
+def test_explicit_scale_is_honoured(tt, oracle):
+    q, k, v, do = oracle.make_inputs(67, 1, 2, 200, 260, 128, sigma=0.5)
+    qn, kn, vn, don = _bf16_inputs(oracle, q, k, v, do)
+    for scale in (0.05, 0.2):
+        o_ref, lse_ref, dq_ref, dk_ref, dv_ref = oracle.attention_backward(qn, kn, vn, don, True, scale)
+        tq, tk, tv, tdo = (_dev(x, torch.bfloat16) for x in (qn, kn, vn, don))
+        out, lse = tt.attention_forward(tq, tk, tv, causal=True, scale=scale)
+        dq, dk, dv = tt.attention_backward(tq, tk, tv, out, lse, tdo, causal=True, scale=scale)
+        tt.check_device_status()
+        for got, ref in ((out, o_ref), (dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+            assert oracle.max_abs_err(_np(got), ref) <= BF16_TOL
+        assert oracle.max_abs_err(_np(lse), lse_ref) <= 2e-2
+
+
+def test_random_shapes_against_oracle(tt, oracle):
+    """Seeded sweep over ragged shapes (query/key counts around the 128/256 tile edges), both
+    head dims of the tensor-core path plus one SIMT head dim, causal on and off."""
+    rng = np.random.default_rng(2024)
+    edges = [1, 2, 63, 64, 65, 127, 128, 129, 191, 255, 256, 257, 300, 384, 511]
+    for case in range(24):
+        D = int(rng.choice([64, 128, 128, 64, 48]))
+        S = int(rng.choice(edges))
+        L = int(rng.choice(edges))
+        causal = bool(rng.integers(2))
+        if causal and L < S:
+            S, L = L, S
+        B, H = int(rng.integers(1, 3)), int(rng.integers(1, 3))
+        q, k, v, do = oracle.make_inputs(1000 + case, B, H, S, L, D, sigma=0.6)
+        qn, kn, vn, don = _bf16_inputs(oracle, q, k, v, do)
+        o_ref, lse_ref, dq_ref, dk_ref, dv_ref = oracle.attention_backward(qn, kn, vn, don, causal)
+        tq, tk, tv, tdo = (_dev(x, torch.bfloat16) for x in (qn, kn, vn, don))
+        out, lse = tt.attention_forward(tq, tk, tv, causal=causal)
+        dq, dk, dv = tt.attention_backward(tq, tk, tv, out, lse, tdo, causal=causal)
+        tt.check_device_status()
+        tag = f"case {case}: B{B} H{H} S{S} L{L} D{D} causal={causal}"
+        for got, ref, name in ((out, o_ref, "o"), (dq, dq_ref, "dq"), (dk, dk_ref, "dk"), (dv, dv_ref, "dv")):
+            # 2e-2 absolute, widened by one bf16 ulp (2^-7 relative) of the largest value: with few keys
+            # and many queries dK/dV reach magnitudes where bf16 OUTPUT rounding alone exceeds 2e-2
+            tol = BF16_TOL + 2.0 ** -7 * float(np.abs(ref).max())
+            assert oracle.max_abs_err(_np(got), ref) <= tol, f"{tag} {name}"
+        assert oracle.max_abs_err(_np(lse), lse_ref) <= 2e-2, tag
+
+
+def test_many_work_items_per_cta(tt, oracle):
+    """More work items than SMs with unequal lengths: the persistent scheduler hands several items
+    to each CTA, and results must not depend on which CTA took which item."""
+    B, H, S, D = 3, 70, 384, 64           # 210 slices x 2 query blocks = 420 forward items
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q, k, v, do = ((torch.randn((B, H, S, D), generator=g, device="cuda") * 0.5).to(torch.bfloat16) for _ in range(4))
+    out, lse = tt.attention_forward(q, k, v, causal=True)
+    dq, dk, dv = tt.attention_backward(q, k, v, out, lse, do, causal=True)
+    out2, lse2 = tt.attention_forward(q, k, v, causal=True)
+    dq2, dk2, dv2 = tt.attention_backward(q, k, v, out2, lse2, do, causal=True)
+    tt.check_device_status()
+    for a, b in ((out, out2), (lse, lse2), (dq, dq2), (dk, dk2), (dv, dv2)):
+        assert torch.equal(a, b)            # bit-identical across runs
+    for (b_, h_) in ((0, 0), (2, 69), (1, 33)):
+        o_ref, _, dq_ref, dk_ref, dv_ref = oracle.attention_backward(
+            _np(q[b_:b_ + 1, h_:h_ + 1]), _np(k[b_:b_ + 1, h_:h_ + 1]), _np(v[b_:b_ + 1, h_:h_ + 1]),
+            _np(do[b_:b_ + 1, h_:h_ + 1]), True)
+        for got, ref in ((out, o_ref), (dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+            assert oracle.max_abs_err(_np(got[b_:b_ + 1, h_:h_ + 1]), ref) <= BF16_TOL
+
+
+def test_config5_single_head_properties(tt, oracle):
+    """BASELINE config 5 shape (S=32768, D=128, causal) on two heads: sampled row blocks against
+    the oracle, first-row identity, finiteness of gradients."""
+    S, D = 32768, 128
+    g = torch.Generator(device="cuda").manual_seed(9)
+    q, k, v = ((torch.randn((1, 2, S, D), generator=g, device="cuda") * 0.5).to(torch.bfloat16) for _ in range(3))
+    do = torch.randn((1, 2, S, D), generator=g, device="cuda").to(torch.bfloat16)
+    out, lse = tt.attention_forward(q, k, v, causal=True)
+    dq, dk, dv = tt.attention_backward(q, k, v, out, lse, do, causal=True)
+    tt.check_device_status()
+    assert torch.equal(out[:, :, 0], v[:, :, 0])
+    for t in (out, dq, dk, dv):
+        assert torch.isfinite(t.float()).all()
+    kn, vn = _np(k[0, 1]), _np(v[0, 1])
+    for row0 in (0, 16000, S - 32):
+        o_ref, lse_ref = oracle.attention_rows(_np(q[0, 1, row0:row0 + 32]), kn, vn, row0, S, causal=True)
+        assert oracle.max_abs_err(_np(out[0, 1, row0:row0 + 32]), o_ref) <= BF16_TOL
+        assert oracle.max_abs_err(_np(lse[0, 1, row0:row0 + 32]), lse_ref) <= 2e-2
+    # the last key is seen only by the last query: dV[last] = P[last,last] * dO[last]
+    p_last = torch.exp(((q[0, 0, -1].float() * k[0, 0, -1].float()).sum() / D ** 0.5) - lse[0, 0, -1])
+    assert torch.allclose(dv[0, 0, -1].float(), p_last * do[0, 0, -1].float(), atol=2e-2)
