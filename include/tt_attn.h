@@ -123,12 +123,20 @@ int tt_attn_bwd_host(const tt_attn_desc* desc, const void* q, const void* k, con
                      void* dq, void* dk, void* dv);
 int tt_attn_decode_host(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
                         void* out, float* lse);
+/* One training step from host buffers: forward and backward of every slice, with the slices cut
+ * into chunks that flow through an upload stream, a compute stream and a download stream, so
+ * the PCIe transfers of both directions overlap the kernels (use pinned host memory; with
+ * pageable memory the copies serialise).  What the Python autograd op does in two calls
+ * (compute, then gradient with the tensors kept on the device, optimizer/operators.py:498-527
+ * pattern of the reference) in one.  `lse` may be null. */
+int tt_attn_fwd_bwd_host(const tt_attn_desc* desc, const void* q, const void* k, const void* v, const void* dout,
+                         void* out, float* lse, void* dq, void* dk, void* dv);
 
 /* ---- pooled device storage -----------------------------------------------------------
  * Replaces the per-object cudaMalloc/cudaFree of src/Tinytensor.cu:17-22,85-93: freed
  * blocks go to size-bucketed free lists of the current device and are reused. */
 int tt_alloc(size_t bytes, void** out_ptr);
-int tt_free(void* ptr);
+int tt_free(void* ptr);   /* does not synchronise: free a block only after the work that uses it has completed */
 int tt_pool_trim(void);                                     /* return cached blocks to the driver */
 int tt_pool_stats(size_t* bytes_in_use, size_t* bytes_cached, uint64_t* n_driver_allocs);
 

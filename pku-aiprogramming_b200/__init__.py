@@ -10,5 +10,6 @@ from . import capi  # noqa: F401  (raises NativeLibraryMissing with the build co
 from .capi import TTError, NativeLibraryMissing, shard_range, launch_count  # noqa: F401
 from .functional import (  # noqa: F401
     attention_forward, attention_backward, attention_decode, decode_workspace_bytes,
-    attention_forward_host, attention_backward_host, attention_decode_host, check_device_status,
+    attention_forward_host, attention_backward_host, attention_decode_host, attention_step_host,
+    check_device_status,
 )

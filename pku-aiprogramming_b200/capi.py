@@ -41,6 +41,7 @@ SIGNATURES = {
     "tt_attn_fwd_host": (c_int, [_DP, _P, _P, _P, _P, _P]),
     "tt_attn_bwd_host": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "tt_attn_decode_host": (c_int, [_DP, _P, _P, _P, _P, _P]),
+    "tt_attn_fwd_bwd_host": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "tt_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
     "tt_free": (c_int, [_P]),
     "tt_pool_trim": (c_int, []),

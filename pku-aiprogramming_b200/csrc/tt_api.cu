@@ -598,6 +598,118 @@ int tt_attn_bwd_host(const tt_attn_desc* d, const void* q, const void* k, const 
     return tt_check_device_status(st);
 }
 
+// ---- pipelined host-buffer training step ----------------------------------------------------
+// The (batch, head) slices are independent, so the step is cut into chunks of slices that flow
+// through three streams: upload (q,k,v,dout of chunk c+1) | forward+backward (chunk c) |
+// download (out,lse,dq,dk,dv of chunk c-1).  With pinned host memory the PCIe transfers of both
+// directions overlap the kernels instead of preceding and following them.
+namespace {
+struct PipeStreams {
+    cudaStream_t in = nullptr, comp = nullptr, out = nullptr;
+    int dev = -1;
+};
+int pipe_streams(PipeStreams** ps) {
+    static thread_local PipeStreams s;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (s.dev != dev) {
+        TT_CUDA(cudaStreamCreateWithFlags(&s.in, cudaStreamNonBlocking), "stream");
+        TT_CUDA(cudaStreamCreateWithFlags(&s.comp, cudaStreamNonBlocking), "stream");
+        TT_CUDA(cudaStreamCreateWithFlags(&s.out, cudaStreamNonBlocking), "stream");
+        s.dev = dev;
+    }
+    *ps = &s;
+    return TT_OK;
+}
+struct EventSet {
+    static const int kN = 3;
+    cudaEvent_t in[kN] = {}, comp[kN] = {}, out[kN] = {};
+    bool ok = false;
+    int make() {
+        for (int i = 0; i < kN; ++i) {
+            TT_CUDA(cudaEventCreateWithFlags(&in[i], cudaEventDisableTiming), "event");
+            TT_CUDA(cudaEventCreateWithFlags(&comp[i], cudaEventDisableTiming), "event");
+            TT_CUDA(cudaEventCreateWithFlags(&out[i], cudaEventDisableTiming), "event");
+        }
+        ok = true;
+        return TT_OK;
+    }
+    ~EventSet() {
+        for (int i = 0; i < kN; ++i) {
+            if (in[i]) cudaEventDestroy(in[i]);
+            if (comp[i]) cudaEventDestroy(comp[i]);
+            if (out[i]) cudaEventDestroy(out[i]);
+        }
+    }
+};
+}  // namespace
+
+int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, const void* v, const void* dout,
+                         void* out, float* lse, void* dq, void* dk, void* dv) {
+    AttnArgs a;
+    TT_TRY(resolve(d, &a, "tt_attn_fwd_bwd_host"));
+    if (!q || !k || !v || !dout || !out || !dq || !dk || !dv)
+        return fail(TT_ERR_NULL, "tt_attn_fwd_bwd_host: q, k, v, dout, out, dq, dk, dv must be non-null");
+    TT_TRY(check_device());
+    const size_t es = a.bf16 ? 2 : 4;
+    const size_t q_slice = (size_t)a.S * a.D * es, k_slice = (size_t)a.L * a.D * es, l_slice = (size_t)a.S * sizeof(float);
+    // chunk: about 32 MiB of q per chunk, at least 1 slice, at most a third of the slices
+    long long per = (long long)((32u << 20) / (q_slice ? q_slice : 1));
+    if (per < 1) per = 1;
+    if (per > (a.BH + 2) / 3) per = (a.BH + 2) / 3;
+    if (per < 1) per = 1;
+    const long long n_chunks = (a.BH + per - 1) / per;
+    constexpr int NB = EventSet::kN;
+    tt_attn_desc dc = *d;
+    dc.B = 1;
+    dc.H = (int32_t)per;
+    const size_t ws_bytes = tt_attn_bwd_workspace_bytes(&dc);
+    DevBuf bq[NB], bk[NB], bv[NB], bdo[NB], bo[NB], bl[NB], bdq[NB], bdk[NB], bdv[NB], bws[NB];
+    const int nb_used = (int)(n_chunks < NB ? n_chunks : NB);
+    for (int i = 0; i < nb_used; ++i) {
+        TT_TRY(bq[i].get(per * q_slice)); TT_TRY(bk[i].get(per * k_slice)); TT_TRY(bv[i].get(per * k_slice));
+        TT_TRY(bdo[i].get(per * q_slice)); TT_TRY(bo[i].get(per * q_slice)); TT_TRY(bl[i].get(per * l_slice));
+        TT_TRY(bdq[i].get(per * q_slice)); TT_TRY(bdk[i].get(per * k_slice)); TT_TRY(bdv[i].get(per * k_slice));
+        TT_TRY(bws[i].get(ws_bytes));
+    }
+    PipeStreams* ps = nullptr;
+    TT_TRY(pipe_streams(&ps));
+    EventSet ev;
+    TT_TRY(ev.make());
+    const char* hq = (const char*)q; const char* hk = (const char*)k; const char* hv = (const char*)v;
+    const char* hdo = (const char*)dout;
+    char* ho = (char*)out; char* hdq = (char*)dq; char* hdk = (char*)dk; char* hdv = (char*)dv;
+    for (long long c = 0; c < n_chunks; ++c) {
+        const int b = (int)(c % NB);
+        const long long s0 = c * per;
+        const long long cnt = (s0 + per <= a.BH) ? per : (a.BH - s0);
+        if (c >= NB) TT_CUDA(cudaStreamWaitEvent(ps->in, ev.out[b], 0), "wait buffer");   // chunk c-NB downloaded
+        TT_CUDA(cudaMemcpyAsync(bq[b].p, hq + s0 * q_slice, cnt * q_slice, cudaMemcpyHostToDevice, ps->in), "upload q");
+        TT_CUDA(cudaMemcpyAsync(bk[b].p, hk + s0 * k_slice, cnt * k_slice, cudaMemcpyHostToDevice, ps->in), "upload k");
+        TT_CUDA(cudaMemcpyAsync(bv[b].p, hv + s0 * k_slice, cnt * k_slice, cudaMemcpyHostToDevice, ps->in), "upload v");
+        TT_CUDA(cudaMemcpyAsync(bdo[b].p, hdo + s0 * q_slice, cnt * q_slice, cudaMemcpyHostToDevice, ps->in), "upload dout");
+        TT_CUDA(cudaEventRecord(ev.in[b], ps->in), "record");
+        TT_CUDA(cudaStreamWaitEvent(ps->comp, ev.in[b], 0), "wait upload");
+        tt_attn_desc di = *d;
+        di.B = 1;
+        di.H = (int32_t)cnt;
+        TT_TRY(tt_attn_fwd(&di, bq[b].p, bk[b].p, bv[b].p, bo[b].p, (float*)bl[b].p, ps->comp));
+        TT_TRY(tt_attn_bwd(&di, bq[b].p, bk[b].p, bv[b].p, bo[b].p, (const float*)bl[b].p, bdo[b].p, bdq[b].p, bdk[b].p,
+                           bdv[b].p, bws[b].p, ws_bytes, ps->comp));
+        TT_CUDA(cudaEventRecord(ev.comp[b], ps->comp), "record");
+        TT_CUDA(cudaStreamWaitEvent(ps->out, ev.comp[b], 0), "wait compute");
+        TT_CUDA(cudaMemcpyAsync(ho + s0 * q_slice, bo[b].p, cnt * q_slice, cudaMemcpyDeviceToHost, ps->out), "download out");
+        if (lse) TT_CUDA(cudaMemcpyAsync(lse + s0 * a.S, bl[b].p, cnt * l_slice, cudaMemcpyDeviceToHost, ps->out), "download lse");
+        TT_CUDA(cudaMemcpyAsync(hdq + s0 * q_slice, bdq[b].p, cnt * q_slice, cudaMemcpyDeviceToHost, ps->out), "download dq");
+        TT_CUDA(cudaMemcpyAsync(hdk + s0 * k_slice, bdk[b].p, cnt * k_slice, cudaMemcpyDeviceToHost, ps->out), "download dk");
+        TT_CUDA(cudaMemcpyAsync(hdv + s0 * k_slice, bdv[b].p, cnt * k_slice, cudaMemcpyDeviceToHost, ps->out), "download dv");
+        TT_CUDA(cudaEventRecord(ev.out[b], ps->out), "record");
+    }
+    TT_CUDA(cudaStreamSynchronize(ps->in), "synchronize");
+    TT_CUDA(cudaStreamSynchronize(ps->comp), "synchronize");
+    return tt_check_device_status(ps->out);
+}
+
 int tt_attn_decode_host(const tt_attn_desc* d, const void* q, const void* k, const void* v, void* out,
                         float* lse) {
     AttnArgs a;

@@ -141,6 +141,22 @@ def attention_backward_host(q, k, v, out, lse, dout, causal=False, scale=None, d
     return dq, dk, dv
 
 
+def attention_step_host(q, k, v, dout, causal=False, scale=None, out=None, lse=None, dq=None, dk=None, dv=None):
+    """Forward + backward from CPU (pinned) tensors with uploads, kernels and downloads pipelined
+    over slice chunks.  Returns (out, lse, dq, dk, dv)."""
+    B, H, S, D = q.shape
+    L = k.shape[2]
+    out = torch.empty_like(q) if out is None else out
+    lse = torch.empty((B, H, S), dtype=torch.float32) if lse is None else lse
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(k) if dk is None else dk
+    dv = torch.empty_like(v) if dv is None else dv
+    d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+    capi.check(capi.lib.tt_attn_fwd_bwd_host(ctypes.byref(d), _host_ptr(q), _host_ptr(k), _host_ptr(v), _host_ptr(dout),
+                                             _host_ptr(out), _host_ptr(lse), _host_ptr(dq), _host_ptr(dk), _host_ptr(dv)))
+    return out, lse, dq, dk, dv
+
+
 def attention_decode_host(q, k, v, scale=None, out=None, lse=None):
     B, H, S, D = q.shape
     L = k.shape[2]

@@ -264,6 +264,23 @@ def test_host_calls_match_device_calls(tt, oracle):
         assert oracle.max_abs_err(a.float().numpy(), _np(b)) <= 1e-2
 
 
+def test_pipelined_step_host_matches_device_calls(tt, oracle):
+    """tt_attn_fwd_bwd_host cuts the slices into chunks and pipelines upload / kernels / download;
+    the results must be those of the plain device calls, chunk boundaries included."""
+    B, H, S, D = 3, 7, 1024, 128          # 21 slices -> several chunks, the last one ragged
+    q, k, v, do = oracle.make_inputs(71, B, H, S, S, D, sigma=0.5)
+    hq, hk, hv, hdo = (torch.from_numpy(oracle.bf16_round(x)).to(torch.bfloat16).pin_memory() for x in (q, k, v, do))
+    out_h, lse_h, dq_h, dk_h, dv_h = tt.attention_step_host(hq, hk, hv, hdo, causal=True)
+    out_d, lse_d = tt.attention_forward(hq.cuda(), hk.cuda(), hv.cuda(), causal=True)
+    dq_d, dk_d, dv_d = tt.attention_backward(hq.cuda(), hk.cuda(), hv.cuda(), out_d, lse_d, hdo.cuda(), causal=True)
+    tt.check_device_status()
+    for a, b in ((out_h, out_d), (lse_h, lse_d), (dq_h, dq_d), (dk_h, dk_d), (dv_h, dv_d)):
+        assert torch.equal(a, b.cpu())
+    # second call reuses pooled buffers and cached streams
+    out_2, _, dq_2, _, _ = tt.attention_step_host(hq, hk, hv, hdo, causal=True)
+    assert torch.equal(out_2, out_h) and torch.equal(dq_2, dq_h)
+
+
 def test_argument_errors(tt):
     q = torch.zeros((1, 1, 8, 64), dtype=torch.bfloat16, device="cuda")
     k = torch.zeros((1, 1, 4, 64), dtype=torch.bfloat16, device="cuda")
