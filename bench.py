@@ -343,6 +343,35 @@ def run_decode(tt, dev, peaks, batch):
         return {"error": str(e)}
 
 
+def run_softmax(tt, dev, peaks):
+    """Row softmax forward and backward on a score-matrix sized input (HBM-bound): fp32
+    [262144, 1024] = 1 GiB per tensor, far above L2.  Algorithmic bytes: forward reads x and
+    writes y (8 B per element), backward reads y, dy and writes dx (12 B per element)."""
+    import torch
+    capi = tt.capi
+    try:
+        rows, cols = 262144, 1024
+        x = torch.randn((rows, cols), device=dev)
+        y, dy, dx = torch.empty_like(x), torch.randn((rows, cols), device=dev), torch.empty_like(x)
+        for _ in range(3):
+            tt.softmax_forward(x, out=y); tt.softmax_backward(y, dy, dx=dx)
+        torch.cuda.synchronize()
+        capi.profile_reset(); capi.profile_enable(True)
+        for _ in range(10):
+            tt.softmax_forward(x, out=y); tt.softmax_backward(y, dy, dx=dx)
+        torch.cuda.synchronize()
+        capi.profile_enable(False)
+        prof = capi.profile_read()
+        out = {"workload": f"fp32 rows [{rows},{cols}]"}
+        for key, nbytes in (("softmax_rows_fwd", 8.0 * rows * cols), ("softmax_rows_bwd", 12.0 * rows * cols)):
+            ms = prof[key][0] / prof[key][1]
+            out[key] = {"ms": ms, "bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
+                        "frac": nbytes / ms / 1e6 / peaks["hbm"]}
+        return out
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -352,6 +381,7 @@ def main():
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-softmax", action="store_true", help="skip the row-softmax leg at N=1")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the S=4096 side measurement at N=1")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--decode-batch", type=int, default=64, help="batch of the decode leg (64 = BASELINE config 4)")
@@ -388,6 +418,8 @@ def main():
                 "fwd_tflops": r3["fwd_tflops"], "pct_of_bf16_peak": r3["pct_of_bf16_peak"], "kernels": r3["kernels"]}
     decode = run_decode(tt, dev, peaks, args.decode_batch) if (rank == 0 and not args.no_decode) else None
 
+    softmax = run_softmax(tt, dev, peaks) if (rank == 0 and world == 1 and not args.no_softmax) else None
+
     # CPU baseline: the oracle on a bounded sample of the same workload (rank 0, N = 1)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -414,6 +446,7 @@ def main():
                        "parallelism": f"{world} x contiguous (batch,head) shards"},
             "fwd_tflops": main_res["fwd_tflops"], "pct_of_bf16_peak": main_res["pct_of_bf16_peak"],
             "roofline": main_res["roofline"], "kernels": main_res["kernels"], "cfg3": side, "decode": decode,
+            "softmax_rows": softmax,
             "cpu_baseline": cpu, "e2e": main_res["e2e"], "clocks": main_res["clocks"],
             "gpu_launches": main_res["gpu_launches"],
         }

@@ -112,6 +112,16 @@ int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const
 int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
                           void* out, float* lse, void* stream);
 
+/* ---- row softmax ------------------------------------------------------------------------
+ * out[r,:] = softmax(in[r,:]) over `cols`, row maximum subtracted; rows = product of the leading
+ * axes.  One launch that reads and writes every element once; replaces SoftmaxForward of
+ * src/Layers.cu:324-349 with its five launches and per-row Thrust loops
+ * (src/Layers_kernels.cu:189-257).  The backward, dx = y * (dy - sum(dy*y)), has no native
+ * counterpart in the reference (its NumPy form is the Softmax part of optimizer/operators.py:
+ * 610-626).  dtype: TT_F32 or TT_BF16 (fp32 arithmetic either way). */
+int tt_softmax_fwd(const void* in, void* out, int64_t rows, int32_t cols, int32_t dtype, void* stream);
+int tt_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int32_t cols, int32_t dtype, void* stream);
+
 /* ---- host-buffer calls (what the reference's Python ops do around each native op:
  * upload NumPy -> run -> download, optimizer/operators.py:502-512) ----------------------
  * Pointers are HOST pointers (pinned memory gives the best copy rate).  Device buffers

@@ -166,6 +166,37 @@ def attention_backward(q, k, v, do, causal=False, scale=None):
 
 
 # --------------------------------------------------------------------------------------
+# row softmax: the adjacent native op (SoftmaxForward, src/Layers.cu:324-349)
+# --------------------------------------------------------------------------------------
+def softmax_rows(x):
+    """Softmax over the last axis with the row maximum subtracted, leading axes flattened to
+    rows: what the native SoftmaxForward computes (src/Layers.cu:324-349: ChannelMax, ChannelSub,
+    ChannelExp, ChannelSum, ChannelDiv) and, call for call, the NumPy form the reference keeps in
+    Softmaxloss.compute (optimizer/operators.py:610-612)."""
+    x = np.asarray(x)
+    z = x.reshape(-1, x.shape[-1])
+    z_exp = np.exp(z - np.max(z, axis=1, keepdims=True))
+    z = z_exp / np.sum(z_exp, axis=1, keepdims=True)
+    return z.reshape(x.shape)
+
+
+def softmax_rows_backward(x, dy):
+    """dx for y = softmax_rows(x): the reference's reverse sweep (autodiff.py:33-61) over
+    exp(x - max) / broadcast(sum), node by node as in `attention_backward`."""
+    x = np.asarray(x); dy = np.asarray(dy)
+    z = x.reshape(-1, x.shape[-1]); g = dy.reshape(z.shape)
+    s = z + np.broadcast_to(-np.max(z, axis=1, keepdims=True), z.shape)   # EWiseAdd with a constant
+    e = np.exp(s)
+    den = np.broadcast_to(np.reshape(np.sum(e, axis=1), (z.shape[0], 1)), z.shape)
+    de_div = g / den                                                      # EWiseDiv.gradient :296-298
+    dden = -g * e / (den ** 2)
+    dden_r = np.reshape(np.sum(dden, axis=1), (z.shape[0], 1))            # BroadcastTo/Reshape/Summation grads
+    de_sum = np.broadcast_to(np.reshape(np.reshape(dden_r, (z.shape[0],)), (z.shape[0], 1)), z.shape)
+    de = de_div + de_sum
+    return (de * np.exp(s)).reshape(x.shape)                              # Exp.gradient :469-470
+
+
+# --------------------------------------------------------------------------------------
 # independent checks of the restatement
 # --------------------------------------------------------------------------------------
 def closed_form_f64(q, k, v, do=None, causal=False, scale=None):

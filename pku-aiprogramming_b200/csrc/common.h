@@ -25,7 +25,7 @@ inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 // Kernel families, for launch accounting and the optional per-kernel event timing.
 enum KernelId {
     K_FWD_TC = 0, K_FWD_SIMT, K_BWD_PREP, K_BWD_DKV, K_BWD_DQ, K_BWD_SIMT_DELTA, K_BWD_SIMT_DQ, K_BWD_SIMT_DKV,
-    K_DECODE, K_DECODE_MERGE, K_PROBE, K_COUNT
+    K_DECODE, K_DECODE_MERGE, K_PROBE, K_SOFTMAX_FWD, K_SOFTMAX_BWD, K_COUNT
 };
 // Scoped around ONE kernel launch: counts it and, when timing is enabled, brackets it with
 // CUDA events on the launching stream.
@@ -57,6 +57,11 @@ cudaError_t attn_bwd_sm100(const AttnArgs& a, void* workspace, cudaStream_t st);
 cudaError_t wait_timeout_probe(long long budget_cycles, cudaStream_t st);
 cudaError_t umma_probe(const void* a, const void* b, const void* vt, int D, float* s_out, float* o_out,
                        cudaStream_t st);
+
+// --- row softmax (adjacent native op of the reference), fp32 or bf16 rows
+cudaError_t softmax_rows_fwd(const void* in, void* out, long long rows, int cols, int bf16, cudaStream_t st);
+cudaError_t softmax_rows_bwd(const void* y, const void* dy, void* dx, long long rows, int cols, int bf16,
+                             cudaStream_t st);
 
 // --- split-KV decode (S == 1, bf16 or float)
 struct DecodePlan {

@@ -50,23 +50,6 @@ struct PoolBuffer {   // workspace taken from the pooled allocator for the durat
     ~PoolBuffer() { tt_free(p); }
 };
 
-template <typename T>
-__global__ void softmax_rows_kernel(const T* in, T* out, long long rows, int cols) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
-    if (row >= rows) return;
-    const T* x = in + row * cols;
-    T* y = out + row * cols;
-    float m = -INFINITY;
-    for (int c = lane; c < cols; c += 32) m = fmaxf(m, (float)x[c]);
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float s = 0.f;
-    for (int c = lane; c < cols; c += 32) s += expf((float)x[c] - m);
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    const float inv = 1.0f / s;
-    for (int c = lane; c < cols; c += 32) y[c] = (T)(expf((float)x[c] - m) * inv);
-}
-
 }  // namespace
 
 template <typename T>
@@ -125,10 +108,25 @@ void SoftmaxForward(const TinyTensor<T>& input, TinyTensor<T>& output) {
     output.resize(input.shape);
     const int cols = input.shape.back();
     const long long rows = cols ? (long long)(input.size / (size_t)cols) : 0;
-    if (rows == 0) return;
-    softmax_rows_kernel<T><<<(unsigned)((rows + 7) / 8), 256>>>(input.p_data, output.p_data, rows, cols);
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e != cudaSuccess) throw std::runtime_error(std::string("SoftmaxForward: ") + cudaGetErrorString(e));
+    int rc = tt_softmax_fwd(input.p_data, output.p_data, rows, cols, std::is_same<T, float>::value ? TT_F32 : TT_BF16, nullptr);
+    if (rc == TT_OK) rc = tt_check_device_status(nullptr);
+    raise(rc, "SoftmaxForward");
+}
+
+template <typename T>
+void SoftmaxBackward(const TinyTensor<T>& output, const TinyTensor<T>& grad_output, TinyTensor<T>& grad_input) {
+    require_gpu(output, "SoftmaxBackward", "output");
+    require_gpu(grad_output, "SoftmaxBackward", "grad_output");
+    if (output.shape.empty() || output.shape != grad_output.shape)
+        throw std::invalid_argument("SoftmaxBackward: output and grad_output must have one shape");
+    if (grad_input.device != "gpu") grad_input.gpu();
+    grad_input.resize(output.shape);
+    const int cols = output.shape.back();
+    const long long rows = cols ? (long long)(output.size / (size_t)cols) : 0;
+    int rc = tt_softmax_bwd(output.p_data, grad_output.p_data, grad_input.p_data, rows, cols,
+                            std::is_same<T, float>::value ? TT_F32 : TT_BF16, nullptr);
+    if (rc == TT_OK) rc = tt_check_device_status(nullptr);
+    raise(rc, "SoftmaxBackward");
 }
 
 template void AttentionForward<float>(const TinyTensor<float>&, const TinyTensor<float>&, const TinyTensor<float>&,
@@ -145,3 +143,4 @@ template void AttentionBackward<__nv_bfloat16>(const TinyTensor<__nv_bfloat16>&,
                                                TinyTensor<__nv_bfloat16>&, TinyTensor<__nv_bfloat16>&,
                                                const TinyTensor<__nv_bfloat16>&, bool, float);
 template void SoftmaxForward<float>(const TinyTensor<float>&, TinyTensor<float>&);
+template void SoftmaxBackward<float>(const TinyTensor<float>&, const TinyTensor<float>&, TinyTensor<float>&);

@@ -28,4 +28,8 @@ void AttentionBackward(const TinyTensor<T>& q, const TinyTensor<T>& k, const Tin
 template <typename T>
 void SoftmaxForward(const TinyTensor<T>& input, TinyTensor<T>& output);
 
+// grad_input = output * (grad_output - rowsum(grad_output * output)) for output = softmax(input).
+template <typename T>
+void SoftmaxBackward(const TinyTensor<T>& output, const TinyTensor<T>& grad_output, TinyTensor<T>& grad_input);
+
 #endif  // TT_HOST_LAYERS_H

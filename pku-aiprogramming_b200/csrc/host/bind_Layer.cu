@@ -25,4 +25,5 @@ PYBIND11_MODULE(myLayer, m) {
           py::arg("grad_k"), py::arg("grad_v"), py::arg("grad_out"), py::arg("causal") = false,
           py::arg("scale") = 0.0f);
     m.def("SoftmaxForward", &SoftmaxForward<float>, py::call_guard<py::gil_scoped_release>());
+    m.def("SoftmaxBackward", &SoftmaxBackward<float>, py::call_guard<py::gil_scoped_release>());
 }

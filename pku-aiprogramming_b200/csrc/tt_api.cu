@@ -35,7 +35,7 @@ static std::atomic<uint64_t> g_launches{0};
 static const char* const kKernelNames[K_COUNT] = {
     "attn_fwd_sm100", "attn_fwd_simt", "attn_bwd_prep", "attn_bwd_sm100_dkv", "attn_bwd_sm100_dq",
     "attn_bwd_simt_delta", "attn_bwd_simt_dq", "attn_bwd_simt_dkv", "attn_decode", "attn_decode_merge",
-    "umma_probe"};
+    "umma_probe", "softmax_rows_fwd", "softmax_rows_bwd"};
 struct TimedLaunch {
     KernelId id;
     cudaEvent_t start, stop;
@@ -441,6 +441,27 @@ int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k
                     attn_decode_static_capacity());
     if (e != cudaSuccess) return cuda_fail(e, "tt_attn_decode_static");
     return TT_OK;
+}
+
+static int softmax_args(const char* who, const void* a, const void* out, int64_t rows, int32_t cols, int32_t dtype) {
+    if ((!a || !out) && rows != 0) return fail(TT_ERR_NULL, "%s: null pointer", who);
+    if (rows < 0 || cols < 1) return fail(TT_ERR_BAD_SHAPE, "%s: rows=%lld cols=%d", who, (long long)rows, cols);
+    if (rows >= (1LL << 31)) return fail(TT_ERR_BAD_SHAPE, "%s: more than 2^31-1 rows", who);
+    if (dtype != TT_F32 && dtype != TT_BF16) return fail(TT_ERR_BAD_DTYPE, "%s: dtype %d unknown", who, dtype);
+    return check_device();
+}
+int tt_softmax_fwd(const void* in, void* out, int64_t rows, int32_t cols, int32_t dtype, void* stream) {
+    int rc = softmax_args("tt_softmax_fwd", in, out, rows, cols, dtype);
+    if (rc != TT_OK || rows == 0) return rc;
+    cudaError_t e = softmax_rows_fwd(in, out, rows, cols, dtype == TT_BF16, (cudaStream_t)stream);
+    return e == cudaSuccess ? TT_OK : cuda_fail(e, "tt_softmax_fwd: launch");
+}
+int tt_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int32_t cols, int32_t dtype, void* stream) {
+    int rc = softmax_args("tt_softmax_bwd", y, dx, rows, cols, dtype);
+    if (rc != TT_OK || rows == 0) return rc;
+    if (!dy) return fail(TT_ERR_NULL, "tt_softmax_bwd: null pointer");
+    cudaError_t e = softmax_rows_bwd(y, dy, dx, rows, cols, dtype == TT_BF16, (cudaStream_t)stream);
+    return e == cudaSuccess ? TT_OK : cuda_fail(e, "tt_softmax_bwd: launch");
 }
 
 int tt_debug_wait_timeout(int64_t budget_cycles, void* stream) {

@@ -99,6 +99,31 @@ def attention_decode(q, k, v, scale=None, out=None, lse=None, workspace=None, ne
     return out, lse
 
 
+def softmax_forward(x, out=None):
+    """Softmax over the last axis of a contiguous CUDA tensor (float32 or bfloat16)."""
+    if not x.is_cuda or not x.is_contiguous() or x.dtype not in _DT:
+        raise ValueError("softmax_forward takes a contiguous float32/bfloat16 CUDA tensor")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    with torch.cuda.device(x.device):
+        out = torch.empty_like(x) if out is None else out
+        capi.check(capi.lib.tt_softmax_fwd(_p(x), _p(out), rows, cols, _DT[x.dtype], _stream_ptr(x)))
+    return out
+
+
+def softmax_backward(y, dy, dx=None):
+    """dx = y * (dy - sum(dy * y, last axis)) for y = softmax(x)."""
+    if not (y.is_cuda and dy.is_cuda and y.is_contiguous() and dy.is_contiguous()) or y.dtype != dy.dtype \
+            or y.shape != dy.shape or y.dtype not in _DT:
+        raise ValueError("softmax_backward takes two contiguous CUDA tensors of one shape and dtype")
+    cols = y.shape[-1]
+    rows = y.numel() // cols if cols else 0
+    with torch.cuda.device(y.device):
+        dx = torch.empty_like(y) if dx is None else dx
+        capi.check(capi.lib.tt_softmax_bwd(_p(y), _p(dy), _p(dx), rows, cols, _DT[y.dtype], _stream_ptr(y)))
+    return dx
+
+
 def check_device_status(device=None):
     """Synchronises the current stream and raises if a bounded device-side wait expired."""
     with torch.cuda.device(device if device is not None else torch.cuda.current_device()):

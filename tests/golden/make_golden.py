@@ -68,6 +68,35 @@ def reference_attention(ops, q, k, v, do, causal, scale):
     return O.numpy(), Q.grad.numpy(), K.grad.numpy(), V.grad.numpy()
 
 
+# name, rows-shape, cols, sigma, seed  (row softmax: the adjacent native op, see oracle.softmax_rows)
+SOFTMAX_CASES = [
+    ("rows_6x10", (6,), 10, 1.0, 20),          # the classifier shape the reference uses it on
+    ("rows_3x5x33", (3, 5), 33, 3.0, 21),
+    ("rows_4x1025", (4,), 1025, 1.0, 22),
+    ("rows_2x2500", (2,), 2500, 2.0, 23),
+]
+
+
+def reference_softmax(ops, x, dy):
+    """Forward: the reference's own NumPy row softmax (Softmaxloss.compute keeps it in
+    `.softmax`); it is defined for 2-D input, so leading axes are flattened as the native
+    SoftmaxForward does.  Backward: the reference's reverse sweep over exp(x - max) / sum."""
+    cols = x.shape[-1]
+    x2 = x.reshape(-1, cols)
+    op = ops.Softmaxloss(ops.Tensor(np.zeros(x2.shape[0], dtype=np.int64), requires_grad=False))
+    op.compute(x2)
+    y = op.softmax.reshape(x.shape)
+    X = ops.Tensor(x2)
+    shift = ops.Tensor(np.ascontiguousarray(np.broadcast_to(-np.max(x2, axis=1, keepdims=True), x2.shape)),
+                       requires_grad=False)
+    e = ops.exp(X + shift)
+    den = ops.broadcast_to(ops.reshape(ops.summation(e, axes=(1,)), (x2.shape[0], 1)), x2.shape)
+    Y = e / den
+    Y.backward(ops.Tensor(dy.reshape(-1, cols), requires_grad=False))
+    assert np.array_equal(Y.numpy(), y.reshape(-1, cols))
+    return y, X.grad.numpy().reshape(x.shape)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -84,6 +113,16 @@ def main():
                  causal=np.int32(causal), scale=np.float32(scale), seed=np.int32(seed),
                  sigma=np.float32(sigma))
         print(f"{name}: wrote {os.path.getsize(path)/1024:.0f} KiB  |O|max={np.abs(o).max():.4f}")
+    os.makedirs(os.path.join(HERE, "softmax_rows"), exist_ok=True)
+    for name, lead, cols, sigma, seed in SOFTMAX_CASES:
+        rng = np.random.Generator(np.random.PCG64([seed, cols]))
+        x = (rng.standard_normal(lead + (cols,)) * sigma).astype(np.float32)
+        dy = rng.standard_normal(lead + (cols,)).astype(np.float32)
+        y, dx = reference_softmax(ops, x, dy)
+        assert y.dtype == np.float32 and dx.dtype == np.float32
+        path = os.path.join(HERE, "softmax_rows", name + ".npz")
+        np.savez(path, x=x, dy=dy, y=y, dx=dx)
+        print(f"softmax_rows/{name}: wrote {os.path.getsize(path)/1024:.0f} KiB")
 
 
 if __name__ == "__main__":

@@ -37,7 +37,7 @@ def test_module_surface(mods):
         for m in methods:
             assert hasattr(getattr(mt, cls), m), (cls, m)
     for fn in ("AttentionForward", "AttentionBackward", "AttentionForward_bf16", "AttentionBackward_bf16",
-               "SoftmaxForward"):
+               "SoftmaxForward", "SoftmaxBackward"):
         assert hasattr(ml, fn)
 
 

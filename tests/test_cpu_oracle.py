@@ -97,3 +97,17 @@ def test_lse_is_log_of_denominator(oracle):
     _, lse = oracle.attention_forward(q, k, v, causal=True)
     _, lse64 = oracle.closed_form_f64(q, k, v, None, True)
     assert np.max(np.abs(lse - lse64)) < 1e-5
+
+
+SOFTMAX_GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "softmax_rows", "*.npz")))
+
+
+@pytest.mark.parametrize("path", SOFTMAX_GOLDEN, ids=[os.path.basename(p)[:-4] for p in SOFTMAX_GOLDEN])
+def test_softmax_oracle_reproduces_reference_bit_exactly(oracle, path):
+    g = np.load(path)
+    assert np.array_equal(oracle.softmax_rows(g["x"]), g["y"])
+    assert np.array_equal(oracle.softmax_rows_backward(g["x"], g["dy"]), g["dx"])
+    # and the closed form of the gradient in float64
+    y = g["y"].astype(np.float64); dy = g["dy"].astype(np.float64)
+    want = y * (dy - np.sum(dy * y, axis=-1, keepdims=True))
+    assert len(SOFTMAX_GOLDEN) >= 4 and oracle.rel_err(g["dx"], want) < 2e-6

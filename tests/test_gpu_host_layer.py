@@ -79,7 +79,13 @@ def test_mylayer_decode_dispatch_and_softmax(mods, oracle):
     y = mt.Tensor_float([1], "gpu")
     ml.SoftmaxForward(mt.Tensor_float(x, "gpu"), y)
     e = np.exp(x - x.max(-1, keepdims=True))
-    assert np.allclose(y.numpy(), e / e.sum(-1, keepdims=True), atol=1e-6)
+    assert np.allclose(y.numpy(), e / e.sum(-1, keepdims=True), atol=1e-6) and y.get_shape() == [5, 7, 33]
+    dy = np.random.default_rng(4).standard_normal(x.shape).astype(np.float32)
+    dx = mt.Tensor_float([1], "gpu")
+    ml.SoftmaxBackward(y, mt.Tensor_float(dy, "gpu"), dx)
+    assert oracle.rel_err(dx.numpy(), oracle.softmax_rows_backward(x, dy)) <= 1e-5
+    with pytest.raises(ValueError):
+        ml.SoftmaxBackward(y, mt.Tensor_float(dy[:, :, :5].copy(), "gpu"), dx)
 
 
 def test_tensor_on_device(mods):
