@@ -87,6 +87,8 @@ def build_host_modules(force: bool = False, verbose: bool = False):
     os.makedirs(HOST_DIR, exist_ok=True)
     suffix = sysconfig.get_config_var("EXT_SUFFIX")
     inc = ["-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"], "-I" + HOST]
+    import torch  # only for the directory that holds ATen/dlpack.h (the DLPack ABI header)
+    inc.append("-I" + os.path.join(os.path.dirname(torch.__file__), "include"))
     flags = [f for f in NVCC_FLAGS if f != "-fvisibility=hidden"]
     # drop the "-Xcompiler" that preceded the removed visibility flag
     cleaned, skip = [], False

@@ -4,11 +4,154 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <ATen/dlpack.h>   // the DLPack ABI structs as shipped with torch (C header, nothing else of torch is used)
+
+#include <cstdint>
+#include <cstring>
+#include <limits>
 #include <sstream>
 
 #include "TinyTensor.h"
 
 namespace py = pybind11;
+
+// ---- DLPack exchange -------------------------------------------------------------------------
+// Export (`__dlpack__`, `__dlpack_device__`): zero-copy view of the tensor's buffer for any
+// consumer of the protocol (torch.from_dlpack, np.from_dlpack for host tensors).  The capsule
+// keeps the Python tensor object alive until the consumer's deleter runs.  Import
+// (`from_dlpack`): a deep copy (device to device when the producer's data is on a GPU), because a
+// TinyTensor owns its buffer.  The reference has neither; its only way out of a tensor is
+// get_data() -> Python list (src/bind_Tensor.cpp:26 of the reference project).
+namespace {
+
+template <typename T> DLDataType dl_dtype();
+template <> DLDataType dl_dtype<float>() { return DLDataType{kDLFloat, 32, 1}; }
+template <> DLDataType dl_dtype<double>() { return DLDataType{kDLFloat, 64, 1}; }
+template <> DLDataType dl_dtype<int>() { return DLDataType{kDLInt, 32, 1}; }
+template <> DLDataType dl_dtype<__nv_bfloat16>() { return DLDataType{kDLBfloat, 16, 1}; }
+
+struct DlExport {
+    py::object owner;                 // keeps the TinyTensor alive
+    std::vector<int64_t> shape, strides;
+    DLManagedTensor managed;
+};
+
+void dl_export_deleter(DLManagedTensor* m) {
+    if (!m) return;
+    py::gil_scoped_acquire gil;
+    delete static_cast<DlExport*>(m->manager_ctx);
+}
+
+void dl_capsule_destructor(PyObject* cap) {
+    // a consumer renames the capsule to "used_dltensor"; only an unconsumed one is released here
+    if (!PyCapsule_IsValid(cap, "dltensor")) return;
+    auto* m = static_cast<DLManagedTensor*>(PyCapsule_GetPointer(cap, "dltensor"));
+    if (m && m->deleter) m->deleter(m);
+}
+
+int device_of_pointer(const void* p) {
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        throw std::runtime_error("cudaPointerGetAttributes failed for a device tensor");
+    }
+    return attr.device;
+}
+
+template <typename T>
+py::tuple dlpack_device(const TinyTensor<T>& t) {
+    if (t.device == "gpu" && t.p_data) return py::make_tuple((int)kDLCUDA, device_of_pointer(t.p_data));
+    if (t.device == "gpu") {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        return py::make_tuple((int)kDLCUDA, dev);
+    }
+    return py::make_tuple((int)kDLCPU, 0);
+}
+
+template <typename T>
+py::capsule dlpack_export(py::object self, py::object /*stream*/) {
+    const auto& t = self.cast<const TinyTensor<T>&>();
+    auto* ex = new DlExport();
+    ex->owner = self;
+    ex->shape.assign(t.shape.begin(), t.shape.end());
+    ex->strides.assign(t.shape.size(), 1);
+    for (int i = (int)t.shape.size() - 2; i >= 0; --i) ex->strides[i] = ex->strides[i + 1] * std::max<int64_t>(ex->shape[i + 1], 1);
+    DLTensor& d = ex->managed.dl_tensor;
+    d.data = t.p_data;
+    d.ndim = (int32_t)t.shape.size();
+    d.dtype = dl_dtype<T>();
+    d.shape = ex->shape.data();
+    d.strides = ex->strides.data();
+    d.byte_offset = 0;
+    if (t.device == "gpu") {
+        // tensor methods and layer calls run on the legacy default stream; make their results
+        // visible to whatever stream the consumer uses
+        if (cudaDeviceSynchronize() != cudaSuccess) {
+            delete ex;
+            throw std::runtime_error("cudaDeviceSynchronize failed before DLPack export");
+        }
+        int dev = 0;
+        if (t.p_data) dev = device_of_pointer(t.p_data); else cudaGetDevice(&dev);
+        d.device = DLDevice{kDLCUDA, dev};
+    } else {
+        d.device = DLDevice{kDLCPU, 0};
+    }
+    ex->managed.manager_ctx = ex;
+    ex->managed.deleter = dl_export_deleter;
+    return py::capsule(&ex->managed, "dltensor", dl_capsule_destructor);
+}
+
+template <typename T>
+TinyTensor<T> dlpack_import(py::object src) {
+    py::object cap_obj = py::hasattr(src, "__dlpack__") ? src.attr("__dlpack__")() : src;
+    PyObject* cap = cap_obj.ptr();
+    if (!PyCapsule_IsValid(cap, "dltensor"))
+        throw std::invalid_argument("from_dlpack: expected an object with __dlpack__ or an unconsumed 'dltensor' capsule");
+    auto* m = static_cast<DLManagedTensor*>(PyCapsule_GetPointer(cap, "dltensor"));
+    const DLTensor& d = m->dl_tensor;
+    const DLDataType want = dl_dtype<T>();
+    auto release = [&]() {
+        PyCapsule_SetName(cap, "used_dltensor");
+        if (m->deleter) m->deleter(m);
+    };
+    std::string err;
+    if (d.dtype.code != want.code || d.dtype.bits != want.bits || d.dtype.lanes != 1) err = "element type does not match this tensor class";
+    const bool on_gpu = d.device.device_type == kDLCUDA || d.device.device_type == kDLCUDAManaged;
+    if (!on_gpu && d.device.device_type != kDLCPU && d.device.device_type != kDLCUDAHost) err = "unsupported device type";
+    std::vector<int> shape(d.ndim > 0 ? d.ndim : 0);
+    int64_t expect = 1;
+    for (int i = d.ndim - 1; i >= 0 && err.empty(); --i) {
+        if (d.shape[i] < 0 || d.shape[i] > std::numeric_limits<int>::max()) err = "extent does not fit the int shape";
+        else if (d.strides && d.shape[i] > 1 && d.strides[i] != expect) err = "only contiguous row-major data can be imported";
+        shape[i] = (int)d.shape[i];
+        expect *= std::max<int64_t>(d.shape[i], 1);
+    }
+    if (!err.empty()) {
+        release();
+        throw std::invalid_argument("from_dlpack: " + err);
+    }
+    try {
+        TinyTensor<T> out(shape, on_gpu ? "gpu" : "cpu");
+        if (out.size) {
+            const char* from = static_cast<const char*>(d.data) + d.byte_offset;
+            if (on_gpu) {
+                cudaError_t e = cudaMemcpy(out.p_data, from, out.size * sizeof(T), cudaMemcpyDefault);
+                if (e != cudaSuccess)
+                    throw std::runtime_error(std::string("from_dlpack: copy failed: ") + cudaGetErrorString(e));
+            } else {
+                std::memcpy(out.p_data, from, out.size * sizeof(T));
+            }
+        }
+        release();
+        return out;
+    } catch (...) {
+        release();
+        throw;
+    }
+}
+
+}  // namespace
 
 template <typename T, typename C>
 void add_common(C& cls) {
@@ -35,6 +178,10 @@ void add_common(C& cls) {
         .def("ReluBackward", &Tensor::ReluBackward)
         .def("SigmoidForward", &Tensor::SigmoidForward)
         .def("SigmoidBackward", &Tensor::SigmoidBackward)
+        .def("data_ptr", [](const Tensor& t) { return (std::uintptr_t)t.p_data; })
+        .def("__dlpack_device__", &dlpack_device<T>)
+        .def("__dlpack__", &dlpack_export<T>, py::arg("stream") = py::none())
+        .def_static("from_dlpack", &dlpack_import<T>, py::arg("source"))
         // fast path for tests and large tensors: a NumPy float32 array instead of a Python list
         .def("numpy", [](const Tensor& t) {
             std::vector<float> host = t.get_data_f32();

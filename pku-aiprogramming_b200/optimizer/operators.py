@@ -1,12 +1,19 @@
 """`Tensor`, the NumPy-backed differentiable ops, and the GPU-backed `Attention` op.
 
 Interface and semantics follow the reference's `optimizer/operators.py` (Tensor :14-187,
-TensorOp :189-191, NumPy ops :194-475, GPU-backed op pattern `FC` :498-532): node data is
-always a NumPy array; an op that uses the GPU uploads its inputs into `myTensor` tensors,
+TensorOp :189-191, NumPy ops :194-475, GPU-backed op pattern `FC` :498-532): node data is a
+NumPy array by default; an op that uses the GPU uploads its inputs into `myTensor` tensors,
 calls a `myLayer` function, and downloads the result.  `Attention` is the op the reference
 lacks; composing MatMul/Transpose/MulScalar/EWiseAdd/Exp/Summation/Reshape/BroadcastTo/EWiseDiv
 from this module gives the same numbers on the CPU (that composition is what the tests check
 the kernels against).
+
+Device-resident nodes: `Tensor(x, device="gpu")` keeps a `myTensor` tensor as the node's data
+instead of a NumPy array, so a chain of device-capable ops (`Attention`, `Softmax`, `+`, `-`,
+scalar `*`, unary `-`, and the reverse sweep's adjoint sums) never leaves the GPU -- the
+reference's GPU ops go through `get_data()` -> Python list -> `np.array` on every call
+(operators.py:56-58, 511 there).  Ops without a device implementation refuse device inputs
+(`TypeError`); `.cpu()` makes the copy explicit.
 """
 from __future__ import annotations
 
@@ -34,10 +41,39 @@ def _native():
     return myTensor, myLayer
 
 
+def _on_device(x) -> bool:
+    """True for a `myTensor` tensor (node data kept on the GPU)."""
+    return hasattr(x, "get_device") and hasattr(x, "get_shape")
+
+
+def _device_dtype(x):
+    name = type(x).__name__
+    return {"Tensor_float": np.dtype(np.float32), "Tensor_double": np.dtype(np.float64),
+            "Tensor_int": np.dtype(np.int32)}.get(name, "bfloat16")
+
+
+def _to_device(array, dtype=None):
+    """A gpu `myTensor` tensor holding `array` (NumPy data is uploaded once; a `myTensor` tensor
+    is taken as is, or copied to the GPU if it lives on the host)."""
+    mt, _ = _native()
+    if _on_device(array):
+        if array.get_device() == "gpu":
+            return array
+        moved = type(array)(array)
+        moved.gpu()
+        return moved
+    cls = mt.Tensor_bf16 if str(dtype) == "bfloat16" else mt.Tensor_float
+    return cls(np.ascontiguousarray(array, dtype=np.float32), "gpu")
+
+
 class Tensor(Value):
     grad: "Tensor"
 
     def __init__(self, array, *, device=None, dtype=None, requires_grad=True, **kwargs):
+        if device == "gpu":
+            src = array.realize_cached_data() if isinstance(array, Tensor) else array
+            self._init(None, [], cached_data=_to_device(src, dtype), requires_grad=requires_grad)
+            return
         if isinstance(array, Tensor):
             data = array.realize_cached_data()
             data = data if dtype is None else np.asarray(data, dtype=dtype)
@@ -51,6 +87,8 @@ class Tensor(Value):
 
     @staticmethod
     def make_from_op(op: Op, inputs):
+        if not getattr(op, "device_ok", False) and any(x.is_device for x in inputs):
+            raise TypeError(f"{type(op).__name__} has no device implementation; call .cpu() on its inputs")
         t = Tensor.__new__(Tensor)
         t._init(op, inputs)
         if not t.requires_grad:
@@ -78,25 +116,47 @@ class Tensor(Value):
         self.cached_data = value.realize_cached_data()
 
     @property
+    def is_device(self) -> bool:
+        return _on_device(self.realize_cached_data())
+
+    @property
     def shape(self):
-        return self.realize_cached_data().shape
+        d = self.realize_cached_data()
+        return tuple(d.get_shape()) if _on_device(d) else d.shape
 
     @property
     def dtype(self):
-        return self.realize_cached_data().dtype
+        d = self.realize_cached_data()
+        return _device_dtype(d) if _on_device(d) else d.dtype
 
     def numpy(self):
-        return self.realize_cached_data()
+        """Node data as a NumPy array (a download for a device-resident node; bf16 widens to float32)."""
+        d = self.realize_cached_data()
+        return d.numpy() if _on_device(d) else d
+
+    def cpu(self):
+        """A NumPy-backed leaf holding this node's data."""
+        return Tensor(self.numpy(), requires_grad=self.requires_grad)
+
+    def gpu(self, dtype=None):
+        """A device-resident leaf holding this node's data (float32, or bf16 with dtype="bfloat16")."""
+        return Tensor(self.realize_cached_data(), device="gpu", dtype=dtype, requires_grad=self.requires_grad)
 
     def backward(self, out_grad=None):
         if out_grad is None:
-            out_grad = Tensor(np.ones(self.shape, dtype=self.dtype), requires_grad=False)
+            d = self.realize_cached_data()
+            if _on_device(d):
+                ones = type(d)(list(d.get_shape()), "gpu")
+                ones.ones()
+                out_grad = Tensor(ones, device="gpu", requires_grad=False)
+            else:
+                out_grad = Tensor(np.ones(self.shape, dtype=self.dtype), requires_grad=False)
         backward_pass(self, out_grad)
 
     def __repr__(self):
-        return "Tensor(" + str(self.realize_cached_data()) + ")"
+        return "Tensor(" + str(self.numpy()) + ")"
 
-    __str__ = lambda self: str(self.realize_cached_data())
+    __str__ = lambda self: str(self.numpy())
 
     def __add__(self, other):
         return EWiseAdd()(self, other) if isinstance(other, Tensor) else AddScalar(other)(self)
@@ -142,19 +202,39 @@ class TensorOp(Op):
 
 
 # ----------------------------------------------------------------------------- NumPy ops
+def _all_or_none_on_device(*arrays) -> bool:
+    n = sum(_on_device(a) for a in arrays)
+    if n not in (0, len(arrays)):
+        raise TypeError("mixing device-resident and NumPy-backed tensors in one op; move one side with .gpu()/.cpu()")
+    return n > 0
+
+
+def _device_copy(a):
+    return type(a)(a)
+
+
 class EWiseAdd(TensorOp):
+    device_ok = True
+
     def compute(self, a, b):
-        return a + b
+        _all_or_none_on_device(a, b)
+        return a + b          # TinyTensor::operator+ on the device, ndarray add on the host
 
     def gradient(self, g, node):
         return g, g
 
 
 class AddScalar(TensorOp):
+    device_ok = True
+
     def __init__(self, scalar):
         self.scalar = scalar
 
     def compute(self, a):
+        if _on_device(a):
+            fill = type(a)(list(a.get_shape()), "gpu")
+            fill.floatks(float(self.scalar))
+            return a + fill
         return a + self.scalar
 
     def gradient(self, g, node):
@@ -171,10 +251,16 @@ class EWiseMul(TensorOp):
 
 
 class MulScalar(TensorOp):
+    device_ok = True
+
     def __init__(self, scalar):
         self.scalar = scalar
 
     def compute(self, a):
+        if _on_device(a):
+            out = _device_copy(a)
+            out.mults(float(self.scalar))
+            return out
         return a * self.scalar
 
     def gradient(self, g, node):
@@ -214,7 +300,13 @@ class DivScalar(TensorOp):
 
 
 class Negate(TensorOp):
+    device_ok = True
+
     def compute(self, a):
+        if _on_device(a):
+            out = _device_copy(a)
+            out.negative()
+            return out
         return -a
 
     def gradient(self, g, node):
@@ -325,12 +417,16 @@ def matmul(a, b): return MatMul()(a, b)
 class Attention(TensorOp):
     """`softmax(scale * q k^T [+ causal mask]) v` on the GPU.
 
-    q `[B,H,S,D]`, k and v `[B,H,L,D]`.  `dtype="float32"` runs the exact fp32 kernels,
-    `dtype="bfloat16"` rounds the inputs to bf16 (nearest even) and runs the tensor-core
-    kernels; node data stays NumPy float32 either way.  The forward keeps `out` and `lse` on
-    the op instance for the backward, like the reference's ops keep their masks
-    (operators.py:577-586 of the reference).
+    q `[B,H,S,D]`, k and v `[B,H,L,D]`.  With NumPy-backed inputs, `dtype="float32"` runs the
+    exact fp32 kernels and `dtype="bfloat16"` rounds the inputs to bf16 (nearest even) and runs
+    the tensor-core kernels; inputs are uploaded and the result comes back as NumPy float32 (the
+    reference's GPU-op pattern).  With device-resident inputs (all three `Tensor_float` or all
+    three `Tensor_bf16`) nothing is copied: the result and the gradients are device-resident
+    nodes of the same element type.  The forward keeps `out` and `lse` on the op instance for
+    the backward, like the reference's ops keep their masks (operators.py:577-586 of the
+    reference).
     """
+    device_ok = True
 
     def __init__(self, causal: bool = False, scale: Optional[float] = None, dtype: str = "float32"):
         if dtype not in ("float32", "bfloat16"):
@@ -338,32 +434,86 @@ class Attention(TensorOp):
         self.causal, self.scale, self.dtype = bool(causal), 0.0 if scale is None else float(scale), dtype
         self._saved = None
 
-    def _names(self):
+    @staticmethod
+    def _names(bf16: bool):
         mt, ml = _native()
-        if self.dtype == "float32":
-            return mt.Tensor_float, ml.AttentionForward, ml.AttentionBackward, mt.Tensor_float
-        return mt.Tensor_bf16, ml.AttentionForward_bf16, ml.AttentionBackward_bf16, mt.Tensor_float
+        if bf16:
+            return mt.Tensor_bf16, ml.AttentionForward_bf16, ml.AttentionBackward_bf16, mt.Tensor_float
+        return mt.Tensor_float, ml.AttentionForward, ml.AttentionBackward, mt.Tensor_float
 
     def compute(self, q, k, v):
-        T, fwd, _, F = self._names()
-        up = lambda a: T(np.ascontiguousarray(a, dtype=np.float32), "gpu")
-        tq, tk, tv = up(q), up(k), up(v)
-        out, lse = T(list(q.shape), "gpu"), F(list(q.shape[:3]), "gpu")
+        resident = _all_or_none_on_device(q, k, v)
+        if resident:
+            if not (type(q) is type(k) is type(v)) or type(q).__name__ not in ("Tensor_float", "Tensor_bf16"):
+                raise TypeError("device-resident q, k, v must all be Tensor_float or all Tensor_bf16")
+            bf16 = type(q).__name__ == "Tensor_bf16"
+            T, fwd, _, F = self._names(bf16)
+            tq, tk, tv, shape = q, k, v, list(q.get_shape())
+        else:
+            bf16 = self.dtype == "bfloat16"
+            T, fwd, _, F = self._names(bf16)
+            up = lambda a: T(np.ascontiguousarray(a, dtype=np.float32), "gpu")
+            tq, tk, tv, shape = up(q), up(k), up(v), list(q.shape)
+        out, lse = T(shape, "gpu"), F(shape[:3], "gpu")
         fwd(tq, tk, tv, out, lse, self.causal, self.scale)
-        self._saved = (tq, tk, tv, out, lse)
-        return out.numpy().astype(q.dtype, copy=False)
+        self._saved = (tq, tk, tv, out, lse, bf16, resident)
+        return out if resident else out.numpy().astype(q.dtype, copy=False)
 
     def gradient(self, out_grad, node):
-        T, _, bwd, _ = self._names()
         if self._saved is None:
             node.realize_cached_data()
-        tq, tk, tv, out, lse = self._saved
-        go = T(np.ascontiguousarray(out_grad.realize_cached_data(), dtype=np.float32), "gpu")
+        tq, tk, tv, out, lse, bf16, resident = self._saved
+        T, _, bwd, _ = self._names(bf16)
+        g = out_grad.realize_cached_data()
+        if _on_device(g):
+            if type(g) is not T:
+                raise TypeError(f"upstream gradient is {type(g).__name__}, the op ran on {T.__name__}")
+            go = g
+        else:
+            go = T(np.ascontiguousarray(g, dtype=np.float32), "gpu")
         gq, gk, gv = T(tq.get_shape(), "gpu"), T(tk.get_shape(), "gpu"), T(tv.get_shape(), "gpu")
         bwd(tq, tk, tv, out, lse, gq, gk, gv, go, self.causal, self.scale)
+        if resident:
+            return tuple(Tensor(t, device="gpu", requires_grad=False) for t in (gq, gk, gv))
         dt = node.inputs[0].dtype
         mk = lambda t: Tensor(t.numpy().astype(dt, copy=False), requires_grad=False)
         return mk(gq), mk(gk), mk(gv)
+
+
+class Softmax(TensorOp):
+    """Softmax over the last axis on the GPU (`myLayer.SoftmaxForward` / `SoftmaxBackward`,
+    float32).  NumPy-backed input: upload, run, download; device-resident input: stays there."""
+    device_ok = True
+
+    def __init__(self):
+        self._y = None
+
+    def compute(self, x):
+        mt, ml = _native()
+        resident = _on_device(x)
+        if resident and type(x).__name__ != "Tensor_float":
+            raise TypeError("Softmax takes float32 data")
+        tx = x if resident else mt.Tensor_float(np.ascontiguousarray(x, dtype=np.float32), "gpu")
+        y = mt.Tensor_float([1], "gpu")
+        ml.SoftmaxForward(tx, y)
+        self._y, self._resident = y, resident
+        return y if resident else y.numpy().astype(x.dtype, copy=False)
+
+    def gradient(self, out_grad, node):
+        mt, ml = _native()
+        if self._y is None:
+            node.realize_cached_data()
+        g = out_grad.realize_cached_data()
+        tg = g if _on_device(g) else mt.Tensor_float(np.ascontiguousarray(g, dtype=np.float32), "gpu")
+        dx = mt.Tensor_float([1], "gpu")
+        ml.SoftmaxBackward(self._y, tg, dx)
+        if self._resident:
+            return Tensor(dx, device="gpu", requires_grad=False)
+        return Tensor(dx.numpy().astype(node.inputs[0].dtype, copy=False), requires_grad=False)
+
+
+def softmax(x):
+    return Softmax()(x)
 
 
 def attention(q, k, v, causal: bool = False, scale: Optional[float] = None, dtype: str = "float32"):

@@ -32,7 +32,8 @@ def test_module_surface(mods):
     mt, ml = mods
     methods = ["Size", "__add__", "__sub__", "__getitem__", "get_shape", "get_device", "get_data", "flatten", "cpu",
                "gpu", "random", "zeros", "ones", "negative", "mults", "floatks", "resize", "ReluForward", "ReluBackward",
-               "SigmoidForward", "SigmoidBackward", "__repr__"]
+               "SigmoidForward", "SigmoidBackward", "__repr__", "numpy", "data_ptr", "__dlpack__", "__dlpack_device__",
+               "from_dlpack"]
     for cls in ("Tensor_float", "Tensor_double", "Tensor_int", "Tensor_bf16"):
         for m in methods:
             assert hasattr(getattr(mt, cls), m), (cls, m)
@@ -120,3 +121,45 @@ def test_composed_attention_reproduces_reference(opt, path):
     o.backward(opt.Tensor(g["do"], requires_grad=False))
     for got, name in ((o, "o"), (q.grad, "dq"), (k.grad, "dk"), (v.grad, "dv")):
         assert np.array_equal(got.numpy(), g[name]), name
+
+
+def test_dlpack_export_of_host_tensors_is_zero_copy(mods):
+    mt, _ = mods
+    for cls, dt in ((mt.Tensor_float, np.float32), (mt.Tensor_double, np.float64), (mt.Tensor_int, np.int32)):
+        x = np.arange(24).reshape(2, 3, 4).astype(dt)
+        t = cls(x, "cpu")
+        assert t.__dlpack_device__() == (1, 0)            # kDLCPU
+        view = np.from_dlpack(t)
+        assert view.dtype == dt and view.shape == (2, 3, 4) and np.array_equal(view, x)
+        assert view.ctypes.data == t.data_ptr()
+        t.floatks(7)                                      # written through the tensor, seen through the view
+        assert (view == 7).all()
+    del t
+    assert (view == 7).all()                              # the capsule keeps the tensor's buffer alive
+
+
+def test_dlpack_import_copies_and_validates(mods):
+    import torch
+    mt, _ = mods
+    x = np.random.default_rng(0).standard_normal((3, 5)).astype(np.float32)
+    t = mt.Tensor_float.from_dlpack(x)
+    assert t.get_device() == "cpu" and t.get_shape() == [3, 5] and np.array_equal(t.numpy(), x)
+    assert t.data_ptr() != x.ctypes.data                  # a TinyTensor owns its buffer: deep copy
+    b = torch.from_numpy(x).bfloat16()
+    tb = mt.Tensor_bf16.from_dlpack(b)
+    assert np.array_equal(tb.numpy(), b.float().numpy())
+    assert mt.Tensor_int.from_dlpack(torch.arange(6, dtype=torch.int32).reshape(2, 3)).get_data() == [0, 1, 2, 3, 4, 5]
+    with pytest.raises(ValueError):
+        mt.Tensor_double.from_dlpack(x)                   # element type mismatch
+    with pytest.raises(ValueError):
+        mt.Tensor_float.from_dlpack(torch.from_numpy(x).t())   # not row-major contiguous
+    with pytest.raises(ValueError):
+        mt.Tensor_float.from_dlpack(object())
+    r = torch.from_dlpack(mt.Tensor_bf16(x, "cpu"))       # bf16 leaves through torch (NumPy has no bf16)
+    assert r.dtype == torch.bfloat16 and torch.equal(r, b)
+
+
+def test_ops_without_device_form_are_marked(opt):
+    ok = {n for n in dir(opt) if isinstance(getattr(opt, n), type) and getattr(getattr(opt, n), "device_ok", False)}
+    assert {"EWiseAdd", "AddScalar", "MulScalar", "Negate", "Attention", "Softmax"} <= ok
+    assert not ({"Exp", "MatMul", "Summation", "EWiseDiv", "Reshape"} & ok)

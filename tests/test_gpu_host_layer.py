@@ -106,3 +106,71 @@ def test_tensor_on_device(mods):
     g = mt.Tensor_float([2, 2], "gpu", [1, 2, 3, 4])
     assert g.resize([3, 2]).get_data() == [1, 2, 3, 4, 0, 0]
     assert mt.Tensor_int([3], "gpu", [1, 2, 3]).negative().get_data() == [-1, -2, -3]
+
+
+def test_dlpack_device_exchange_with_torch(mods):
+    import torch
+    mt, _ = mods
+    x = np.random.default_rng(1).standard_normal((4, 6, 8)).astype(np.float32)
+    t = mt.Tensor_float(x, "gpu")
+    kind, dev = t.__dlpack_device__()
+    assert kind == 2 and dev == torch.cuda.current_device()          # kDLCUDA
+    view = torch.from_dlpack(t)
+    assert view.is_cuda and view.dtype == torch.float32 and tuple(view.shape) == (4, 6, 8)
+    assert view.data_ptr() == t.data_ptr()                           # zero copy
+    assert np.array_equal(view.cpu().numpy(), x)
+    view.mul_(2.0)
+    torch.cuda.synchronize()
+    assert np.array_equal(t.numpy(), x * 2)
+    tb = mt.Tensor_bf16(x, "gpu")
+    vb = torch.from_dlpack(tb)
+    assert vb.dtype == torch.bfloat16 and torch.equal(vb.cpu(), torch.from_numpy(x).bfloat16())
+    src = torch.randn(5, 7, device="cuda").bfloat16()
+    back = mt.Tensor_bf16.from_dlpack(src)                           # device-to-device deep copy
+    assert back.get_device() == "gpu" and back.data_ptr() != src.data_ptr()
+    assert np.array_equal(back.numpy(), src.float().cpu().numpy())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_device_resident_graph_never_leaves_the_gpu(opt, oracle, mods, dtype):
+    """loss = <attention(q*2, k, v) + q - k*0.5, w> with every node's data a gpu myTensor tensor."""
+    mt, _ = mods
+    q0, k0, v0, w0 = oracle.make_inputs(61, 1, 2, 160, 160, 64)
+    if dtype == "bfloat16":
+        q0, k0, v0, w0 = (oracle.bf16_round(a) for a in (q0, k0, v0, w0))
+    q, k, v = (opt.Tensor(a, device="gpu", dtype=dtype) for a in (q0, k0, v0))
+    w = opt.Tensor(w0, device="gpu", dtype=dtype, requires_grad=False)
+    y = opt.attention(q * 2.0, k, v, causal=True) + q - k * 0.5
+    y.backward(w)
+    cls = mt.Tensor_bf16 if dtype == "bfloat16" else mt.Tensor_float
+    for node in (y, q.grad, k.grad, v.grad):
+        assert node.is_device and type(node.realize_cached_data()) is cls
+        assert node.realize_cached_data().get_device() == "gpu"
+    q2, k2, v2 = opt.Tensor(q0), opt.Tensor(k0), opt.Tensor(v0)
+    y2 = opt.attention_composed(q2 * 2.0, k2, v2, causal=True) + q2 - k2 * 0.5
+    y2.backward(opt.Tensor(w0, requires_grad=False))
+    for a, b, name in ((y, y2, "y"), (q.grad, q2.grad, "dq"), (k.grad, k2.grad, "dk"), (v.grad, v2.grad, "dv")):
+        if dtype == "float32":
+            assert oracle.rel_err(a.numpy(), b.numpy()) <= 1e-5, name
+        else:   # bf16 nodes round every intermediate; 2e-2 plus one bf16 ulp of the largest value
+            assert oracle.max_abs_err(a.numpy(), b.numpy()) <= 2e-2 + 2.0 ** -7 * np.abs(b.numpy()).max(), name
+    ones = opt.Tensor(q0, device="gpu")
+    (ones * 3.0).backward()                                          # default seed: ones on the device
+    assert ones.grad.is_device and np.array_equal(ones.grad.numpy(), np.full(q0.shape, 3.0, np.float32))
+
+
+def test_device_resident_rules_and_softmax_op(opt, oracle):
+    x0 = np.random.default_rng(5).standard_normal((6, 40)).astype(np.float32)
+    g0 = np.random.default_rng(6).standard_normal((6, 40)).astype(np.float32)
+    xd = opt.Tensor(x0, device="gpu")
+    with pytest.raises(TypeError):
+        opt.exp(xd)                                   # no device form: refuse instead of copying silently
+    with pytest.raises(TypeError):
+        xd + opt.Tensor(x0)                           # mixed residency
+    assert np.array_equal(opt.exp(xd.cpu()).numpy(), np.exp(x0))
+    for x in (xd, opt.Tensor(x0)):
+        y = opt.softmax(x)
+        y.backward(opt.Tensor(g0, device="gpu", requires_grad=False) if x.is_device else opt.Tensor(g0, requires_grad=False))
+        assert y.is_device == x.is_device and x.grad.is_device == x.is_device
+        assert oracle.rel_err(y.numpy(), oracle.softmax_rows(x0)) <= 1e-5
+        assert oracle.rel_err(x.grad.numpy(), oracle.softmax_rows_backward(x0, g0)) <= 1e-5
