@@ -372,6 +372,42 @@ def run_softmax(tt, dev, peaks):
         return {"error": str(e)}
 
 
+def run_fc(tt, dev, peaks):
+    """The projection either side of attention at config 3's size: x [B*S = 16384, H*D = 4096] bf16
+    times w [4096, 4096] (+ bias), forward and the two backward products, each 2*M*K*N flops on the
+    tcgen05 GEMM kernel.  Operands (134 MB + 34 MB + 134 MB) exceed L2."""
+    import torch
+    capi = tt.capi
+    try:
+        M, K, N = 16384, 4096, 4096
+        x = torch.randn((M, K), device=dev).to(torch.bfloat16)
+        w = (torch.randn((K, N), device=dev) / 64).to(torch.bfloat16)
+        b = torch.randn((N,), device=dev).to(torch.bfloat16)
+        dy = torch.randn((M, N), device=dev).to(torch.bfloat16)
+        y = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+        legs = {"fwd": lambda: tt.fc_forward(x, w, b, out=y),
+                "dx": lambda: tt.fc_backward(x, w, dy, need_dw=False, need_db=False),
+                "dw": lambda: tt.fc_backward(x, w, dy, need_dx=False, need_db=False)}
+        out = {"workload": f"bf16 x [{M},{K}] . w [{K},{N}] + bias"}
+        fl = 2.0 * M * K * N
+        for name, fn in legs.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            capi.profile_reset(); capi.profile_enable(True)
+            for _ in range(10):
+                fn()
+            torch.cuda.synchronize()
+            capi.profile_enable(False)
+            ms_total, n = capi.profile_read()["fc_gemm_sm100"]
+            ms = ms_total / n
+            out[name] = {"ms": ms, "bound": "tensor", "achieved": fl / ms / 1e9, "peak": peaks["bf16"],
+                         "unit": "TFLOP/s", "frac": fl / ms / 1e9 / peaks["bf16"]}
+        return out
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -381,6 +417,7 @@ def main():
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-fc", action="store_true", help="skip the fully connected layer leg at N=1")
     ap.add_argument("--no-softmax", action="store_true", help="skip the row-softmax leg at N=1")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the S=4096 side measurement at N=1")
     ap.add_argument("--e2e-steps", type=int, default=2)
@@ -418,6 +455,7 @@ def main():
                 "fwd_tflops": r3["fwd_tflops"], "pct_of_bf16_peak": r3["pct_of_bf16_peak"], "kernels": r3["kernels"]}
     decode = run_decode(tt, dev, peaks, args.decode_batch) if (rank == 0 and not args.no_decode) else None
 
+    fc = run_fc(tt, dev, peaks) if (rank == 0 and world == 1 and not args.no_fc) else None
     softmax = run_softmax(tt, dev, peaks) if (rank == 0 and world == 1 and not args.no_softmax) else None
 
     # CPU baseline: the oracle on a bounded sample of the same workload (rank 0, N = 1)
@@ -446,7 +484,7 @@ def main():
                        "parallelism": f"{world} x contiguous (batch,head) shards"},
             "fwd_tflops": main_res["fwd_tflops"], "pct_of_bf16_peak": main_res["pct_of_bf16_peak"],
             "roofline": main_res["roofline"], "kernels": main_res["kernels"], "cfg3": side, "decode": decode,
-            "softmax_rows": softmax,
+            "softmax_rows": softmax, "fc": fc,
             "cpu_baseline": cpu, "e2e": main_res["e2e"], "clocks": main_res["clocks"],
             "gpu_launches": main_res["gpu_launches"],
         }

@@ -122,6 +122,23 @@ int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k
 int tt_softmax_fwd(const void* in, void* out, int64_t rows, int32_t cols, int32_t dtype, void* stream);
 int tt_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int32_t cols, int32_t dtype, void* stream);
 
+/* ---- fully connected layer ------------------------------------------------------------------
+ * y[rows,out] = x[rows,in] . w[in,out] + bias[out]  (bias may be NULL), all row-major; replaces
+ * FcForward of src/Layers.cu:9-40 (cublasSgemm through a handle created and destroyed per call
+ * plus a rank-1 GEMM for the bias, src/Layers_kernels.cu:10-30).  tt_fc_bwd replaces FcBackward
+ * of src/Layers.cu:42-79: dx = dy . w^T, dw = x^T . dy, db = column sums of dy (db_scalar != 0:
+ * one value, the sum over all of dy, for the reference's single-value bias); each of dx, dw, db
+ * may be NULL and is then skipped.  bf16 with in % 8 == 0 and out % 8 == 0 runs the tcgen05
+ * kernel (fp32 accumulation), float and other shapes an fp32 SIMT kernel; tt_fc_path says
+ * which (1 = tensor cores).  The workspace is only needed for db. */
+int tt_fc_fwd(const void* x, const void* w, const void* bias, void* y, int64_t rows, int32_t in_features,
+              int32_t out_features, int32_t dtype, void* stream);
+size_t tt_fc_bwd_workspace_bytes(int64_t rows, int32_t in_features, int32_t out_features, int32_t dtype);
+int tt_fc_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw, void* db, int32_t db_scalar, int64_t rows,
+              int32_t in_features, int32_t out_features, int32_t dtype, void* workspace, size_t workspace_bytes,
+              void* stream);
+int tt_fc_path(int64_t rows, int32_t in_features, int32_t out_features, int32_t dtype);
+
 /* ---- host-buffer calls (what the reference's Python ops do around each native op:
  * upload NumPy -> run -> download, optimizer/operators.py:502-512) ----------------------
  * Pointers are HOST pointers (pinned memory gives the best copy rate).  Device buffers

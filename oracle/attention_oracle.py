@@ -197,6 +197,39 @@ def softmax_rows_backward(x, dy):
 
 
 # --------------------------------------------------------------------------------------
+# fully connected layer: FcForward / FcBackward (src/Layers.cu:9-79)
+# --------------------------------------------------------------------------------------
+def fc_forward(x, w, b=None):
+    """y = x w + 1 b^T for x [rows, in], w [in, out], b [out] (or a single value, broadcast to all
+    outputs): what FcForward computes with two GEMMs (src/Layers.cu:23-39), written with the
+    reference's NumPy ops: MatMul.compute (operators.py:417-418), BroadcastTo.compute (:370-371),
+    EWiseAdd.compute (:195-196).  Leading axes of x are flattened to rows as the native op does."""
+    x = np.asarray(x); w = np.asarray(w)
+    x2 = x.reshape(-1, x.shape[-1])
+    y = np.matmul(x2, w)
+    if b is not None:
+        b = np.asarray(b)
+        bv = np.broadcast_to(b.reshape(1, -1), y.shape)
+        y = y + bv
+    return y.reshape(x.shape[:-1] + (w.shape[1],))
+
+
+def fc_backward(x, w, dy, scalar_bias=False):
+    """(dx, dw, db): FcBackward (src/Layers.cu:64-78) = MatMul.gradient (operators.py:421-429) for
+    dx = dy w^T and dw = x^T dy, and the adjoint of the broadcast bias, Summation over the rows
+    (BroadcastTo.gradient, operators.py:373-380); a single-value bias receives the sum over all
+    of dy (src/Layers.cu:68-74)."""
+    x = np.asarray(x); w = np.asarray(w); dy = np.asarray(dy)
+    x2 = x.reshape(-1, x.shape[-1]); g = dy.reshape(-1, w.shape[1])
+    dx = np.matmul(g, np.swapaxes(w, -1, -2))
+    dw = np.matmul(np.swapaxes(x2, -1, -2), g)
+    db = np.sum(g, axis=0)
+    if scalar_bias:
+        db = np.sum(db, axis=0).reshape(1)
+    return dx.reshape(x.shape), dw, db
+
+
+# --------------------------------------------------------------------------------------
 # independent checks of the restatement
 # --------------------------------------------------------------------------------------
 def closed_form_f64(q, k, v, do=None, causal=False, scale=None):

@@ -40,6 +40,10 @@ SIGNATURES = {
     "tt_attn_decode_static": (c_int, [_DP, _P, _P, _P, _P, _P, _P]),
     "tt_softmax_fwd": (c_int, [_P, _P, c_int64, c_int32, c_int32, _P]),
     "tt_softmax_bwd": (c_int, [_P, _P, _P, c_int64, c_int32, c_int32, _P]),
+    "tt_fc_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int32, c_int32, c_int32, _P]),
+    "tt_fc_bwd_workspace_bytes": (c_size_t, [c_int64, c_int32, c_int32, c_int32]),
+    "tt_fc_bwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int32, c_int64, c_int32, c_int32, c_int32, _P, c_size_t, _P]),
+    "tt_fc_path": (c_int, [c_int64, c_int32, c_int32, c_int32]),
     "tt_attn_fwd_host": (c_int, [_DP, _P, _P, _P, _P, _P]),
     "tt_attn_bwd_host": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "tt_attn_decode_host": (c_int, [_DP, _P, _P, _P, _P, _P]),

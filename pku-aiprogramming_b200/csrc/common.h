@@ -25,7 +25,7 @@ inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 // Kernel families, for launch accounting and the optional per-kernel event timing.
 enum KernelId {
     K_FWD_TC = 0, K_FWD_SIMT, K_BWD_PREP, K_BWD_DKV, K_BWD_DQ, K_BWD_SIMT_DELTA, K_BWD_SIMT_DQ, K_BWD_SIMT_DKV,
-    K_DECODE, K_DECODE_MERGE, K_PROBE, K_SOFTMAX_FWD, K_SOFTMAX_BWD, K_COUNT
+    K_DECODE, K_DECODE_MERGE, K_PROBE, K_SOFTMAX_FWD, K_SOFTMAX_BWD, K_FC_GEMM, K_FC_SIMT, K_FC_COLSUM, K_COUNT
 };
 // Scoped around ONE kernel launch: counts it and, when timing is enabled, brackets it with
 // CUDA events on the launching stream.
@@ -62,6 +62,20 @@ cudaError_t umma_probe(const void* a, const void* b, const void* vt, int D, floa
 cudaError_t softmax_rows_fwd(const void* in, void* out, long long rows, int cols, int bf16, cudaStream_t st);
 cudaError_t softmax_rows_bwd(const void* y, const void* dy, void* dx, long long rows, int cols, int bf16,
                              cudaStream_t st);
+
+// --- fully connected layer: C[M,N] = op(A) op(B) (+ bias[N]), row-major, fp32 accumulation.
+//   a_mn = 0: A stored [M,K];  a_mn = 1: A stored [K,M] (the product uses its transpose)
+//   b_mn = 1: B stored [K,N];  b_mn = 0: B stored [N,K] (the product uses its transpose)
+// bf16 with 16-byte row pitches runs the tcgen05 kernel, everything else the fp32 SIMT kernel.
+bool fc_gemm_tc_supported(const void* A, const void* B, const void* C, const void* bias, long long M, int N, int K,
+                          int a_mn, int b_mn, int bf16);
+cudaError_t fc_gemm(const void* A, const void* B, void* C, const void* bias, long long M, int N, int K, int a_mn,
+                    int b_mn, int bf16, cudaStream_t st);
+// out[n] = sum over rows of X[M,N] (scalar_bias: out[0] = sum of everything); workspace of
+// fc_colsum_workspace(M, N) bytes holds the per-range partial sums.
+size_t fc_colsum_workspace(long long M, int N);
+cudaError_t fc_colsum(const void* X, void* out, long long M, int N, int bf16, int scalar_bias, void* workspace,
+                      cudaStream_t st);
 
 // --- split-KV decode (S == 1, bf16 or float)
 struct DecodePlan {

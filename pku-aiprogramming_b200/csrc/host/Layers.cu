@@ -129,6 +129,77 @@ void SoftmaxBackward(const TinyTensor<T>& output, const TinyTensor<T>& grad_outp
     raise(rc, "SoftmaxBackward");
 }
 
+namespace {
+template <typename T>
+void fc_dims(const TinyTensor<T>& input, const TinyTensor<T>& weight, const TinyTensor<T>& bias, const char* who,
+             long long& rows, int& fin, int& fout, bool& scalar_bias) {
+    require_gpu(input, who, "input"); require_gpu(weight, who, "weight"); require_gpu(bias, who, "bias");
+    if (input.shape.empty() || weight.shape.size() != 2 || input.shape.back() != weight.shape[0])
+        throw std::invalid_argument(std::string(who) + ": input [..., in] and weight [in, out] do not agree");
+    fin = weight.shape[0];
+    fout = weight.shape[1];
+    rows = fin ? (long long)(input.size / (size_t)fin) : 0;
+    scalar_bias = bias.shape.size() == 1 && bias.shape[0] == 1 && fout != 1;
+    if (!scalar_bias && bias.size != (size_t)fout)
+        throw std::invalid_argument(std::string(who) + ": bias must hold out_features values or one value");
+}
+}  // namespace
+
+template <typename T>
+void FcForward(const TinyTensor<T>& input, TinyTensor<T>& output, const TinyTensor<T>& weight, const TinyTensor<T>& bias) {
+    const char* who = "FcForward";
+    long long rows; int fin, fout; bool scalar_bias;
+    fc_dims(input, weight, bias, who, rows, fin, fout, scalar_bias);
+    std::vector<int> oshape(input.shape.begin(), input.shape.end() - 1);
+    oshape.push_back(fout);
+    if (output.device != "gpu") output.gpu();
+    output.resize(oshape);
+    const int dt = std::is_same<T, float>::value ? TT_F32 : TT_BF16;
+    int rc;
+    if (scalar_bias) {   // one value for every output: spread it, as the reference does (src/Layers.cu:29-34)
+        TinyTensor<T> b1(bias);
+        TinyTensor<T> full(std::vector<int>{fout}, "gpu");
+        full.floatks(b1.get_data_f32()[0]);
+        rc = tt_fc_fwd(input.p_data, weight.p_data, full.p_data, output.p_data, rows, fin, fout, dt, nullptr);
+        if (rc == TT_OK) rc = tt_check_device_status(nullptr);   // `full` must outlive the kernel
+    } else {
+        rc = tt_fc_fwd(input.p_data, weight.p_data, bias.p_data, output.p_data, rows, fin, fout, dt, nullptr);
+        if (rc == TT_OK) rc = tt_check_device_status(nullptr);
+    }
+    raise(rc, who);
+}
+
+template <typename T>
+void FcBackward(const TinyTensor<T>& input, const TinyTensor<T>& /*output*/, const TinyTensor<T>& weight,
+                const TinyTensor<T>& bias, TinyTensor<T>& grad_input, const TinyTensor<T>& grad_output,
+                TinyTensor<T>& grad_weight, TinyTensor<T>& grad_bias) {
+    const char* who = "FcBackward";
+    long long rows; int fin, fout; bool scalar_bias;
+    fc_dims(input, weight, bias, who, rows, fin, fout, scalar_bias);
+    require_gpu(grad_output, who, "grad_output");
+    if (grad_output.size != (size_t)rows * (size_t)fout)
+        throw std::invalid_argument(std::string(who) + ": grad_output does not match [rows, out_features]");
+    for (TinyTensor<T>* t : {&grad_input, &grad_weight, &grad_bias})
+        if (t->device != "gpu") t->gpu();
+    grad_input.resize(input.shape);
+    grad_weight.resize(weight.shape);
+    grad_bias.resize(bias.shape);
+    const int dt = std::is_same<T, float>::value ? TT_F32 : TT_BF16;
+    PoolBuffer ws(tt_fc_bwd_workspace_bytes(rows, fin, fout, dt));
+    int rc = tt_fc_bwd(input.p_data, weight.p_data, grad_output.p_data, grad_input.p_data, grad_weight.p_data,
+                       grad_bias.p_data, scalar_bias ? 1 : 0, rows, fin, fout, dt, ws.p, ws.bytes, nullptr);
+    if (rc == TT_OK) rc = tt_check_device_status(nullptr);
+    raise(rc, who);
+}
+
+#define TT_INSTANTIATE_FC(T)                                                                                          \
+    template void FcForward<T>(const TinyTensor<T>&, TinyTensor<T>&, const TinyTensor<T>&, const TinyTensor<T>&);      \
+    template void FcBackward<T>(const TinyTensor<T>&, const TinyTensor<T>&, const TinyTensor<T>&, const TinyTensor<T>&, \
+                                TinyTensor<T>&, const TinyTensor<T>&, TinyTensor<T>&, TinyTensor<T>&);
+TT_INSTANTIATE_FC(float)
+TT_INSTANTIATE_FC(__nv_bfloat16)
+#undef TT_INSTANTIATE_FC
+
 template void AttentionForward<float>(const TinyTensor<float>&, const TinyTensor<float>&, const TinyTensor<float>&,
                                       TinyTensor<float>&, TinyTensor<float>&, bool, float);
 template void AttentionForward<__nv_bfloat16>(const TinyTensor<__nv_bfloat16>&, const TinyTensor<__nv_bfloat16>&,

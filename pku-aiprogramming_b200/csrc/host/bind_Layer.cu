@@ -26,4 +26,9 @@ PYBIND11_MODULE(myLayer, m) {
           py::arg("scale") = 0.0f);
     m.def("SoftmaxForward", &SoftmaxForward<float>, py::call_guard<py::gil_scoped_release>());
     m.def("SoftmaxBackward", &SoftmaxBackward<float>, py::call_guard<py::gil_scoped_release>());
+    // argument orders of the reference's FcForward / FcBackward (src/bind_Layer.cpp:12-13 there)
+    m.def("FcForward", &FcForward<float>, py::call_guard<py::gil_scoped_release>());
+    m.def("FcBackward", &FcBackward<float>, py::call_guard<py::gil_scoped_release>());
+    m.def("FcForward_bf16", &FcForward<__nv_bfloat16>, py::call_guard<py::gil_scoped_release>());
+    m.def("FcBackward_bf16", &FcBackward<__nv_bfloat16>, py::call_guard<py::gil_scoped_release>());
 }

@@ -35,7 +35,8 @@ static std::atomic<uint64_t> g_launches{0};
 static const char* const kKernelNames[K_COUNT] = {
     "attn_fwd_sm100", "attn_fwd_simt", "attn_bwd_prep", "attn_bwd_sm100_dkv", "attn_bwd_sm100_dq",
     "attn_bwd_simt_delta", "attn_bwd_simt_dq", "attn_bwd_simt_dkv", "attn_decode", "attn_decode_merge",
-    "umma_probe", "softmax_rows_fwd", "softmax_rows_bwd"};
+    "umma_probe", "softmax_rows_fwd", "softmax_rows_bwd", "fc_gemm_sm100", "fc_gemm_simt",
+    "fc_colsum"};
 struct TimedLaunch {
     KernelId id;
     cudaEvent_t start, stop;
@@ -462,6 +463,63 @@ int tt_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int32_
     if (!dy) return fail(TT_ERR_NULL, "tt_softmax_bwd: null pointer");
     cudaError_t e = softmax_rows_bwd(y, dy, dx, rows, cols, dtype == TT_BF16, (cudaStream_t)stream);
     return e == cudaSuccess ? TT_OK : cuda_fail(e, "tt_softmax_bwd: launch");
+}
+
+static int fc_args(const char* who, int64_t rows, int32_t in_f, int32_t out_f, int32_t dtype) {
+    if (rows < 0 || in_f < 1 || out_f < 1)
+        return fail(TT_ERR_BAD_SHAPE, "%s: rows=%lld in_features=%d out_features=%d", who, (long long)rows, in_f, out_f);
+    if (rows >= (1LL << 31)) return fail(TT_ERR_BAD_SHAPE, "%s: more than 2^31-1 rows", who);
+    if (dtype != TT_F32 && dtype != TT_BF16) return fail(TT_ERR_BAD_DTYPE, "%s: dtype %d unknown", who, dtype);
+    return check_device();
+}
+int tt_fc_fwd(const void* x, const void* w, const void* bias, void* y, int64_t rows, int32_t in_features,
+              int32_t out_features, int32_t dtype, void* stream) {
+    int rc = fc_args("tt_fc_fwd", rows, in_features, out_features, dtype);
+    if (rc != TT_OK || rows == 0) return rc;
+    if (!x || !w || !y) return fail(TT_ERR_NULL, "tt_fc_fwd: null pointer");
+    cudaError_t e = fc_gemm(x, w, y, bias, rows, out_features, in_features, 0, 1, dtype == TT_BF16, (cudaStream_t)stream);
+    return e == cudaSuccess ? TT_OK : cuda_fail(e, "tt_fc_fwd: launch");
+}
+size_t tt_fc_bwd_workspace_bytes(int64_t rows, int32_t in_features, int32_t out_features, int32_t dtype) {
+    (void)in_features; (void)dtype;
+    if (rows < 1 || out_features < 1) return 0;
+    return fc_colsum_workspace(rows, out_features);
+}
+int tt_fc_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw, void* db, int32_t db_scalar, int64_t rows,
+              int32_t in_features, int32_t out_features, int32_t dtype, void* workspace, size_t workspace_bytes,
+              void* stream) {
+    int rc = fc_args("tt_fc_bwd", rows, in_features, out_features, dtype);
+    if (rc != TT_OK) return rc;
+    if (rows && (!dy || (dx && !w) || (dw && !x)))
+        return fail(TT_ERR_NULL, "tt_fc_bwd: null pointer (dy always, w for dx, x for dw)");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int bf16 = dtype == TT_BF16;
+    const size_t esz = bf16 ? 2 : 4;
+    if (rows == 0) {   // empty batch: the parameter gradients are zero
+        cudaError_t e = cudaSuccess;
+        if (dw) e = cudaMemsetAsync(dw, 0, (size_t)in_features * out_features * esz, st);
+        if (e == cudaSuccess && db) e = cudaMemsetAsync(db, 0, (db_scalar ? 1 : (size_t)out_features) * esz, st);
+        return e == cudaSuccess ? TT_OK : cuda_fail(e, "tt_fc_bwd: memset");
+    }
+    cudaError_t e = cudaSuccess;
+    // dx[rows,in] = dy[rows,out] . w[in,out]^T
+    if (dx) e = fc_gemm(dy, w, dx, nullptr, rows, in_features, out_features, 0, 0, bf16, st);
+    // dw[in,out] = x[rows,in]^T . dy[rows,out]
+    if (e == cudaSuccess && dw) e = fc_gemm(x, dy, dw, nullptr, in_features, out_features, (int)rows, 1, 1, bf16, st);
+    if (e == cudaSuccess && db) {
+        const size_t need = fc_colsum_workspace(rows, out_features);
+        if (!workspace || workspace_bytes < need)
+            return fail(TT_ERR_WORKSPACE, "tt_fc_bwd: workspace of %zu bytes needed for the bias gradient, %zu given", need,
+                        workspace_bytes);
+        e = fc_colsum(dy, db, rows, out_features, bf16, db_scalar != 0, workspace, st);
+    }
+    return e == cudaSuccess ? TT_OK : cuda_fail(e, "tt_fc_bwd: launch");
+}
+int tt_fc_path(int64_t rows, int32_t in_features, int32_t out_features, int32_t dtype) {
+    // alignment of the pointers is checked at the call; pools and torch hand out >= 256-byte alignment
+    return fc_gemm_tc_supported(nullptr, nullptr, nullptr, nullptr, rows, out_features, in_features, 0, 1, dtype == TT_BF16) &&
+                   fc_gemm_tc_supported(nullptr, nullptr, nullptr, nullptr, in_features, out_features, (int)rows, 1, 1, dtype == TT_BF16)
+               ? 1 : 0;
 }
 
 int tt_debug_wait_timeout(int64_t budget_cycles, void* stream) {

@@ -124,6 +124,43 @@ def softmax_backward(y, dy, dx=None):
     return dx
 
 
+def _fc_check(x, w):
+    if not (x.is_cuda and w.is_cuda and x.is_contiguous() and w.is_contiguous()) or x.dtype != w.dtype \
+            or x.dtype not in _DT or w.dim() != 2 or x.dim() < 1 or x.shape[-1] != w.shape[0]:
+        raise ValueError("fc takes contiguous CUDA tensors x [..., in] and w [in, out] of one dtype (float32/bfloat16)")
+    return x.numel() // x.shape[-1] if x.shape[-1] else 0, w.shape[0], w.shape[1]
+
+
+def fc_forward(x, w, bias=None, out=None):
+    """y = x @ w + bias for x `[..., in]`, w `[in, out]`, bias `[out]` or None."""
+    rows, fin, fout = _fc_check(x, w)
+    if bias is not None and (bias.dtype != x.dtype or tuple(bias.shape) != (fout,) or not bias.is_cuda):
+        raise ValueError(f"bias must be a CUDA tensor of shape ({fout},) and dtype {x.dtype}")
+    with torch.cuda.device(x.device):
+        if out is None:
+            out = torch.empty(tuple(x.shape[:-1]) + (fout,), dtype=x.dtype, device=x.device)
+        capi.check(capi.lib.tt_fc_fwd(_p(x), _p(w), _p(bias), _p(out), rows, fin, fout, _DT[x.dtype], _stream_ptr(x)))
+    return out
+
+
+def fc_backward(x, w, dy, need_dx=True, need_dw=True, need_db=True, scalar_bias=False, workspace=None):
+    """(dx, dw, db) of `fc_forward` for upstream gradient dy `[..., out]`; skipped ones are None."""
+    rows, fin, fout = _fc_check(x, w)
+    if dy.dtype != x.dtype or not dy.is_cuda or not dy.is_contiguous() or tuple(dy.shape) != tuple(x.shape[:-1]) + (fout,):
+        raise ValueError("dy must be a contiguous CUDA tensor shaped like the layer's output")
+    with torch.cuda.device(x.device):
+        dx = torch.empty_like(x) if need_dx else None
+        dw = torch.empty_like(w) if need_dw else None
+        db = torch.empty((1 if scalar_bias else fout,), dtype=x.dtype, device=x.device) if need_db else None
+        need = int(capi.lib.tt_fc_bwd_workspace_bytes(rows, fin, fout, _DT[x.dtype])) if need_db else 0
+        if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+            workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+        nbytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+        capi.check(capi.lib.tt_fc_bwd(_p(x), _p(w), _p(dy), _p(dx), _p(dw), _p(db), int(bool(scalar_bias)), rows, fin, fout,
+                                      _DT[x.dtype], _p(workspace), nbytes, _stream_ptr(x)))
+    return dx, dw, db
+
+
 def check_device_status(device=None):
     """Synchronises the current stream and raises if a bounded device-side wait expired."""
     with torch.cuda.device(device if device is not None else torch.cuda.current_device()):

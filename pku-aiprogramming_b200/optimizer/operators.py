@@ -516,6 +516,61 @@ def softmax(x):
     return Softmax()(x)
 
 
+class FC(TensorOp):
+    """`input @ weight + bias` on the GPU (`myLayer.FcForward` / `FcBackward`), the reference's
+    `FC` op (operators.py:498-532 there: same constructor flag, same three inputs, bias of shape
+    `[out]` or `[1]`).  NumPy-backed inputs are uploaded (`dtype` picks float32 or bf16 kernels)
+    and results downloaded; device-resident inputs (all `Tensor_float` or all `Tensor_bf16`) stay
+    on the GPU, as do the three gradients."""
+    device_ok = True
+
+    def __init__(self, use_bias=True, dtype: str = "float32"):
+        if dtype not in ("float32", "bfloat16"):
+            raise ValueError("dtype must be 'float32' or 'bfloat16'")
+        self.use_bias, self.dtype = bool(use_bias), dtype
+        self._saved = None
+
+    def _pick(self, resident, sample):
+        mt, ml = _native()
+        bf16 = (type(sample).__name__ == "Tensor_bf16") if resident else self.dtype == "bfloat16"
+        return (mt.Tensor_bf16, ml.FcForward_bf16, ml.FcBackward_bf16) if bf16 else (mt.Tensor_float, ml.FcForward, ml.FcBackward)
+
+    def compute(self, x, w, b):
+        resident = _all_or_none_on_device(x, w, b)
+        T, fwd, _ = self._pick(resident, x)
+        if resident and not (type(x) is type(w) is type(b) is T):
+            raise TypeError("device-resident input, weight and bias must share one tensor class")
+        up = (lambda a: a) if resident else (lambda a: T(np.ascontiguousarray(a, dtype=np.float32), "gpu"))
+        tx, tw, tb = up(x), up(w), up(b)
+        if not self.use_bias:
+            tb = T(tb)
+            tb.zeros()
+        out = T([1], "gpu")
+        fwd(tx, out, tw, tb)
+        self._saved = (tx, tw, tb, out, resident)
+        return out if resident else out.numpy().astype(x.dtype, copy=False)
+
+    def gradient(self, out_grad, node):
+        if self._saved is None:
+            node.realize_cached_data()
+        tx, tw, tb, out, resident = self._saved
+        T, _, bwd = self._pick(True, tx)
+        g = out_grad.realize_cached_data()
+        tg = g if _on_device(g) else T(np.ascontiguousarray(g, dtype=np.float32), "gpu")
+        gx, gw, gb = T([1], "gpu"), T([1], "gpu"), T([1], "gpu")
+        bwd(tx, out, tw, tb, gx, tg, gw, gb)
+        if not self.use_bias:
+            gb.zeros()
+        if resident:
+            return tuple(Tensor(t, device="gpu", requires_grad=False) for t in (gx, gw, gb))
+        dt = node.inputs[0].dtype
+        return tuple(Tensor(t.numpy().astype(dt, copy=False), requires_grad=False) for t in (gx, gw, gb))
+
+
+def fc(input, weight, bias, use_bias=True, dtype: str = "float32"):
+    return FC(use_bias, dtype)(input, weight, bias)
+
+
 def attention(q, k, v, causal: bool = False, scale: Optional[float] = None, dtype: str = "float32"):
     return Attention(causal, scale, dtype)(q, k, v)
 

@@ -97,6 +97,22 @@ def reference_softmax(ops, x, dy):
     return y, X.grad.numpy().reshape(x.shape)
 
 
+# name, rows, in_features, out_features, seed  (fully connected layer, see oracle.fc_forward)
+FC_CASES = [
+    ("fc_32x784x100", 32, 784, 100, 30),       # the first layer of the reference's MNIST model
+    ("fc_7x10x3", 7, 10, 3, 31),
+    ("fc_130x72x264", 130, 72, 264, 32),       # crosses the 128-row and 256-column tile edges
+]
+
+
+def reference_fc(ops, x, w, b, dy):
+    """y = x @ w + broadcast(b) with the reference's ops and its reverse sweep for the gradients."""
+    X, W, Bv = ops.Tensor(x), ops.Tensor(w), ops.Tensor(b)
+    Y = X @ W + ops.broadcast_to(ops.reshape(Bv, (1, b.shape[0])), (x.shape[0], w.shape[1]))
+    Y.backward(ops.Tensor(dy, requires_grad=False))
+    return Y.numpy(), X.grad.numpy(), W.grad.numpy(), Bv.grad.numpy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -113,6 +129,18 @@ def main():
                  causal=np.int32(causal), scale=np.float32(scale), seed=np.int32(seed),
                  sigma=np.float32(sigma))
         print(f"{name}: wrote {os.path.getsize(path)/1024:.0f} KiB  |O|max={np.abs(o).max():.4f}")
+    os.makedirs(os.path.join(HERE, "fc"), exist_ok=True)
+    for name, rows, fin, fout, seed in FC_CASES:
+        rng = np.random.Generator(np.random.PCG64([seed, rows]))
+        x = rng.standard_normal((rows, fin)).astype(np.float32)
+        w = (rng.standard_normal((fin, fout)) / np.sqrt(fin)).astype(np.float32)
+        b = rng.standard_normal((fout,)).astype(np.float32)
+        dy = rng.standard_normal((rows, fout)).astype(np.float32)
+        y, dx, dw, db = reference_fc(ops, x, w, b, dy)
+        assert all(t.dtype == np.float32 for t in (y, dx, dw, db)) and db.shape == (fout,)
+        path = os.path.join(HERE, "fc", name + ".npz")
+        np.savez(path, x=x, w=w, b=b, dy=dy, y=y, dx=dx, dw=dw, db=db)
+        print(f"fc/{name}: wrote {os.path.getsize(path)/1024:.0f} KiB")
     os.makedirs(os.path.join(HERE, "softmax_rows"), exist_ok=True)
     for name, lead, cols, sigma, seed in SOFTMAX_CASES:
         rng = np.random.Generator(np.random.PCG64([seed, cols]))

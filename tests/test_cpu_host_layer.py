@@ -38,7 +38,7 @@ def test_module_surface(mods):
         for m in methods:
             assert hasattr(getattr(mt, cls), m), (cls, m)
     for fn in ("AttentionForward", "AttentionBackward", "AttentionForward_bf16", "AttentionBackward_bf16",
-               "SoftmaxForward", "SoftmaxBackward"):
+               "SoftmaxForward", "SoftmaxBackward", "FcForward", "FcBackward", "FcForward_bf16", "FcBackward_bf16"):
         assert hasattr(ml, fn)
 
 
@@ -161,5 +161,5 @@ def test_dlpack_import_copies_and_validates(mods):
 
 def test_ops_without_device_form_are_marked(opt):
     ok = {n for n in dir(opt) if isinstance(getattr(opt, n), type) and getattr(getattr(opt, n), "device_ok", False)}
-    assert {"EWiseAdd", "AddScalar", "MulScalar", "Negate", "Attention", "Softmax"} <= ok
+    assert {"EWiseAdd", "AddScalar", "MulScalar", "Negate", "Attention", "Softmax", "FC"} <= ok
     assert not ({"Exp", "MatMul", "Summation", "EWiseDiv", "Reshape"} & ok)

@@ -111,3 +111,17 @@ def test_softmax_oracle_reproduces_reference_bit_exactly(oracle, path):
     y = g["y"].astype(np.float64); dy = g["dy"].astype(np.float64)
     want = y * (dy - np.sum(dy * y, axis=-1, keepdims=True))
     assert len(SOFTMAX_GOLDEN) >= 4 and oracle.rel_err(g["dx"], want) < 2e-6
+
+
+FC_GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "fc", "*.npz")))
+
+
+@pytest.mark.parametrize("path", FC_GOLDEN, ids=[os.path.basename(p)[:-4] for p in FC_GOLDEN])
+def test_fc_oracle_reproduces_reference_bit_exactly(oracle, path):
+    g = np.load(path)
+    assert np.array_equal(oracle.fc_forward(g["x"], g["w"], g["b"]), g["y"])
+    dx, dw, db = oracle.fc_backward(g["x"], g["w"], g["dy"])
+    assert np.array_equal(dx, g["dx"]) and np.array_equal(dw, g["dw"]) and np.array_equal(db, g["db"])
+    assert len(FC_GOLDEN) >= 3
+    _, _, db1 = oracle.fc_backward(g["x"], g["w"], g["dy"], scalar_bias=True)
+    assert db1.shape == (1,) and abs(float(db1[0]) - float(g["dy"].astype(np.float64).sum())) < 1e-3 * g["dy"].size ** 0.5

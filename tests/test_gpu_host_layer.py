@@ -174,3 +174,34 @@ def test_device_resident_rules_and_softmax_op(opt, oracle):
         assert y.is_device == x.is_device and x.grad.is_device == x.is_device
         assert oracle.rel_err(y.numpy(), oracle.softmax_rows(x0)) <= 1e-5
         assert oracle.rel_err(x.grad.numpy(), oracle.softmax_rows_backward(x0, g0)) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_fc_op_numpy_and_device_resident(opt, oracle, mods, dtype):
+    """The reference's FC op (input, weight, bias; bias [out] or [1]) through myLayer.FcForward/FcBackward."""
+    rng = np.random.default_rng(12)
+    x0 = rng.standard_normal((48, 72)).astype(np.float32)
+    w0 = (rng.standard_normal((72, 40)) / 8).astype(np.float32)
+    b0 = rng.standard_normal(40).astype(np.float32)
+    g0 = rng.standard_normal((48, 40)).astype(np.float32)
+    if dtype == "bfloat16":
+        x0, w0, b0, g0 = (oracle.bf16_round(a) for a in (x0, w0, b0, g0))
+    ok = (lambda a, b: oracle.rel_err(a, b) <= 1e-5) if dtype == "float32" else \
+         (lambda a, b: oracle.max_abs_err(a, b) <= 2.0 ** -8 * np.abs(b).max() + 1e-3)
+    dx_r, dw_r, db_r = oracle.fc_backward(x0, w0, g0)
+    for resident in (False, True):
+        kw = dict(device="gpu", dtype=dtype) if resident else {}
+        x, w, b = opt.Tensor(x0, **kw), opt.Tensor(w0, **kw), opt.Tensor(b0, **kw)
+        y = opt.fc(x, w, b, dtype=dtype)
+        y.backward(opt.Tensor(g0, requires_grad=False, **kw))
+        assert y.is_device == resident and x.grad.is_device == resident
+        assert ok(y.numpy(), oracle.fc_forward(x0, w0, b0))
+        assert ok(x.grad.numpy(), dx_r) and ok(w.grad.numpy(), dw_r) and ok(b.grad.numpy(), db_r)
+    # single-value bias and use_bias=False, the two special cases of the reference op
+    x, w, b1 = opt.Tensor(x0), opt.Tensor(w0), opt.Tensor(np.array([0.5], np.float32))
+    y = opt.fc(x, w, b1, dtype=dtype)
+    y.backward(opt.Tensor(g0, requires_grad=False))
+    assert ok(y.numpy(), oracle.fc_forward(x0, w0, np.full(40, 0.5, np.float32)))
+    assert b1.grad.shape == (1,) and ok(b1.grad.numpy(), oracle.fc_backward(x0, w0, g0, scalar_bias=True)[2])
+    y = opt.fc(opt.Tensor(x0), opt.Tensor(w0), opt.Tensor(b0), use_bias=False, dtype=dtype)
+    assert ok(y.numpy(), oracle.fc_forward(x0, w0))
