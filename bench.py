@@ -343,14 +343,14 @@ def run_decode(tt, dev, peaks, batch):
         return {"error": str(e)}
 
 
-def run_softmax(tt, dev, peaks):
+def run_softmax(tt, dev, peaks, rows=262144):
     """Row softmax forward and backward on a score-matrix sized input (HBM-bound): fp32
     [262144, 1024] = 1 GiB per tensor, far above L2.  Algorithmic bytes: forward reads x and
     writes y (8 B per element), backward reads y, dy and writes dx (12 B per element)."""
     import torch
     capi = tt.capi
     try:
-        rows, cols = 262144, 1024
+        cols = 1024
         x = torch.randn((rows, cols), device=dev)
         y, dy, dx = torch.empty_like(x), torch.randn((rows, cols), device=dev), torch.empty_like(x)
         for _ in range(3):
@@ -372,14 +372,14 @@ def run_softmax(tt, dev, peaks):
         return {"error": str(e)}
 
 
-def run_fc(tt, dev, peaks):
+def run_fc(tt, dev, peaks, M=16384):
     """The projection either side of attention at config 3's size: x [B*S = 16384, H*D = 4096] bf16
     times w [4096, 4096] (+ bias), forward and the two backward products, each 2*M*K*N flops on the
     tcgen05 GEMM kernel.  Operands (134 MB + 34 MB + 134 MB) exceed L2."""
     import torch
     capi = tt.capi
     try:
-        M, K, N = 16384, 4096, 4096
+        K, N = 4096, 4096
         x = torch.randn((M, K), device=dev).to(torch.bfloat16)
         w = (torch.randn((K, N), device=dev) / 64).to(torch.bfloat16)
         b = torch.randn((N,), device=dev).to(torch.bfloat16)
@@ -417,6 +417,10 @@ def main():
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--only", choices=["softmax", "fc"], help="run just this side leg and print its block "
+                    "(used for profiler captures of that kernel; not the benchmark line)")
+    ap.add_argument("--fc-rows", type=int, default=16384, help="rows of x in the fully connected leg")
+    ap.add_argument("--softmax-rows", type=int, default=262144, help="rows of the row-softmax leg")
     ap.add_argument("--no-fc", action="store_true", help="skip the fully connected layer leg at N=1")
     ap.add_argument("--no-softmax", action="store_true", help="skip the row-softmax leg at N=1")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the S=4096 side measurement at N=1")
@@ -445,6 +449,12 @@ def main():
     tt = importlib.import_module("pku-aiprogramming_b200")
     peaks = load_peaks()
 
+    if args.only:
+        if rank == 0:
+            res = run_fc(tt, dev, peaks, args.fc_rows) if args.only == "fc" else run_softmax(tt, dev, peaks, args.softmax_rows)
+            print(json.dumps({"leg": args.only, "result": res}), flush=True)
+        return
+
     main_res = run_workload(tt, args.workload, args.steps, args.warmup, world, rank, dev, peaks, args.e2e_steps,
                             sample_clocks=(rank == 0))
     side = None
@@ -455,8 +465,8 @@ def main():
                 "fwd_tflops": r3["fwd_tflops"], "pct_of_bf16_peak": r3["pct_of_bf16_peak"], "kernels": r3["kernels"]}
     decode = run_decode(tt, dev, peaks, args.decode_batch) if (rank == 0 and not args.no_decode) else None
 
-    fc = run_fc(tt, dev, peaks) if (rank == 0 and world == 1 and not args.no_fc) else None
-    softmax = run_softmax(tt, dev, peaks) if (rank == 0 and world == 1 and not args.no_softmax) else None
+    fc = run_fc(tt, dev, peaks, args.fc_rows) if (rank == 0 and world == 1 and not args.no_fc) else None
+    softmax = run_softmax(tt, dev, peaks, args.softmax_rows) if (rank == 0 and world == 1 and not args.no_softmax) else None
 
     # CPU baseline: the oracle on a bounded sample of the same workload (rank 0, N = 1)
     cpu = None
