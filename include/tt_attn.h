@@ -57,6 +57,10 @@ typedef struct tt_attn_desc {
     int32_t dtype;    /* tt_dtype of q,k,v,out and gradients */
     int32_t causal;   /* 0 / 1 */
     float scale;      /* <= 0 -> 1/sqrt(D) */
+    int32_t Hkv;      /* key/value heads; 0 or H: one per query head.  Hkv < H (H % Hkv == 0) is grouped
+                       * (GQA / MQA) attention: k, v, dk, dv are [B,Hkv,L,D] and query head h reads
+                       * key/value head h / (H/Hkv); dk, dv are summed over the group.  No counterpart
+                       * in the reference. */
 } tt_attn_desc;
 
 /* ---- forward -------------------------------------------------------------------------
@@ -111,6 +115,21 @@ int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const
  *     serialise them. */
 int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
                           void* out, float* lse, void* stream);
+
+/* ---- decode over a paged and/or ragged key/value cache -----------------------------------
+ * tt_attn_decode for serving-style caches (no counterpart in the reference).  bf16, D = 64 or
+ * 128, S = 1; desc->L is the longest sequence any batch entry may have.
+ *   block_table != NULL: k_pool, v_pool are page pools [pages, Hkv, page_size, D]; key r of batch
+ *       entry b is row r % page_size of page block_table[b * max_pages + r / page_size]
+ *       (device array of B * max_pages int32); page_size * max_pages >= L.
+ *   block_table == NULL: k_pool, v_pool are dense [B, Hkv, L, D] as in tt_attn_decode.
+ *   seq_lens != NULL: device array of B int32, batch entry b attends to its first seq_lens[b]
+ *       keys (clamped to 0..L); an entry with no keys gets out = 0 and lse = -inf.
+ * Grouped heads (desc->Hkv < H) read each key/value row once for the whole group when the group
+ * size is 2, 4 or 8.  Workspace: tt_attn_decode_workspace_bytes(desc). */
+int tt_attn_decode_paged(const tt_attn_desc* desc, const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_table, const int32_t* seq_lens, int32_t page_size, int32_t max_pages,
+                         void* out, float* lse, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- row softmax ------------------------------------------------------------------------
  * out[r,:] = softmax(in[r,:]) over `cols`, row maximum subtracted; rows = product of the leading

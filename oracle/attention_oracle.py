@@ -166,6 +166,33 @@ def attention_backward(q, k, v, do, causal=False, scale=None):
 
 
 # --------------------------------------------------------------------------------------
+# grouped heads (GQA / MQA): an extension without a counterpart in the reference, defined through
+# its ops -- each key/value head is broadcast to the query heads of its group (BroadcastTo.compute,
+# operators.py:370-371) and the gradients of the copies are summed (BroadcastTo.gradient :373-380)
+# --------------------------------------------------------------------------------------
+def expand_kv_heads(x, H):
+    """`[B,Hkv,L,D]` -> `[B,H,L,D]`: query head h reads key/value head h // (H // Hkv)."""
+    x = np.asarray(x)
+    B, Hkv, L, D = x.shape
+    g = H // Hkv
+    return np.ascontiguousarray(np.broadcast_to(x.reshape(B, Hkv, 1, L, D), (B, Hkv, g, L, D))).reshape(B, H, L, D)
+
+
+def reduce_kv_heads(dx, Hkv):
+    """Adjoint of `expand_kv_heads`: sums the gradients of the copies of each key/value head."""
+    dx = np.asarray(dx)
+    B, H, L, D = dx.shape
+    return np.sum(dx.reshape(B, Hkv, H // Hkv, L, D), axis=2)
+
+
+def attention_backward_grouped(q, k, v, do, causal=False, scale=None):
+    """`attention_backward` for k, v with fewer heads than q."""
+    H, Hkv = q.shape[1], k.shape[1]
+    o, lse, dq, dk, dv = attention_backward(q, expand_kv_heads(k, H), expand_kv_heads(v, H), do, causal, scale)
+    return o, lse, dq, reduce_kv_heads(dk, Hkv), reduce_kv_heads(dv, Hkv)
+
+
+# --------------------------------------------------------------------------------------
 # row softmax: the adjacent native op (SoftmaxForward, src/Layers.cu:324-349)
 # --------------------------------------------------------------------------------------
 def softmax_rows(x):

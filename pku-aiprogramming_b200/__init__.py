@@ -11,5 +11,5 @@ from .capi import TTError, NativeLibraryMissing, shard_range, launch_count  # no
 from .functional import (  # noqa: F401
     attention_forward, attention_backward, attention_decode, decode_workspace_bytes,
     attention_forward_host, attention_backward_host, attention_decode_host, attention_step_host,
-    check_device_status, softmax_forward, softmax_backward, fc_forward, fc_backward,
+    check_device_status, softmax_forward, softmax_backward, fc_forward, fc_backward, attention_decode_paged,
 )

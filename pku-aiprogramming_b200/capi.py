@@ -26,7 +26,7 @@ STATUS_NAMES = {
 # every symbol include/tt_attn.h declares: name -> (restype, argtypes)
 class Desc(ctypes.Structure):
     _fields_ = [("B", c_int32), ("H", c_int32), ("S", c_int32), ("L", c_int32), ("D", c_int32),
-                ("dtype", c_int32), ("causal", c_int32), ("scale", c_float)]
+                ("dtype", c_int32), ("causal", c_int32), ("scale", c_float), ("Hkv", c_int32)]
 
 
 _P = c_void_p
@@ -37,6 +37,7 @@ SIGNATURES = {
     "tt_attn_bwd": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
     "tt_attn_decode_workspace_bytes": (c_size_t, [_DP]),
     "tt_attn_decode": (c_int, [_DP, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
+    "tt_attn_decode_paged": (c_int, [_DP, _P, _P, _P, _P, _P, c_int32, c_int32, _P, _P, _P, c_size_t, _P]),
     "tt_attn_decode_static": (c_int, [_DP, _P, _P, _P, _P, _P, _P]),
     "tt_softmax_fwd": (c_int, [_P, _P, c_int64, c_int32, c_int32, _P]),
     "tt_softmax_bwd": (c_int, [_P, _P, _P, c_int64, c_int32, c_int32, _P]),
@@ -110,9 +111,9 @@ def check(rc: int) -> None:
         raise TTError(code, last_error())
 
 
-def make_desc(B, H, S, L, D, dtype, causal=False, scale=None) -> Desc:
+def make_desc(B, H, S, L, D, dtype, causal=False, scale=None, Hkv=None) -> Desc:
     return Desc(int(B), int(H), int(S), int(L), int(D), int(dtype), 1 if causal else 0,
-                float(scale) if scale is not None else 0.0)
+                float(scale) if scale is not None else 0.0, int(Hkv) if Hkv else 0)
 
 
 def shard_range(n_slices: int, world: int, rank: int):

@@ -57,7 +57,8 @@ struct BwdParams {
     float scale, scale_log2;
     unsigned int* status;
     unsigned int* sched_counter;   // zero at launch; work items are taken with atomicAdd
-    int n_items;                   // slices * n_tiles
+    int n_items;                   // resident slices * n_tiles
+    int group;                     // query heads per key/value head (1 = ordinary multi-head attention)
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
 };
@@ -78,9 +79,27 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 // Persistent like the forward: one CTA per SM takes (slice, resident tile) items from a global
 // counter, heavy items of a slice first; the loader runs up to two items ahead and the first
 // MMAs of the next item overlap the write-out of the accumulators of the current one.
+// With grouped heads (group g > 1) query slice bh reads key/value slice bh / g.  The dQ pass keeps
+// one query slice resident and streams its key/value slice; the dK/dV pass keeps one key/value
+// slice resident and streams the query tiles of its g query heads one head after the other into
+// the same accumulators, which is the sum over the group that dK and dV are.
 struct BwdItem {
-    int bh, r0, t_begin, t_end;
+    int bh;        // resident slice (key/value slice when keys are resident, query slice otherwise)
+    int r0, t_begin, t_end;
+    int nt;        // streamed tiles per streamed slice
+    int n_it;      // streamed tiles of the item (nt x group when keys are resident)
 };
+template <bool kKeysResident>
+__device__ __forceinline__ void bwd_stream_tile(const BwdItem& w, int u, int group, int& t, int& slice) {
+    if (kKeysResident) {
+        const int hh = u / w.nt;
+        t = w.t_begin + (u - hh * w.nt);
+        slice = w.bh * group + hh;
+    } else {
+        t = w.t_begin + u;
+        slice = w.bh / group;
+    }
+}
 template <bool kKeysResident>
 __device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p) {
     BwdItem w;
@@ -98,6 +117,8 @@ __device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p)
         w.t_end = p.causal ? min(n_kv, ((min(rt * 128 + 127, p.S - 1) + off) >> 7) + 1) : n_kv;
     }
     w.r0 = rt * 128;   // first resident row (key or query index)
+    w.nt = max(0, w.t_end - w.t_begin);
+    w.n_it = kKeysResident ? w.nt * p.group : w.nt;
     return w;
 }
 
@@ -208,15 +229,19 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             }
             // per-column statistics (keys resident): thread ctid fetches -lse2 (ctid < 128) or -delta
             // of streamed query (ctid & 127), one tile ahead of its use
-            const float* stat_src = (ctid < 128 ? p.lse2 : p.delta) + (long long)bh * p.S;
+            const float* stat_src = (ctid < 128 ? p.lse2 : p.delta);
             const float stat_oob = (ctid < 128) ? -INFINITY : 0.f;
+            auto stat_fetch = [&](int u) -> float {   // statistic of streamed query (ctid & 127) of streamed tile u
+                int tt, qs;
+                bwd_stream_tile<kKeysResident>(w, u, p.group, tt, qs);
+                const int qrow = tt * 128 + (ctid & 127);
+                return qrow < p.S ? -stat_src[(long long)qs * p.S + qrow] : stat_oob;
+            };
             float stat_next = stat_oob;
-            if (kKeysResident) {
-                const int qrow = w.t_begin * 128 + (ctid & 127);
-                stat_next = qrow < p.S ? -stat_src[qrow] : stat_oob;
-            }
-            for (int t = w.t_begin; t < w.t_end; ++t, ++git) {
-                const int it = t - w.t_begin;
+            if (kKeysResident && w.n_it > 0) stat_next = stat_fetch(0);
+            for (int u = 0; u < w.n_it; ++u, ++git) {
+                const int it = u;
+                const int t = kKeysResident ? w.t_begin + u % w.nt : w.t_begin + u;
                 const bool tr = (k == 0 && wq == 0 && lane == 0);
                 const int c0 = t * 128;                            // first streamed row of this tile
                 if (tr) TT_BTRACE(wg, it, 0);
@@ -225,10 +250,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 if (kKeysResident) {
                     s_stat[(git & 1) * 256 + ctid] = stat_next;
                     named_bar_sync(1, 256);
-                    if (t + 1 < w.t_end) {
-                        const int qrow = (t + 1) * 128 + (ctid & 127);
-                        stat_next = qrow < p.S ? -stat_src[qrow] : stat_oob;
-                    }
+                    if (u + 1 < w.n_it) stat_next = stat_fetch(u + 1);
                 }
                 // visible columns of this thread's row inside the tile: [vis_lo, vis_hi)
                 int vis_lo = 0, vis_hi = 128;
@@ -394,15 +416,17 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                     load_tile(sR + Cfg::kTileBytes, &tmR1, bar_res_full, w.r0, w.bh);
                 }
                 __syncwarp();
-                for (int t = w.t_begin; t < w.t_end; ++t, ++git) {
+                for (int u = 0; u < w.n_it; ++u, ++git) {
                     const int st = git % kStages;
+                    int t, ts;
+                    bwd_stream_tile<kKeysResident>(w, u, p.group, t, ts);
                     mbar_wait(&bar_st_empty[st], ((git / kStages) & 1) ^ 1, wctx, BB_STEMPTY + st, (int)git);
                     __syncwarp();
                     if (elect_one()) {
                         mbar_arrive_expect_tx(&bar_st_full[st], 2 * Cfg::kTileBytes);
                         unsigned char* dst = sT + st * 2 * Cfg::kTileBytes;
-                        load_tile(dst, &tmT0, &bar_st_full[st], t * 128, w.bh);
-                        load_tile(dst + Cfg::kTileBytes, &tmT1, &bar_st_full[st], t * 128, w.bh);
+                        load_tile(dst, &tmT0, &bar_st_full[st], t * 128, ts);
+                        load_tile(dst + Cfg::kTileBytes, &tmT1, &bar_st_full[st], t * 128, ts);
                     }
                     __syncwarp();
                 }
@@ -447,7 +471,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 __syncwarp();
                 if (item < 0) break;
                 const BwdItem w = bwd_decode_item<kKeysResident>(item, p);
-                const int n_it = w.t_end - w.t_begin;
+                const int n_it = w.n_it;
                 mbar_wait(bar_res_full, k & 1, wctx, BB_RES, k);
                 __syncwarp();
                 if (n_it > 0) {
@@ -583,8 +607,8 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     TmapStorage tq, tk, tv, tdo;
     const char* why = nullptr;
     if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
-    if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH, 128, &why)) return cudaErrorInvalidValue;
-    if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tdo, a.dout, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
     auto M = [](TmapStorage& t) -> CUtensorMap& { return *reinterpret_cast<CUtensorMap*>(t.bytes); };
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, true, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -609,8 +633,9 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     p.out0 = (__nv_bfloat16*)a.dv;
     p.out1 = (__nv_bfloat16*)a.dk;
+    p.group = a.group;
     p.n_tiles = (a.L + 127) / 128;
-    p.n_items = (int)(a.BH * p.n_tiles);
+    p.n_items = (int)(a.BH / a.group * p.n_tiles);
     p.sched_counter = next_bwd_sched_counter(st, &e);
     if (e != cudaSuccess) return e;
     {

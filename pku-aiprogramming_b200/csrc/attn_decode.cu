@@ -13,6 +13,8 @@
 //   - lanes/warps of a CTA are merged through shared memory; with more than one key range
 //     per slice the unnormalised (max, sum, out) partials go to the workspace and a small
 //     second kernel merges them.
+#include <stdlib.h>
+
 #include "common.h"
 #include <atomic>
 
@@ -66,148 +68,198 @@ __device__ __forceinline__ void merge_state(float& m, float& l, float (&o)[8], f
     m = mn;
 }
 
-// partial layout in the workspace, per unit: [m, l, o[D]] floats
-template <int D>
-__global__ void __launch_bounds__(kDecThreads, 4)
+// Where the key/value rows of a (batch, key/value head) slice live, and how many of them count.
+//   dense:  k, v are [slices, L, D]                           (block_table == nullptr)
+//   paged:  k, v are page pools [pages, hkv, page_size, D]; row r of batch entry b is in page
+//           block_table[b * max_pages + r / page_size] at row r % page_size
+//   seq_lens (optional): batch entry b has seq_lens[b] <= L keys; the rest is ignored
+struct DecodeRows {
+    const int* block_table;
+    const int* seq_lens;
+    int page_size, max_pages, hkv;
+};
+
+// partial layout in the workspace, per (unit, query head of the group): [m, l, o[D]] floats
+//
+// One CTA = one (key/value slice, key range) unit.  With grouped heads (G query heads share a
+// key/value head) the CTA scores its rows against all G queries, so K and V cross HBM once for
+// the whole group.  kMap: the generic fallback for group sizes without an instantiation -- one
+// query per CTA, key/value slice = query slice / group (the group's CTAs are neighbours in the
+// grid, so the re-reads mostly hit L2).
+template <int D, int G>
+__global__ void __launch_bounds__(kDecThreads, (G == 1 ? 4 : (G <= 4 ? 2 : 1)))
 attn_decode_bf16_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                         const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ lse, float* __restrict__ partial, int L, int splits, int chunk,
-                        float scale_log2) {
+                        float scale_log2, int map_group, DecodeRows rows) {
     constexpr int LPR = D / 8;        // lanes per key row
     constexpr int RPI = 32 / LPR;     // rows per warp load instruction
-    __shared__ float sm_m[kDecWarps], sm_l[kDecWarps];
-    __shared__ float sm_o[kDecWarps][D];
+    __shared__ float sm_m[G][kDecWarps], sm_l[G][kDecWarps];
+    __shared__ float sm_o[G][kDecWarps][D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane / LPR, seg = lane % LPR;
     const long long unit = blockIdx.x;
-    const long long bh = unit / splits;
-    const int split = (int)(unit - bh * splits);
+    const long long slice = unit / splits;                 // query slice when G == 1, key/value slice otherwise
+    const int split = (int)(unit - slice * splits);
+    const long long kvs = (G == 1) ? slice / map_group : slice;
+    const long long q0 = (G == 1) ? slice : slice * G;     // first query slice of this CTA
+    const int b = (int)(kvs / rows.hkv), hk = (int)(kvs % rows.hkv);
+    const int Lb = rows.seq_lens ? min(L, max(0, rows.seq_lens[b])) : L;
     const int k0 = split * chunk;
-    const int k1 = min(L, k0 + chunk);
+    const int k1 = min(Lb, k0 + chunk);
 
-    float qf[8];
-    {
-        uint4 qv = *reinterpret_cast<const uint4*>(q + bh * D + seg * 8);
-        qf[0] = bf_lo(qv.x) * scale_log2; qf[1] = bf_hi(qv.x) * scale_log2;
-        qf[2] = bf_lo(qv.y) * scale_log2; qf[3] = bf_hi(qv.y) * scale_log2;
-        qf[4] = bf_lo(qv.z) * scale_log2; qf[5] = bf_hi(qv.z) * scale_log2;
-        qf[6] = bf_lo(qv.w) * scale_log2; qf[7] = bf_hi(qv.w) * scale_log2;
-    }
-    const __nv_bfloat16* kb = k + (bh * (long long)L) * D + seg * 8;
-    const __nv_bfloat16* vb = v + (bh * (long long)L) * D + seg * 8;
-    float m = -INFINITY, l = 0.f, o[8];
+    float qf[G][8];
 #pragma unroll
-    for (int t = 0; t < 8; ++t) o[t] = 0.f;
+    for (int g = 0; g < G; ++g) {
+        uint4 qv = *reinterpret_cast<const uint4*>(q + (q0 + g) * D + seg * 8);
+        qf[g][0] = bf_lo(qv.x) * scale_log2; qf[g][1] = bf_hi(qv.x) * scale_log2;
+        qf[g][2] = bf_lo(qv.y) * scale_log2; qf[g][3] = bf_hi(qv.y) * scale_log2;
+        qf[g][4] = bf_lo(qv.z) * scale_log2; qf[g][5] = bf_hi(qv.z) * scale_log2;
+        qf[g][6] = bf_lo(qv.w) * scale_log2; qf[g][7] = bf_hi(qv.w) * scale_log2;
+    }
+    // element offset of key/value row r of this slice (without the lane's segment)
+    const int* table = rows.block_table ? rows.block_table + (long long)b * rows.max_pages : nullptr;
+    auto row_off = [&](int r) -> long long {
+        if (table == nullptr) return (kvs * (long long)L + r) * D;
+        const int pg = r / rows.page_size;
+        const int page = table[pg];
+        return (((long long)page * rows.hkv + hk) * rows.page_size + (r - pg * rows.page_size)) * D;
+    };
+    const __nv_bfloat16* kb = k + seg * 8;
+    const __nv_bfloat16* vb = v + seg * 8;
+    float m[G], l[G], o[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) o[g][t] = 0.f;
+    }
 
     constexpr int kRowsPerIter = kDecWarps * RPI * kUnroll;   // rows a CTA consumes per iteration
     for (int base = k0 + warp * (RPI * kUnroll); base < k1; base += kRowsPerIter) {
         uint4 kv[kUnroll], vv[kUnroll];
         bool ok[kUnroll];
+        long long ro[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             int r = base + u * RPI + sub;
             ok[u] = r < k1;
-            int rr = ok[u] ? r : k0;   // any valid row; its score is discarded below
-            kv[u] = ld_stream16(kb + (long long)rr * D);
+            ro[u] = row_off(ok[u] ? r : k0);   // any valid row; its score is discarded below
         }
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            int r = base + u * RPI + sub;
-            int rr = ok[u] ? r : k0;
-            vv[u] = ld_stream16(vb + (long long)rr * D);
-        }
-        float s[kUnroll];
+        for (int u = 0; u < kUnroll; ++u) kv[u] = ld_stream16(kb + ro[u]);
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            float x = dot8(kv[u], qf);
+        for (int u = 0; u < kUnroll; ++u) vv[u] = ld_stream16(vb + ro[u]);
 #pragma unroll
-            for (int off = LPR / 2; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
-            s[u] = ok[u] ? x : -INFINITY;
-        }
-        float mx = s[0];
-#pragma unroll
-        for (int u = 1; u < kUnroll; ++u) mx = fmaxf(mx, s[u]);
-        if (mx > m) {   // uniform across the lanes of a row group
-            float corr = (m == -INFINITY) ? 0.f : exp2f(m - mx);
-            l *= corr;
-#pragma unroll
-            for (int t = 0; t < 8; ++t) o[t] *= corr;
-            m = mx;
-        }
-        if (m != -INFINITY) {
+        for (int g = 0; g < G; ++g) {
+            float s[kUnroll];
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
-                float pu = exp2f(s[u] - m);
-                l += pu;
-                axpy8(pu, vv[u], o);
+                float x = dot8(kv[u], qf[g]);
+#pragma unroll
+                for (int off = LPR / 2; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+                s[u] = ok[u] ? x : -INFINITY;
+            }
+            float mx = s[0];
+#pragma unroll
+            for (int u = 1; u < kUnroll; ++u) mx = fmaxf(mx, s[u]);
+            if (mx > m[g]) {   // uniform across the lanes of a row group
+                float corr = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mx);
+                l[g] *= corr;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) o[g][t] *= corr;
+                m[g] = mx;
+            }
+            if (m[g] != -INFINITY) {
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    float pu = exp2f(s[u] - m[g]);
+                    l[g] += pu;
+                    axpy8(pu, vv[u], o[g]);
+                }
             }
         }
     }
-    // merge the RPI row groups of the warp (states live at lanes with equal `seg`)
 #pragma unroll
-    for (int off = 16; off >= LPR; off >>= 1) {
-        float m2 = __shfl_xor_sync(0xffffffffu, m, off);
-        float l2 = __shfl_xor_sync(0xffffffffu, l, off);
-        float o2[8];
+    for (int g = 0; g < G; ++g) {
+        // merge the RPI row groups of the warp (states live at lanes with equal `seg`)
 #pragma unroll
-        for (int t = 0; t < 8; ++t) o2[t] = __shfl_xor_sync(0xffffffffu, o[t], off);
-        merge_state(m, l, o, m2, l2, o2);
-    }
-    if (lane < LPR) {
-        if (lane == 0) {
-            sm_m[warp] = m;
-            sm_l[warp] = l;
+        for (int off = 16; off >= LPR; off >>= 1) {
+            float m2 = __shfl_xor_sync(0xffffffffu, m[g], off);
+            float l2 = __shfl_xor_sync(0xffffffffu, l[g], off);
+            float o2[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) o2[t] = __shfl_xor_sync(0xffffffffu, o[g][t], off);
+            merge_state(m[g], l[g], o[g], m2, l2, o2);
         }
+        if (lane < LPR) {
+            if (lane == 0) {
+                sm_m[g][warp] = m[g];
+                sm_l[g][warp] = l[g];
+            }
 #pragma unroll
-        for (int t = 0; t < 8; ++t) sm_o[warp][seg * 8 + t] = o[t];
+            for (int t = 0; t < 8; ++t) sm_o[g][warp][seg * 8 + t] = o[g][t];
+        }
     }
     __syncthreads();
     if (threadIdx.x < D) {
         const int d = threadIdx.x;
-        float M = sm_m[0];
 #pragma unroll
-        for (int w = 1; w < kDecWarps; ++w) M = fmaxf(M, sm_m[w]);
-        float Lsum = 0.f, O = 0.f;
+        for (int g = 0; g < G; ++g) {
+            float M = sm_m[g][0];
 #pragma unroll
-        for (int w = 0; w < kDecWarps; ++w) {
-            float a = (sm_m[w] == -INFINITY) ? 0.f : exp2f(sm_m[w] - M);
-            Lsum = fmaf(sm_l[w], a, Lsum);
-            O = fmaf(sm_o[w][d], a, O);
-        }
-        if (splits == 1) {
-            out[bh * D + d] = __float2bfloat16_rn(O / Lsum);
-            if (d == 0 && lse != nullptr) lse[bh] = (M + log2f(Lsum)) * 0.6931471805599453f;
-        } else {
-            float* pu = partial + unit * (D + 2);
-            pu[2 + d] = O;
-            if (d == 0) {
-                pu[0] = M;
-                pu[1] = Lsum;
+            for (int w = 1; w < kDecWarps; ++w) M = fmaxf(M, sm_m[g][w]);
+            float Lsum = 0.f, O = 0.f;
+#pragma unroll
+            for (int w = 0; w < kDecWarps; ++w) {
+                float a = (sm_m[g][w] == -INFINITY) ? 0.f : exp2f(sm_m[g][w] - M);
+                Lsum = fmaf(sm_l[g][w], a, Lsum);
+                O = fmaf(sm_o[g][w][d], a, O);
+            }
+            if (splits == 1) {
+                // a sequence without keys (seq_lens[b] == 0) has no distribution: output 0, lse -inf
+                out[(q0 + g) * D + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
+                if (d == 0 && lse != nullptr) lse[q0 + g] = (M + log2f(Lsum)) * 0.6931471805599453f;
+            } else {
+                float* pu = partial + (unit * G + g) * (D + 2);
+                pu[2 + d] = O;
+                if (d == 0) {
+                    pu[0] = M;
+                    pu[1] = Lsum;
+                }
             }
         }
     }
 }
 
+// out[bh] from the `splits` partial states of its key ranges.  G as in the kernel above: the
+// partials of query head g of key/value slice kvs are at ((kvs * splits + s) * G + g).
 template <int D>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
-                                         float* __restrict__ lse, int splits) {
+                                         float* __restrict__ lse, int splits, int G) {
     const long long bh = blockIdx.x;
     const int d = threadIdx.x;
-    const float* pb = partial + bh * splits * (D + 2);
+    const long long kvs = bh / G;
+    const int g = (int)(bh - kvs * G);
+    const float* pb = partial + ((kvs * splits) * G + g) * (D + 2);
+    const long long stride = (long long)G * (D + 2);
     float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, pb[s * (D + 2)]);
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, pb[s * stride]);
     float Lsum = 0.f, O = 0.f;
     for (int s = 0; s < splits; ++s) {
-        float ms = pb[s * (D + 2)];
+        float ms = pb[s * stride];
         float a = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-        Lsum = fmaf(pb[s * (D + 2) + 1], a, Lsum);
-        O = fmaf(pb[s * (D + 2) + 2 + d], a, O);
+        Lsum = fmaf(pb[s * stride + 1], a, Lsum);
+        O = fmaf(pb[s * stride + 2 + d], a, O);
     }
-    out[bh * D + d] = __float2bfloat16_rn(O / Lsum);
+    out[bh * D + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
     if (d == 0 && lse != nullptr) lse[bh] = (M + log2f(Lsum)) * 0.6931471805599453f;
 }
 
 static int env_int(const char* name, int dflt);
+
+static bool decode_group_instantiated(int g) { return g == 1 || g == 2 || g == 4 || g == 8; }
 
 DecodePlan attn_decode_plan(const AttnArgs& a) {
     DecodePlan pl{1, a.L, 0};
@@ -216,7 +268,8 @@ DecodePlan attn_decode_plan(const AttnArgs& a) {
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     const long long resident = (long long)n_sm * 4;
     const long long target = resident * 12;
-    long long splits = (target + a.BH - 1) / a.BH;
+    const long long cta_slices = decode_group_instantiated(a.group) ? a.BH / a.group : a.BH;
+    long long splits = (target + cta_slices - 1) / cta_slices;
     long long max_splits = a.L / 256;
     if (max_splits < 1) max_splits = 1;
     if (splits > max_splits) splits = max_splits;
@@ -232,27 +285,71 @@ DecodePlan attn_decode_plan(const AttnArgs& a) {
     return pl;
 }
 
+template <int D, int G>
+static void launch_decode_g(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaStream_t st, const DecodeRows& rows) {
+    const long long units = (a.BH / G) * pl.splits;
+    attn_decode_bf16_kernel<D, G><<<(unsigned)units, kDecThreads, 0, st>>>(
+        (const __nv_bfloat16*)a.q, (const __nv_bfloat16*)a.k, (const __nv_bfloat16*)a.v, (__nv_bfloat16*)a.out, a.lse,
+        (float*)ws, a.L, pl.splits, pl.chunk, a.scale * 1.4426950408889634f, a.group, rows);
+}
+
 template <int D>
 static cudaError_t launch_decode(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaStream_t st,
-                                 bool allow_timing = true) {
-    const long long units = a.BH * pl.splits;
+                                 bool allow_timing = true, const DecodeView* view = nullptr) {
+    DecodeRows rows{nullptr, nullptr, 0, 0, 1};
+    if (view) rows = DecodeRows{view->block_table, view->seq_lens, view->page_size, view->max_pages, view->hkv};
+    const int G = decode_group_instantiated(a.group) ? a.group : 1;
     {
         LaunchScope ls(K_DECODE, st, allow_timing);
-        attn_decode_bf16_kernel<D><<<(unsigned)units, kDecThreads, 0, st>>>(
-            (const __nv_bfloat16*)a.q, (const __nv_bfloat16*)a.k, (const __nv_bfloat16*)a.v, (__nv_bfloat16*)a.out,
-            a.lse, (float*)ws, a.L, pl.splits, pl.chunk, a.scale * 1.4426950408889634f);
+        switch (G) {
+            case 8: launch_decode_g<D, 8>(a, pl, ws, st, rows); break;
+            case 4: launch_decode_g<D, 4>(a, pl, ws, st, rows); break;
+            case 2: launch_decode_g<D, 2>(a, pl, ws, st, rows); break;
+            default: launch_decode_g<D, 1>(a, pl, ws, st, rows); break;
+        }
     }
     if (pl.splits > 1) {
         LaunchScope ls(K_DECODE_MERGE, st, allow_timing);
         attn_decode_merge_kernel<D><<<(unsigned)a.BH, D, 0, st>>>((const float*)ws, (__nv_bfloat16*)a.out, a.lse,
-                                                                  pl.splits);
+                                                                  pl.splits, G);
     }
     return cudaGetLastError();
 }
 
-cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaStream_t st) {
-    if (a.bf16 && a.S == 1 && a.D == 128) return launch_decode<128>(a, pl, ws, st);
-    if (a.bf16 && a.S == 1 && a.D == 64) return launch_decode<64>(a, pl, ws, st);
+// Grouped heads on a dense cache, as a tensor-core problem: the G query heads of a key/value head
+// are contiguous in q [B, Hkv*G, 1, D], i.e. they ARE a [B, Hkv, G, D] tensor of G query rows per
+// key/value head, and out / lse have the matching layout.  The forward kernel then computes the
+// whole group against each K/V tile with two MMAs, which the SIMT kernel cannot keep up with from
+// G = 4 on (it is instruction-bound: G dot products and G softmax updates per loaded row).  No
+// key splitting there, so it needs enough (batch, key/value head) items to fill the GPU.
+bool attn_decode_uses_fwd_kernel(const AttnArgs& a) {
+    if (!(a.bf16 && a.S == 1 && a.group >= 4)) return false;
+    const char* f = getenv("TT_DECODE_GQA_PATH");
+    if (f && f[0] == 's') return false;                     // "simt"
+    AttnArgs g = a;
+    g.BH = a.BH / a.group;
+    g.S = a.group;
+    g.group = 1;
+    g.causal = 0;
+    if (!attn_fwd_sm100_supported(g)) return false;
+    if (f && f[0] == 't') return true;                      // "tc"
+    int dev = 0, n_sm = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    return g.BH >= n_sm;
+}
+
+cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaStream_t st, const DecodeView* view) {
+    if (!(view && (view->block_table || view->seq_lens)) && attn_decode_uses_fwd_kernel(a)) {
+        AttnArgs g = a;
+        g.BH = a.BH / a.group;
+        g.S = a.group;
+        g.group = 1;
+        g.causal = 0;
+        return attn_fwd_sm100(g, st);
+    }
+    if (a.bf16 && a.S == 1 && a.D == 128) return launch_decode<128>(a, pl, ws, st, true, view);
+    if (a.bf16 && a.S == 1 && a.D == 64) return launch_decode<64>(a, pl, ws, st, true, view);
+    if (view && (view->block_table || view->seq_lens)) return cudaErrorNotSupported;   // paged / ragged: bf16, D 64 or 128
     return attn_fwd_simt(a, st);
 }
 

@@ -57,6 +57,7 @@ struct FwdParams {
     unsigned int* status;
     unsigned int* sched_counter;   // zero at launch; work items are taken with atomicAdd
     int n_items;                   // slices * n_qblk
+    int group;                     // query heads per key/value head: query slice bh reads key/value slice bh / group
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
 };
@@ -398,7 +399,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     const int st = t % kStages;
                     mbar_wait(&bar_kv_empty[st], ((t / kStages) & 1) ^ 1, wctx, BAR_KVEMPTY + st, (int)t);
                     __syncwarp();
-                    load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], j * 128, w.bh);
+                    load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], j * 128, w.bh / p.group);
                     ++t;
                 };
                 if (w.n_tiles[0] > 0) load_q(0);
@@ -572,8 +573,8 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     TmapStorage tq, tk, tv;
     const char* why = nullptr;
     if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
-    if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH, 128, &why)) return cudaErrorInvalidValue;
-    if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
@@ -584,6 +585,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.L = a.L;
     p.n_qblk = (a.S + 255) / 256;
     p.causal = a.causal;
+    p.group = a.group;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = device_status_word();
     p.trace = g_fwd_trace;

@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt_kernel(const T* __
                                                                       const T* __restrict__ k,
                                                                       const T* __restrict__ v, T* __restrict__ out,
                                                                       float* __restrict__ lse, int S, int L, int D,
-                                                                      int causal, float scale) {
+                                                                      int causal, float scale, int group) {
     extern __shared__ float smem[];
     const int pitch = D + 1;
     float* sQ = smem;
@@ -75,8 +75,8 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt_kernel(const T* __
     const int row0 = (int)(blockIdx.x % nblk) * kRowsPerBlock;
     const int off = L - S;
     q += bh * (long long)S * D;
-    k += bh * (long long)L * D;
-    v += bh * (long long)L * D;
+    k += (bh / group) * (long long)L * D;   // grouped heads: query slice bh reads key/value slice bh / group
+    v += (bh / group) * (long long)L * D;
     out += bh * (long long)S * D;
 
     stage_rows<T>(sQ, q, row0, S, D, 1.0f);
@@ -158,7 +158,7 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ dout,
     const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dq, int S, int L, int D,
-    int causal, float scale) {
+    int causal, float scale, int group) {
     extern __shared__ float smem[];
     const int pitch = D + 1;
     float* sQ = smem;
@@ -173,8 +173,8 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt_kernel(
     q += bh * (long long)S * D;
     dout += bh * (long long)S * D;
     dq += bh * (long long)S * D;
-    k += bh * (long long)L * D;
-    v += bh * (long long)L * D;
+    k += (bh / group) * (long long)L * D;
+    v += (bh / group) * (long long)L * D;
     lse += bh * S;
     delta += bh * S;
 
@@ -242,7 +242,7 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ dout,
     const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dk, T* __restrict__ dv, int S,
-    int L, int D, int causal, float scale) {
+    int L, int D, int causal, float scale, int group) {
     extern __shared__ float smem[];
     const int pitch = D + 1;
     float* sK = smem;
@@ -256,14 +256,15 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(
     const long long bh = blockIdx.x / nblk;
     const int key0 = (int)(blockIdx.x % nblk) * kRowsPerBlock;
     const int off = L - S;
-    q += bh * (long long)S * D;
-    dout += bh * (long long)S * D;
+    // bh is the key/value slice; its `group` query heads are slices bh*group .. bh*group+group-1
+    q += bh * group * (long long)S * D;
+    dout += bh * group * (long long)S * D;
     k += bh * (long long)L * D;
     v += bh * (long long)L * D;
     dk += bh * (long long)L * D;
     dv += bh * (long long)L * D;
-    lse += bh * S;
-    delta += bh * S;
+    lse += bh * group * S;
+    delta += bh * group * S;
 
     stage_rows<T>(sK, k, key0, L, D, 1.0f);
     stage_rows<T>(sV, v, key0, L, D, 1.0f);
@@ -275,6 +276,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(
     // first query that can see the first key of this block: i >= key0 - off
     int i_begin = causal ? max(0, key0 - off) : 0;
     i_begin = (i_begin / kColsPerTile) * kColsPerTile;
+    for (int hh = 0; hh < group; ++hh, q += (long long)S * D, dout += (long long)S * D, lse += S, delta += S)
     for (int i0 = i_begin; i0 < S; i0 += kColsPerTile) {
         __syncthreads();
         stage_rows<T>(sQ, q, i0, S, D, 1.0f);
@@ -349,7 +351,7 @@ static cudaError_t launch_fwd_simt(const AttnArgs& a, cudaStream_t st) {
         LaunchScope ls(K_FWD_SIMT, st);
         attn_fwd_simt_kernel<T, NV><<<grid, kSimtThreads, smem, st>>>((const T*)a.q, (const T*)a.k, (const T*)a.v,
                                                                       (T*)a.out, a.lse, a.S, a.L, a.D, a.causal,
-                                                                      a.scale);
+                                                                      a.scale, a.group);
     }
     return cudaGetLastError();
 }
@@ -373,14 +375,14 @@ static cudaError_t launch_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t
         LaunchScope ls(K_BWD_SIMT_DQ, st);
         attn_bwd_dq_simt_kernel<T, NV><<<gq, kSimtThreads, smem_q, st>>>(
             (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dq, a.S, a.L, a.D,
-            a.causal, a.scale);
+            a.causal, a.scale, a.group);
     }
-    unsigned gk = (unsigned)(((a.L + kRowsPerBlock - 1) / kRowsPerBlock) * a.BH);
+    unsigned gk = (unsigned)(((a.L + kRowsPerBlock - 1) / kRowsPerBlock) * (a.BH / a.group));
     {
         LaunchScope ls(K_BWD_SIMT_DKV, st);
         attn_bwd_dkv_simt_kernel<T, NV><<<gk, kSimtThreads, smem_kv, st>>>(
             (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dk, (T*)a.dv, a.S,
-            a.L, a.D, a.causal, a.scale);
+            a.L, a.D, a.causal, a.scale, a.group);
     }
     return cudaGetLastError();
 }

@@ -9,7 +9,8 @@ namespace ttk {
 
 // Fully resolved launch arguments (device pointers, scale already defaulted).
 struct AttnArgs {
-    long long BH;   // B*H independent slices
+    long long BH;   // B*H query slices
+    int group;      // query heads per key/value head (>= 1); k, v, dk, dv have BH / group slices
     int S, L, D;
     int causal;
     int bf16;       // 1: __nv_bfloat16 tensors, 0: float
@@ -84,7 +85,21 @@ struct DecodePlan {
     size_t ws_bytes;   // partials: splits * BH * (D + 2) floats (0 when splits == 1)
 };
 DecodePlan attn_decode_plan(const AttnArgs& a);
-cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& plan, void* workspace, cudaStream_t st);
+// Optional description of where the key/value rows live (bf16, D in {64,128} only):
+//   block_table != null: k, v are page pools [pages, hkv, page_size, D] and row r of batch entry b
+//                        is row r % page_size of page block_table[b * max_pages + r / page_size];
+//   seq_lens != null:    batch entry b has seq_lens[b] (<= L) keys, the rest is ignored.
+struct DecodeView {
+    const int* block_table = nullptr;
+    const int* seq_lens = nullptr;
+    int page_size = 0, max_pages = 0;
+    int hkv = 1;   // key/value heads per batch entry
+};
+cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& plan, void* workspace, cudaStream_t st,
+                        const DecodeView* view = nullptr);
+// true when a dense grouped-head decode goes to the tcgen05 forward kernel (group >= 4, enough
+// key/value slices to fill the GPU; TT_DECODE_GQA_PATH=simt|tc overrides)
+bool attn_decode_uses_fwd_kernel(const AttnArgs& a);
 // Same kernels, partials in the library's own fixed device array (no allocation anywhere).
 // *too_big is set when the plan needs more than the array holds (nothing is launched then).
 size_t attn_decode_static_capacity();

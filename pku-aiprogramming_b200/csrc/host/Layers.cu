@@ -27,9 +27,11 @@ tt_attn_desc describe(const TinyTensor<T>& q, const TinyTensor<T>& k, const Tiny
                       const char* who) {
     if (q.shape.size() != 4 || k.shape.size() != 4 || v.shape.size() != 4)
         throw std::invalid_argument(std::string(who) + ": q, k, v must be 4-D [B,H,rows,D]");
-    if (k.shape != v.shape || q.shape[0] != k.shape[0] || q.shape[1] != k.shape[1] || q.shape[3] != k.shape[3])
-        throw std::invalid_argument(std::string(who) + ": q, k, v shapes do not agree");
+    if (k.shape != v.shape || q.shape[0] != k.shape[0] || k.shape[1] < 1 || q.shape[1] % k.shape[1] != 0 ||
+        q.shape[3] != k.shape[3])
+        throw std::invalid_argument(std::string(who) + ": q, k, v shapes do not agree (k, v heads must divide q heads)");
     tt_attn_desc d;
+    d.Hkv = k.shape[1];   // fewer key/value heads than query heads: grouped attention
     d.B = q.shape[0];
     d.H = q.shape[1];
     d.S = q.shape[2];

@@ -297,8 +297,12 @@ static int resolve(const tt_attn_desc* d, AttnArgs* a, const char* who) {
     if (d->causal && d->L < d->S)
         return fail(TT_ERR_BAD_SHAPE, "%s: causal with L=%d < S=%d leaves query rows without keys", who, d->L, d->S);
     if (!std::isfinite(d->scale)) return fail(TT_ERR_BAD_SHAPE, "%s: scale is not finite", who);
+    const int hkv = d->Hkv > 0 ? d->Hkv : d->H;
+    if (hkv > d->H || d->H % hkv != 0)
+        return fail(TT_ERR_BAD_SHAPE, "%s: Hkv=%d must divide H=%d", who, d->Hkv, d->H);
     memset(a, 0, sizeof(*a));
     a->BH = (long long)d->B * d->H;
+    a->group = d->H / hkv;
     a->S = d->S;
     a->L = d->L;
     a->D = d->D;
@@ -522,6 +526,47 @@ int tt_fc_path(int64_t rows, int32_t in_features, int32_t out_features, int32_t 
                ? 1 : 0;
 }
 
+int tt_attn_decode_paged(const tt_attn_desc* desc, const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_table, const int32_t* seq_lens, int32_t page_size, int32_t max_pages,
+                         void* out, float* lse, void* workspace, size_t workspace_bytes, void* stream) {
+    AttnArgs a;
+    int rc = resolve(desc, &a, "tt_attn_decode_paged");
+    if (rc != TT_OK) return rc;
+    if (a.S != 1) return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_paged: S must be 1, got %d", a.S);
+    if (!a.bf16 || !(a.D == 64 || a.D == 128))
+        return fail(TT_ERR_BAD_DTYPE, "tt_attn_decode_paged: bf16 with D = 64 or 128 only (dtype %d, D %d)", desc->dtype, a.D);
+    if (!q || !k_pool || !v_pool || !out) return fail(TT_ERR_NULL, "tt_attn_decode_paged: q, k, v and out must be non-null");
+    if (block_table) {
+        if (page_size < 1 || max_pages < 1)
+            return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_paged: page_size=%d max_pages=%d must be >= 1", page_size, max_pages);
+        if ((long long)page_size * max_pages < a.L)
+            return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_paged: L=%d exceeds page_size*max_pages=%lld", a.L,
+                        (long long)page_size * max_pages);
+    }
+    if (!(aligned16(q) && aligned16(k_pool) && aligned16(v_pool)))
+        return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_paged: q, k, v must be 16-byte aligned");
+    if ((rc = check_device()) != TT_OK) return rc;
+    a.causal = 0;
+    DecodePlan pl = attn_decode_plan(a);
+    if (pl.ws_bytes > 0) {
+        if (!workspace || workspace_bytes < pl.ws_bytes)
+            return fail(TT_ERR_WORKSPACE, "tt_attn_decode_paged: workspace of %zu bytes required, %zu given", pl.ws_bytes,
+                        workspace_bytes);
+        if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+            return fail(TT_ERR_WORKSPACE, "tt_attn_decode_paged: workspace must be 256-byte aligned");
+    }
+    a.q = q; a.k = k_pool; a.v = v_pool; a.out = out; a.lse = lse;
+    DecodeView view;
+    view.block_table = block_table;
+    view.seq_lens = seq_lens;
+    view.page_size = page_size;
+    view.max_pages = max_pages;
+    view.hkv = desc->Hkv > 0 ? desc->Hkv : desc->H;
+    cudaError_t e = attn_decode(a, pl, workspace, (cudaStream_t)stream, &view);
+    if (e != cudaSuccess) return cuda_fail(e, "tt_attn_decode_paged: launch");
+    return TT_OK;
+}
+
 int tt_debug_wait_timeout(int64_t budget_cycles, void* stream) {
     if (budget_cycles < 1 || budget_cycles > 4000000000LL)
         return fail(TT_ERR_BAD_SHAPE, "tt_debug_wait_timeout: budget of %lld cycles outside 1..4e9", (long long)budget_cycles);
@@ -635,7 +680,7 @@ int tt_attn_fwd_host(const tt_attn_desc* d, const void* q, const void* k, const 
     if (!q || !k || !v || !out) return fail(TT_ERR_NULL, "tt_attn_fwd_host: q, k, v and out must be non-null");
     TT_TRY(check_device());
     const size_t es = a.bf16 ? 2 : 4;
-    const size_t nq = (size_t)a.BH * a.S * a.D * es, nk = (size_t)a.BH * a.L * a.D * es;
+    const size_t nq = (size_t)a.BH * a.S * a.D * es, nk = (size_t)(a.BH / a.group) * a.L * a.D * es;
     const size_t nl = (size_t)a.BH * a.S * sizeof(float);
     DevBuf dq_, dk_, dv_, do_, dl_;
     TT_TRY(dq_.get(nq)); TT_TRY(dk_.get(nk)); TT_TRY(dv_.get(nk)); TT_TRY(do_.get(nq)); TT_TRY(dl_.get(nl));
@@ -657,7 +702,7 @@ int tt_attn_bwd_host(const tt_attn_desc* d, const void* q, const void* k, const 
         return fail(TT_ERR_NULL, "tt_attn_bwd_host: all tensor pointers must be non-null");
     TT_TRY(check_device());
     const size_t es = a.bf16 ? 2 : 4;
-    const size_t nq = (size_t)a.BH * a.S * a.D * es, nk = (size_t)a.BH * a.L * a.D * es;
+    const size_t nq = (size_t)a.BH * a.S * a.D * es, nk = (size_t)(a.BH / a.group) * a.L * a.D * es;
     const size_t nl = (size_t)a.BH * a.S * sizeof(float);
     const size_t nws = tt_attn_bwd_workspace_bytes(d);
     DevBuf bq, bk, bv, bo, bl, bdo, bdq, bdk, bdv, bws;
@@ -737,18 +782,21 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
     if (per < 1) per = 1;
     if (per > (a.BH + 2) / 3) per = (a.BH + 2) / 3;
     if (per < 1) per = 1;
+    per = (per + a.group - 1) / a.group * a.group;   // a chunk holds whole groups of query heads
     const long long n_chunks = (a.BH + per - 1) / per;
     constexpr int NB = EventSet::kN;
     tt_attn_desc dc = *d;
     dc.B = 1;
     dc.H = (int32_t)per;
+    dc.Hkv = (int32_t)(per / a.group);
     const size_t ws_bytes = tt_attn_bwd_workspace_bytes(&dc);
     DevBuf bq[NB], bk[NB], bv[NB], bdo[NB], bo[NB], bl[NB], bdq[NB], bdk[NB], bdv[NB], bws[NB];
     const int nb_used = (int)(n_chunks < NB ? n_chunks : NB);
     for (int i = 0; i < nb_used; ++i) {
-        TT_TRY(bq[i].get(per * q_slice)); TT_TRY(bk[i].get(per * k_slice)); TT_TRY(bv[i].get(per * k_slice));
+        const long long perk = per / a.group;
+        TT_TRY(bq[i].get(per * q_slice)); TT_TRY(bk[i].get(perk * k_slice)); TT_TRY(bv[i].get(perk * k_slice));
         TT_TRY(bdo[i].get(per * q_slice)); TT_TRY(bo[i].get(per * q_slice)); TT_TRY(bl[i].get(per * l_slice));
-        TT_TRY(bdq[i].get(per * q_slice)); TT_TRY(bdk[i].get(per * k_slice)); TT_TRY(bdv[i].get(per * k_slice));
+        TT_TRY(bdq[i].get(per * q_slice)); TT_TRY(bdk[i].get(perk * k_slice)); TT_TRY(bdv[i].get(perk * k_slice));
         TT_TRY(bws[i].get(ws_bytes));
     }
     PipeStreams* ps = nullptr;
@@ -762,16 +810,18 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
         const int b = (int)(c % NB);
         const long long s0 = c * per;
         const long long cnt = (s0 + per <= a.BH) ? per : (a.BH - s0);
+        const long long k0 = s0 / a.group, kcnt = cnt / a.group;   // the chunk's key/value slices
         if (c >= NB) TT_CUDA(cudaStreamWaitEvent(ps->in, ev.out[b], 0), "wait buffer");   // chunk c-NB downloaded
         TT_CUDA(cudaMemcpyAsync(bq[b].p, hq + s0 * q_slice, cnt * q_slice, cudaMemcpyHostToDevice, ps->in), "upload q");
-        TT_CUDA(cudaMemcpyAsync(bk[b].p, hk + s0 * k_slice, cnt * k_slice, cudaMemcpyHostToDevice, ps->in), "upload k");
-        TT_CUDA(cudaMemcpyAsync(bv[b].p, hv + s0 * k_slice, cnt * k_slice, cudaMemcpyHostToDevice, ps->in), "upload v");
+        TT_CUDA(cudaMemcpyAsync(bk[b].p, hk + k0 * k_slice, kcnt * k_slice, cudaMemcpyHostToDevice, ps->in), "upload k");
+        TT_CUDA(cudaMemcpyAsync(bv[b].p, hv + k0 * k_slice, kcnt * k_slice, cudaMemcpyHostToDevice, ps->in), "upload v");
         TT_CUDA(cudaMemcpyAsync(bdo[b].p, hdo + s0 * q_slice, cnt * q_slice, cudaMemcpyHostToDevice, ps->in), "upload dout");
         TT_CUDA(cudaEventRecord(ev.in[b], ps->in), "record");
         TT_CUDA(cudaStreamWaitEvent(ps->comp, ev.in[b], 0), "wait upload");
         tt_attn_desc di = *d;
         di.B = 1;
         di.H = (int32_t)cnt;
+        di.Hkv = (int32_t)kcnt;
         TT_TRY(tt_attn_fwd(&di, bq[b].p, bk[b].p, bv[b].p, bo[b].p, (float*)bl[b].p, ps->comp));
         TT_TRY(tt_attn_bwd(&di, bq[b].p, bk[b].p, bv[b].p, bo[b].p, (const float*)bl[b].p, bdo[b].p, bdq[b].p, bdk[b].p,
                            bdv[b].p, bws[b].p, ws_bytes, ps->comp));
@@ -780,8 +830,8 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
         TT_CUDA(cudaMemcpyAsync(ho + s0 * q_slice, bo[b].p, cnt * q_slice, cudaMemcpyDeviceToHost, ps->out), "download out");
         if (lse) TT_CUDA(cudaMemcpyAsync(lse + s0 * a.S, bl[b].p, cnt * l_slice, cudaMemcpyDeviceToHost, ps->out), "download lse");
         TT_CUDA(cudaMemcpyAsync(hdq + s0 * q_slice, bdq[b].p, cnt * q_slice, cudaMemcpyDeviceToHost, ps->out), "download dq");
-        TT_CUDA(cudaMemcpyAsync(hdk + s0 * k_slice, bdk[b].p, cnt * k_slice, cudaMemcpyDeviceToHost, ps->out), "download dk");
-        TT_CUDA(cudaMemcpyAsync(hdv + s0 * k_slice, bdv[b].p, cnt * k_slice, cudaMemcpyDeviceToHost, ps->out), "download dv");
+        TT_CUDA(cudaMemcpyAsync(hdk + k0 * k_slice, bdk[b].p, kcnt * k_slice, cudaMemcpyDeviceToHost, ps->out), "download dk");
+        TT_CUDA(cudaMemcpyAsync(hdv + k0 * k_slice, bdv[b].p, kcnt * k_slice, cudaMemcpyDeviceToHost, ps->out), "download dv");
         TT_CUDA(cudaEventRecord(ev.out[b], ps->out), "record");
     }
     TT_CUDA(cudaStreamSynchronize(ps->in), "synchronize");
@@ -797,7 +847,7 @@ int tt_attn_decode_host(const tt_attn_desc* d, const void* q, const void* k, con
     if (!q || !k || !v || !out) return fail(TT_ERR_NULL, "tt_attn_decode_host: q, k, v and out must be non-null");
     TT_TRY(check_device());
     const size_t es = a.bf16 ? 2 : 4;
-    const size_t nq = (size_t)a.BH * a.D * es, nk = (size_t)a.BH * a.L * a.D * es;
+    const size_t nq = (size_t)a.BH * a.D * es, nk = (size_t)(a.BH / a.group) * a.L * a.D * es;
     const size_t nl = (size_t)a.BH * sizeof(float);
     const size_t nws = tt_attn_decode_workspace_bytes(d);
     DevBuf bq, bk, bv, bo, bl, bws;

@@ -2,7 +2,7 @@
 
 torch is used for device memory and streams only: every call hands raw device pointers
 to the C ABI (`capi.lib`).  Shapes follow the reference's row-major layout:
-q/out `[B,H,S,D]`, k/v `[B,H,L,D]`, lse `[B,H,S]` fp32.
+q/out `[B,H,S,D]`, k/v `[B,Hkv,L,D]` (Hkv = H, or a divisor of H for grouped heads), lse `[B,H,S]` fp32.
 """
 from __future__ import annotations
 
@@ -28,8 +28,10 @@ def _check_inputs(q, k, v):
     if q.dtype not in _DT or k.dtype != q.dtype or v.dtype != q.dtype:
         raise ValueError(f"q, k, v must share dtype float32 or bfloat16, got {q.dtype}, {k.dtype}, {v.dtype}")
     B, H, S, D = q.shape
-    if k.shape[0] != B or k.shape[1] != H or k.shape[3] != D or tuple(v.shape) != tuple(k.shape):
-        raise ValueError(f"shape mismatch: q {tuple(q.shape)} k {tuple(k.shape)} v {tuple(v.shape)}")
+    Hkv = k.shape[1]
+    if k.shape[0] != B or Hkv < 1 or H % Hkv != 0 or k.shape[3] != D or tuple(v.shape) != tuple(k.shape):
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)} k {tuple(k.shape)} v {tuple(v.shape)} "
+                         "(k, v heads must divide q heads)")
     return B, H, S, k.shape[2], D
 
 
@@ -49,7 +51,7 @@ def attention_forward(q, k, v, causal=False, scale=None, out=None, lse=None, nee
             out = torch.empty_like(q)
         if lse is None and need_lse:
             lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
-        d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+        d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale, Hkv=k.shape[1])
         capi.check(capi.lib.tt_attn_fwd(ctypes.byref(d), _p(q), _p(k), _p(v), _p(out), _p(lse), _stream_ptr(q)))
     return out, lse
 
@@ -63,7 +65,7 @@ def attention_backward(q, k, v, out, lse, dout, causal=False, scale=None, worksp
     if tuple(lse.shape) != (B, H, S) or lse.dtype != torch.float32 or not lse.is_contiguous():
         raise ValueError("lse must be contiguous float32 [B,H,S]")
     with torch.cuda.device(q.device):
-        d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+        d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale, Hkv=k.shape[1])
         need = int(capi.lib.tt_attn_bwd_workspace_bytes(ctypes.byref(d)))
         if workspace is None or workspace.numel() * workspace.element_size() < need:
             workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
@@ -74,8 +76,8 @@ def attention_backward(q, k, v, out, lse, dout, causal=False, scale=None, worksp
     return dq, dk, dv
 
 
-def decode_workspace_bytes(B, H, L, D, dtype=torch.bfloat16) -> int:
-    d = capi.make_desc(B, H, 1, L, D, _DT[dtype], False, None)
+def decode_workspace_bytes(B, H, L, D, dtype=torch.bfloat16, Hkv=None) -> int:
+    d = capi.make_desc(B, H, 1, L, D, _DT[dtype], False, None, Hkv=Hkv)
     return int(capi.lib.tt_attn_decode_workspace_bytes(ctypes.byref(d)))
 
 
@@ -89,13 +91,63 @@ def attention_decode(q, k, v, scale=None, out=None, lse=None, workspace=None, ne
             out = torch.empty_like(q)
         if lse is None and need_lse:
             lse = torch.empty((B, H, 1), dtype=torch.float32, device=q.device)
-        d = capi.make_desc(B, H, 1, L, D, _DT[q.dtype], False, scale)
+        d = capi.make_desc(B, H, 1, L, D, _DT[q.dtype], False, scale, Hkv=k.shape[1])
         need = int(capi.lib.tt_attn_decode_workspace_bytes(ctypes.byref(d)))
         if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
             workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
         nbytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
         capi.check(capi.lib.tt_attn_decode(ctypes.byref(d), _p(q), _p(k), _p(v), _p(out), _p(lse),
                                            _p(workspace), nbytes, _stream_ptr(q)))
+    return out, lse
+
+
+def attention_decode_paged(q, k_pool, v_pool, block_table=None, seq_lens=None, max_len=None, scale=None, out=None,
+                           lse=None, workspace=None, need_lse=True):
+    """Single-query attention over a paged and/or ragged cache (bf16, D 64 or 128).
+
+    q `[B,H,1,D]`.  With `block_table` (int32 `[B, max_pages]`, CUDA): k_pool, v_pool are page pools
+    `[pages, Hkv, page_size, D]`.  Without: dense `[B,Hkv,L,D]`.  `seq_lens` (int32 `[B]`, CUDA)
+    limits each batch entry to its first seq_lens[b] keys.  `max_len`: longest possible sequence
+    (default: page_size * max_pages, or L of the dense cache)."""
+    if q.dim() != 4 or q.shape[2] != 1 or not q.is_cuda or not q.is_contiguous() or q.dtype != torch.bfloat16:
+        raise ValueError("q must be a contiguous CUDA bfloat16 tensor [B,H,1,D]")
+    B, H, _, D = q.shape
+    for name, t in (("k_pool", k_pool), ("v_pool", v_pool)):
+        if t.dim() != 4 or not t.is_cuda or not t.is_contiguous() or t.dtype != q.dtype or t.shape[3] != D:
+            raise ValueError(f"{name} must be a contiguous CUDA bfloat16 tensor with last axis {D}")
+    if tuple(k_pool.shape) != tuple(v_pool.shape):
+        raise ValueError("k_pool and v_pool must have one shape")
+    for name, t, shp in (("block_table", block_table, None), ("seq_lens", seq_lens, (B,))):
+        if t is not None and (t.dtype != torch.int32 or not t.is_cuda or not t.is_contiguous() or
+                              (shp is not None and tuple(t.shape) != shp)):
+            raise ValueError(f"{name} must be a contiguous CUDA int32 tensor" + (f" of shape {shp}" if shp else ""))
+    Hkv = k_pool.shape[1]
+    if H % Hkv != 0:
+        raise ValueError(f"key/value heads {Hkv} must divide query heads {H}")
+    if block_table is not None:
+        if block_table.dim() != 2 or block_table.shape[0] != B:
+            raise ValueError("block_table must be [B, max_pages]")
+        page_size, max_pages = k_pool.shape[2], block_table.shape[1]
+        L = int(max_len) if max_len is not None else page_size * max_pages
+    else:
+        if k_pool.shape[0] != B:
+            raise ValueError("a dense cache must be [B,Hkv,L,D]")
+        page_size, max_pages = 0, 0
+        L = int(max_len) if max_len is not None else k_pool.shape[2]
+        if L > k_pool.shape[2]:
+            raise ValueError("max_len exceeds the cache length")
+    with torch.cuda.device(q.device):
+        out = torch.empty_like(q) if out is None else out
+        if lse is None and need_lse:
+            lse = torch.empty((B, H, 1), dtype=torch.float32, device=q.device)
+        d = capi.make_desc(B, H, 1, L, D, capi.TT_BF16, False, scale, Hkv=Hkv)
+        need = int(capi.lib.tt_attn_decode_workspace_bytes(ctypes.byref(d)))
+        if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+            workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+        nbytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+        capi.check(capi.lib.tt_attn_decode_paged(ctypes.byref(d), _p(q), _p(k_pool), _p(v_pool), _p(block_table),
+                                                 _p(seq_lens), page_size, max_pages, _p(out), _p(lse), _p(workspace),
+                                                 nbytes, _stream_ptr(q)))
     return out, lse
 
 
@@ -185,7 +237,7 @@ def attention_forward_host(q, k, v, causal=False, scale=None, out=None, lse=None
         out = torch.empty_like(q)
     if lse is None:
         lse = torch.empty((B, H, S), dtype=torch.float32)
-    d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+    d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale, Hkv=k.shape[1])
     capi.check(capi.lib.tt_attn_fwd_host(ctypes.byref(d), _host_ptr(q), _host_ptr(k), _host_ptr(v),
                                          _host_ptr(out), _host_ptr(lse)))
     return out, lse
@@ -197,7 +249,7 @@ def attention_backward_host(q, k, v, out, lse, dout, causal=False, scale=None, d
     dq = torch.empty_like(q) if dq is None else dq
     dk = torch.empty_like(k) if dk is None else dk
     dv = torch.empty_like(v) if dv is None else dv
-    d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+    d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale, Hkv=k.shape[1])
     capi.check(capi.lib.tt_attn_bwd_host(ctypes.byref(d), _host_ptr(q), _host_ptr(k), _host_ptr(v), _host_ptr(out),
                                          _host_ptr(lse), _host_ptr(dout), _host_ptr(dq), _host_ptr(dk), _host_ptr(dv)))
     return dq, dk, dv
@@ -213,7 +265,7 @@ def attention_step_host(q, k, v, dout, causal=False, scale=None, out=None, lse=N
     dq = torch.empty_like(q) if dq is None else dq
     dk = torch.empty_like(k) if dk is None else dk
     dv = torch.empty_like(v) if dv is None else dv
-    d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale)
+    d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale, Hkv=k.shape[1])
     capi.check(capi.lib.tt_attn_fwd_bwd_host(ctypes.byref(d), _host_ptr(q), _host_ptr(k), _host_ptr(v), _host_ptr(dout),
                                              _host_ptr(out), _host_ptr(lse), _host_ptr(dq), _host_ptr(dk), _host_ptr(dv)))
     return out, lse, dq, dk, dv
@@ -226,7 +278,7 @@ def attention_decode_host(q, k, v, scale=None, out=None, lse=None):
         out = torch.empty_like(q)
     if lse is None:
         lse = torch.empty((B, H, 1), dtype=torch.float32)
-    d = capi.make_desc(B, H, 1, L, D, _DT[q.dtype], False, scale)
+    d = capi.make_desc(B, H, 1, L, D, _DT[q.dtype], False, scale, Hkv=k.shape[1])
     capi.check(capi.lib.tt_attn_decode_host(ctypes.byref(d), _host_ptr(q), _host_ptr(k), _host_ptr(v),
                                             _host_ptr(out), _host_ptr(lse)))
     return out, lse

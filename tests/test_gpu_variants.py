@@ -1,0 +1,172 @@
+"""GPU parity of the attention variants on the same kernels: grouped heads (GQA / MQA) in forward,
+backward and decode, and decode over paged and ragged key/value caches.  The oracle composes them
+from the reference's ops (heads broadcast / gradients summed; pages gathered into a dense cache).
+Tolerances as for the base op: fp32 rel 1e-5, bf16 abs 2e-2 (+ one bf16 ulp of the largest value for
+gradients, which grow with the group size)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available()
+    return torch
+
+
+def make_grouped(oracle, seed, B, H, Hkv, S, L, D, bf16):
+    q, _, _, do = oracle.make_inputs(seed, B, H, S, L, D)
+    _, k, v, _ = oracle.make_inputs(seed + 1, B, Hkv, S, L, D)
+    if bf16:
+        q, k, v, do = (oracle.bf16_round(a) for a in (q, k, v, do))
+    return q, k, v, do
+
+
+@pytest.mark.parametrize("B,H,Hkv,S,L,D,causal", [(1, 8, 2, 300, 300, 128, True), (2, 4, 1, 130, 260, 64, True),
+                                                  (1, 6, 3, 257, 257, 128, False), (1, 8, 8, 128, 128, 64, True)])
+def test_grouped_heads_tensor_core_fwd_bwd(tt, oracle, torch_cuda, B, H, Hkv, S, L, D, causal):
+    torch = torch_cuda
+    q, k, v, do = make_grouped(oracle, 70 + H + Hkv, B, H, Hkv, S, L, D, True)
+    tq, tk, tv, tdo = (torch.from_numpy(a).cuda().bfloat16() for a in (q, k, v, do))
+    d = tt.capi.make_desc(B, H, S, L, D, tt.capi.TT_BF16, causal, None, Hkv=Hkv)
+    import ctypes
+    assert tt.capi.lib.tt_attn_fwd_path(ctypes.byref(d)) == b"tcgen05"
+    out, lse = tt.attention_forward(tq, tk, tv, causal=causal)
+    dq, dk, dv = tt.attention_backward(tq, tk, tv, out, lse, tdo, causal=causal)
+    tt.check_device_status()
+    assert tuple(dk.shape) == (B, Hkv, L, D)
+    o_r, lse_r, dq_r, dk_r, dv_r = oracle.attention_backward_grouped(q, k, v, do, causal)
+    assert oracle.max_abs_err(out.float().cpu().numpy(), o_r) <= 2e-2
+    assert oracle.max_abs_err(lse.cpu().numpy(), lse_r) <= 1e-3
+    for got, ref, name in ((dq, dq_r, "dq"), (dk, dk_r, "dk"), (dv, dv_r, "dv")):
+        assert oracle.max_abs_err(got.float().cpu().numpy(), ref) <= 2e-2 + 2.0 ** -7 * np.abs(ref).max(), name
+
+
+@pytest.mark.parametrize("B,H,Hkv,S,L,D,causal", [(2, 4, 2, 40, 72, 32, True), (1, 6, 1, 33, 33, 48, False)])
+def test_grouped_heads_fp32_exact_kernels(tt, oracle, torch_cuda, B, H, Hkv, S, L, D, causal):
+    torch = torch_cuda
+    q, k, v, do = make_grouped(oracle, 80 + H, B, H, Hkv, S, L, D, False)
+    tq, tk, tv, tdo = (torch.from_numpy(a).cuda() for a in (q, k, v, do))
+    out, lse = tt.attention_forward(tq, tk, tv, causal=causal)
+    dq, dk, dv = tt.attention_backward(tq, tk, tv, out, lse, tdo, causal=causal)
+    o_r, _, dq_r, dk_r, dv_r = oracle.attention_backward_grouped(q, k, v, do, causal)
+    for got, ref, name in ((out, o_r, "o"), (dq, dq_r, "dq"), (dk, dk_r, "dk"), (dv, dv_r, "dv")):
+        assert oracle.rel_err(got.cpu().numpy(), ref) <= 1e-5, name
+
+
+def test_grouped_heads_pipelined_host_step(tt, oracle, torch_cuda):
+    torch = torch_cuda
+    B, H, Hkv, S, D = 2, 8, 2, 256, 128
+    q, k, v, do = make_grouped(oracle, 91, B, H, Hkv, S, S, D, True)
+    hq, hk, hv, hdo = (torch.from_numpy(a).bfloat16().pin_memory() for a in (q, k, v, do))
+    out, lse, dq, dk, dv = tt.attention_step_host(hq, hk, hv, hdo, causal=True)
+    o_r, _, dq_r, dk_r, dv_r = oracle.attention_backward_grouped(q, k, v, do, True)
+    assert oracle.max_abs_err(out.float().numpy(), o_r) <= 2e-2
+    for got, ref in ((dq, dq_r), (dk, dk_r), (dv, dv_r)):
+        assert oracle.max_abs_err(got.float().numpy(), ref) <= 2e-2 + 2.0 ** -7 * np.abs(ref).max()
+
+
+def dense_decode_ref(oracle, q, k, v, lens=None):
+    """Per batch entry: the oracle forward on the first lens[b] keys (heads expanded to the group)."""
+    B, H = q.shape[:2]
+    out = np.zeros_like(q)
+    lse = np.full((B, H, 1), -np.inf, np.float32)
+    for b in range(B):
+        n = k.shape[2] if lens is None else int(lens[b])
+        if n == 0:
+            continue
+        kb, vb = oracle.expand_kv_heads(k[b:b + 1, :, :n], H), oracle.expand_kv_heads(v[b:b + 1, :, :n], H)
+        o, l = oracle.attention_forward(q[b:b + 1], kb, vb, False)
+        out[b], lse[b] = o[0], l[0]
+    return out, lse
+
+
+@pytest.mark.parametrize("H,Hkv,D", [(8, 8, 128), (8, 4, 128), (8, 2, 64), (8, 1, 128), (6, 2, 128), (16, 2, 64)])
+def test_decode_grouped_heads(tt, oracle, torch_cuda, H, Hkv, D):
+    """Group sizes 1, 2, 4, 8 (one pass over K/V per group) and 3 (mapped fallback)."""
+    torch = torch_cuda
+    B, L = 3, 1500
+    q, k, v, _ = make_grouped(oracle, 100 + H + Hkv, B, H, Hkv, 1, L, D, True)
+    tq, tk, tv = (torch.from_numpy(a).cuda().bfloat16() for a in (q, k, v))
+    out, lse = tt.attention_decode(tq, tk, tv)
+    o_r, lse_r = dense_decode_ref(oracle, q, k, v)
+    assert oracle.max_abs_err(out.float().cpu().numpy(), o_r) <= 2e-2
+    assert oracle.max_abs_err(lse.cpu().numpy(), lse_r) <= 1e-3
+
+
+@pytest.mark.parametrize("H,Hkv,D", [(8, 2, 128), (16, 2, 64), (32, 1, 128)])
+def test_decode_grouped_heads_on_the_forward_kernel(tt, oracle, torch_cuda, monkeypatch, H, Hkv, D):
+    """Dense grouped decode with group >= 4 can run as a [B,Hkv,G,D] forward problem on the tcgen05
+    kernel (the default once B*Hkv fills the GPU); both routes must agree with the oracle."""
+    torch = torch_cuda
+    B, L = 2, 1000
+    q, k, v, _ = make_grouped(oracle, 140 + H, B, H, Hkv, 1, L, D, True)
+    tq, tk, tv = (torch.from_numpy(a).cuda().bfloat16() for a in (q, k, v))
+    o_r, lse_r = dense_decode_ref(oracle, q, k, v)
+    for route in ("tc", "simt"):
+        monkeypatch.setenv("TT_DECODE_GQA_PATH", route)
+        before = tt.capi.launch_count()
+        out, lse = tt.attention_decode(tq, tk, tv)
+        tt.check_device_status()
+        assert tt.capi.launch_count() - before == (1 if route == "tc" else 2), route   # one forward launch vs split + merge
+        assert oracle.max_abs_err(out.float().cpu().numpy(), o_r) <= 2e-2, route
+        assert oracle.max_abs_err(lse.cpu().numpy(), lse_r) <= 1e-3, route
+    monkeypatch.delenv("TT_DECODE_GQA_PATH")
+
+
+@pytest.mark.parametrize("H,Hkv,D,page", [(8, 2, 128, 64), (4, 4, 64, 16), (8, 1, 128, 128), (6, 2, 64, 48)])
+def test_decode_paged_and_ragged(tt, oracle, torch_cuda, H, Hkv, D, page):
+    torch = torch_cuda
+    rng = np.random.default_rng(H * 100 + page)
+    B, max_pages = 5, 12
+    cap = page * max_pages
+    lens = np.array([cap, 0, 1, page * 3 + 5, cap - 7], np.int32)
+    q, k, v, _ = make_grouped(oracle, 120 + page, B, H, Hkv, 1, cap, D, True)
+    # scatter the dense cache into a shuffled page pool with some unused pages
+    n_pages = B * max_pages + 9
+    perm = rng.permutation(n_pages)[:B * max_pages].astype(np.int32).reshape(B, max_pages)
+    k_pool = rng.standard_normal((n_pages, Hkv, page, D)).astype(np.float32)   # unused pages hold noise
+    v_pool = rng.standard_normal((n_pages, Hkv, page, D)).astype(np.float32)
+    for b in range(B):
+        for pg in range(max_pages):
+            k_pool[perm[b, pg]] = k[b, :, pg * page:(pg + 1) * page]
+            v_pool[perm[b, pg]] = v[b, :, pg * page:(pg + 1) * page]
+    tq = torch.from_numpy(q).cuda().bfloat16()
+    tkp, tvp = (torch.from_numpy(a).cuda().bfloat16() for a in (k_pool, v_pool))
+    table, tl = torch.from_numpy(perm).cuda(), torch.from_numpy(lens).cuda()
+    o_r, lse_r = dense_decode_ref(oracle, q, k, v, lens)
+    out, lse = tt.attention_decode_paged(tq, tkp, tvp, block_table=table, seq_lens=tl)
+    tt.check_device_status()
+    assert oracle.max_abs_err(out.float().cpu().numpy(), o_r) <= 2e-2
+    got_lse = lse.cpu().numpy()
+    assert np.isneginf(got_lse[1]).all() and float(out[1].float().abs().max()) == 0.0   # the empty sequence
+    keep = lens > 0
+    assert oracle.max_abs_err(got_lse[keep], lse_r[keep]) <= 1e-3
+    # dense cache with lengths, and the paged call without lengths (= every page full)
+    tk, tv = (torch.from_numpy(a).cuda().bfloat16() for a in (k, v))
+    out2, _ = tt.attention_decode_paged(tq, tk, tv, seq_lens=tl)
+    assert torch.equal(out2, out)
+    out3, _ = tt.attention_decode_paged(tq, tkp, tvp, block_table=table)
+    o_full, _ = dense_decode_ref(oracle, q, k, v)
+    assert oracle.max_abs_err(out3.float().cpu().numpy(), o_full) <= 2e-2
+
+
+def test_variant_argument_errors(tt, torch_cuda):
+    torch = torch_cuda
+    q = torch.randn(2, 6, 1, 64, device="cuda").bfloat16()
+    with pytest.raises(ValueError):
+        tt.attention_decode(q, torch.randn(2, 4, 100, 64, device="cuda").bfloat16(), torch.randn(2, 4, 100, 64, device="cuda").bfloat16())
+    pool = torch.randn(10, 2, 16, 64, device="cuda").bfloat16()
+    table = torch.zeros(2, 3, dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError):
+        tt.attention_decode_paged(q, pool, pool, block_table=table, max_len=16 * 3 + 1)     # longer than the table covers
+    with pytest.raises(ValueError):
+        tt.attention_decode_paged(q, pool, pool, block_table=table.long())
+    with pytest.raises(ValueError):
+        tt.attention_decode_paged(q.float(), pool.float(), pool.float(), block_table=table)
+    c = tt.capi
+    import ctypes
+    d = c.make_desc(2, 6, 8, 8, 64, c.TT_BF16, False, None, Hkv=4)
+    assert c.lib.tt_attn_fwd(ctypes.byref(d), None, None, None, None, None, None) == c.TT_ERR_BAD_SHAPE
