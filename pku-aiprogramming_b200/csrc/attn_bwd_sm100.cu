@@ -136,9 +136,21 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
     unsigned char* aux = smem + (2 + 2 * kStages) * Cfg::kTileBytes;
     uint64_t* bar_res_full = reinterpret_cast<uint64_t*>(aux);   // TMA -> MMA (resident pair)
     uint64_t* bar_res_empty = bar_res_full + 1;                  // MMA (last score GEMMs of the item) -> TMA
-    uint64_t* bar_st_full = bar_res_empty + 1;                   // [kStages]
-    uint64_t* bar_st_empty = bar_st_full + kStages;              // [kStages]
-    uint64_t* bar_s_full = bar_st_empty + kStages;
+    // The two streamed tensors have rings of their own (kN0 + kN1 = 2 * kStages tiles of shared memory).
+    // T0 (Q | K) is read by the first score GEMM of a tile, issued half an iteration EARLY, and by the
+    // last accumulation GEMM of the tile; T1 (dO | V) by the second score GEMM and, with keys
+    // resident, by dV.  With queries resident V is dead as soon as dP is computed, so one slot is
+    // enough for it and K gets three: K(t+1) must have landed when iteration t has barely begun, and
+    // with two slots its load could only start at the end of iteration t-1 (measured: the MMA warp
+    // waited ~1300 cycles per tile for it).
+    constexpr int kN1 = kKeysResident ? kStages : kStages / 2;   // D = 128: 2 | 1 slots;  D = 64: 4 | 2
+    constexpr int kN0 = 2 * kStages - kN1;                       // D = 128: 2 | 3 slots;  D = 64: 4 | 6
+    static_assert(kN0 <= 6 && kN1 <= 4 && kN1 >= 1, "barrier arrays below are sized for these ring lengths");
+    uint64_t* bar_t0_full = bar_res_empty + 1;                   // [6]
+    uint64_t* bar_t0_empty = bar_t0_full + 6;                    // [6]
+    uint64_t* bar_t1_full = bar_t0_empty + 6;                    // [4]
+    uint64_t* bar_t1_empty = bar_t1_full + 4;                    // [4]
+    uint64_t* bar_s_full = bar_t1_empty + 4;
     uint64_t* bar_dp_full = bar_s_full + 1;
     uint64_t* bar_p_full = bar_dp_full + 1;
     uint64_t* bar_ds_full = bar_p_full + 1;
@@ -159,9 +171,13 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
         *abort_flag = 0;
         mbar_init(bar_res_full, 1);
         mbar_init(bar_res_empty, 1);
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&bar_st_full[s], 1);
-            mbar_init(&bar_st_empty[s], 1);
+        for (int s = 0; s < kN0; ++s) {
+            mbar_init(&bar_t0_full[s], 1);
+            mbar_init(&bar_t0_empty[s], 1);
+        }
+        for (int s = 0; s < kN1; ++s) {
+            mbar_init(&bar_t1_full[s], 1);
+            mbar_init(&bar_t1_empty[s], 1);
         }
         mbar_init(bar_s_full, 1);
         mbar_init(bar_dp_full, 1);
@@ -231,14 +247,20 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             // of streamed query (ctid & 127), one tile ahead of its use
             const float* stat_src = (ctid < 128 ? p.lse2 : p.delta);
             const float stat_oob = (ctid < 128) ? -INFINITY : 0.f;
-            auto stat_fetch = [&](int u) -> float {   // statistic of streamed query (ctid & 127) of streamed tile u
+            // The load of the next tile's statistic is issued a whole iteration before its value is
+            // used: nothing may consume `stat_raw` (not even a negation or a select) until the store
+            // at the top of the next iteration, or the warp waits out the load latency right here
+            // (measured: ~1100 cycles per tile).
+            float stat_raw = 0.f;
+            bool stat_ok = false;
+            auto stat_issue = [&](int u) {   // statistic of streamed query (ctid & 127) of streamed tile u
                 int tt, qs;
                 bwd_stream_tile<kKeysResident>(w, u, p.group, tt, qs);
                 const int qrow = tt * 128 + (ctid & 127);
-                return qrow < p.S ? -stat_src[(long long)qs * p.S + qrow] : stat_oob;
+                stat_ok = qrow < p.S;
+                if (stat_ok) stat_raw = stat_src[(long long)qs * p.S + qrow];
             };
-            float stat_next = stat_oob;
-            if (kKeysResident && w.n_it > 0) stat_next = stat_fetch(0);
+            if (kKeysResident && w.n_it > 0) stat_issue(0);
             for (int u = 0; u < w.n_it; ++u, ++git) {
                 const int it = u;
                 const int t = kKeysResident ? w.t_begin + u % w.nt : w.t_begin + u;
@@ -248,9 +270,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 const float* st_nlse = s_stat + (git & 1) * 256;   // -lse2 of the 128 streamed queries
                 const float* st_ndelta = st_nlse + 128;            // -delta
                 if (kKeysResident) {
-                    s_stat[(git & 1) * 256 + ctid] = stat_next;
+                    s_stat[(git & 1) * 256 + ctid] = stat_ok ? -stat_raw : stat_oob;
                     named_bar_sync(1, 256);
-                    if (u + 1 < w.n_it) stat_next = stat_fetch(u + 1);
+                    if (u + 1 < w.n_it) stat_issue(u + 1);
                 }
                 // visible columns of this thread's row inside the tile: [vis_lo, vis_hi)
                 int vis_lo = 0, vis_hi = 128;
@@ -417,16 +439,21 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 }
                 __syncwarp();
                 for (int u = 0; u < w.n_it; ++u, ++git) {
-                    const int st = git % kStages;
+                    const int s0 = git % kN0, s1 = git % kN1;
                     int t, ts;
                     bwd_stream_tile<kKeysResident>(w, u, p.group, t, ts);
-                    mbar_wait(&bar_st_empty[st], ((git / kStages) & 1) ^ 1, wctx, BB_STEMPTY + st, (int)git);
+                    mbar_wait(&bar_t0_empty[s0], ((git / kN0) & 1) ^ 1, wctx, BB_STEMPTY + s0, (int)git);
                     __syncwarp();
                     if (elect_one()) {
-                        mbar_arrive_expect_tx(&bar_st_full[st], 2 * Cfg::kTileBytes);
-                        unsigned char* dst = sT + st * 2 * Cfg::kTileBytes;
-                        load_tile(dst, &tmT0, &bar_st_full[st], t * 128, ts);
-                        load_tile(dst + Cfg::kTileBytes, &tmT1, &bar_st_full[st], t * 128, ts);
+                        mbar_arrive_expect_tx(&bar_t0_full[s0], Cfg::kTileBytes);
+                        load_tile(sT + s0 * Cfg::kTileBytes, &tmT0, &bar_t0_full[s0], t * 128, ts);
+                    }
+                    __syncwarp();
+                    mbar_wait(&bar_t1_empty[s1], ((git / kN1) & 1) ^ 1, wctx, BB_STEMPTY + 6 + s1, (int)git);
+                    __syncwarp();
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&bar_t1_full[s1], Cfg::kTileBytes);
+                        load_tile(sT + (kN0 + s1) * Cfg::kTileBytes, &tmT1, &bar_t1_full[s1], t * 128, ts);
                     }
                     __syncwarp();
                 }
@@ -443,19 +470,19 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             const uint64_t dR_base = umma_smem_desc(sR_addr, 16, 1024);                   // K-major
             const uint64_t dT_base = umma_smem_desc(sT_addr, 16, 1024);                   // K-major
             const uint64_t dT_mn_base = umma_smem_desc(sT_addr, Cfg::kSubBytes, 1024);    // MN-major
-            // G1 / G2: tmem[col] = R_which T_which^T for the pair in `slot`
-            auto issue_score = [&](int which, int slot, uint32_t col) {
+            // G1 / G2: tmem[col] = R_which T^T for the streamed tile at index `tile` of the stream buffers
+            auto issue_score = [&](int which, int tile, uint32_t col) {
                 const uint64_t a0 = umma_desc_advance(dR_base, which * Cfg::kTileBytes);
-                const uint64_t b0 = umma_desc_advance(dT_base, (slot * 2 + which) * Cfg::kTileBytes);
+                const uint64_t b0 = umma_desc_advance(dT_base, tile * Cfg::kTileBytes);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t o = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
                     umma_ss(tmem_u + col, umma_desc_advance(a0, o), umma_desc_advance(b0, o), idesc_s, kk > 0);
                 }
             };
-            // G3 / G4: tmem[acc] (+)= bf16 A at tmem[a_col] (two 32-column halves) times T_which (MN-major)
-            auto issue_acc = [&](int which, int slot, uint32_t a_col, uint32_t acc_col, bool accumulate) {
-                const uint64_t b0 = umma_desc_advance(dT_mn_base, (slot * 2 + which) * Cfg::kTileBytes);
+            // G3 / G4: tmem[acc] (+)= bf16 A at tmem[a_col] (two 32-column halves) times the streamed tile (MN-major)
+            auto issue_acc = [&](int tile, uint32_t a_col, uint32_t acc_col, bool accumulate) {
+                const uint64_t b0 = umma_desc_advance(dT_mn_base, tile * Cfg::kTileBytes);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     const uint32_t a = tmem_u + a_col + (kk >> 2) * 64 + (kk & 3) * 8;
@@ -477,21 +504,25 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 if (n_it > 0) {
                     // first scores of the item; the S / dP columns are free because the G3 / G4 of the
                     // previous item were issued earlier by this warp and execute in order
-                    const int st0 = git % kStages;
-                    mbar_wait(&bar_st_full[st0], (git / kStages) & 1, wctx, BB_STFULL + st0, (int)git);
+                    const int f0 = git % kN0, f1 = git % kN1;
+                    mbar_wait(&bar_t0_full[f0], (git / kN0) & 1, wctx, BB_STFULL + f0, (int)git);
                     __syncwarp();
                     tc_fence_after();
-                    issue_score(0, st0, kColS);
+                    issue_score(0, f0, kColS);
                     tc_commit(bar_s_full);
-                    issue_score(1, st0, kColDP);
+                    mbar_wait(&bar_t1_full[f1], (git / kN1) & 1, wctx, BB_STFULL + 6 + f1, (int)git);
+                    __syncwarp();
+                    tc_fence_after();
+                    issue_score(1, kN0 + f1, kColDP);
                     tc_commit(bar_dp_full);
+                    if (!kKeysResident) tc_commit(&bar_t1_empty[f1]);   // dP was the only use of this V tile
                     if (n_it == 1) tc_commit(bar_res_empty);   // those were the item's last reads of the resident pair
                 }
                 for (int it = 0; it < n_it; ++it) {
                     const uint32_t g = git + it;
-                    const int slot = g % kStages;
+                    const int a0s = g % kN0, a1s = g % kN1;                  // slots of this tile
                     const bool has_next = it + 1 < n_it;
-                    const int nslot = (g + 1) % kStages;
+                    const int n0s = (g + 1) % kN0, n1s = (g + 1) % kN1;      // slots of the next tile
                     const bool tr = (k == 0 && lane == 0);
                     if (tr) TT_BTRACE(2, it, 0);
                     mbar_wait(bar_p_full, g & 1, wctx, BB_PFULL, it);
@@ -503,12 +534,15 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                         mbar_wait(bar_acc_free, (k & 1) ^ 1, wctx, BB_FINAL + 1, k);
                         __syncwarp();
                     }
-                    if (kKeysResident) issue_acc(1, slot, kColS, kColAcc0, it > 0);     // dV += P^T dO
+                    if (kKeysResident) {
+                        issue_acc(kN0 + a1s, kColS, kColAcc0, it > 0);                   // dV += P^T dO
+                        tc_commit(&bar_t1_empty[a1s]);                                   // last read of dO(t)
+                    }
                     if (has_next) {
-                        mbar_wait(&bar_st_full[nslot], ((g + 1) / kStages) & 1, wctx, BB_STFULL + nslot, it + 1);
+                        mbar_wait(&bar_t0_full[n0s], ((g + 1) / kN0) & 1, wctx, BB_STFULL + n0s, it + 1);
                         __syncwarp();
                         tc_fence_after();
-                        issue_score(0, nslot, kColS);
+                        issue_score(0, n0s, kColS);
                         tc_commit(bar_s_full);
                     }
                     if (tr) TT_BTRACE(2, it, 2);
@@ -516,11 +550,15 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                     __syncwarp();
                     tc_fence_after();
                     if (tr) TT_BTRACE(2, it, 3);
-                    issue_acc(0, slot, kColDP, kColAcc1, it > 0);                        // dK += dS^T Q | dQ += dS K
-                    tc_commit(&bar_st_empty[slot]);
+                    issue_acc(a0s, kColDP, kColAcc1, it > 0);                            // dK += dS^T Q | dQ += dS K
+                    tc_commit(&bar_t0_empty[a0s]);                                       // last read of Q(t) | K(t)
                     if (has_next) {
-                        issue_score(1, nslot, kColDP);
+                        mbar_wait(&bar_t1_full[n1s], ((g + 1) / kN1) & 1, wctx, BB_STFULL + 6 + n1s, it + 1);
+                        __syncwarp();
+                        tc_fence_after();
+                        issue_score(1, kN0 + n1s, kColDP);
                         tc_commit(bar_dp_full);
+                        if (!kKeysResident) tc_commit(&bar_t1_empty[n1s]);   // dP was the only use of V(t+1)
                         if (it + 2 == n_it) tc_commit(bar_res_empty);   // last reads of the resident pair
                     }
                     if (tr) TT_BTRACE(2, it, 4);
