@@ -243,20 +243,26 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 row_nlse2 = pack_f32x2(nl, nl);
                 row_ndelta2 = pack_f32x2(nd, nd);
             }
-            // per-column statistics (keys resident): thread ctid fetches -lse2 (ctid < 128) or -delta
-            // of streamed query (ctid & 127), one tile ahead of its use
-            const float* stat_src = (ctid < 128 ? p.lse2 : p.delta);
-            const float stat_oob = (ctid < 128) ? -INFINITY : 0.f;
+            // per-column statistics (keys resident): each warpgroup stages the statistics of ITS 64
+            // streamed queries (columns wg*64..+63), one tile ahead of their use -- thread j of the
+            // warpgroup fetches -lse2 (j < 64) or -delta (j >= 64) of query wg*64 + (j & 63) -- so the
+            // hand-over needs only a barrier among the warpgroup's own 128 threads and the two
+            // warpgroups are free to drift apart (they share the special-function units)
+            const int stat_j = ctid & 127;
+            const int stat_q = wg * 64 + (stat_j & 63);          // query inside the streamed tile
+            const int stat_slot = (stat_j >> 6) * 128 + stat_q;  // [-lse2 | -delta][128]
+            const float* stat_src = (stat_j < 64 ? p.lse2 : p.delta);
+            const float stat_oob = (stat_j < 64) ? -INFINITY : 0.f;
             // The load of the next tile's statistic is issued a whole iteration before its value is
             // used: nothing may consume `stat_raw` (not even a negation or a select) until the store
             // at the top of the next iteration, or the warp waits out the load latency right here
             // (measured: ~1100 cycles per tile).
             float stat_raw = 0.f;
             bool stat_ok = false;
-            auto stat_issue = [&](int u) {   // statistic of streamed query (ctid & 127) of streamed tile u
+            auto stat_issue = [&](int u) {   // this thread's statistic of streamed tile u
                 int tt, qs;
                 bwd_stream_tile<kKeysResident>(w, u, p.group, tt, qs);
-                const int qrow = tt * 128 + (ctid & 127);
+                const int qrow = tt * 128 + stat_q;
                 stat_ok = qrow < p.S;
                 if (stat_ok) stat_raw = stat_src[(long long)qs * p.S + qrow];
             };
@@ -270,8 +276,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 const float* st_nlse = s_stat + (git & 1) * 256;   // -lse2 of the 128 streamed queries
                 const float* st_ndelta = st_nlse + 128;            // -delta
                 if (kKeysResident) {
-                    s_stat[(git & 1) * 256 + ctid] = stat_ok ? -stat_raw : stat_oob;
-                    named_bar_sync(1, 256);
+                    s_stat[(git & 1) * 256 + stat_slot] = stat_ok ? -stat_raw : stat_oob;
+                    named_bar_sync(1 + wg, 128);
                     if (u + 1 < w.n_it) stat_issue(u + 1);
                 }
                 // visible columns of this thread's row inside the tile: [vis_lo, vis_hi)
@@ -291,23 +297,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 tc_fence_after();
                 if (tr) TT_BTRACE(wg, it, 2);
                 uint64_t pf2[32];     // this thread's 64 probabilities, fp32 pairs
-                uint32_t sr[2][32];
-                if (!kKeysResident) {
-                    // nothing is written back into the S columns in this pass: release them as soon as
-                    // they are in registers so that the next tile's scores overlap these exponentials
-                    tmem_ld32(tS, sr[0]);
-                    tmem_ld32(tS + 32, sr[1]);
-                    tmem_wait_ld();
-                    tc_fence_before();
-                    mbar_arrive(bar_p_full);
-                }
-#pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    if (kKeysResident) {
-                        tmem_ld32(tS + cc * 32, sr[cc]);
-                        tmem_wait_ld();
-                    }
-                    uint32_t pk[16];
+                uint32_t sr[2][32], dr[2][32];
+                // Nothing is written back into the S columns: they are released as soon as they are in
+                // registers, so the next tile's score GEMM runs under these exponentials.  (With keys
+                // resident the bf16 P^T that dV needs joins dS^T in the dP columns in phase B.)
+                auto phase_a = [&](int cc) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
                         const int col = wg * 64 + cc * 32 + e;
@@ -327,38 +321,54 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                             p1 = (col + 1 >= vis_lo && col + 1 < vis_hi) ? p1 : 0.f;
                         }
                         pf2[cc * 16 + (e >> 1)] = pack_f32x2(p0, p1);
-                        if (kKeysResident) pk[e >> 1] = pack_bf16x2(p0, p1);
                     }
-                    if (kKeysResident) tmem_st16(tS + cc * 16, pk);
-                }
-                if (kKeysResident) {
-                    tmem_wait_st();
-                    tc_fence_before();
-                    mbar_arrive(bar_p_full);
-                }
+                };
+                // dS = P * (dP - delta) for one chunk, written over the dP columns just read
+                auto phase_b = [&](int cc) {
+                    uint32_t pk[16], pkp[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const int col = wg * 64 + cc * 32 + e;
+                        const uint64_t nd = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_ndelta + col) : row_ndelta2;
+                        const uint64_t tdiff = add_f32x2(pack_f32x2(__uint_as_float(dr[cc][e]), __uint_as_float(dr[cc][e + 1])), nd);
+                        const uint64_t ds = mul_f32x2(pf2[cc * 16 + (e >> 1)], tdiff);
+                        float x0, x1;
+                        unpack_f32x2(ds, x0, x1);
+                        pk[e >> 1] = pack_bf16x2(x0, x1);
+                        if (kKeysResident) {
+                            float q0, q1;
+                            unpack_f32x2(pf2[cc * 16 + (e >> 1)], q0, q1);
+                            pkp[e >> 1] = pack_bf16x2(q0, q1);
+                        }
+                    }
+                    if (kKeysResident) {
+                        // the 32 fp32 dP columns just read now hold 16 columns of bf16 P^T and 16 of dS^T
+                        tmem_st16(tDP + cc * 32, pkp);
+                        tmem_st16(tDP + cc * 32 + 16, pk);
+                    } else {
+                        tmem_st16(tDP + cc * 16, pk);
+                    }
+                };
+                // (Issuing these loads further ahead of their use -- both chunks at once, or one chunk
+                // ahead under the previous chunk's arithmetic -- was measured slower, twice.)
+                tmem_ld32(tS, sr[0]);
+                tmem_wait_ld();
+                phase_a(0);
+                tmem_ld32(tS + 32, sr[1]);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(bar_p_full);                // all of S(t) is in registers: its columns are free
+                phase_a(1);
                 if (tr) TT_BTRACE(wg, it, 3);
-                // ---------------- phase B: dS = P * (dP - delta)
                 mbar_wait(bar_dp_full, git & 1, wctx, BB_DPFULL, it);
                 __syncwarp();
                 tc_fence_after();
                 if (tr) TT_BTRACE(wg, it, 4);
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
-                    uint32_t dr[32];
-                    tmem_ld32(tDP + cc * 32, dr);
+                    tmem_ld32(tDP + cc * 32, dr[cc]);
                     tmem_wait_ld();
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const int col = wg * 64 + cc * 32 + e;
-                        const uint64_t nd = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_ndelta + col) : row_ndelta2;
-                        const uint64_t tdiff = add_f32x2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), nd);
-                        const uint64_t ds = mul_f32x2(pf2[cc * 16 + (e >> 1)], tdiff);
-                        float x0, x1;
-                        unpack_f32x2(ds, x0, x1);
-                        pk[e >> 1] = pack_bf16x2(x0, x1);
-                    }
-                    tmem_st16(tDP + cc * 16, pk);
+                    phase_b(cc);
                 }
                 tmem_wait_st();
                 tc_fence_before();
@@ -480,12 +490,17 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                     umma_ss(tmem_u + col, umma_desc_advance(a0, o), umma_desc_advance(b0, o), idesc_s, kk > 0);
                 }
             };
-            // G3 / G4: tmem[acc] (+)= bf16 A at tmem[a_col] (two 32-column halves) times the streamed tile (MN-major)
-            auto issue_acc = [&](int tile, uint32_t a_col, uint32_t acc_col, bool accumulate) {
+            // G3 / G4: tmem[acc] (+)= bf16 A in tensor memory times the streamed tile (MN-major).  A is what
+            // phase B left in the dP columns: with queries resident, each warpgroup's 64 dS values in the
+            // first 32 of its 64 columns; with keys resident, per 32-column chunk 16 columns of P^T
+            // (part = 0) then 16 of dS^T (part = 1).  K step kk covers 16 streamed rows = 8 columns.
+            auto issue_acc = [&](int tile, int part, uint32_t acc_col, bool accumulate) {
                 const uint64_t b0 = umma_desc_advance(dT_mn_base, tile * Cfg::kTileBytes);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t a = tmem_u + a_col + (kk >> 2) * 64 + (kk & 3) * 8;
+                    const uint32_t in_wg = kKeysResident ? (uint32_t)(((kk & 3) >> 1) * 32 + part * 16 + (kk & 1) * 8)
+                                                         : (uint32_t)((kk & 3) * 8);
+                    const uint32_t a = tmem_u + kColDP + (kk >> 2) * 64 + in_wg;
                     umma_ts(tmem_u + acc_col, a, umma_desc_advance(b0, kk * 2048), idesc_acc,
                             (accumulate || kk > 0) ? 1u : 0u);
                 }
@@ -525,19 +540,10 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                     const int n0s = (g + 1) % kN0, n1s = (g + 1) % kN1;      // slots of the next tile
                     const bool tr = (k == 0 && lane == 0);
                     if (tr) TT_BTRACE(2, it, 0);
-                    mbar_wait(bar_p_full, g & 1, wctx, BB_PFULL, it);
+                    mbar_wait(bar_p_full, g & 1, wctx, BB_PFULL, it);   // S(t) is in registers: its columns are free
                     __syncwarp();
                     tc_fence_after();
                     if (tr) TT_BTRACE(2, it, 1);
-                    if (it == 0) {
-                        // the accumulator columns must have been read out by the previous item's epilogue
-                        mbar_wait(bar_acc_free, (k & 1) ^ 1, wctx, BB_FINAL + 1, k);
-                        __syncwarp();
-                    }
-                    if (kKeysResident) {
-                        issue_acc(kN0 + a1s, kColS, kColAcc0, it > 0);                   // dV += P^T dO
-                        tc_commit(&bar_t1_empty[a1s]);                                   // last read of dO(t)
-                    }
                     if (has_next) {
                         mbar_wait(&bar_t0_full[n0s], ((g + 1) / kN0) & 1, wctx, BB_STFULL + n0s, it + 1);
                         __syncwarp();
@@ -546,11 +552,20 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                         tc_commit(bar_s_full);
                     }
                     if (tr) TT_BTRACE(2, it, 2);
-                    mbar_wait(bar_ds_full, g & 1, wctx, BB_DSFULL, it);
+                    mbar_wait(bar_ds_full, g & 1, wctx, BB_DSFULL, it);  // dS^T (and P^T) are in the dP columns
                     __syncwarp();
                     tc_fence_after();
                     if (tr) TT_BTRACE(2, it, 3);
-                    issue_acc(a0s, kColDP, kColAcc1, it > 0);                            // dK += dS^T Q | dQ += dS K
+                    if (it == 0) {
+                        // the accumulator columns must have been read out by the previous item's epilogue
+                        mbar_wait(bar_acc_free, (k & 1) ^ 1, wctx, BB_FINAL + 1, k);
+                        __syncwarp();
+                    }
+                    if (kKeysResident) {
+                        issue_acc(kN0 + a1s, 0, kColAcc0, it > 0);                       // dV += P^T dO
+                        tc_commit(&bar_t1_empty[a1s]);                                   // last read of dO(t)
+                    }
+                    issue_acc(a0s, kKeysResident ? 1 : 0, kColAcc1, it > 0);             // dK += dS^T Q | dQ += dS K
                     tc_commit(&bar_t0_empty[a0s]);                                       // last read of Q(t) | K(t)
                     if (has_next) {
                         mbar_wait(&bar_t1_full[n1s], ((g + 1) / kN1) & 1, wctx, BB_STFULL + 6 + n1s, it + 1);

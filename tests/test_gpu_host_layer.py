@@ -205,3 +205,47 @@ def test_fc_op_numpy_and_device_resident(opt, oracle, mods, dtype):
     assert b1.grad.shape == (1,) and ok(b1.grad.numpy(), oracle.fc_backward(x0, w0, g0, scalar_bias=True)[2])
     y = opt.fc(opt.Tensor(x0), opt.Tensor(w0), opt.Tensor(b0), use_bias=False, dtype=dtype)
     assert ok(y.numpy(), oracle.fc_forward(x0, w0))
+
+
+def test_projection_attention_projection_block_on_device(opt, oracle, mods):
+    """x -> FC (qkv) -> attention -> FC (out), every node device-resident bf16, against the same
+    block built from this package's NumPy ops (the reference's way of writing it)."""
+    rng = np.random.default_rng(21)
+    B, H, S, D = 1, 2, 128, 64
+    E = H * D
+    r = lambda *shape, s=1.0: oracle.bf16_round((rng.standard_normal(shape) * s).astype(np.float32))
+    x0, wq0, wk0, wv0, wo0 = r(B * S, E), r(E, E, s=E ** -0.5), r(E, E, s=E ** -0.5), r(E, E, s=E ** -0.5), r(E, E, s=E ** -0.5)
+    bz0, g0 = np.zeros(E, np.float32), r(B * S, E)
+
+    def heads(t):    # [B*S, H*D] -> [B,H,S,D]
+        return opt.transpose(opt.reshape(t, (B, S, H, D)), (1, 2))
+
+    # NumPy-backed graph (CPU): matmul + composed attention
+    x, wq, wk, wv, wo = (opt.Tensor(a) for a in (x0, wq0, wk0, wv0, wo0))
+    q, k, v = heads(x @ wq), heads(x @ wk), heads(x @ wv)
+    o = opt.attention_composed(q, k, v, causal=True)
+    y_ref = opt.reshape(opt.transpose(o, (1, 2)), (B * S, E)) @ wo
+    y_ref.backward(opt.Tensor(g0, requires_grad=False))
+
+    # device graph: the projections and attention run on the GPU; the head split/merge is a
+    # layout change the device tensors do not offer, so q, k, v are produced per head instead
+    kw = dict(device="gpu", dtype="bfloat16")
+    xd, wod, bd = opt.Tensor(x0, **kw), opt.Tensor(wo0, **kw), opt.Tensor(bz0, **kw)
+    outs = []
+    wgrads = []
+    for h in range(H):
+        cols = slice(h * D, (h + 1) * D)
+        wqh, wkh, wvh = (opt.Tensor(np.ascontiguousarray(w[:, cols]), **kw) for w in (wq0, wk0, wv0))
+        bh = opt.Tensor(np.zeros(D, np.float32), **kw)
+        qh, kh, vh = (opt.fc(xd, w, bh, use_bias=False) for w in (wqh, wkh, wvh))      # [S, D] each
+        as4 = lambda t: opt.Tensor(mods[0].Tensor_bf16(t.realize_cached_data()).resize([1, 1, S, D]), **kw)
+        oh = opt.attention(as4(qh), as4(kh), as4(vh), causal=True)
+        assert oh.is_device
+        outs.append(oh.numpy().reshape(S, D))
+        wgrads.append((wqh, wkh, wvh))
+    o_dev = np.concatenate(outs, axis=1)                                                 # [S, E]
+    y = opt.fc(opt.Tensor(oracle.bf16_round(o_dev), **kw), wod, bd, use_bias=False)
+    assert y.is_device
+    tol = lambda ref: 2e-2 + 2.0 ** -7 * np.abs(ref).max()
+    assert oracle.max_abs_err(o_dev, np.transpose(o.numpy(), (0, 2, 1, 3)).reshape(B * S, E)) <= tol(o.numpy())
+    assert oracle.max_abs_err(y.numpy(), y_ref.numpy()) <= tol(y_ref.numpy())
