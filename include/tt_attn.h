@@ -116,6 +116,20 @@ int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const
 int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k, const void* v,
                           void* out, float* lse, void* stream);
 
+/* ---- padded batches -------------------------------------------------------------------------
+ * tt_attn_fwd / tt_attn_bwd with a key padding length per batch entry (no counterpart in the
+ * reference): kv_lens is a device array of B int32; batch entry b attends to its first kv_lens[b]
+ * keys (clamped to 1..L), the rest of its k, v rows is padding.  dk, dv rows of padded keys are
+ * zero.  Query rows are all computed (give padded queries a zero dout).  The causal mask keeps its
+ * alignment to the full L.  Padding rows must hold finite values (zeros are customary): a masked
+ * probability of exactly 0 still meets them in the P.V and dS.K products.  kv_lens == NULL is the
+ * unpadded call. */
+int tt_attn_fwd_padded(const tt_attn_desc* desc, const void* q, const void* k, const void* v, const int32_t* kv_lens,
+                       void* out, float* lse, void* stream);
+int tt_attn_bwd_padded(const tt_attn_desc* desc, const void* q, const void* k, const void* v, const int32_t* kv_lens,
+                       const void* out, const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- decode over a paged and/or ragged key/value cache -----------------------------------
  * tt_attn_decode for serving-style caches (no counterpart in the reference).  bf16, D = 64 or
  * 128, S = 1; desc->L is the longest sequence any batch entry may have.

@@ -35,6 +35,8 @@ SIGNATURES = {
     "tt_attn_fwd": (c_int, [_DP, _P, _P, _P, _P, _P, _P]),
     "tt_attn_bwd_workspace_bytes": (c_size_t, [_DP]),
     "tt_attn_bwd": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
+    "tt_attn_fwd_padded": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P]),
+    "tt_attn_bwd_padded": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
     "tt_attn_decode_workspace_bytes": (c_size_t, [_DP]),
     "tt_attn_decode": (c_int, [_DP, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
     "tt_attn_decode_paged": (c_int, [_DP, _P, _P, _P, _P, _P, c_int32, c_int32, _P, _P, _P, c_size_t, _P]),

@@ -59,6 +59,8 @@ struct BwdParams {
     unsigned int* sched_counter;   // zero at launch; work items are taken with atomicAdd
     int n_items;                   // resident slices * n_tiles
     int group;                     // query heads per key/value head (1 = ordinary multi-head attention)
+    const int* kv_lens;            // optional key padding lengths per batch entry (see AttnArgs)
+    int H;                         // query heads per batch entry
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
 };
@@ -88,6 +90,7 @@ struct BwdItem {
     int r0, t_begin, t_end;
     int nt;        // streamed tiles per streamed slice
     int n_it;      // streamed tiles of the item (nt x group when keys are resident)
+    int Lv;        // keys that count for this slice (<= L; fewer with key padding)
 };
 template <bool kKeysResident>
 __device__ __forceinline__ void bwd_stream_tile(const BwdItem& w, int u, int group, int& t, int& slice) {
@@ -105,14 +108,19 @@ __device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p)
     BwdItem w;
     const int off = p.L - p.S;
     w.bh = item / p.n_tiles;
+    // batch entry: a resident key/value slice is bh / (H / group), a resident query slice bh / H
+    w.Lv = valid_keys(p.kv_lens, kKeysResident ? ((long long)w.bh * p.group) / p.H : (long long)w.bh / p.H, p.L);
     int rt;
     if (kKeysResident) {
         rt = item % p.n_tiles;                                        // early key tiles are the heavy ones
         w.t_end = (p.S + 127) >> 7;
         w.t_begin = p.causal ? (max(0, rt * 128 - off) >> 7) : 0;
+        // a key tile that is all padding gets zero gradients: one streamed tile keeps the pipeline's
+        // hand-offs alive, the epilogue writes zeros
+        if (rt * 128 >= w.Lv) w.t_end = min(w.t_end, w.t_begin + 1);
     } else {
         rt = p.n_tiles - 1 - (item % p.n_tiles);                      // late query tiles are the heavy ones
-        const int n_kv = (p.L + 127) >> 7;
+        const int n_kv = (w.Lv + 127) >> 7;
         w.t_begin = 0;
         w.t_end = p.causal ? min(n_kv, ((min(rt * 128 + 127, p.S - 1) + off) >> 7) + 1) : n_kv;
     }
@@ -285,7 +293,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 if (kKeysResident) {
                     if (p.causal) vis_lo = max(0, rrow - off - c0);           // query >= key - off
                 } else {
-                    vis_hi = p.L - c0;
+                    vis_hi = w.Lv - c0;
                     if (p.causal) vis_hi = min(vis_hi, rrow + off + 1 - c0);  // key <= query + off
                     vis_hi = min(vis_hi, 128);
                 }
@@ -399,6 +407,12 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                     const bool is_acc0 = kKeysResident && a == 0;
                     __nv_bfloat16* dst = (is_acc0 ? p.out0 : p.out1) + ((long long)bh * n_rows + rrow) * D + wg * kHalf;
                     const float mul = is_acc0 ? 1.0f : p.scale;
+                    if (kKeysResident && rrow >= w.Lv) {   // gradients of padded keys are zero
+#pragma unroll
+                        for (int cc = 0; cc < kHalf / 32; ++cc)
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) acc[a][cc][e] = 0u;
+                    }
 #pragma unroll
                     for (int cc = 0; cc < kHalf / 32; ++cc) {
 #pragma unroll
@@ -687,6 +701,8 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.out0 = (__nv_bfloat16*)a.dv;
     p.out1 = (__nv_bfloat16*)a.dk;
     p.group = a.group;
+    p.kv_lens = a.kv_lens;
+    p.H = a.H;
     p.n_tiles = (a.L + 127) / 128;
     p.n_items = (int)(a.BH / a.group * p.n_tiles);
     p.sched_counter = next_bwd_sched_counter(st, &e);

@@ -58,6 +58,8 @@ struct FwdParams {
     unsigned int* sched_counter;   // zero at launch; work items are taken with atomicAdd
     int n_items;                   // slices * n_qblk
     int group;                     // query heads per key/value head: query slice bh reads key/value slice bh / group
+    const int* kv_lens;            // optional key padding lengths per batch entry (see AttnArgs)
+    int H;
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
 };
@@ -137,6 +139,7 @@ __device__ __forceinline__ uint64_t softmax_exp_half(const uint32_t (&sr)[4][32]
 // first MMAs of item n+1 overlap the epilogue (normalise, store O) of item n.
 struct FwdItem {
     int bh, q0, n_tiles[2], n_max;
+    int Lv;   // keys that count for this slice (<= L; fewer with key padding)
 };
 __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p) {
     FwdItem w;
@@ -144,7 +147,8 @@ __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p)
     const int qb = p.n_qblk - 1 - (item % p.n_qblk);
     w.q0 = qb * 256;
     const int off = p.L - p.S;
-    const int n_kv_total = (p.L + 127) >> 7;
+    w.Lv = valid_keys(p.kv_lens, w.bh / p.H, p.L);
+    const int n_kv_total = (w.Lv + 127) >> 7;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r0 = w.q0 + 128 * i;
@@ -267,10 +271,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 if (tr) TT_TRACE(i, j, 1);
                 // visible columns of this row inside the tile: [0, lim)
                 const int kv0 = j << 7;
-                const bool need_mask = (kv0 + 128 > p.L) || (p.causal && (kv0 + 127 > (w.q0 + 128 * i) + off));
+                const bool need_mask = (kv0 + 128 > w.Lv) || (p.causal && (kv0 + 127 > (w.q0 + 128 * i) + off));
                 int lim = 128;
                 if (need_mask) {
-                    lim = p.L;
+                    lim = w.Lv;
                     if (p.causal) lim = min(lim, row + off + 1);
                     lim -= kv0;
                 }
@@ -586,6 +590,8 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.n_qblk = (a.S + 255) / 256;
     p.causal = a.causal;
     p.group = a.group;
+    p.kv_lens = a.kv_lens;
+    p.H = a.H;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = device_status_word();
     p.trace = g_fwd_trace;

@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt_kernel(const T* __
                                                                       const T* __restrict__ k,
                                                                       const T* __restrict__ v, T* __restrict__ out,
                                                                       float* __restrict__ lse, int S, int L, int D,
-                                                                      int causal, float scale, int group) {
+                                                                      int causal, float scale, int group, const int* __restrict__ kv_lens, int H) {
     extern __shared__ float smem[];
     const int pitch = D + 1;
     float* sQ = smem;
@@ -88,8 +88,9 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt_kernel(const T* __
 #pragma unroll
         for (int t = 0; t < NV; ++t) o[r][t] = 0.f;
     }
+    const int Lv = valid_keys(kv_lens, bh / H, L);            // keys beyond it are padding
     int last_row = min(row0 + kRowsPerBlock, S) - 1;
-    int col_end = causal ? min(L, last_row + off + 1) : L;  // exclusive
+    int col_end = causal ? min(Lv, last_row + off + 1) : Lv;  // exclusive
     for (int c0 = 0; c0 < col_end; c0 += kColsPerTile) {
         __syncthreads();
         stage_rows<T>(sK, k, c0, L, D, 1.0f);
@@ -107,7 +108,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt_kernel(const T* __
         for (int r = 0; r < kRowsPerWarp; ++r) {
             const int row = row0 + warp * kRowsPerWarp + r;
             float sv = s[r] * scale;
-            bool valid = col < L && (!causal || col <= row + off);
+            bool valid = col < Lv && (!causal || col <= row + off);
             sv = valid ? sv : -INFINITY;
             float mnew = fmaxf(m[r], warp_max(sv));
             float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - mnew);
@@ -158,7 +159,7 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ dout,
     const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dq, int S, int L, int D,
-    int causal, float scale, int group) {
+    int causal, float scale, int group, const int* __restrict__ kv_lens, int H) {
     extern __shared__ float smem[];
     const int pitch = D + 1;
     float* sQ = smem;
@@ -189,8 +190,9 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt_kernel(
 #pragma unroll
         for (int t = 0; t < NV; ++t) acc[r][t] = 0.f;
     }
+    const int Lv = valid_keys(kv_lens, bh / H, L);
     int last_row = min(row0 + kRowsPerBlock, S) - 1;
-    int col_end = causal ? min(L, last_row + off + 1) : L;
+    int col_end = causal ? min(Lv, last_row + off + 1) : Lv;
     for (int c0 = 0; c0 < col_end; c0 += kColsPerTile) {
         __syncthreads();
         stage_rows<T>(sK, k, c0, L, D, 1.0f);
@@ -212,7 +214,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt_kernel(
 #pragma unroll
         for (int r = 0; r < kRowsPerWarp; ++r) {
             const int row = row0 + warp * kRowsPerWarp + r;
-            bool valid = col < L && row < S && (!causal || col <= row + off);
+            bool valid = col < Lv && row < S && (!causal || col <= row + off);
             float p = valid ? expf(s[r] * scale - row_lse[r]) : 0.f;
             float ds = p * (dp[r] - row_delta[r]);
             for (int jj = 0; jj < kColsPerTile; ++jj) {
@@ -242,7 +244,7 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ dout,
     const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dk, T* __restrict__ dv, int S,
-    int L, int D, int causal, float scale, int group) {
+    int L, int D, int causal, float scale, int group, const int* __restrict__ kv_lens, int H) {
     extern __shared__ float smem[];
     const int pitch = D + 1;
     float* sK = smem;
@@ -266,6 +268,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(
     lse += bh * group * S;
     delta += bh * group * S;
 
+    const int Lv = valid_keys(kv_lens, (bh * group) / H, L);   // padded keys get zero gradients
     stage_rows<T>(sK, k, key0, L, D, 1.0f);
     stage_rows<T>(sV, v, key0, L, D, 1.0f);
     float aK[kRowsPerWarp][NV], aV[kRowsPerWarp][NV];
@@ -303,7 +306,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(
 #pragma unroll
         for (int r = 0; r < kRowsPerWarp; ++r) {
             const int key = key0 + warp * kRowsPerWarp + r;
-            bool valid = i < S && key < L && (!causal || key <= i + off);
+            bool valid = i < S && key < Lv && (!causal || key <= i + off);
             float p = valid ? expf(s[r] * scale - sLse[lane]) : 0.f;
             float ds = p * (dp[r] - sDelta[lane]);
             for (int jj = 0; jj < kColsPerTile; ++jj) {
@@ -351,7 +354,7 @@ static cudaError_t launch_fwd_simt(const AttnArgs& a, cudaStream_t st) {
         LaunchScope ls(K_FWD_SIMT, st);
         attn_fwd_simt_kernel<T, NV><<<grid, kSimtThreads, smem, st>>>((const T*)a.q, (const T*)a.k, (const T*)a.v,
                                                                       (T*)a.out, a.lse, a.S, a.L, a.D, a.causal,
-                                                                      a.scale, a.group);
+                                                                      a.scale, a.group, a.kv_lens, a.H);
     }
     return cudaGetLastError();
 }
@@ -375,14 +378,14 @@ static cudaError_t launch_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t
         LaunchScope ls(K_BWD_SIMT_DQ, st);
         attn_bwd_dq_simt_kernel<T, NV><<<gq, kSimtThreads, smem_q, st>>>(
             (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dq, a.S, a.L, a.D,
-            a.causal, a.scale, a.group);
+            a.causal, a.scale, a.group, a.kv_lens, a.H);
     }
     unsigned gk = (unsigned)(((a.L + kRowsPerBlock - 1) / kRowsPerBlock) * (a.BH / a.group));
     {
         LaunchScope ls(K_BWD_SIMT_DKV, st);
         attn_bwd_dkv_simt_kernel<T, NV><<<gk, kSimtThreads, smem_kv, st>>>(
             (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dk, (T*)a.dv, a.S,
-            a.L, a.D, a.causal, a.scale, a.group);
+            a.L, a.D, a.causal, a.scale, a.group, a.kv_lens, a.H);
     }
     return cudaGetLastError();
 }

@@ -19,7 +19,15 @@ struct AttnArgs {
     void* out;
     float* lse;     // forward: written (may be null); backward: read
     void *dq, *dk, *dv;
+    // optional key padding: batch entry b attends to its first kv_lens[b] keys (1..L; device int32
+    // [B]); null = all L.  H = query heads per batch entry (batch entry of query slice bh = bh / H).
+    const int* kv_lens;
+    int H;
 };
+// keys that count for batch entry b (device side)
+__device__ __forceinline__ int valid_keys(const int* kv_lens, long long b, int L) {
+    return kv_lens ? min(L, max(1, kv_lens[b])) : L;
+}
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 

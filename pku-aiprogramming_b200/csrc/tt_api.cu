@@ -303,6 +303,8 @@ static int resolve(const tt_attn_desc* d, AttnArgs* a, const char* who) {
     memset(a, 0, sizeof(*a));
     a->BH = (long long)d->B * d->H;
     a->group = d->H / hkv;
+    a->H = d->H;
+    a->kv_lens = nullptr;
     a->S = d->S;
     a->L = d->L;
     a->D = d->D;
@@ -329,15 +331,16 @@ const char* tt_attn_bwd_path(const tt_attn_desc* desc) {
     return attn_bwd_sm100_supported(a) ? "tcgen05" : "simt";
 }
 
-int tt_attn_fwd(const tt_attn_desc* desc, const void* q, const void* k, const void* v, void* out, float* lse,
-                void* stream) {
+static int attn_fwd_common(const char* who, const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                           const int32_t* kv_lens, void* out, float* lse, void* stream) {
     AttnArgs a;
-    int rc = resolve(desc, &a, "tt_attn_fwd");
+    int rc = resolve(desc, &a, who);
     if (rc != TT_OK) return rc;
-    if (!q || !k || !v || !out) return fail(TT_ERR_NULL, "tt_attn_fwd: q, k, v and out must be non-null");
+    if (!q || !k || !v || !out) return fail(TT_ERR_NULL, "%s: q, k, v and out must be non-null", who);
     if ((rc = check_device()) != TT_OK) return rc;
     g_err[0] = 0;
     a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
+    a.kv_lens = kv_lens;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
     if (attn_fwd_sm100_supported(a) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out)) {
@@ -346,8 +349,16 @@ int tt_attn_fwd(const tt_attn_desc* desc, const void* q, const void* k, const vo
     } else {
         e = attn_fwd_simt(a, st);
     }
-    if (e != cudaSuccess) return cuda_fail(e, "tt_attn_fwd: launch");
+    if (e != cudaSuccess) return cuda_fail(e, who);
     return TT_OK;
+}
+int tt_attn_fwd(const tt_attn_desc* desc, const void* q, const void* k, const void* v, void* out, float* lse,
+                void* stream) {
+    return attn_fwd_common("tt_attn_fwd", desc, q, k, v, nullptr, out, lse, stream);
+}
+int tt_attn_fwd_padded(const tt_attn_desc* desc, const void* q, const void* k, const void* v, const int32_t* kv_lens,
+                       void* out, float* lse, void* stream) {
+    return attn_fwd_common("tt_attn_fwd_padded", desc, q, k, v, kv_lens, out, lse, stream);
 }
 
 size_t tt_attn_bwd_workspace_bytes(const tt_attn_desc* desc) {
@@ -358,23 +369,24 @@ size_t tt_attn_bwd_workspace_bytes(const tt_attn_desc* desc) {
     return simt > tc ? simt : tc;
 }
 
-int tt_attn_bwd(const tt_attn_desc* desc, const void* q, const void* k, const void* v, const void* out,
-                const float* lse, const void* dout, void* dq, void* dk, void* dv, void* workspace,
-                size_t workspace_bytes, void* stream) {
+static int attn_bwd_common(const char* who, const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                           const int32_t* kv_lens, const void* out, const float* lse, const void* dout, void* dq, void* dk,
+                           void* dv, void* workspace, size_t workspace_bytes, void* stream) {
     AttnArgs a;
-    int rc = resolve(desc, &a, "tt_attn_bwd");
+    int rc = resolve(desc, &a, who);
     if (rc != TT_OK) return rc;
     if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv)
-        return fail(TT_ERR_NULL, "tt_attn_bwd: all tensor pointers must be non-null");
+        return fail(TT_ERR_NULL, "%s: all tensor pointers must be non-null", who);
     size_t need = tt_attn_bwd_workspace_bytes(desc);
     if (!workspace || workspace_bytes < need)
-        return fail(TT_ERR_WORKSPACE, "tt_attn_bwd: workspace of %zu bytes required, %zu given", need, workspace_bytes);
+        return fail(TT_ERR_WORKSPACE, "%s: workspace of %zu bytes required, %zu given", who, need, workspace_bytes);
     if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
-        return fail(TT_ERR_WORKSPACE, "tt_attn_bwd: workspace must be 256-byte aligned");
+        return fail(TT_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned", who);
     if ((rc = check_device()) != TT_OK) return rc;
     g_err[0] = 0;
     a.q = q; a.k = k; a.v = v; a.out = const_cast<void*>(out); a.lse = const_cast<float*>(lse); a.dout = dout;
     a.dq = dq; a.dk = dk; a.dv = dv;
+    a.kv_lens = kv_lens;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
     bool al = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(dout) && aligned16(dq) &&
@@ -385,8 +397,20 @@ int tt_attn_bwd(const tt_attn_desc* desc, const void* q, const void* k, const vo
     } else {
         e = attn_bwd_simt(a, (float*)workspace, st);
     }
-    if (e != cudaSuccess) return cuda_fail(e, "tt_attn_bwd: launch");
+    if (e != cudaSuccess) return cuda_fail(e, who);
     return TT_OK;
+}
+int tt_attn_bwd(const tt_attn_desc* desc, const void* q, const void* k, const void* v, const void* out,
+                const float* lse, const void* dout, void* dq, void* dk, void* dv, void* workspace,
+                size_t workspace_bytes, void* stream) {
+    return attn_bwd_common("tt_attn_bwd", desc, q, k, v, nullptr, out, lse, dout, dq, dk, dv, workspace, workspace_bytes,
+                           stream);
+}
+int tt_attn_bwd_padded(const tt_attn_desc* desc, const void* q, const void* k, const void* v, const int32_t* kv_lens,
+                       const void* out, const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+    return attn_bwd_common("tt_attn_bwd_padded", desc, q, k, v, kv_lens, out, lse, dout, dq, dk, dv, workspace,
+                           workspace_bytes, stream);
 }
 
 size_t tt_attn_decode_workspace_bytes(const tt_attn_desc* desc) {

@@ -43,22 +43,38 @@ def _p(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def attention_forward(q, k, v, causal=False, scale=None, out=None, lse=None, need_lse=True):
-    """`softmax(scale * q k^T [+causal]) v` -> (out, lse).  Asynchronous on the current stream."""
+def _check_lens(kv_lens, B, device):
+    if kv_lens is None:
+        return None
+    if not isinstance(kv_lens, torch.Tensor) or kv_lens.dtype != torch.int32 or not kv_lens.is_cuda \
+            or not kv_lens.is_contiguous() or tuple(kv_lens.shape) != (B,):
+        raise ValueError(f"kv_lens must be a contiguous CUDA int32 tensor of shape ({B},)")
+    return kv_lens
+
+
+def attention_forward(q, k, v, causal=False, scale=None, out=None, lse=None, need_lse=True, kv_lens=None):
+    """`softmax(scale * q k^T [+causal]) v` -> (out, lse).  Asynchronous on the current stream.
+    `kv_lens` (int32 `[B]`, CUDA): batch entry b attends to its first kv_lens[b] keys only."""
     B, H, S, L, D = _check_inputs(q, k, v)
+    kv_lens = _check_lens(kv_lens, B, q.device)
     with torch.cuda.device(q.device):
         if out is None:
             out = torch.empty_like(q)
         if lse is None and need_lse:
             lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
         d = capi.make_desc(B, H, S, L, D, _DT[q.dtype], causal, scale, Hkv=k.shape[1])
-        capi.check(capi.lib.tt_attn_fwd(ctypes.byref(d), _p(q), _p(k), _p(v), _p(out), _p(lse), _stream_ptr(q)))
+        if kv_lens is None:
+            capi.check(capi.lib.tt_attn_fwd(ctypes.byref(d), _p(q), _p(k), _p(v), _p(out), _p(lse), _stream_ptr(q)))
+        else:
+            capi.check(capi.lib.tt_attn_fwd_padded(ctypes.byref(d), _p(q), _p(k), _p(v), _p(kv_lens), _p(out), _p(lse),
+                                                   _stream_ptr(q)))
     return out, lse
 
 
-def attention_backward(q, k, v, out, lse, dout, causal=False, scale=None, workspace=None):
-    """(dq, dk, dv) for upstream gradient `dout`; `out`, `lse` from `attention_forward`."""
+def attention_backward(q, k, v, out, lse, dout, causal=False, scale=None, workspace=None, kv_lens=None):
+    """(dq, dk, dv) for upstream gradient `dout`; `out`, `lse` from `attention_forward` (same `kv_lens`)."""
     B, H, S, L, D = _check_inputs(q, k, v)
+    kv_lens = _check_lens(kv_lens, B, q.device)
     for name, t, shp in (("out", out, q.shape), ("dout", dout, q.shape)):
         if tuple(t.shape) != tuple(shp) or t.dtype != q.dtype or not t.is_cuda or not t.is_contiguous():
             raise ValueError(f"{name} must be a contiguous CUDA tensor of shape {tuple(shp)} and dtype {q.dtype}")
@@ -70,9 +86,14 @@ def attention_backward(q, k, v, out, lse, dout, causal=False, scale=None, worksp
         if workspace is None or workspace.numel() * workspace.element_size() < need:
             workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        capi.check(capi.lib.tt_attn_bwd(ctypes.byref(d), _p(q), _p(k), _p(v), _p(out), _p(lse), _p(dout),
-                                        _p(dq), _p(dk), _p(dv), _p(workspace),
-                                        workspace.numel() * workspace.element_size(), _stream_ptr(q)))
+        nbytes = workspace.numel() * workspace.element_size()
+        if kv_lens is None:
+            capi.check(capi.lib.tt_attn_bwd(ctypes.byref(d), _p(q), _p(k), _p(v), _p(out), _p(lse), _p(dout),
+                                            _p(dq), _p(dk), _p(dv), _p(workspace), nbytes, _stream_ptr(q)))
+        else:
+            capi.check(capi.lib.tt_attn_bwd_padded(ctypes.byref(d), _p(q), _p(k), _p(v), _p(kv_lens), _p(out), _p(lse),
+                                                   _p(dout), _p(dq), _p(dk), _p(dv), _p(workspace), nbytes,
+                                                   _stream_ptr(q)))
     return dq, dk, dv
 
 

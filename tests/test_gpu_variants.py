@@ -170,3 +170,69 @@ def test_variant_argument_errors(tt, torch_cuda):
     import ctypes
     d = c.make_desc(2, 6, 8, 8, 64, c.TT_BF16, False, None, Hkv=4)
     assert c.lib.tt_attn_fwd(ctypes.byref(d), None, None, None, None, None, None) == c.TT_ERR_BAD_SHAPE
+
+
+def padded_ref(oracle, q, k, v, do, lens, causal):
+    """Per batch entry: the oracle on the first lens[b] keys; causal mask aligned to the FULL length
+    (query i of S sees keys j <= i + (L - S)), gradients of padded keys zero."""
+    B, H, S, D = q.shape
+    Hkv, L = k.shape[1], k.shape[2]
+    o = np.zeros_like(q); dq = np.zeros_like(q); dk = np.zeros_like(k); dv = np.zeros_like(v)
+    lse = np.zeros((B, H, S), np.float32)
+    for b in range(B):
+        n = int(lens[b])
+        kb, vb = oracle.expand_kv_heads(k[b:b + 1, :, :n], H), oracle.expand_kv_heads(v[b:b + 1, :, :n], H)
+        qb, dob = q[b:b + 1].astype(np.float64), do[b:b + 1].astype(np.float64)
+        s = np.matmul(qb, np.swapaxes(kb, -1, -2).astype(np.float64)) / np.sqrt(D)
+        if causal:
+            i, j = np.arange(S)[:, None], np.arange(n)[None, :]
+            s = np.where(j <= i + (L - S), s, -np.inf)
+        m = s.max(-1, keepdims=True)
+        e = np.exp(s - m)
+        den = e.sum(-1, keepdims=True)
+        p = e / den
+        ob = np.matmul(p, vb.astype(np.float64))
+        dp = np.matmul(dob, np.swapaxes(vb, -1, -2).astype(np.float64))
+        ds = p * (dp - (dob * ob).sum(-1, keepdims=True))
+        o[b] = ob[0]; lse[b] = (m + np.log(den))[0, ..., 0]
+        dq[b] = (np.matmul(ds, kb.astype(np.float64)) / np.sqrt(D))[0]
+        dk[b, :, :n] = oracle.reduce_kv_heads(np.matmul(np.swapaxes(ds, -1, -2), qb) / np.sqrt(D), Hkv)[0]
+        dv[b, :, :n] = oracle.reduce_kv_heads(np.matmul(np.swapaxes(p, -1, -2), dob), Hkv)[0]
+    return o, lse, dq, dk, dv
+
+
+@pytest.mark.parametrize("bf16,B,H,Hkv,S,L,D,causal,lens", [
+    (True, 3, 4, 4, 384, 384, 128, False, [384, 130, 1]),
+    (True, 3, 4, 2, 300, 300, 64, True, [300, 129, 64]),
+    (True, 2, 2, 2, 130, 400, 128, True, [400, 290]),
+    (False, 3, 2, 1, 40, 72, 32, True, [72, 40, 33]),
+    (False, 2, 3, 3, 33, 50, 48, False, [50, 7]),
+])
+def test_key_padding_lengths_fwd_bwd(tt, oracle, torch_cuda, bf16, B, H, Hkv, S, L, D, causal, lens):
+    torch = torch_cuda
+    q, k, v, do = make_grouped(oracle, 150 + S + D, B, H, Hkv, S, L, D, bf16)
+    cast = (lambda a: torch.from_numpy(a).cuda().bfloat16()) if bf16 else (lambda a: torch.from_numpy(a).cuda())
+    tq, tk, tv, tdo = (cast(a) for a in (q, k, v, do))
+    tl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    out, lse = tt.attention_forward(tq, tk, tv, causal=causal, kv_lens=tl)
+    dq, dk, dv = tt.attention_backward(tq, tk, tv, out, lse, tdo, causal=causal, kv_lens=tl)
+    tt.check_device_status()
+    o_r, lse_r, dq_r, dk_r, dv_r = padded_ref(oracle, q, k, v, do, lens, causal)
+    f = lambda t: t.float().cpu().numpy()
+    if bf16:
+        assert oracle.max_abs_err(f(out), o_r) <= 2e-2 and oracle.max_abs_err(lse.cpu().numpy(), lse_r) <= 1e-3
+        for got, ref, name in ((dq, dq_r, "dq"), (dk, dk_r, "dk"), (dv, dv_r, "dv")):
+            assert oracle.max_abs_err(f(got), ref) <= 2e-2 + 2.0 ** -7 * np.abs(ref).max(), name
+    else:
+        for got, ref, name in ((out, o_r, "o"), (dq, dq_r, "dq"), (dk, dk_r, "dk"), (dv, dv_r, "dv")):
+            assert oracle.rel_err(f(got), ref) <= 1e-5, name
+    for b, n in enumerate(lens):   # padded keys: exactly zero gradients
+        assert float(dk[b, :, n:].float().abs().max() if n < L else 0.0) == 0.0
+        assert float(dv[b, :, n:].float().abs().max() if n < L else 0.0) == 0.0
+    # full lengths reproduce the unpadded call bit for bit
+    full = torch.full((B,), L, dtype=torch.int32, device="cuda")
+    out2, lse2 = tt.attention_forward(tq, tk, tv, causal=causal, kv_lens=full)
+    out3, lse3 = tt.attention_forward(tq, tk, tv, causal=causal)
+    assert torch.equal(out2, out3) and torch.equal(lse2, lse3)
+    with pytest.raises(ValueError):
+        tt.attention_forward(tq, tk, tv, kv_lens=tl.long())
