@@ -4,11 +4,11 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg5]
 
 One step = causal bf16 attention forward + backward over one batch of synthetic input.
-Default workload `cfg5` (BASELINE config 5): Q,K,V,dO [B=1,H=64,S=32768,D=128], Q/K/V ~
+Default workload `cfg5` (benchmark configuration 5): Q,K,V,dO [B=1,H=64,S=32768,D=128], Q/K/V ~
 0.5*N(0,1), dO ~ N(0,1).  With N > 1 (launched under torchrun, one process per GPU) the 64
 heads are sharded over the ranks in contiguous ranges -- strong scaling, no collective on the
 data path -- and the step all-gathers O over NCCL on a side stream, overlapped with the
-backward.  At N = 1 the line also carries `cfg3` (BASELINE config 3, [4,32,4096,128]: the shape
+backward.  At N = 1 the line also carries `cfg3` (benchmark configuration 3, [4,32,4096,128]: the shape
 the forward target is stated on) and `decode` (config 4).  `--workload cfg3` makes config 3 the
 main workload (weak scaling: every rank owns its own 128 slices).  FLOPs are counted as the task defines them: 2 per MAC,
 forward = 2 GEMMs, backward = 5 GEMMs (2.5x forward), causal = half of dense.
@@ -310,7 +310,7 @@ def run_workload(tt, name, steps, warmup, world, rank, dev, peaks, e2e_steps, sa
 
 
 def run_decode(tt, dev, peaks, batch):
-    """BASELINE config 4 (HBM-bound): reported beside the step metric, not part of it."""
+    """benchmark configuration 4 (HBM-bound): reported beside the step metric, not part of it."""
     import torch
     capi = tt.capi
     try:
@@ -425,7 +425,7 @@ def main():
     ap.add_argument("--no-softmax", action="store_true", help="skip the row-softmax leg at N=1")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the S=4096 side measurement at N=1")
     ap.add_argument("--e2e-steps", type=int, default=2)
-    ap.add_argument("--decode-batch", type=int, default=64, help="batch of the decode leg (64 = BASELINE config 4)")
+    ap.add_argument("--decode-batch", type=int, default=64, help="batch of the decode leg (64 = benchmark configuration 4)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]

@@ -30,7 +30,7 @@ from oracle.attention_oracle import make_inputs, causal_mask, MASK_VALUE  # noqa
 
 # name, B, H, S, L, D, causal, sigma, seed
 CASES = [
-    ("cfg1_f32_b2h4s64d32", 2, 4, 64, 64, 32, False, 1.0, 0),       # BASELINE config 1
+    ("cfg1_f32_b2h4s64d32", 2, 4, 64, 64, 32, False, 1.0, 0),       # benchmark configuration 1
     ("causal_b1h2s48d32", 1, 2, 48, 48, 32, True, 1.0, 1),
     ("causal_ragged_b1h2s40l72d64", 1, 2, 40, 72, 64, True, 0.5, 2),  # L != S, bottom-right aligned
     ("cross_b1h3s17l33d16", 1, 3, 17, 33, 16, False, 1.0, 3),

@@ -35,7 +35,7 @@ def test_reference_outputs_match_float64_closed_form(oracle, path):
 
 
 def test_config1_inputs_regenerate_from_seed(oracle):
-    """BASELINE config 1: Q/K/V/dO [2,4,64,32] ~ N(0,1) from seed 0; the fixture stores exactly
+    """benchmark configuration 1: Q/K/V/dO [2,4,64,32] ~ N(0,1) from seed 0; the fixture stores exactly
     what `make_inputs` produces, so any rank can rebuild its shard."""
     g = np.load(os.path.join(os.path.dirname(__file__), "golden", "cfg1_f32_b2h4s64d32.npz"))
     q, k, v, do = oracle.make_inputs(0, 2, 4, 64, 64, 32)

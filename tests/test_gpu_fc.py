@@ -119,7 +119,7 @@ def test_fc_leading_axes_empty_and_errors(tt, oracle, torch_cuda):
 
 
 def test_fc_projection_size_properties(tt, torch_cuda):
-    """The projection of BASELINE config 3 (tokens 16384, width 4096), where a float64 oracle pass
+    """The projection of benchmark configuration 3 (tokens 16384, width 4096), where a float64 oracle pass
     is too slow: linearity in x, agreement of dW with the forward kernel run on transposed data,
     and spot rows against float64."""
     torch = torch_cuda

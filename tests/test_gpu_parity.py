@@ -92,7 +92,7 @@ FWD_CASES = [
     (1, 1, 257, 257, 64, False, 1.0),      # one row into the third tile
     (1, 2, 130, 515, 128, True, 0.5),      # L != S, bottom-right aligned diagonal
     (1, 1, 1, 300, 128, False, 1.0),       # a single query through the prefill kernel
-    (1, 2, 1024, 1024, 64, True, 0.5),     # BASELINE config 2 shape, 2 heads
+    (1, 2, 1024, 1024, 64, True, 0.5),     # benchmark configuration 2 shape, 2 heads
     (1, 1, 1024, 1024, 128, False, 0.5),
     (1, 1, 1536, 1536, 128, True, 0.5),    # more key tiles than ring stages
 ]
@@ -209,7 +209,7 @@ def test_decode_f32_uses_exact_path(tt, oracle):
 
 # ----------------------------------------------------------------------------- full-size properties
 def test_config3_forward_properties(tt, oracle):
-    """BASELINE config 3 shape (B=4,H=32,S=4096,D=128, causal) at full size.
+    """benchmark configuration 3 shape (B=4,H=32,S=4096,D=128, causal) at full size.
 
     The oracle cannot materialise 4096x4096 scores for 128 slices in seconds, so the check is
     (i) sampled row blocks of sampled slices against the oracle, (ii) row 0 of every slice
@@ -395,7 +395,7 @@ def test_many_work_items_per_cta(tt, oracle):
 
 
 def test_config5_single_head_properties(tt, oracle):
-    """BASELINE config 5 shape (S=32768, D=128, causal) on two heads: sampled row blocks against
+    """benchmark configuration 5 shape (S=32768, D=128, causal) on two heads: sampled row blocks against
     the oracle, first-row identity, finiteness of gradients."""
     S, D = 32768, 128
     g = torch.Generator(device="cuda").manual_seed(9)
