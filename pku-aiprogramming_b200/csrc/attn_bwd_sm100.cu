@@ -36,11 +36,16 @@ struct BwdCfg {
     static constexpr int kSub = D / 64;
     static constexpr int kSubBytes = 128 * 128;
     static constexpr int kTileBytes = kSub * kSubBytes;
-    static constexpr int kStages = (D == 128) ? 2 : 4;              // streamed (T0,T1) pairs in flight
+    // Streamed tiles held in shared memory.  At D = 128 (32 KB tiles) the two resident tiles, five
+    // streamed ones and 3 KB of barriers and staging are EXACTLY the 227 KB a CTA may have, so there
+    // is no slack for aligning the base by hand: the kernel declares the dynamic array 1024-byte
+    // aligned and refuses to run (status word) if the base is not.
+    static constexpr int kStreamTiles = (D == 128) ? 5 : 8;
     static constexpr int kThreads = 384;
     static constexpr int kTmemCols = 512;
-    static constexpr int kAuxBytes = 4096;                           // barriers + lse/delta staging
-    static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + kAuxBytes + 1024;
+    static constexpr int kAuxBytes = 3072;                           // 1 KB barriers + 2 KB lse/delta staging
+    static constexpr int kSmemBytes = (2 + kStreamTiles) * kTileBytes + kAuxBytes;
+    static_assert(kSmemBytes <= 227 * 1024, "exceeds the shared memory of one CTA");
 };
 
 enum BwdBarId { BB_RES = 0, BB_STFULL = 10, BB_STEMPTY = 20, BB_SFULL = 30, BB_DPFULL = 31, BB_PFULL = 32,
@@ -136,23 +141,29 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                       const __grid_constant__ CUtensorMap tmT0, const __grid_constant__ CUtensorMap tmT1,
                       const BwdParams p) {
     using Cfg = BwdCfg<D>;
-    constexpr int kStages = Cfg::kStages;
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = smem_raw;
+    if ((smem_u32(smem_raw) & 1023u) != 0u) {   // the 128-byte swizzle of TMA and UMMA needs 1024-byte aligned tiles
+        if (threadIdx.x == 0 && atomicCAS(p.status, 0u, (8u << 16) | (blockIdx.x & 0xffffu)) == 0u) {
+            p.status[1] = 0xA116u;   // "alignment"
+            p.status[2] = smem_u32(smem_raw);
+            p.status[3] = 0u;
+        }
+        return;                      // every thread of every CTA takes this exit together: nothing was started
+    }
     unsigned char* sR = smem;                                 // R0, R1
-    unsigned char* sT = smem + 2 * Cfg::kTileBytes;           // kStages x (T0, T1)
-    unsigned char* aux = smem + (2 + 2 * kStages) * Cfg::kTileBytes;
+    unsigned char* sT = smem + 2 * Cfg::kTileBytes;           // kStreamTiles streamed tiles: T0 ring, then T1 ring
+    unsigned char* aux = smem + (2 + Cfg::kStreamTiles) * Cfg::kTileBytes;
     uint64_t* bar_res_full = reinterpret_cast<uint64_t*>(aux);   // TMA -> MMA (resident pair)
     uint64_t* bar_res_empty = bar_res_full + 1;                  // MMA (last score GEMMs of the item) -> TMA
-    // The two streamed tensors have rings of their own (kN0 + kN1 = 2 * kStages tiles of shared memory).
-    // T0 (Q | K) is read by the first score GEMM of a tile, issued half an iteration EARLY, and by the
-    // last accumulation GEMM of the tile; T1 (dO | V) by the second score GEMM and, with keys
-    // resident, by dV.  With queries resident V is dead as soon as dP is computed, so one slot is
-    // enough for it and K gets three: K(t+1) must have landed when iteration t has barely begun, and
-    // with two slots its load could only start at the end of iteration t-1 (measured: the MMA warp
-    // waited ~1300 cycles per tile for it).
-    constexpr int kN1 = kKeysResident ? kStages : kStages / 2;   // D = 128: 2 | 1 slots;  D = 64: 4 | 2
-    constexpr int kN0 = 2 * kStages - kN1;                       // D = 128: 2 | 3 slots;  D = 64: 4 | 6
+    // The two streamed tensors have rings of their own.  T0 (Q | K) is read by the first score GEMM of
+    // a tile, which is issued as soon as the PREVIOUS tile's scores are in registers, and by the last
+    // accumulation GEMM of the tile: T0(t+1) must have landed when tile t has barely begun, while
+    // T0(t-1) was needed until the end of tile t-1 -- three slots.  T1 (dO | V) is read by the second
+    // score GEMM (end of the previous tile) and, with keys resident, by dV: two slots.  With two T0
+    // slots the MMA warp waited ~1300 cycles per tile for the load (measured, both passes).
+    constexpr int kN0 = (D == 128) ? 3 : (kKeysResident ? 4 : 6);
+    constexpr int kN1 = Cfg::kStreamTiles - kN0;                 // D = 128: 2;  D = 64: 4 | 2
     static_assert(kN0 <= 6 && kN1 <= 4 && kN1 >= 1, "barrier arrays below are sized for these ring lengths");
     uint64_t* bar_t0_full = bar_res_empty + 1;                   // [6]
     uint64_t* bar_t0_empty = bar_t0_full + 6;                    // [6]
@@ -166,7 +177,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
     uint64_t* bar_acc_free = bar_final + 1;                      // compute (accumulators read out) -> MMA
     uint64_t* bar_sched_full = bar_acc_free + 1;                 // [2]
     uint64_t* bar_sched_empty = bar_sched_full + 2;              // [2]
-    int* sched_item = reinterpret_cast<int*>(bar_sched_empty + 2);   // [2]
+    uint64_t* bar_stat = bar_sched_empty + 2;                    // [2] per warpgroup: a tile's statistics are staged
+    int* sched_item = reinterpret_cast<int*>(bar_stat + 2);      // [2]
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sched_item + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     float* s_stat = reinterpret_cast<float*>(aux + 1024);     // [2 buffers][2: -lse2, -delta][128]
@@ -194,6 +206,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
         mbar_init(bar_final, 1);
         mbar_init(bar_acc_free, 256);
         for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_stat[i], 128);
             mbar_init(&bar_sched_full[i], 1);
             mbar_init(&bar_sched_empty[i], 257);   // MMA warp (1) + 256 compute threads
         }
@@ -274,7 +287,21 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 stat_ok = qrow < p.S;
                 if (stat_ok) stat_raw = stat_src[(long long)qs * p.S + qrow];
             };
-            if (kKeysResident && w.n_it > 0) stat_issue(0);
+            // Staging runs one tile ahead and is split-phase: the statistic of tile u+1 is written to
+            // the other half of the double buffer in the MIDDLE of tile u, followed by an arrive on the
+            // warpgroup's mbarrier; the matching wait at the top of tile u+1 then finds the phase long
+            // complete.  (A bar.sync at the top of every tile made each warp wait for the slowest of
+            // its warpgroup: ~500 cycles per tile.)  A thread's own reads of a buffer all precede its
+            // next arrive, so nobody overwrites a buffer that is still being read.
+            auto stat_publish = [&](uint32_t g) {
+                s_stat[(g & 1) * 256 + stat_slot] = stat_ok ? -stat_raw : stat_oob;
+                mbar_arrive(&bar_stat[wg]);
+            };
+            if (kKeysResident && w.n_it > 0) {
+                stat_issue(0);
+                stat_publish(git);            // first tile of the item: the one exposed load
+                if (w.n_it > 1) stat_issue(1);
+            }
             for (int u = 0; u < w.n_it; ++u, ++git) {
                 const int it = u;
                 const int t = kKeysResident ? w.t_begin + u % w.nt : w.t_begin + u;
@@ -283,11 +310,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 if (tr) TT_BTRACE(wg, it, 0);
                 const float* st_nlse = s_stat + (git & 1) * 256;   // -lse2 of the 128 streamed queries
                 const float* st_ndelta = st_nlse + 128;            // -delta
-                if (kKeysResident) {
-                    s_stat[(git & 1) * 256 + stat_slot] = stat_ok ? -stat_raw : stat_oob;
-                    named_bar_sync(1 + wg, 128);
-                    if (u + 1 < w.n_it) stat_issue(u + 1);
-                }
+                if (kKeysResident) mbar_wait(&bar_stat[wg], git & 1, wctx, BB_PREAD, it);   // tile u's statistics are staged
                 // visible columns of this thread's row inside the tile: [vis_lo, vis_hi)
                 int vis_lo = 0, vis_hi = 128;
                 if (kKeysResident) {
@@ -298,7 +321,26 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                     vis_hi = min(vis_hi, 128);
                 }
                 const bool need_mask = (vis_lo > 0) || (vis_hi < 128);
+                // With keys resident the per-column statistics come from shared memory.  They are fetched
+                // into registers BEFORE each wait on the tensor pipe (16-byte loads): inside the phases
+                // they would sit behind the tensor-memory waits, and shared memory is busy feeding the
+                // score GEMMs just then (measured: 850 cycles per 32-column chunk against 625 in the
+                // other pass, which keeps its statistics in registers).
+                uint64_t stat_reg[2][16];
+                auto load_stats = [&](const float* src) {
+                    if (kKeysResident) {
+#pragma unroll
+                        for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+                            for (int e4 = 0; e4 < 8; ++e4) {
+                                const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(src + wg * 64 + cc * 32 + e4 * 4);
+                                stat_reg[cc][2 * e4] = v.x;
+                                stat_reg[cc][2 * e4 + 1] = v.y;
+                            }
+                    }
+                };
                 // ---------------- phase A: P = exp2(S*c - lse2)
+                load_stats(st_nlse);
                 if (tr) TT_BTRACE(wg, it, 1);
                 mbar_wait(bar_s_full, git & 1, wctx, BB_SFULL, it);
                 __syncwarp();
@@ -309,11 +351,16 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 // Nothing is written back into the S columns: they are released as soon as they are in
                 // registers, so the next tile's score GEMM runs under these exponentials.  (With keys
                 // resident the bf16 P^T that dV needs joins dS^T in the dP columns in phase B.)
-                auto phase_a = [&](int cc) {
+                // The mask test must stay OUT of the unrolled loop: a branch per pair makes every pair a
+                // basic block of its own, nothing is scheduled across them and each pair then pays its
+                // shared-memory, FMA and special-function latencies in full (measured: 55 cycles per pair
+                // against 32 at the special-function unit's rate).
+                auto phase_a_body = [&](auto masked_c, int cc) {
+                    constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
                         const int col = wg * 64 + cc * 32 + e;
-                        const uint64_t nl = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_nlse + col) : row_nlse2;
+                        const uint64_t nl = kKeysResident ? stat_reg[cc][e >> 1] : row_nlse2;
                         const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, nl);
                         float p0, p1;
                         if ((((e >> 1) * kPoly) % 8) < kPoly) {   // kPoly of every 8 pairs on the FMA pipes
@@ -324,20 +371,23 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                             p0 = ex2_approx(a0);
                             p1 = ex2_approx(a1);
                         }
-                        if (need_mask) {
+                        if (kMasked) {
                             p0 = (col >= vis_lo && col < vis_hi) ? p0 : 0.f;
                             p1 = (col + 1 >= vis_lo && col + 1 < vis_hi) ? p1 : 0.f;
                         }
                         pf2[cc * 16 + (e >> 1)] = pack_f32x2(p0, p1);
                     }
                 };
+                auto phase_a = [&](int cc) {
+                    if (need_mask) phase_a_body(std::true_type{}, cc);
+                    else phase_a_body(std::false_type{}, cc);
+                };
                 // dS = P * (dP - delta) for one chunk, written over the dP columns just read
                 auto phase_b = [&](int cc) {
                     uint32_t pk[16], pkp[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
-                        const int col = wg * 64 + cc * 32 + e;
-                        const uint64_t nd = kKeysResident ? *reinterpret_cast<const uint64_t*>(st_ndelta + col) : row_ndelta2;
+                        const uint64_t nd = kKeysResident ? stat_reg[cc][e >> 1] : row_ndelta2;
                         const uint64_t tdiff = add_f32x2(pack_f32x2(__uint_as_float(dr[cc][e]), __uint_as_float(dr[cc][e + 1])), nd);
                         const uint64_t ds = mul_f32x2(pf2[cc * 16 + (e >> 1)], tdiff);
                         float x0, x1;
@@ -368,6 +418,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 mbar_arrive(bar_p_full);                // all of S(t) is in registers: its columns are free
                 phase_a(1);
                 if (tr) TT_BTRACE(wg, it, 3);
+                load_stats(st_ndelta);
+                if (kKeysResident && u + 1 < w.n_it) {
+                    stat_publish(git + 1);                     // its load was issued a tile ago
+                    if (u + 2 < w.n_it) stat_issue(u + 2);
+                }
                 mbar_wait(bar_dp_full, git & 1, wctx, BB_DPFULL, it);
                 __syncwarp();
                 tc_fence_after();
