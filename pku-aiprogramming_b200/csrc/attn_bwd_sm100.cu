@@ -49,7 +49,7 @@ struct BwdCfg {
 };
 
 enum BwdBarId { BB_RES = 0, BB_STFULL = 10, BB_STEMPTY = 20, BB_SFULL = 30, BB_DPFULL = 31, BB_PFULL = 32,
-                BB_DSFULL = 33, BB_FINAL = 34, BB_PREAD = 35 };
+                BB_DSFULL = 33, BB_FINAL = 34, BB_STAT = 35 };
 
 struct BwdParams {
     __nv_bfloat16* out0;   // keys resident: dV ; else unused
@@ -310,7 +310,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 if (tr) TT_BTRACE(wg, it, 0);
                 const float* st_nlse = s_stat + (git & 1) * 256;   // -lse2 of the 128 streamed queries
                 const float* st_ndelta = st_nlse + 128;            // -delta
-                if (kKeysResident) mbar_wait(&bar_stat[wg], git & 1, wctx, BB_PREAD, it);   // tile u's statistics are staged
+                if (kKeysResident) mbar_wait(&bar_stat[wg], git & 1, wctx, BB_STAT, it);   // tile u's statistics are staged
                 // visible columns of this thread's row inside the tile: [vis_lo, vis_hi)
                 int vis_lo = 0, vis_hi = 128;
                 if (kKeysResident) {
