@@ -236,3 +236,31 @@ def test_key_padding_lengths_fwd_bwd(tt, oracle, torch_cuda, bf16, B, H, Hkv, S,
     assert torch.equal(out2, out3) and torch.equal(lse2, lse3)
     with pytest.raises(ValueError):
         tt.attention_forward(tq, tk, tv, kv_lens=tl.long())
+
+
+def test_random_combinations_of_variants(tt, oracle, torch_cuda):
+    """Seeded sweep over combinations the targeted tests do not pair up: head dim x grouping x causal
+    x ragged L x key padding, forward and backward through the tensor-core kernels."""
+    torch = torch_cuda
+    import random
+    rnd = random.Random(2024)
+    for case in range(24):
+        D = rnd.choice([64, 128]); B = rnd.randint(1, 2); Hkv = rnd.choice([1, 2, 3]); g = rnd.choice([1, 2, 4])
+        H = Hkv * g
+        S = rnd.choice([1, 17, 128, 129, 255, 300]); causal = rnd.random() < 0.5
+        L = S if rnd.random() < 0.4 else rnd.choice([S + 1, S + 127, S + 200])
+        lo = (L - S + 1) if causal else 1                      # a causal row must keep at least one key
+        lens = [rnd.randint(lo, L) for _ in range(B)] if rnd.random() < 0.6 else [L] * B
+        q, k, v, do = make_grouped(oracle, 1000 + case, B, H, Hkv, S, L, D, True)
+        tq, tk, tv, tdo = (torch.from_numpy(a).cuda().bfloat16() for a in (q, k, v, do))
+        tl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        out, lse = tt.attention_forward(tq, tk, tv, causal=causal, kv_lens=tl)
+        dq, dk, dv = tt.attention_backward(tq, tk, tv, out, lse, tdo, causal=causal, kv_lens=tl)
+        tt.check_device_status()
+        o_r, lse_r, dq_r, dk_r, dv_r = padded_ref(oracle, q, k, v, do, lens, causal)
+        tag = dict(case=case, B=B, H=H, Hkv=Hkv, S=S, L=L, D=D, causal=causal, lens=lens)
+        f = lambda t: t.float().cpu().numpy()
+        assert oracle.max_abs_err(f(out), o_r) <= 2e-2, tag
+        assert oracle.max_abs_err(lse.cpu().numpy(), lse_r) <= 1e-3, tag
+        for got, ref in ((dq, dq_r), (dk, dk_r), (dv, dv_r)):
+            assert oracle.max_abs_err(f(got), ref) <= 2e-2 + 2.0 ** -7 * np.abs(ref).max(), tag
