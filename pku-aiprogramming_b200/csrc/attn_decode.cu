@@ -261,9 +261,57 @@ static int env_int(const char* name, int dflt);
 
 static bool decode_group_instantiated(int g) { return g == 1 || g == 2 || g == 4 || g == 8; }
 
-DecodePlan attn_decode_plan(const AttnArgs& a) {
-    DecodePlan pl{1, a.L, 0};
+// Grouped heads on a dense cache, as a tensor-core problem: the G query heads of a key/value head
+// are contiguous in q [B, Hkv*G, 1, D], i.e. they ARE a [B, Hkv, G, D] tensor of G query rows per
+// key/value head, and out / lse have the matching layout.  The forward kernel then computes the
+// whole group against each K/V tile with two MMAs, which the SIMT kernel cannot keep up with from
+// G = 4 on (it is instruction-bound: G dot products and G softmax updates per loaded row).
+// With fewer (batch, key/value head) items than SMs the keys are split as well: K and V viewed as
+// [slices * splits, L / splits, D] are `splits` independent problems per slice (the forward kernel
+// reads the query rows of slice s / splits), whose normalised partial outputs and log-sum-exps a
+// second kernel merges.
+static AttnArgs decode_as_forward(const AttnArgs& a, int splits) {
+    AttnArgs g = a;
+    g.BH = a.BH / a.group * splits;
+    g.S = a.group;
+    g.L = a.L / splits;
+    g.group = 1;
+    g.causal = 0;
+    g.q_div = splits;
+    g.kv_lens = nullptr;
+    return g;
+}
+static int decode_tc_splits(const AttnArgs& a) {   // 0: do not use the forward kernel
+    if (!(a.bf16 && a.S == 1 && a.group >= 4)) return 0;
+    const char* f = getenv("TT_DECODE_GQA_PATH");
+    if (f && f[0] == 's') return 0;                           // "simt"
+    if (!attn_fwd_sm100_supported(decode_as_forward(a, 1))) return 0;
+    int dev = 0, n_sm = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    const long long slices = a.BH / a.group;
+    if (slices >= n_sm) return 1;
+    // about two items per SM, ranges of at least 256 keys that divide L exactly
+    const long long want = (2LL * n_sm + slices - 1) / slices;
+    for (long long s = want; s <= 64 && a.L / s >= 256; ++s)
+        if (a.L % s == 0) return (int)s;
+    for (long long s = want - 1; s >= 2; --s)
+        if (a.L % s == 0 && a.L / s >= 256) return (int)s;
+    return (f && f[0] == 't') ? 1 : 0;                        // "tc": unsplit rather than SIMT
+}
+
+DecodePlan attn_decode_plan(const AttnArgs& a, bool allow_tc) {
+    DecodePlan pl{1, a.L, 0, 0};
     if (!(a.bf16 && (a.D == 64 || a.D == 128) && a.S == 1)) return pl;   // SIMT forward handles it
+    if (allow_tc) {
+        pl.tc_splits = decode_tc_splits(a);
+        if (pl.tc_splits == 1) return pl;
+        if (pl.tc_splits > 1) {   // partial outputs (bf16) and log-sum-exps (fp32) of every key range
+            pl.splits = pl.tc_splits;
+            pl.chunk = a.L / pl.tc_splits;
+            pl.ws_bytes = align256((size_t)a.BH * pl.tc_splits * a.D * 2) + align256((size_t)a.BH * pl.tc_splits * 4);
+            return pl;
+        }
+    }
     int dev = 0, n_sm = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     const long long resident = (long long)n_sm * 4;
@@ -283,6 +331,28 @@ DecodePlan attn_decode_plan(const AttnArgs& a) {
     pl.chunk = chunk;
     pl.ws_bytes = splits > 1 ? align256((size_t)splits * a.BH * (a.D + 2) * sizeof(float)) : 0;
     return pl;
+}
+
+// Merge of the forward kernel's per-range results: out[bh] = sum_c w_c O_c / sum_c w_c with
+// w_c = exp(lse_c - max lse); partial O is [kvs, splits, G, D] bf16, partial lse [kvs, splits, G].
+template <int D>
+__global__ void attn_decode_tc_merge_kernel(const __nv_bfloat16* __restrict__ po, const float* __restrict__ plse,
+                                            __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int splits, int G) {
+    const long long bh = blockIdx.x;
+    const int d = threadIdx.x;
+    const long long kvs = bh / G;
+    const int g = (int)(bh - kvs * G);
+    float m = -INFINITY;
+    for (int c = 0; c < splits; ++c) m = fmaxf(m, plse[(kvs * splits + c) * G + g]);
+    float den = 0.f, acc = 0.f;
+    for (int c = 0; c < splits; ++c) {
+        const long long row = (kvs * splits + c) * G + g;
+        const float w = expf(plse[row] - m);
+        den += w;
+        acc = fmaf(w, __bfloat162float(po[row * D + d]), acc);
+    }
+    out[bh * D + d] = __float2bfloat16_rn(acc / den);
+    if (d == 0 && lse != nullptr) lse[bh] = m + logf(den);
 }
 
 template <int D, int G>
@@ -316,36 +386,23 @@ static cudaError_t launch_decode(const AttnArgs& a, const DecodePlan& pl, void* 
     return cudaGetLastError();
 }
 
-// Grouped heads on a dense cache, as a tensor-core problem: the G query heads of a key/value head
-// are contiguous in q [B, Hkv*G, 1, D], i.e. they ARE a [B, Hkv, G, D] tensor of G query rows per
-// key/value head, and out / lse have the matching layout.  The forward kernel then computes the
-// whole group against each K/V tile with two MMAs, which the SIMT kernel cannot keep up with from
-// G = 4 on (it is instruction-bound: G dot products and G softmax updates per loaded row).  No
-// key splitting there, so it needs enough (batch, key/value head) items to fill the GPU.
-bool attn_decode_uses_fwd_kernel(const AttnArgs& a) {
-    if (!(a.bf16 && a.S == 1 && a.group >= 4)) return false;
-    const char* f = getenv("TT_DECODE_GQA_PATH");
-    if (f && f[0] == 's') return false;                     // "simt"
-    AttnArgs g = a;
-    g.BH = a.BH / a.group;
-    g.S = a.group;
-    g.group = 1;
-    g.causal = 0;
-    if (!attn_fwd_sm100_supported(g)) return false;
-    if (f && f[0] == 't') return true;                      // "tc"
-    int dev = 0, n_sm = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-    return g.BH >= n_sm;
-}
-
 cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaStream_t st, const DecodeView* view) {
-    if (!(view && (view->block_table || view->seq_lens)) && attn_decode_uses_fwd_kernel(a)) {
-        AttnArgs g = a;
-        g.BH = a.BH / a.group;
-        g.S = a.group;
-        g.group = 1;
-        g.causal = 0;
-        return attn_fwd_sm100(g, st);
+    const bool plain = !(view && (view->block_table || view->seq_lens));
+    if (plain && pl.tc_splits == 1) return attn_fwd_sm100(decode_as_forward(a, 1), st);
+    if (plain && pl.tc_splits > 1) {
+        AttnArgs g = decode_as_forward(a, pl.tc_splits);
+        __nv_bfloat16* po = (__nv_bfloat16*)ws;
+        float* plse = (float*)((unsigned char*)ws + align256((size_t)a.BH * pl.tc_splits * a.D * 2));
+        g.out = po;
+        g.lse = plse;
+        cudaError_t e = attn_fwd_sm100(g, st);
+        if (e != cudaSuccess) return e;
+        LaunchScope ls(K_DECODE_MERGE, st);
+        if (a.D == 128)
+            attn_decode_tc_merge_kernel<128><<<(unsigned)a.BH, 128, 0, st>>>(po, plse, (__nv_bfloat16*)a.out, a.lse, pl.tc_splits, a.group);
+        else
+            attn_decode_tc_merge_kernel<64><<<(unsigned)a.BH, 64, 0, st>>>(po, plse, (__nv_bfloat16*)a.out, a.lse, pl.tc_splits, a.group);
+        return cudaGetLastError();
     }
     if (a.bf16 && a.S == 1 && a.D == 128) return launch_decode<128>(a, pl, ws, st, true, view);
     if (a.bf16 && a.S == 1 && a.D == 64) return launch_decode<64>(a, pl, ws, st, true, view);

@@ -60,6 +60,7 @@ struct FwdParams {
     int group;                     // query heads per key/value head: query slice bh reads key/value slice bh / group
     const int* kv_lens;            // optional key padding lengths per batch entry (see AttnArgs)
     int H;
+    int q_div;                     // query slice = output slice / q_div
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
 };
@@ -396,7 +397,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 auto load_q = [&](int i) {
                     mbar_wait(&bar_q_empty[i], (q_uses[i] & 1) ^ 1, wctx, 5 + i, k);
                     __syncwarp();
-                    load_tile(sQ + i * Cfg::kTileBytes, &tmQ, &bar_q_full[i], w.q0 + 128 * i, w.bh);
+                    load_tile(sQ + i * Cfg::kTileBytes, &tmQ, &bar_q_full[i], w.q0 + 128 * i, w.bh / p.q_div);
                     ++q_uses[i];
                 };
                 auto load_kv = [&](const CUtensorMap* tm, int j) {   // ring order: K_0, V_0, K_1, V_1, ...
@@ -576,7 +577,8 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     using Cfg = FwdCfg<D>;
     TmapStorage tq, tk, tv;
     const char* why = nullptr;
-    if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    const int q_div = a.q_div > 0 ? a.q_div : 1;
+    if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH / q_div, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -592,6 +594,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.group = a.group;
     p.kv_lens = a.kv_lens;
     p.H = a.H;
+    p.q_div = q_div;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = device_status_word();
     p.trace = g_fwd_trace;

@@ -23,6 +23,9 @@ struct AttnArgs {
     // [B]); null = all L.  H = query heads per batch entry (batch entry of query slice bh = bh / H).
     const int* kv_lens;
     int H;
+    // forward kernel only: query slice = output slice / q_div (0 or 1: the same slice).  Lets several
+    // key ranges of one slice run as work items of their own, each with its own output rows.
+    int q_div;
 };
 // keys that count for batch entry b (device side)
 __device__ __forceinline__ int valid_keys(const int* kv_lens, long long b, int L) {
@@ -91,8 +94,13 @@ struct DecodePlan {
     int splits;        // key ranges per slice
     int chunk;         // keys per range (multiple of 64)
     size_t ws_bytes;   // partials: splits * BH * (D + 2) floats (0 when splits == 1)
+    // grouped heads on the tcgen05 forward kernel (see attn_decode.cu): 0 = not taken, 1 = whole key
+    // range per (batch, key/value head), > 1 = that many key ranges each, merged by a second kernel
+    int tc_splits;
 };
-DecodePlan attn_decode_plan(const AttnArgs& a);
+// allow_tc = false: plan for the SIMT split-KV kernel whatever the shape (paged / ragged caches and
+// the no-allocation entry point need it)
+DecodePlan attn_decode_plan(const AttnArgs& a, bool allow_tc = true);
 // Optional description of where the key/value rows live (bf16, D in {64,128} only):
 //   block_table != null: k, v are page pools [pages, hkv, page_size, D] and row r of batch entry b
 //                        is row r % page_size of page block_table[b * max_pages + r / page_size];
@@ -105,9 +113,7 @@ struct DecodeView {
 };
 cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& plan, void* workspace, cudaStream_t st,
                         const DecodeView* view = nullptr);
-// true when a dense grouped-head decode goes to the tcgen05 forward kernel (group >= 4, enough
-// key/value slices to fill the GPU; TT_DECODE_GQA_PATH=simt|tc overrides)
-bool attn_decode_uses_fwd_kernel(const AttnArgs& a);
+
 // Same kernels, partials in the library's own fixed device array (no allocation anywhere).
 // *too_big is set when the plan needs more than the array holds (nothing is launched then).
 size_t attn_decode_static_capacity();

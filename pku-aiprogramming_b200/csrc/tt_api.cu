@@ -417,7 +417,9 @@ size_t tt_attn_decode_workspace_bytes(const tt_attn_desc* desc) {
     AttnArgs a;
     if (resolve(desc, &a, "tt_attn_decode_workspace_bytes") != TT_OK) return 0;
     if (a.S != 1) return 0;
-    return attn_decode_plan(a).ws_bytes;
+    // enough for every route a call with this descriptor can take (dense, paged or ragged)
+    const size_t w1 = attn_decode_plan(a, true).ws_bytes, w2 = attn_decode_plan(a, false).ws_bytes;
+    return w1 > w2 ? w1 : w2;
 }
 
 int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const void* v, void* out, float* lse,
@@ -459,7 +461,7 @@ int tt_attn_decode_static(const tt_attn_desc* desc, const void* q, const void* k
         return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_static: q, k, v must be 16-byte aligned");
     if ((rc = check_device()) != TT_OK) return rc;
     a.causal = 0;
-    DecodePlan pl = attn_decode_plan(a);
+    DecodePlan pl = attn_decode_plan(a, /*allow_tc=*/false);   // this entry point is the SIMT kernel on the fixed array
     a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
     bool too_big = false;
     cudaError_t e = attn_decode_static(a, pl, (cudaStream_t)stream, &too_big);
@@ -571,7 +573,7 @@ int tt_attn_decode_paged(const tt_attn_desc* desc, const void* q, const void* k_
         return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_paged: q, k, v must be 16-byte aligned");
     if ((rc = check_device()) != TT_OK) return rc;
     a.causal = 0;
-    DecodePlan pl = attn_decode_plan(a);
+    DecodePlan pl = attn_decode_plan(a, /*allow_tc=*/!(block_table || seq_lens));
     if (pl.ws_bytes > 0) {
         if (!workspace || workspace_bytes < pl.ws_bytes)
             return fail(TT_ERR_WORKSPACE, "tt_attn_decode_paged: workspace of %zu bytes required, %zu given", pl.ws_bytes,

@@ -110,10 +110,27 @@ def test_decode_grouped_heads_on_the_forward_kernel(tt, oracle, torch_cuda, monk
         before = tt.capi.launch_count()
         out, lse = tt.attention_decode(tq, tk, tv)
         tt.check_device_status()
-        assert tt.capi.launch_count() - before == (1 if route == "tc" else 2), route   # one forward launch vs split + merge
+        # both routes split the 1000 keys here (few slices): forward kernel + merge | split kernel + merge
+        assert tt.capi.launch_count() - before == 2, route
         assert oracle.max_abs_err(out.float().cpu().numpy(), o_r) <= 2e-2, route
         assert oracle.max_abs_err(lse.cpu().numpy(), lse_r) <= 1e-3, route
     monkeypatch.delenv("TT_DECODE_GQA_PATH")
+
+
+@pytest.mark.parametrize("B,H,Hkv,L,D", [(2, 8, 2, 4096, 128), (1, 32, 4, 3000, 64), (160, 4, 1, 300, 128)])
+def test_decode_grouped_heads_key_split_on_the_forward_kernel(tt, oracle, torch_cuda, B, H, Hkv, L, D):
+    """Default routing: few (batch, key/value head) slices -> the keys are split into ranges that run as
+    forward-kernel work items and are merged; many slices -> one item per slice, no merge."""
+    torch = torch_cuda
+    q, k, v, _ = make_grouped(oracle, 170 + H, B, H, Hkv, 1, L, D, True)
+    tq, tk, tv = (torch.from_numpy(a).cuda().bfloat16() for a in (q, k, v))
+    before = tt.capi.launch_count()
+    out, lse = tt.attention_decode(tq, tk, tv)
+    tt.check_device_status()
+    assert tt.capi.launch_count() - before == (1 if B * Hkv >= 148 else 2)
+    o_r, lse_r = dense_decode_ref(oracle, q, k, v)
+    assert oracle.max_abs_err(out.float().cpu().numpy(), o_r) <= 2e-2
+    assert oracle.max_abs_err(lse.cpu().numpy(), lse_r) <= 1e-3
 
 
 @pytest.mark.parametrize("H,Hkv,D,page", [(8, 2, 128, 64), (4, 4, 64, 16), (8, 1, 128, 128), (6, 2, 64, 48)])
