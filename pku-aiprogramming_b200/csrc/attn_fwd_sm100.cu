@@ -259,6 +259,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (item < 0) break;
             const FwdItem w = fwd_decode_item(item, p);
             const int nt = w.n_tiles[i];
+            // per-item stamps of the traced CTA (role slot 0/1 = query tile, row = item number k)
+            if (p.trace != nullptr && (int)blockIdx.x == p.trace_block && wq == 0 && (threadIdx.x & 31) == 0 && k < 64) {
+                p.trace[(i * 64 + k) * 8 + 6] = clock64();
+                p.trace[(i * 64 + k) * 8 + 7] = nt;
+            }
             if (nt == 0) continue;
             const int row = w.q0 + 128 * i + wq * 32 + lane;
             float m2 = -INFINITY;   // running max in the scaled log2 domain
