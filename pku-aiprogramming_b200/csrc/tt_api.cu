@@ -773,23 +773,19 @@ int pipe_streams(PipeStreams** ps) {
 }
 struct EventSet {
     static const int kN = 3;
-    cudaEvent_t in[kN] = {}, comp[kN] = {}, out[kN] = {};
+    // per buffer set: q,k,v uploaded | dO uploaded | forward done | backward done | all downloaded
+    cudaEvent_t in[kN] = {}, in_do[kN] = {}, fwd[kN] = {}, comp[kN] = {}, out[kN] = {};
     bool ok = false;
     int make() {
-        for (int i = 0; i < kN; ++i) {
-            TT_CUDA(cudaEventCreateWithFlags(&in[i], cudaEventDisableTiming), "event");
-            TT_CUDA(cudaEventCreateWithFlags(&comp[i], cudaEventDisableTiming), "event");
-            TT_CUDA(cudaEventCreateWithFlags(&out[i], cudaEventDisableTiming), "event");
-        }
+        for (cudaEvent_t* arr : {in, in_do, fwd, comp, out})
+            for (int i = 0; i < kN; ++i) TT_CUDA(cudaEventCreateWithFlags(&arr[i], cudaEventDisableTiming), "event");
         ok = true;
         return TT_OK;
     }
     ~EventSet() {
-        for (int i = 0; i < kN; ++i) {
-            if (in[i]) cudaEventDestroy(in[i]);
-            if (comp[i]) cudaEventDestroy(comp[i]);
-            if (out[i]) cudaEventDestroy(out[i]);
-        }
+        for (cudaEvent_t* arr : {in, in_do, fwd, comp, out})
+            for (int i = 0; i < kN; ++i)
+                if (arr[i]) cudaEventDestroy(arr[i]);
     }
 };
 }  // namespace
@@ -841,20 +837,26 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
         TT_CUDA(cudaMemcpyAsync(bq[b].p, hq + s0 * q_slice, cnt * q_slice, cudaMemcpyHostToDevice, ps->in), "upload q");
         TT_CUDA(cudaMemcpyAsync(bk[b].p, hk + k0 * k_slice, kcnt * k_slice, cudaMemcpyHostToDevice, ps->in), "upload k");
         TT_CUDA(cudaMemcpyAsync(bv[b].p, hv + k0 * k_slice, kcnt * k_slice, cudaMemcpyHostToDevice, ps->in), "upload v");
-        TT_CUDA(cudaMemcpyAsync(bdo[b].p, hdo + s0 * q_slice, cnt * q_slice, cudaMemcpyHostToDevice, ps->in), "upload dout");
+        // the forward needs q, k, v only: it starts while dO is still on its way, and its results go
+        // back to the host while the backward runs
         TT_CUDA(cudaEventRecord(ev.in[b], ps->in), "record");
+        TT_CUDA(cudaMemcpyAsync(bdo[b].p, hdo + s0 * q_slice, cnt * q_slice, cudaMemcpyHostToDevice, ps->in), "upload dout");
+        TT_CUDA(cudaEventRecord(ev.in_do[b], ps->in), "record");
         TT_CUDA(cudaStreamWaitEvent(ps->comp, ev.in[b], 0), "wait upload");
         tt_attn_desc di = *d;
         di.B = 1;
         di.H = (int32_t)cnt;
         di.Hkv = (int32_t)kcnt;
         TT_TRY(tt_attn_fwd(&di, bq[b].p, bk[b].p, bv[b].p, bo[b].p, (float*)bl[b].p, ps->comp));
+        TT_CUDA(cudaEventRecord(ev.fwd[b], ps->comp), "record");
+        TT_CUDA(cudaStreamWaitEvent(ps->comp, ev.in_do[b], 0), "wait upload");
         TT_TRY(tt_attn_bwd(&di, bq[b].p, bk[b].p, bv[b].p, bo[b].p, (const float*)bl[b].p, bdo[b].p, bdq[b].p, bdk[b].p,
                            bdv[b].p, bws[b].p, ws_bytes, ps->comp));
         TT_CUDA(cudaEventRecord(ev.comp[b], ps->comp), "record");
-        TT_CUDA(cudaStreamWaitEvent(ps->out, ev.comp[b], 0), "wait compute");
+        TT_CUDA(cudaStreamWaitEvent(ps->out, ev.fwd[b], 0), "wait forward");
         TT_CUDA(cudaMemcpyAsync(ho + s0 * q_slice, bo[b].p, cnt * q_slice, cudaMemcpyDeviceToHost, ps->out), "download out");
         if (lse) TT_CUDA(cudaMemcpyAsync(lse + s0 * a.S, bl[b].p, cnt * l_slice, cudaMemcpyDeviceToHost, ps->out), "download lse");
+        TT_CUDA(cudaStreamWaitEvent(ps->out, ev.comp[b], 0), "wait backward");
         TT_CUDA(cudaMemcpyAsync(hdq + s0 * q_slice, bdq[b].p, cnt * q_slice, cudaMemcpyDeviceToHost, ps->out), "download dq");
         TT_CUDA(cudaMemcpyAsync(hdk + k0 * k_slice, bdk[b].p, kcnt * k_slice, cudaMemcpyDeviceToHost, ps->out), "download dk");
         TT_CUDA(cudaMemcpyAsync(hdv + k0 * k_slice, bdv[b].p, kcnt * k_slice, cudaMemcpyDeviceToHost, ps->out), "download dv");
