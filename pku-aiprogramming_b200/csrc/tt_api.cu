@@ -661,6 +661,9 @@ int tt_check_device_status(void* stream) {
     if (e != cudaSuccess) return cuda_fail(e, "tt_check_device_status: copy");
     if (h[0] == 0) return TT_OK;
     cudaMemset(dptr, 0, sizeof(h));
+    if ((h[0] >> 16) == 8u)   // the backward kernel found its dynamic shared memory not 1024-byte aligned and did nothing
+        return fail(TT_ERR_CUDA, "kernel refused to run: dynamic shared memory base 0x%x is not 1024-byte aligned (block %u)",
+                    h[2], h[0] & 0xffffu);
     return fail(TT_ERR_TIMEOUT, "a device-side wait expired: block %u, barrier id %u, iteration %u, warp %u",
                 h[0] & 0xffffu, h[1], h[2], h[3]);
 }
