@@ -178,7 +178,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
     uint64_t* bar_sched_full = bar_acc_free + 1;                 // [2]
     uint64_t* bar_sched_empty = bar_sched_full + 2;              // [2]
     uint64_t* bar_stat = bar_sched_empty + 2;                    // [2] per warpgroup: a tile's statistics are staged
-    int* sched_item = reinterpret_cast<int*>(bar_stat + 2);      // [2]
+    uint64_t* bar_res_tmem = bar_stat + 2;                       // compute -> MMA: resident pair copied to tensor memory
+    int* sched_item = reinterpret_cast<int*>(bar_res_tmem + 1);  // [2]
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sched_item + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     float* s_stat = reinterpret_cast<float*>(aux + 1024);     // [2 buffers][2: -lse2, -delta][128]
@@ -186,11 +187,23 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
     const int warp = uniform_warp_idx();
     const int lane = threadIdx.x & 31;
     const int off = p.L - p.S;
+    // With queries resident only one accumulator (dQ) is needed, which leaves 128 tensor-memory
+    // columns free.  The compute threads copy the resident Q and dO tiles there at the start of an
+    // item (bf16, D/2 columns each), and from the item's second tile on they are the A operands of
+    // the two score GEMMs, which then read only the streamed tile from shared memory: half the
+    // bytes of an MMA with both operands in shared memory, whose 8 KB per 64 cycles are all an SM
+    // can deliver (measured: 2040 -> 1810 cycles per tile).  The first tile's score GEMMs still take
+    // both operands from shared memory so that they can be issued under the previous item's epilogue.
+    constexpr bool kResidentInTmem = !kKeysResident;
+    constexpr uint32_t kColRes = 256;   // Q at [256, 256 + D/2), dO at [256 + D/2, 256 + D)
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(bar_res_full, 1);
-        mbar_init(bar_res_empty, 1);
+        // the resident pair may be reloaded when the MMA warp has issued its last reads of it and, where
+        // the compute threads copy it to tensor memory, when all of them have done so (short items
+        // release it in their prologue, before the compute threads have even begun the item)
+        mbar_init(bar_res_empty, kResidentInTmem ? 257 : 1);
         for (int s = 0; s < kN0; ++s) {
             mbar_init(&bar_t0_full[s], 1);
             mbar_init(&bar_t0_empty[s], 1);
@@ -207,6 +220,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
         mbar_init(bar_acc_free, 256);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_stat[i], 128);
+            if (i == 0) mbar_init(bar_res_tmem, 256);
             mbar_init(&bar_sched_full[i], 1);
             mbar_init(&bar_sched_empty[i], 257);   // MMA warp (1) + 256 compute threads
         }
@@ -255,6 +269,35 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             const BwdItem w = bwd_decode_item<kKeysResident>(item, p);
             const int bh = w.bh;
             const int rrow = w.r0 + wq * 32 + lane;            // this thread's resident row
+            // per-item stamps of the traced CTA: row k of warpgroup wg, slots 6 (start) and 7 (tiles)
+            if (p.trace != nullptr && (int)blockIdx.x == p.trace_block && wq == 0 && lane == 0 && k < 64) {
+                p.trace[(wg * 64 + k) * 8 + 6] = clock64();
+                p.trace[(wg * 64 + k) * 8 + 7] = w.n_it;
+            }
+            if (kResidentInTmem) {
+                // warpgroup 0 copies this thread's row of Q, warpgroup 1 its row of dO, out of the
+                // 128-byte-swizzled shared-memory tile (16-byte chunk j of row r sits at chunk j ^ (r & 7));
+                // two consecutive bf16 values per 32-bit column, low half first, as the MMA expects.
+                // The previous item's GEMMs are done with these columns: its epilogue waited for them.
+                mbar_wait(bar_res_full, k & 1, wctx, BB_RES, k);
+                const int r_in = wq * 32 + lane;
+                const unsigned char* tile = sR + wg * Cfg::kTileBytes + r_in * 128;
+                const uint32_t tdst = tmem_base + lane_off + kColRes + wg * (D / 2);
+#pragma unroll
+                for (int sb = 0; sb < Cfg::kSub; ++sb) {
+                    uint32_t r[32];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 v4 = *reinterpret_cast<const uint4*>(tile + sb * Cfg::kSubBytes + ((j ^ (r_in & 7)) << 4));
+                        r[4 * j + 0] = v4.x; r[4 * j + 1] = v4.y; r[4 * j + 2] = v4.z; r[4 * j + 3] = v4.w;
+                    }
+                    tmem_st32(tdst + sb * 32, r);
+                }
+                mbar_arrive(bar_res_empty);   // this thread's reads of the shared-memory tiles are done
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar_res_tmem);
+            }
             // row constants (queries resident) as packed pairs of the NEGATED values
             uint64_t row_nlse2 = 0, row_ndelta2 = 0;
             if (!kKeysResident) {
@@ -550,13 +593,17 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             const uint64_t dT_base = umma_smem_desc(sT_addr, 16, 1024);                   // K-major
             const uint64_t dT_mn_base = umma_smem_desc(sT_addr, Cfg::kSubBytes, 1024);    // MN-major
             // G1 / G2: tmem[col] = R_which T^T for the streamed tile at index `tile` of the stream buffers
-            auto issue_score = [&](int which, int tile, uint32_t col) {
+            auto issue_score = [&](int which, int tile, uint32_t col, bool a_in_tmem = false) {
                 const uint64_t a0 = umma_desc_advance(dR_base, which * Cfg::kTileBytes);
                 const uint64_t b0 = umma_desc_advance(dT_base, tile * Cfg::kTileBytes);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t o = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
-                    umma_ss(tmem_u + col, umma_desc_advance(a0, o), umma_desc_advance(b0, o), idesc_s, kk > 0);
+                    if (kResidentInTmem && a_in_tmem)   // A = resident tile in tensor memory: 8 columns per K step of 16
+                        umma_ts(tmem_u + col, tmem_u + kColRes + which * (D / 2) + kk * 8, umma_desc_advance(b0, o), idesc_s,
+                                kk > 0);
+                    else
+                        umma_ss(tmem_u + col, umma_desc_advance(a0, o), umma_desc_advance(b0, o), idesc_s, kk > 0);
                 }
             };
             // G3 / G4: tmem[acc] (+)= bf16 A in tensor memory times the streamed tile (MN-major).  A is what
@@ -613,11 +660,16 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                     __syncwarp();
                     tc_fence_after();
                     if (tr) TT_BTRACE(2, it, 1);
+                    if (kResidentInTmem && it == 0) {   // complete long ago: the copy precedes the compute threads' first tile
+                        mbar_wait(bar_res_tmem, k & 1, wctx, BB_RES + 2, k);
+                        __syncwarp();
+                        tc_fence_after();
+                    }
                     if (has_next) {
                         mbar_wait(&bar_t0_full[n0s], ((g + 1) / kN0) & 1, wctx, BB_STFULL + n0s, it + 1);
                         __syncwarp();
                         tc_fence_after();
-                        issue_score(0, n0s, kColS);
+                        issue_score(0, n0s, kColS, true);
                         tc_commit(bar_s_full);
                     }
                     if (tr) TT_BTRACE(2, it, 2);
@@ -640,7 +692,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                         mbar_wait(&bar_t1_full[n1s], ((g + 1) / kN1) & 1, wctx, BB_STFULL + 6 + n1s, it + 1);
                         __syncwarp();
                         tc_fence_after();
-                        issue_score(1, kN0 + n1s, kColDP);
+                        issue_score(1, kN0 + n1s, kColDP, true);
                         tc_commit(bar_dp_full);
                         if (!kKeysResident) tc_commit(&bar_t1_empty[n1s]);   // dP was the only use of V(t+1)
                         if (it + 2 == n_it) tc_commit(bar_res_empty);   // last reads of the resident pair

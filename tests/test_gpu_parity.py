@@ -415,3 +415,24 @@ def test_config5_single_head_properties(tt, oracle):
     # the last key is seen only by the last query: dV[last] = P[last,last] * dO[last]
     p_last = torch.exp(((q[0, 0, -1].float() * k[0, 0, -1].float()).sum() / D ** 0.5) - lse[0, 0, -1])
     assert torch.allclose(dv[0, 0, -1].float(), p_last * do[0, 0, -1].float(), atol=2e-2)
+
+
+def test_backward_many_short_items(tt, oracle):
+    """Thousands of work items of one or two streamed tiles each (causal, S = L = 256): item turnover
+    is where the persistent kernels hand buffers over (resident tiles, accumulators, tensor-memory
+    copies), so it gets its own case; every wait is bounded, a stall shows as TT_ERR_TIMEOUT."""
+    import torch
+    B, H, S, D = 10, 64, 256, 128
+    g = torch.Generator(device="cuda").manual_seed(77)
+    mk = lambda s: (torch.randn((B, H, S, D), generator=g, device="cuda") * s).to(torch.bfloat16)
+    q, k, v, do = mk(0.5), mk(0.5), mk(1.0), mk(1.0)
+    for _ in range(3):
+        out, lse = tt.attention_forward(q, k, v, causal=True)
+        dq, dk, dv = tt.attention_backward(q, k, v, out, lse, do, causal=True)
+    tt.check_device_status()
+    f = lambda t, b, h: t[b:b + 1, h:h + 1].float().cpu().numpy()
+    for b, h in ((0, 0), (4, 31), (9, 63)):
+        o_r, _, dq_r, dk_r, dv_r = oracle.attention_backward(f(q, b, h), f(k, b, h), f(v, b, h), f(do, b, h), True)
+        assert oracle.max_abs_err(f(out, b, h), o_r) <= 2e-2
+        for got, ref in ((dq, dq_r), (dk, dk_r), (dv, dv_r)):
+            assert oracle.max_abs_err(f(got, b, h), ref) <= 2e-2 + 2.0 ** -7 * np.abs(ref).max()
