@@ -164,20 +164,21 @@ attn_decode_bf16_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             float mx = s[0];
 #pragma unroll
             for (int u = 1; u < kUnroll; ++u) mx = fmaxf(mx, s[u]);
-            if (mx > m[g]) {   // uniform across the lanes of a row group
-                float corr = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mx);
-                l[g] *= corr;
+            // branch-free running-maximum update (a branch per query head would cut the unrolled
+            // body into basic blocks and nothing would be scheduled across the heads): the
+            // correction is exactly 1 when the maximum did not move and 0 for a state that was empty
+            const float mnew = fmaxf(m[g], mx);
+            const float mref = (mnew == -INFINITY) ? 0.f : mnew;   // no inf - inf when nothing is visible yet
+            const float corr = exp2f(m[g] - mref);
+            l[g] *= corr;
 #pragma unroll
-                for (int t = 0; t < 8; ++t) o[g][t] *= corr;
-                m[g] = mx;
-            }
-            if (m[g] != -INFINITY) {
+            for (int t = 0; t < 8; ++t) o[g][t] *= corr;
+            m[g] = mnew;
 #pragma unroll
-                for (int u = 0; u < kUnroll; ++u) {
-                    float pu = exp2f(s[u] - m[g]);
-                    l[g] += pu;
-                    axpy8(pu, vv[u], o[g]);
-                }
+            for (int u = 0; u < kUnroll; ++u) {
+                const float pu = exp2f(s[u] - mref);             // masked rows: exp2(-inf) = 0
+                l[g] += pu;
+                axpy8(pu, vv[u], o[g]);
             }
         }
     }
