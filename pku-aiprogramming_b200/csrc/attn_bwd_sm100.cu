@@ -19,9 +19,16 @@
 //   G4: acc1 += dS T0  (A tensor memory, B MN-major)  [dK or dQ]
 //
 // Roles: warps 0-7 = two compute warpgroups (thread <-> resident row; warpgroup w owns
-// score columns [64w, 64w+64)), warp 8 = MMA issuer, warp 9 = TMA loader.
-// Tensor memory: S [0,128), dP [128,256), acc0 [256,256+D), acc1 [256+D,256+2D); the bf16
-// P / dS written by warpgroup w overlay columns [64w,64w+32) of S / dP.
+// score columns [64w, 64w+64)), warp 8 = MMA issuer, warp 9 = TMA loader and work-item scheduler.
+// Tensor memory: S [0,128), dP [128,256), acc0 [256,256+D), acc1 [256+D,256+2D).  A compute
+// thread reads its S values (which frees the S columns for the next tile's G1 at once), forms P in
+// registers, reads its dP values, and writes the bf16 dS^T -- with keys resident also the bf16
+// P^T -- over the dP columns it has just read; G3, G4 and the next G2 follow back to back.
+// With queries resident acc0 is not needed: its columns hold a copy of the resident pair, which
+// from an item's second tile on is the A operand of G1 and G2 (tensor memory instead of shared
+// memory, which is the scarcer bandwidth).
+// Shared memory: the resident pair plus rings of 3 (T0) and 2 (T1) streamed tiles at D = 128,
+// barriers and 2 KB of per-column statistics: exactly 227 KB.
 #include "common.h"
 #include "sm100_ptx.cuh"
 #include <stdlib.h>
