@@ -73,6 +73,7 @@ struct BwdParams {
     int group;                     // query heads per key/value head (1 = ordinary multi-head attention)
     const int* kv_lens;            // optional key padding lengths per batch entry (see AttnArgs)
     int H;                         // query heads per batch entry
+    int wide_stores;               // 1: the outputs are 32-byte aligned, the epilogue uses 32-byte stores
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
 };
@@ -521,13 +522,18 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
 #pragma unroll
                     for (int cc = 0; cc < kHalf / 32; ++cc) {
 #pragma unroll
-                        for (int e = 0; e < 32; e += 8) {
-                            uint4 o4;
-                            o4.x = pack_bf16x2(__uint_as_float(acc[a][cc][e + 0]) * mul, __uint_as_float(acc[a][cc][e + 1]) * mul);
-                            o4.y = pack_bf16x2(__uint_as_float(acc[a][cc][e + 2]) * mul, __uint_as_float(acc[a][cc][e + 3]) * mul);
-                            o4.z = pack_bf16x2(__uint_as_float(acc[a][cc][e + 4]) * mul, __uint_as_float(acc[a][cc][e + 5]) * mul);
-                            o4.w = pack_bf16x2(__uint_as_float(acc[a][cc][e + 6]) * mul, __uint_as_float(acc[a][cc][e + 7]) * mul);
-                            *reinterpret_cast<uint4*>(dst + cc * 32 + e) = o4;
+                        for (int e = 0; e < 32; e += 16) {
+                            uint32_t o8[8];
+#pragma unroll
+                            for (int q2 = 0; q2 < 8; ++q2)
+                                o8[q2] = pack_bf16x2(__uint_as_float(acc[a][cc][e + 2 * q2]) * mul,
+                                                     __uint_as_float(acc[a][cc][e + 2 * q2 + 1]) * mul);
+                            if (p.wide_stores) {
+                                st_global_32B(dst + cc * 32 + e, o8);
+                            } else {
+                                *reinterpret_cast<uint4*>(dst + cc * 32 + e) = make_uint4(o8[0], o8[1], o8[2], o8[3]);
+                                *reinterpret_cast<uint4*>(dst + cc * 32 + e + 8) = make_uint4(o8[4], o8[5], o8[6], o8[7]);
+                            }
                         }
                     }
                 }
@@ -817,6 +823,11 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.group = a.group;
     p.kv_lens = a.kv_lens;
     p.H = a.H;
+    {
+        const char* ws_env = getenv("TT_ST256");
+        const uintptr_t al = reinterpret_cast<uintptr_t>(a.dq) | reinterpret_cast<uintptr_t>(a.dk) | reinterpret_cast<uintptr_t>(a.dv);
+        p.wide_stores = ((al & 31) == 0 && !(ws_env && ws_env[0] == '0')) ? 1 : 0;
+    }
     p.n_tiles = (a.L + 127) / 128;
     p.n_items = (int)(a.BH / a.group * p.n_tiles);
     p.sched_counter = next_bwd_sched_counter(st, &e);

@@ -63,6 +63,9 @@ struct FwdParams {
     int q_div;                     // query slice = output slice / q_div
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
+    int trace_item;     // which of the CTA's work items gets the per-iteration stamps (TT_TRACE_ITEM, default 0)
+    int s0_ahead;       // 1: issue the next item's S_0(0) in a causal item's idle last iteration (TT_FWD_S0_AHEAD=0 disables)
+    int wide_stores;    // 1: `out` is 32-byte aligned, the epilogue uses 32-byte stores (TT_ST256=0 disables)
 };
 
 #define TT_TRACE(role, iter, slot)                                                                  \
@@ -269,7 +272,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             float m2 = -INFINITY;   // running max in the scaled log2 domain
             float l = 0.f;          // running sum of exp2(s*c - m2)
             for (int j = 0; j < nt; ++j, ++s_cnt) {
-                const bool tr = (k == 0 && wq == 0 && lane == 0);
+                const bool tr = (k == p.trace_item && wq == 0 && lane == 0);
                 if (tr) TT_TRACE(i, j, 0);
                 mbar_wait(&bar_s_full[i], s_cnt & 1, wctx, BAR_SFULL + i, j);
                 __syncwarp();
@@ -355,13 +358,17 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
                 for (int cc = 0; cc < D / 32; ++cc) {
 #pragma unroll
-                    for (int e = 0; e < 32; e += 8) {
-                        uint4 o4;
-                        o4.x = pack_bf16x2(__uint_as_float(orr[cc][e + 0]) * inv, __uint_as_float(orr[cc][e + 1]) * inv);
-                        o4.y = pack_bf16x2(__uint_as_float(orr[cc][e + 2]) * inv, __uint_as_float(orr[cc][e + 3]) * inv);
-                        o4.z = pack_bf16x2(__uint_as_float(orr[cc][e + 4]) * inv, __uint_as_float(orr[cc][e + 5]) * inv);
-                        o4.w = pack_bf16x2(__uint_as_float(orr[cc][e + 6]) * inv, __uint_as_float(orr[cc][e + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + cc * 32 + e) = o4;
+                    for (int e = 0; e < 32; e += 16) {
+                        uint32_t o8[8];
+#pragma unroll
+                        for (int q2 = 0; q2 < 8; ++q2)
+                            o8[q2] = pack_bf16x2(__uint_as_float(orr[cc][e + 2 * q2]) * inv, __uint_as_float(orr[cc][e + 2 * q2 + 1]) * inv);
+                        if (p.wide_stores) {
+                            st_global_32B(orow + cc * 32 + e, o8);
+                        } else {
+                            *reinterpret_cast<uint4*>(orow + cc * 32 + e) = make_uint4(o8[0], o8[1], o8[2], o8[3]);
+                            *reinterpret_cast<uint4*>(orow + cc * 32 + e + 8) = make_uint4(o8[4], o8[5], o8[6], o8[7]);
+                        }
                     }
                 }
                 if (p.lse != nullptr) p.lse[(long long)w.bh * p.S + row] = (m2 + log2f(l)) * 0.6931471805599453f;
@@ -460,8 +467,15 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     umma_ts(d, a + kk * 8, umma_desc_advance(b0, kk * 2048), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
                 }
             };
+            // Causal items give query tile 1 one key/value tile more than tile 0, so in an item's last
+            // iteration slot 0 has nothing to do.  That gap is used: the item that follows is fetched
+            // early and its S_0(0) issued right there (`s0_ahead`), so that softmax warpgroup 0 finds
+            // its first scores waiting instead of sitting out tile 1's last iteration plus a GEMM.
+            int ahead_item = -2;       // next work item when fetched early (-2: not fetched)
+            bool s0_ahead = false;     // S_0(0) of the current item was issued during the previous item
             for (int k = 0;; ++k) {
-                const int item = next_item(k);
+                const int item = (ahead_item != -2) ? ahead_item : next_item(k);
+                ahead_item = -2;
                 __syncwarp();
                 if (elect_one()) mbar_arrive(&bar_sched_empty[k & 1]);
                 __syncwarp();
@@ -473,6 +487,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     wait_item(t);   // K_0
                     tc_fence_after();
                     for (int i = 0; i < 2; ++i) {
+                        if (i == 0 && s0_ahead) {   // done already, including the bookkeeping of Q_0
+                            s0_ahead = false;
+                            continue;
+                        }
                         if (w.n_tiles[i] > 0) {
                             mbar_wait(&bar_q_full[i], q_uses[i] & 1, wctx, BAR_QFULL + i, k);
                             ++q_uses[i];
@@ -497,7 +515,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                                 ++o_uses[i];
                                 __syncwarp();
                             }
-                            const bool tr = (k == 0 && lane == 0);
+                            const bool tr = (k == p.trace_item && lane == 0);
                             if (tr) TT_TRACE(2, j, 4 * i + 0);
                             mbar_wait(&bar_p_full[2 * i], p_cnt[i] & 1, wctx, BAR_PFULL + 2 * i, j);
                             __syncwarp();
@@ -522,6 +540,27 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                                 if (tr) TT_TRACE(2, j, 4 * i + 3);
                             } else {
                                 tc_commit(&bar_o_final[i]);
+                            }
+                        }
+                    }
+                    if (p.s0_ahead && j + 1 == w.n_max && w.n_tiles[0] < w.n_max) {
+                        // last iteration, slot 0 idle: S_0(0) of the next item (its K_0 is ring item t + 2 n_max)
+                        ahead_item = next_item(k + 1);
+                        __syncwarp();
+                        if (ahead_item >= 0) {
+                            const FwdItem wn = fwd_decode_item(ahead_item, p);
+                            if (wn.n_tiles[0] > 0) {
+                                const uint32_t tn = t + 2 * (uint32_t)w.n_max;
+                                wait_item(tn);
+                                tc_fence_after();
+                                mbar_wait(&bar_q_full[0], q_uses[0] & 1, wctx, BAR_QFULL, k + 1);
+                                ++q_uses[0];
+                                __syncwarp();
+                                tc_fence_after();
+                                issue_s(0, tn);
+                                tc_commit(&bar_s_full[0]);
+                                if (wn.n_tiles[0] == 1) tc_commit(&bar_q_empty[0]);   // that was this tile's last S
+                                s0_ahead = true;
                             }
                         }
                     }
@@ -604,6 +643,14 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.status = device_status_word();
     p.trace = g_fwd_trace;
     p.trace_block = g_fwd_trace_block;
+    {
+        const char* ti = getenv("TT_TRACE_ITEM");
+        p.trace_item = (ti && *ti) ? atoi(ti) : 0;
+        const char* sa = getenv("TT_FWD_S0_AHEAD");
+        p.s0_ahead = (sa && sa[0] == '0') ? 0 : 1;
+        const char* ws = getenv("TT_ST256");
+        p.wide_stores = ((reinterpret_cast<uintptr_t>(a.out) & 31) == 0 && !(ws && ws[0] == '0')) ? 1 : 0;
+    }
     p.n_items = (int)(a.BH * p.n_qblk);
     p.sched_counter = next_sched_counter(st, &e);
     if (e != cudaSuccess) return e;

@@ -313,6 +313,15 @@ __device__ __forceinline__ void ex2_poly_x2(uint64_t x, float& r0, float& r1) {
     r1 = __uint_as_float(__float_as_uint(a1) + (__float_as_uint(i1) << 23));
 }
 
+// 32-byte global store (one full sector per lane and instruction; sm_100).  `p` must be 32-byte
+// aligned.  Row-per-lane epilogues issue half as many store instructions with it, and those sit in
+// the same memory-instruction queue as the tensor-memory loads of the other warps.
+__device__ __forceinline__ void st_global_32B(void* p, const uint32_t (&r)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
