@@ -53,7 +53,7 @@ template <bool kAMn, bool kBMn>
 __global__ void __launch_bounds__(192, 1)
 fc_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-                     int tiles_m, int tiles_n, unsigned int* status) {
+                     int tiles_m, int tiles_n, int wide, unsigned int* status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -192,13 +192,16 @@ fc_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 const int col0 = n0 + c * 32;
                 if (row < M) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const int col = col0 + g * 8;
-                        if (col < N) {   // N % 8 == 0: a group of 8 columns is inside or outside as a whole
+                    for (int g2 = 0; g2 < 2; ++g2) {
+                        uint32_t o8[8];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int g = g2 * 2 + h;
+                            const int col = col0 + g * 8;
                             float v[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g * 8 + e]);
-                            if (bias) {
+                            if (bias && col < N) {
                                 const uint4 bb = *reinterpret_cast<const uint4*>(bias + col);
                                 const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
@@ -207,12 +210,16 @@ fc_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                     v[2 * e + 1] += __uint_as_float(bw[e] & 0xffff0000u);
                                 }
                             }
-                            uint4 o;
-                            o.x = pack_bf16x2(v[0], v[1]);
-                            o.y = pack_bf16x2(v[2], v[3]);
-                            o.z = pack_bf16x2(v[4], v[5]);
-                            o.w = pack_bf16x2(v[6], v[7]);
-                            *reinterpret_cast<uint4*>(crow + col) = o;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) o8[h * 4 + e] = pack_bf16x2(v[2 * e], v[2 * e + 1]);
+                        }
+                        // N % 8 == 0: a group of 8 columns is inside or outside as a whole
+                        const int col = col0 + g2 * 16;
+                        if (wide && col + 16 <= N) {
+                            st_global_32B(crow + col, o8);   // one full sector per lane and instruction
+                        } else {
+                            if (col < N) *reinterpret_cast<uint4*>(crow + col) = make_uint4(o8[0], o8[1], o8[2], o8[3]);
+                            if (col + 8 < N) *reinterpret_cast<uint4*>(crow + col + 8) = make_uint4(o8[4], o8[5], o8[6], o8[7]);
                         }
                     }
                 }
@@ -351,7 +358,9 @@ cudaError_t launch_tc(const void* A, const void* B, void* C, const void* bias, i
     LaunchScope ls(K_FC_GEMM, st);
     fc_gemm_sm100_kernel<kAMn, kBMn><<<grid, 192, kGemmSmem, st>>>(
         *reinterpret_cast<CUtensorMap*>(ta.bytes), *reinterpret_cast<CUtensorMap*>(tb.bytes), (__nv_bfloat16*)C,
-        (const __nv_bfloat16*)bias, M, N, K, tiles_m, tiles_n, device_status_word());
+        (const __nv_bfloat16*)bias, M, N, K, tiles_m, tiles_n,
+        ((reinterpret_cast<uintptr_t>(C) & 31) == 0 && N % 16 == 0) ? 1 : 0,   // 32-byte stores possible
+        device_status_word());
     return cudaGetLastError();
 }
 
