@@ -38,6 +38,12 @@
 namespace ttk {
 using namespace sm100;
 
+// Registers per thread after setmaxnreg (compute warpgroups / the loader-and-MMA warpgroup).
+#ifndef TT_BWD_REGS_COMPUTE
+#define TT_BWD_REGS_COMPUTE 216
+#define TT_BWD_REGS_OTHER 72
+#endif
+
 template <int D>
 struct BwdCfg {
     static constexpr int kSub = D / 64;
@@ -49,6 +55,13 @@ struct BwdCfg {
     // aligned and refuses to run (status word) if the base is not.
     static constexpr int kStreamTiles = (D == 128) ? 5 : 8;
     static constexpr int kThreads = 384;
+    // The pool a CTA's setmaxnreg can draw from is what the launch allocated: kRegsLaunch per thread
+    // (the __launch_bounds__ figure rounded down to a multiple of 8).  A split above it never completes.
+    static constexpr int kRegsLaunch = 168;
+    static constexpr int kRegsCompute = TT_BWD_REGS_COMPUTE;
+    static constexpr int kRegsOther = TT_BWD_REGS_OTHER;
+    static_assert(256 * kRegsCompute + 128 * kRegsOther <= kThreads * kRegsLaunch, "register split exceeds the CTA's pool");
+    static_assert(kRegsCompute % 8 == 0 && kRegsOther % 8 == 0, "setmaxnreg takes multiples of 8");
     static constexpr int kTmemCols = 512;
     static constexpr int kAuxBytes = 3072;                           // 1 KB barriers + 2 KB lse/delta staging
     static constexpr int kSmemBytes = (2 + kStreamTiles) * kTileBytes + kAuxBytes;
@@ -143,7 +156,8 @@ __device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p)
     return w;
 }
 
-template <int D, bool kKeysResident, int kPoly>
+// kTrace: compiled with the cycle stamps (debug aid; launched only while a trace buffer is set).
+template <int D, bool kKeysResident, int kPoly, bool kTrace>
 __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_constant__ CUtensorMap tmR1,
                       const __grid_constant__ CUtensorMap tmT0, const __grid_constant__ CUtensorMap tmT1,
@@ -260,7 +274,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
 
     if (warp < 8) {
         // ============================================================ compute warpgroups
-        setmaxnreg_inc<224>();
+        setmaxnreg_inc<Cfg::kRegsCompute>();
         const int wg = warp >> 2;
         const int wq = warp & 3;
         const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
@@ -278,7 +292,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             const int bh = w.bh;
             const int rrow = w.r0 + wq * 32 + lane;            // this thread's resident row
             // per-item stamps of the traced CTA: row k of warpgroup wg, slots 6 (start) and 7 (tiles)
-            if (p.trace != nullptr && (int)blockIdx.x == p.trace_block && wq == 0 && lane == 0 && k < 64) {
+            if (kTrace && p.trace != nullptr && (int)blockIdx.x == p.trace_block && wq == 0 && lane == 0 && k < 64) {
                 p.trace[(wg * 64 + k) * 8 + 6] = clock64();
                 p.trace[(wg * 64 + k) * 8 + 7] = w.n_it;
             }
@@ -356,7 +370,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             for (int u = 0; u < w.n_it; ++u, ++git) {
                 const int it = u;
                 const int t = kKeysResident ? w.t_begin + u % w.nt : w.t_begin + u;
-                const bool tr = (k == 0 && wq == 0 && lane == 0);
+                const bool tr = kTrace && (k == 0 && wq == 0 && lane == 0);
                 const int c0 = t * 128;                            // first streamed row of this tile
                 if (tr) TT_BTRACE(wg, it, 0);
                 const float* st_nlse = s_stat + (git & 1) * 256;   // -lse2 of the 128 streamed queries
@@ -541,7 +555,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             __syncwarp();
         }
     } else {
-        setmaxnreg_dec<56>();
+        setmaxnreg_dec<Cfg::kRegsOther>();
         if (warp == 9) {
             // ============================================================ TMA loader + scheduler (whole
             // warp runs the control flow, one elected lane issues)
@@ -667,7 +681,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                     const int a0s = g % kN0, a1s = g % kN1;                  // slots of this tile
                     const bool has_next = it + 1 < n_it;
                     const int n0s = (g + 1) % kN0, n1s = (g + 1) % kN1;      // slots of the next tile
-                    const bool tr = (k == 0 && lane == 0);
+                    const bool tr = kTrace && (k == 0 && lane == 0);
                     if (tr) TT_BTRACE(2, it, 0);
                     mbar_wait(bar_p_full, g & 1, wctx, BB_PFULL, it);   // S(t) is in registers: its columns are free
                     __syncwarp();
@@ -780,7 +794,7 @@ void attn_bwd_set_trace(long long* device_buf, int block, int pass) {
     g_bwd_trace_mode = device_buf ? pass : 0;
 }
 
-template <int D, int kPoly>
+template <int D, int kPoly, bool kTrace>
 static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     using Cfg = BwdCfg<D>;
     float* delta = reinterpret_cast<float*>(ws);
@@ -798,10 +812,10 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tdo, a.dout, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
     auto M = [](TmapStorage& t) -> CUtensorMap& { return *reinterpret_cast<CUtensorMap*>(t.bytes); };
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, true, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, true, kPoly, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, false, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, false, kPoly, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     BwdParams p;
@@ -834,7 +848,7 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     {
         LaunchScope ls(K_BWD_DKV, st);
-        attn_bwd_sm100_kernel<D, true, kPoly><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, true, kPoly, kTrace><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tk), M(tv), M(tq), M(tdo), p);
     }
     // dQ: queries resident, stream (K, V)
@@ -847,7 +861,7 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     {
         LaunchScope ls(K_BWD_DQ, st);
-        attn_bwd_sm100_kernel<D, false, kPoly><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, false, kPoly, kTrace><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tq), M(tdo), M(tk), M(tv), p);
     }
     return cudaGetLastError();
@@ -857,19 +871,14 @@ static int bwd_poly_setting() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("TT_BWD_POLY");
-        v = (e && *e) ? atoi(e) : 0;
-        if (v != 0 && v != 2 && v != 4 && v != 6) v = 0;
+        v = (e && *e && atoi(e) > 0) ? 1 : 0;   // on: 4 of every 8 pairs of exponentials by polynomial
     }
     return v;
 }
 template <int D>
 static cudaError_t launch_bwd_d(const AttnArgs& a, void* ws, cudaStream_t st) {
-    switch (bwd_poly_setting()) {
-        case 2: return launch_bwd<D, 2>(a, ws, st);
-        case 4: return launch_bwd<D, 4>(a, ws, st);
-        case 6: return launch_bwd<D, 6>(a, ws, st);
-        default: return launch_bwd<D, 0>(a, ws, st);
-    }
+    if (g_bwd_trace_mode != 0) return launch_bwd<D, 0, true>(a, ws, st);
+    return bwd_poly_setting() ? launch_bwd<D, 4, false>(a, ws, st) : launch_bwd<D, 0, false>(a, ws, st);
 }
 cudaError_t attn_bwd_sm100(const AttnArgs& a, void* ws, cudaStream_t st) {
     return a.D == 128 ? launch_bwd_d<128>(a, ws, st) : launch_bwd_d<64>(a, ws, st);

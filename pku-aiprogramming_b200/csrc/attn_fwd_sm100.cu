@@ -32,6 +32,11 @@
 namespace ttk {
 using namespace sm100;
 
+#ifndef TT_FWD_REGS_SOFTMAX
+#define TT_FWD_REGS_SOFTMAX 216
+#define TT_FWD_REGS_OTHER 72
+#endif
+
 template <int D>
 struct FwdCfg {
     static constexpr int kTile = 128;                     // rows per Q tile and keys per K/V tile
@@ -40,6 +45,15 @@ struct FwdCfg {
     static constexpr int kTileBytes = kSub * kSubBytes;   // 32 KiB (D=128), 16 KiB (D=64)
     static constexpr int kStages = (D == 128) ? 4 : 8;    // K/V ring depth (tiles)
     static constexpr int kThreads = 384;
+    // Register split after setmaxnreg: the two softmax warpgroups grow to kRegsSoftmax, the third
+    // warpgroup (loader, MMA issuer, two idle warps) shrinks to kRegsOther.  The pool a CTA can draw
+    // from is what the launch allocated (kRegsLaunch per thread, the __launch_bounds__ figure rounded
+    // down to a multiple of 8); a split that asks for more than the pool never completes.
+    static constexpr int kRegsLaunch = 168;
+    static constexpr int kRegsSoftmax = TT_FWD_REGS_SOFTMAX;
+    static constexpr int kRegsOther = TT_FWD_REGS_OTHER;
+    static_assert(256 * kRegsSoftmax + 128 * kRegsOther <= kThreads * kRegsLaunch, "register split exceeds the CTA's pool");
+    static_assert(kRegsSoftmax % 8 == 0 && kRegsOther % 8 == 0, "setmaxnreg takes multiples of 8");
     static constexpr int kTmemCols = 512;
     static constexpr int kBarBytes = 1024;
     static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + kBarBytes + 1024;  // +1024: alignment slack
@@ -169,7 +183,9 @@ __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p)
     return w;
 }
 
-template <int D, int kPoly>
+// kTrace: compiled with the cycle stamps (debug aid; costs registers in every role, so the
+// product launches the kTrace = false instantiation unless a trace buffer is set).
+template <int D, int kPoly, bool kTrace>
 __global__ void __launch_bounds__(FwdCfg<D>::kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -245,7 +261,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
     if (warp < 8) {
         // =========================================================== softmax warpgroups
-        setmaxnreg_inc<224>();
+        setmaxnreg_inc<Cfg::kRegsSoftmax>();
         const int i = warp >> 2;                    // query tile
         const int wq = warp & 3;                    // TMEM lane quarter of this warp
         const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
@@ -263,7 +279,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const FwdItem w = fwd_decode_item(item, p);
             const int nt = w.n_tiles[i];
             // per-item stamps of the traced CTA (role slot 0/1 = query tile, row = item number k)
-            if (p.trace != nullptr && (int)blockIdx.x == p.trace_block && wq == 0 && (threadIdx.x & 31) == 0 && k < 64) {
+            if (kTrace && p.trace != nullptr && (int)blockIdx.x == p.trace_block && wq == 0 && (threadIdx.x & 31) == 0 && k < 64) {
                 p.trace[(i * 64 + k) * 8 + 6] = clock64();
                 p.trace[(i * 64 + k) * 8 + 7] = nt;
             }
@@ -272,7 +288,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             float m2 = -INFINITY;   // running max in the scaled log2 domain
             float l = 0.f;          // running sum of exp2(s*c - m2)
             for (int j = 0; j < nt; ++j, ++s_cnt) {
-                const bool tr = (k == p.trace_item && wq == 0 && lane == 0);
+                const bool tr = kTrace && (k == p.trace_item && wq == 0 && lane == 0);
                 if (tr) TT_TRACE(i, j, 0);
                 mbar_wait(&bar_s_full[i], s_cnt & 1, wctx, BAR_SFULL + i, j);
                 __syncwarp();
@@ -376,7 +392,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             __syncwarp();
         }
     } else {
-        setmaxnreg_dec<56>();
+        setmaxnreg_dec<Cfg::kRegsOther>();
         if (warp == 9) {
             // ======================================================= TMA loader + scheduler (whole warp
             // runs the control flow, one elected lane issues)
@@ -406,17 +422,18 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 __syncwarp();
                 if (item < 0) break;
                 const FwdItem w = fwd_decode_item(item, p);
+                const int q_bh = w.bh / p.q_div, kv_bh = w.bh / p.group;   // slices of Q and of K/V this item reads
                 auto load_q = [&](int i) {
                     mbar_wait(&bar_q_empty[i], (q_uses[i] & 1) ^ 1, wctx, 5 + i, k);
                     __syncwarp();
-                    load_tile(sQ + i * Cfg::kTileBytes, &tmQ, &bar_q_full[i], w.q0 + 128 * i, w.bh / p.q_div);
+                    load_tile(sQ + i * Cfg::kTileBytes, &tmQ, &bar_q_full[i], w.q0 + 128 * i, q_bh);
                     ++q_uses[i];
                 };
                 auto load_kv = [&](const CUtensorMap* tm, int j) {   // ring order: K_0, V_0, K_1, V_1, ...
                     const int st = t % kStages;
                     mbar_wait(&bar_kv_empty[st], ((t / kStages) & 1) ^ 1, wctx, BAR_KVEMPTY + st, (int)t);
                     __syncwarp();
-                    load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], j * 128, w.bh / p.group);
+                    load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], j * 128, kv_bh);
                     ++t;
                 };
                 if (w.n_tiles[0] > 0) load_q(0);
@@ -515,7 +532,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                                 ++o_uses[i];
                                 __syncwarp();
                             }
-                            const bool tr = (k == p.trace_item && lane == 0);
+                            const bool tr = kTrace && (k == p.trace_item && lane == 0);
                             if (tr) TT_TRACE(2, j, 4 * i + 0);
                             mbar_wait(&bar_p_full[2 * i], p_cnt[i] & 1, wctx, BAR_PFULL + 2 * i, j);
                             __syncwarp();
@@ -610,13 +627,12 @@ static int fwd_poly_setting() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("TT_FWD_POLY");
-        v = (e && *e) ? atoi(e) : 0;
-        if (v < 0 || v > 4) v = 0;
+        v = (e && *e && atoi(e) > 0) ? 1 : 0;   // on: 2 of every 8 exponentials by polynomial
     }
     return v;
 }
 
-template <int D, int kPoly>
+template <int D, int kPoly, bool kTrace>
 static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     using Cfg = FwdCfg<D>;
     TmapStorage tq, tk, tv;
@@ -625,7 +641,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH / q_div, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kPoly, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     FwdParams p;
@@ -659,7 +675,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     unsigned grid = (unsigned)std::min<long long>(p.n_items, n_sm);
     {
         LaunchScope ls(K_FWD_TC, st);
-        attn_fwd_sm100_kernel<D, kPoly><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_fwd_sm100_kernel<D, kPoly, kTrace><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
             *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
     }
@@ -668,13 +684,8 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
 
 template <int D>
 static cudaError_t launch_fwd_d(const AttnArgs& a, cudaStream_t st) {
-    switch (fwd_poly_setting()) {
-        case 1: return launch_fwd<D, 1>(a, st);
-        case 3: return launch_fwd<D, 3>(a, st);
-        case 4: return launch_fwd<D, 4>(a, st);
-        case 2: return launch_fwd<D, 2>(a, st);
-        default: return launch_fwd<D, 0>(a, st);
-    }
+    if (g_fwd_trace != nullptr) return launch_fwd<D, 0, true>(a, st);
+    return fwd_poly_setting() ? launch_fwd<D, 2, false>(a, st) : launch_fwd<D, 0, false>(a, st);
 }
 cudaError_t attn_fwd_sm100(const AttnArgs& a, cudaStream_t st) {
     return a.D == 128 ? launch_fwd_d<128>(a, st) : launch_fwd_d<64>(a, st);
