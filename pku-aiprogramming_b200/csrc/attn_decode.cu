@@ -20,6 +20,9 @@
 
 namespace ttk {
 
+#ifndef TT_DEC_TWO_BLOCKS_UP_TO
+#define TT_DEC_TWO_BLOCKS_UP_TO 4
+#endif
 constexpr int kDecThreads = 256;
 constexpr int kDecWarps = kDecThreads / 32;
 constexpr int kUnroll = 4;
@@ -87,7 +90,7 @@ struct DecodeRows {
 // query per CTA, key/value slice = query slice / group (the group's CTAs are neighbours in the
 // grid, so the re-reads mostly hit L2).
 template <int D, int G>
-__global__ void __launch_bounds__(kDecThreads, (G == 1 ? 4 : (G <= 4 ? 2 : 1)))
+__global__ void __launch_bounds__(kDecThreads, (G == 1 ? 4 : (G <= TT_DEC_TWO_BLOCKS_UP_TO ? 2 : 1)))
 attn_decode_bf16_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                         const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ lse, float* __restrict__ partial, int L, int splits, int chunk,
@@ -345,6 +348,11 @@ __global__ void attn_decode_tc_merge_kernel(const __nv_bfloat16* __restrict__ po
     const int g = (int)(bh - kvs * G);
     float m = -INFINITY;
     for (int c = 0; c < splits; ++c) m = fmaxf(m, plse[(kvs * splits + c) * G + g]);
+    if (m == -INFINITY) {   // no range held a key (an empty sequence of a paged cache)
+        out[bh * D + d] = __float2bfloat16_rn(0.f);
+        if (d == 0 && lse != nullptr) lse[bh] = -INFINITY;
+        return;
+    }
     float den = 0.f, acc = 0.f;
     for (int c = 0; c < splits; ++c) {
         const long long row = (kvs * splits + c) * G + g;
@@ -384,6 +392,70 @@ static cudaError_t launch_decode(const AttnArgs& a, const DecodePlan& pl, void* 
         attn_decode_merge_kernel<D><<<(unsigned)a.BH, D, 0, st>>>((const float*)ws, (__nv_bfloat16*)a.out, a.lse,
                                                                   pl.splits, G);
     }
+    return cudaGetLastError();
+}
+
+// Decode over a paged cache as a forward problem: the same [batch x key/value heads, G, D] view as
+// above, with the forward kernel's loader gathering each 128-key tile page by page through the
+// block table.  With few slices the key range is cut into `splits` ranges of `chunk` keys (work
+// items of their own, merged afterwards); a range past a sequence's end yields a zero partial with
+// log-sum-exp -inf, which the merge gives no weight.
+static AttnArgs paged_as_forward(const AttnArgs& a, const DecodeView& v, int splits, int chunk) {
+    AttnArgs g = decode_as_forward(a, 1);
+    g.BH = a.BH / a.group * splits;
+    g.q_div = splits;
+    g.kv_chunk = splits > 1 ? chunk : 0;
+    g.H = v.hkv;                    // key/value slices per batch entry
+    g.kv_lens = v.seq_lens;
+    g.block_table = v.block_table;
+    g.page_size = v.page_size;
+    g.max_pages = v.max_pages;
+    return g;
+}
+static void paged_split(const AttnArgs& a, int* splits, int* chunk) {
+    int dev = 0, n_sm = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    const long long slices = a.BH / a.group;
+    *splits = 1;
+    *chunk = a.L;
+    if (2 * slices >= n_sm) return;
+    // about two items per SM, ranges of whole 128-key tiles and at least 256 keys
+    const long long want = (2LL * n_sm + slices - 1) / slices;
+    long long c = ((a.L + want - 1) / want + 127) / 128 * 128;
+    if (c < 256) c = 256;
+    const long long n = (a.L + c - 1) / c;
+    if (n < 2) return;
+    *splits = (int)n;
+    *chunk = (int)c;
+}
+int attn_decode_paged_on_forward(const AttnArgs& a, const DecodeView& v, size_t* ws_bytes) {
+    *ws_bytes = 0;
+    if (!(a.bf16 && a.S == 1 && a.group >= 4 && v.block_table != nullptr)) return 0;
+    const char* f = getenv("TT_DECODE_GQA_PATH");
+    if (f && f[0] == 's') return 0;                           // "simt"
+    int splits, chunk;
+    paged_split(a, &splits, &chunk);
+    if (!attn_fwd_sm100_supported(paged_as_forward(a, v, splits, chunk))) return 0;
+    if (splits > 1) *ws_bytes = align256((size_t)a.BH * splits * a.D * 2) + align256((size_t)a.BH * splits * 4);
+    return splits;
+}
+cudaError_t attn_decode_paged_forward(const AttnArgs& a, const DecodeView& v, int splits, void* ws, cudaStream_t st) {
+    int s2, chunk;
+    paged_split(a, &s2, &chunk);
+    if (s2 != splits) return cudaErrorInvalidValue;
+    AttnArgs g = paged_as_forward(a, v, splits, chunk);
+    if (splits == 1) return attn_fwd_sm100(g, st);
+    __nv_bfloat16* po = (__nv_bfloat16*)ws;
+    float* plse = (float*)((unsigned char*)ws + align256((size_t)a.BH * splits * a.D * 2));
+    g.out = po;
+    g.lse = plse;
+    cudaError_t e = attn_fwd_sm100(g, st);
+    if (e != cudaSuccess) return e;
+    LaunchScope ls(K_DECODE_MERGE, st);
+    if (a.D == 128)
+        attn_decode_tc_merge_kernel<128><<<(unsigned)a.BH, 128, 0, st>>>(po, plse, (__nv_bfloat16*)a.out, a.lse, splits, a.group);
+    else
+        attn_decode_tc_merge_kernel<64><<<(unsigned)a.BH, 64, 0, st>>>(po, plse, (__nv_bfloat16*)a.out, a.lse, splits, a.group);
     return cudaGetLastError();
 }
 

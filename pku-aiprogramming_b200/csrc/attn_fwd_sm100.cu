@@ -75,6 +75,9 @@ struct FwdParams {
     const int* kv_lens;            // optional key padding lengths per batch entry (see AttnArgs)
     int H;
     int q_div;                     // query slice = output slice / q_div
+    const int* block_table;        // kPaged only: K and V are page pools (see AttnArgs)
+    int page_size, max_pages;
+    int kv_chunk;                  // kPaged: keys per output slice when a slice's keys are split (0: not split)
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
     int trace_item;     // which of the CTA's work items gets the per-iteration stamps (TT_TRACE_ITEM, default 0)
@@ -158,14 +161,23 @@ __device__ __forceinline__ uint64_t softmax_exp_half(const uint32_t (&sr)[4][32]
 struct FwdItem {
     int bh, q0, n_tiles[2], n_max;
     int Lv;   // keys that count for this slice (<= L; fewer with key padding)
+    int kvs, key0;   // kPaged: key/value slice and first key of this item
 };
+template <bool kPaged = false>
 __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p) {
     FwdItem w;
     w.bh = item / p.n_qblk;
     const int qb = p.n_qblk - 1 - (item % p.n_qblk);
     w.q0 = qb * 256;
     const int off = p.L - p.S;
-    w.Lv = valid_keys(p.kv_lens, w.bh / p.H, p.L);
+    if (kPaged) {   // a paged cache may hold empty sequences, and an item may cover one key range of its slice
+        w.kvs = w.bh / p.q_div;
+        w.key0 = (w.bh - w.kvs * p.q_div) * p.kv_chunk;
+        const int len = p.kv_lens ? min(p.L, max(0, p.kv_lens[w.kvs / p.H])) : p.L;
+        w.Lv = p.kv_chunk > 0 ? max(0, min(len - w.key0, p.kv_chunk)) : len;
+    } else {
+        w.Lv = valid_keys(p.kv_lens, w.bh / p.H, p.L);
+    }
     const int n_kv_total = (w.Lv + 127) >> 7;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -185,7 +197,9 @@ __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p)
 
 // kTrace: compiled with the cycle stamps (debug aid; costs registers in every role, so the
 // product launches the kTrace = false instantiation unless a trace buffer is set).
-template <int D, int kPoly, bool kTrace>
+// kPaged: K and V tiles are gathered page by page through the block table (decode over a paged
+// cache run as a [batch x key/value heads, group, D] forward problem).
+template <int D, int kPoly, bool kTrace, bool kPaged>
 __global__ void __launch_bounds__(FwdCfg<D>::kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -276,15 +290,21 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             __syncwarp();
             mbar_arrive(&bar_sched_empty[k & 1]);
             if (item < 0) break;
-            const FwdItem w = fwd_decode_item(item, p);
+            const FwdItem w = fwd_decode_item<kPaged>(item, p);
             const int nt = w.n_tiles[i];
             // per-item stamps of the traced CTA (role slot 0/1 = query tile, row = item number k)
             if (kTrace && p.trace != nullptr && (int)blockIdx.x == p.trace_block && wq == 0 && (threadIdx.x & 31) == 0 && k < 64) {
                 p.trace[(i * 64 + k) * 8 + 6] = clock64();
                 p.trace[(i * 64 + k) * 8 + 7] = nt;
             }
-            if (nt == 0) continue;
             const int row = w.q0 + 128 * i + wq * 32 + lane;
+            if (kPaged && w.Lv == 0 && row < p.S) {   // empty sequence: zero output, log-sum-exp -inf
+                uint4* orow = reinterpret_cast<uint4*>(p.out + ((long long)w.bh * p.S + row) * D);
+#pragma unroll
+                for (int e = 0; e < D / 8; ++e) orow[e] = make_uint4(0u, 0u, 0u, 0u);
+                if (p.lse != nullptr) p.lse[(long long)w.bh * p.S + row] = -INFINITY;
+            }
+            if (nt == 0) continue;
             float m2 = -INFINITY;   // running max in the scaled log2 domain
             float l = 0.f;          // running sum of exp2(s*c - m2)
             for (int j = 0; j < nt; ++j, ++s_cnt) {
@@ -421,7 +441,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
                 __syncwarp();
                 if (item < 0) break;
-                const FwdItem w = fwd_decode_item(item, p);
+                const FwdItem w = fwd_decode_item<kPaged>(item, p);
                 const int q_bh = w.bh / p.q_div, kv_bh = w.bh / p.group;   // slices of Q and of K/V this item reads
                 auto load_q = [&](int i) {
                     mbar_wait(&bar_q_empty[i], (q_uses[i] & 1) ^ 1, wctx, 5 + i, k);
@@ -433,7 +453,30 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     const int st = t % kStages;
                     mbar_wait(&bar_kv_empty[st], ((t / kStages) & 1) ^ 1, wctx, BAR_KVEMPTY + st, (int)t);
                     __syncwarp();
-                    load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], j * 128, kv_bh);
+                    if constexpr (kPaged) {
+                        // One TMA box per page (or one 128-row box out of a larger page); lanes issue
+                        // side by side.  Only pages that hold counted keys are fetched: the rows after
+                        // them are masked in S and zeroed in V by the MMA warp.
+                        unsigned char* dst = sKV + st * Cfg::kTileBytes;
+                        const int box_rows = min(p.page_size, 128);
+                        const int key0 = j * 128;
+                        const int n_box = min(128 / box_rows, (w.Lv - key0 + box_rows - 1) / box_rows);
+                        if (lane == 0) mbar_arrive_expect_tx(&bar_kv_full[st], (uint32_t)(n_box * box_rows * D * 2));
+                        __syncwarp();
+                        if (lane < n_box) {
+                            const int key = w.key0 + key0 + lane * box_rows;
+                            const int lp = key / p.page_size;
+                            const int page = __ldg(p.block_table + (long long)(w.kvs / p.H) * p.max_pages + lp);
+                            const int z = page * p.H + (w.kvs % p.H);
+#pragma unroll
+                            for (int sb = 0; sb < Cfg::kSub; ++sb)
+                                tma_load_3d(dst + sb * Cfg::kSubBytes + lane * box_rows * 128, tm, &bar_kv_full[st], sb * 64,
+                                            key - lp * p.page_size, z);
+                        }
+                        __syncwarp();
+                    } else {
+                        load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], j * 128, kv_bh);
+                    }
                     ++t;
                 };
                 if (w.n_tiles[0] > 0) load_q(0);
@@ -497,7 +540,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 if (elect_one()) mbar_arrive(&bar_sched_empty[k & 1]);
                 __syncwarp();
                 if (item < 0) break;
-                const FwdItem w = fwd_decode_item(item, p);
+                const FwdItem w = fwd_decode_item<kPaged>(item, p);
                 // S_i(0) for both tiles.  The S/P columns are free: the P V MMAs of the previous item
                 // were issued earlier by this warp and execute in order.
                 if (w.n_max > 0) {
@@ -523,6 +566,20 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 for (int j = 0; j < w.n_max; ++j) {
                     const uint32_t item_v = t + 2 * j + 1, item_k = t + 2 * j + 2;
                     wait_item(item_v);
+                    if constexpr (kPaged) {
+                        // Rows of the last V tile past the sequence's end hold whatever the pool (or the
+                        // ring slot) held; their P is exactly 0, but 0 x NaN is not, so they are zeroed.
+                        const int rv = w.Lv - j * 128;
+                        if (rv < 128) {
+                            unsigned char* vt = sKV + (item_v % kStages) * Cfg::kTileBytes;
+#pragma unroll
+                            for (int sb = 0; sb < Cfg::kSub; ++sb)
+                                for (int o = rv * 128 + lane * 16; o < 128 * 128; o += 32 * 16)
+                                    *reinterpret_cast<uint4*>(vt + sb * Cfg::kSubBytes + o) = make_uint4(0u, 0u, 0u, 0u);
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                        }
+                    }
                     bool k_waited = false;
                     for (int i = 0; i < 2; ++i) {
                         if (j < w.n_tiles[i]) {
@@ -565,7 +622,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                         ahead_item = next_item(k + 1);
                         __syncwarp();
                         if (ahead_item >= 0) {
-                            const FwdItem wn = fwd_decode_item(ahead_item, p);
+                            const FwdItem wn = fwd_decode_item<kPaged>(ahead_item, p);
                             if (wn.n_tiles[0] > 0) {
                                 const uint32_t tn = t + 2 * (uint32_t)w.n_max;
                                 wait_item(tn);
@@ -598,6 +655,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
 // ------------------------------------------------------------------------------ host side
 bool attn_fwd_sm100_supported(const AttnArgs& a) {
+    if (a.block_table != nullptr) {   // paged K/V: whole pages per TMA box, one query tile, no mask
+        const int ps = a.page_size;
+        if (!(ps >= 8 && (128 % ps == 0 || ps % 128 == 0) && a.max_pages >= 1 && a.causal == 0 && a.group == 1 && a.S <= 128))
+            return false;
+        if (a.q_div > 1 ? !(a.kv_chunk >= 128 && a.kv_chunk % 128 == 0) : a.kv_chunk != 0) return false;
+    }
     return a.bf16 && (a.D == 64 || a.D == 128) && a.S >= 1 && a.L >= 1 && a.BH * (long long)((a.S + 255) / 256) < (1LL << 31);
 }
 
@@ -632,16 +695,25 @@ static int fwd_poly_setting() {
     return v;
 }
 
-template <int D, int kPoly, bool kTrace>
+template <int D, int kPoly, bool kTrace, bool kPaged = false>
 static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     using Cfg = FwdCfg<D>;
     TmapStorage tq, tk, tv;
     const char* why = nullptr;
     const int q_div = a.q_div > 0 ? a.q_div : 1;
     if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH / q_div, 128, &why)) return cudaErrorInvalidValue;
-    if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
-    if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kPoly, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (kPaged) {
+        // The pools' page count is not known here; the extent only bounds what TMA may touch, and
+        // the block table names the pages that exist.
+        const uint64_t slices = 0x7fffffffull;
+        const uint32_t box_rows = (uint32_t)std::min(a.page_size, 128);
+        if (!make_tmap_bf16(&tk, a.k, D, (uint64_t)a.page_size, slices, box_rows, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16(&tv, a.v, D, (uint64_t)a.page_size, slices, box_rows, &why)) return cudaErrorInvalidValue;
+    } else {
+        if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+    }
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kPoly, kTrace, kPaged>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     FwdParams p;
@@ -655,6 +727,10 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.kv_lens = a.kv_lens;
     p.H = a.H;
     p.q_div = q_div;
+    p.block_table = a.block_table;
+    p.page_size = a.page_size;
+    p.max_pages = a.max_pages;
+    p.kv_chunk = a.kv_chunk;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = device_status_word();
     p.trace = g_fwd_trace;
@@ -663,7 +739,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
         const char* ti = getenv("TT_TRACE_ITEM");
         p.trace_item = (ti && *ti) ? atoi(ti) : 0;
         const char* sa = getenv("TT_FWD_S0_AHEAD");
-        p.s0_ahead = (sa && sa[0] == '0') ? 0 : 1;
+        p.s0_ahead = ((sa && sa[0] == '0') || kPaged) ? 0 : 1;
         const char* ws = getenv("TT_ST256");
         p.wide_stores = ((reinterpret_cast<uintptr_t>(a.out) & 31) == 0 && !(ws && ws[0] == '0')) ? 1 : 0;
     }
@@ -675,7 +751,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     unsigned grid = (unsigned)std::min<long long>(p.n_items, n_sm);
     {
         LaunchScope ls(K_FWD_TC, st);
-        attn_fwd_sm100_kernel<D, kPoly, kTrace><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_fwd_sm100_kernel<D, kPoly, kTrace, kPaged><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
             *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
     }
@@ -684,6 +760,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
 
 template <int D>
 static cudaError_t launch_fwd_d(const AttnArgs& a, cudaStream_t st) {
+    if (a.block_table != nullptr) return launch_fwd<D, 0, false, true>(a, st);
     if (g_fwd_trace != nullptr) return launch_fwd<D, 0, true>(a, st);
     return fwd_poly_setting() ? launch_fwd<D, 2, false>(a, st) : launch_fwd<D, 0, false>(a, st);
 }

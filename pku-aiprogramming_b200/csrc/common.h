@@ -26,6 +26,15 @@ struct AttnArgs {
     // forward kernel only: query slice = output slice / q_div (0 or 1: the same slice).  Lets several
     // key ranges of one slice run as work items of their own, each with its own output rows.
     int q_div;
+    // forward kernel only, used by decode over a paged cache: k and v are page pools
+    // [pages, H, page_size, D] (H = key/value heads here) and key r of batch entry b is row
+    // r % page_size of page block_table[b * max_pages + r / page_size].  kv_lens may then hold 0
+    // (an empty sequence: zero output, log-sum-exp -inf).  page_size divides 128 or is a multiple of it.
+    // With kv_chunk > 0 output slice s covers keys [c * kv_chunk, (c + 1) * kv_chunk) of key/value slice
+    // s / q_div, c = s % q_div (kv_chunk a multiple of 128); L stays the whole key range.
+    const int* block_table;
+    int page_size, max_pages;
+    int kv_chunk;
 };
 // keys that count for batch entry b (device side)
 __device__ __forceinline__ int valid_keys(const int* kv_lens, long long b, int L) {
@@ -113,6 +122,13 @@ struct DecodeView {
 };
 cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& plan, void* workspace, cudaStream_t st,
                         const DecodeView* view = nullptr);
+
+// Paged decode with grouped heads (group >= 4) on the tcgen05 forward kernel; the SIMT split-KV
+// kernel serves every other paged call.
+// Returns the number of key ranges per slice (0: route not taken, 1: no merge, no workspace).
+int attn_decode_paged_on_forward(const AttnArgs& a, const DecodeView& view, size_t* ws_bytes);
+cudaError_t attn_decode_paged_forward(const AttnArgs& a, const DecodeView& view, int splits, void* workspace,
+                                      cudaStream_t st);
 
 // Same kernels, partials in the library's own fixed device array (no allocation anywhere).
 // *too_big is set when the plan needs more than the array holds (nothing is launched then).

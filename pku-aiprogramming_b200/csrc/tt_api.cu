@@ -4,6 +4,7 @@
 #include "common.h"
 
 #include <cuda.h>
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdarg>
@@ -419,7 +420,17 @@ size_t tt_attn_decode_workspace_bytes(const tt_attn_desc* desc) {
     if (a.S != 1) return 0;
     // enough for every route a call with this descriptor can take (dense, paged or ragged)
     const size_t w1 = attn_decode_plan(a, true).ws_bytes, w2 = attn_decode_plan(a, false).ws_bytes;
-    return w1 > w2 ? w1 : w2;
+    size_t w3 = 0;
+    {   // the paged route on the forward kernel (its split depends on the shape only; page size 128 stands in)
+        static const int one_page = 0;
+        DecodeView v;
+        v.block_table = &one_page;
+        v.page_size = 128;
+        v.max_pages = (a.L + 127) / 128;
+        v.hkv = desc->Hkv > 0 ? desc->Hkv : desc->H;
+        attn_decode_paged_on_forward(a, v, &w3);
+    }
+    return std::max(w1, std::max(w2, w3));
 }
 
 int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const void* v, void* out, float* lse,
@@ -573,6 +584,26 @@ int tt_attn_decode_paged(const tt_attn_desc* desc, const void* q, const void* k_
         return fail(TT_ERR_BAD_SHAPE, "tt_attn_decode_paged: q, k, v must be 16-byte aligned");
     if ((rc = check_device()) != TT_OK) return rc;
     a.causal = 0;
+    DecodeView view;
+    view.block_table = block_table;
+    view.seq_lens = seq_lens;
+    view.page_size = page_size;
+    view.max_pages = max_pages;
+    view.hkv = desc->Hkv > 0 ? desc->Hkv : desc->H;
+    a.q = q; a.k = k_pool; a.v = v_pool; a.out = out; a.lse = lse;
+    size_t paged_ws = 0;
+    if (const int splits = attn_decode_paged_on_forward(a, view, &paged_ws)) {   // grouped heads over a paged cache
+        if (paged_ws > 0) {
+            if (!workspace || workspace_bytes < paged_ws)
+                return fail(TT_ERR_WORKSPACE, "tt_attn_decode_paged: workspace of %zu bytes required, %zu given", paged_ws,
+                            workspace_bytes);
+            if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+                return fail(TT_ERR_WORKSPACE, "tt_attn_decode_paged: workspace must be 256-byte aligned");
+        }
+        cudaError_t e = attn_decode_paged_forward(a, view, splits, workspace, (cudaStream_t)stream);
+        if (e != cudaSuccess) return cuda_fail(e, "tt_attn_decode_paged: launch");
+        return TT_OK;
+    }
     DecodePlan pl = attn_decode_plan(a, /*allow_tc=*/!(block_table || seq_lens));
     if (pl.ws_bytes > 0) {
         if (!workspace || workspace_bytes < pl.ws_bytes)
@@ -581,13 +612,6 @@ int tt_attn_decode_paged(const tt_attn_desc* desc, const void* q, const void* k_
         if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
             return fail(TT_ERR_WORKSPACE, "tt_attn_decode_paged: workspace must be 256-byte aligned");
     }
-    a.q = q; a.k = k_pool; a.v = v_pool; a.out = out; a.lse = lse;
-    DecodeView view;
-    view.block_table = block_table;
-    view.seq_lens = seq_lens;
-    view.page_size = page_size;
-    view.max_pages = max_pages;
-    view.hkv = desc->Hkv > 0 ? desc->Hkv : desc->H;
     cudaError_t e = attn_decode(a, pl, workspace, (cudaStream_t)stream, &view);
     if (e != cudaSuccess) return cuda_fail(e, "tt_attn_decode_paged: launch");
     return TT_OK;
