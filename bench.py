@@ -334,11 +334,55 @@ def run_decode(tt, dev, peaks, batch):
         ms = a.elapsed_time(b) / 20
         by = 2.0 * dB * dH * dL * dD * 2 + 2.0 * dB * dH * dD * 2
         kms = dprof["attn_decode"][0] / dprof["attn_decode"][1]
+        del dk_, dv_
         return {"workload": f"bf16 decode Q [{dB},32,1,128], K/V [{dB},32,8192,128]", "ms": ms, "gbs": by / ms / 1e6,
+                "grouped": run_decode_grouped(tt, dev, peaks, dB),
                 "roofline": {"bound": "hbm", "achieved": by / kms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
                              "frac": by / kms / 1e6 / peaks["hbm"],
                              "traffic": NCU_TRAFFIC_BYTES.get("attn_decode") if dB == 64 else None,
                              "kernel": "attn_decode", "peak_source": f"hbm_gbs of {peaks['source']} MEASURED_PEAKS.json"}}
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e)}
+
+
+def run_decode_grouped(tt, dev, peaks, dB, hkv=8, page=64):
+    """The serving form of the decode configuration: 32 query heads over 8 key/value heads (groups
+    of 4), cache dense and as a shuffled pool of 64-row pages.  Both run as a [B*Hkv, 4, D]
+    problem on the tcgen05 forward kernel (the paged one gathers its tiles page by page); GB/s
+    counts the K and V bytes, which cross HBM once per group."""
+    import torch
+    try:
+        dH, dL, dD = 32, 8192, 128
+        q = torch.randn((dB, dH, 1, dD), device=dev).to(torch.bfloat16)
+        k = torch.randn((dB, hkv, dL, dD), device=dev).to(torch.bfloat16)
+        v = torch.randn((dB, hkv, dL, dD), device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        ws = torch.empty(max(tt.decode_workspace_bytes(dB, dH, dL, dD, Hkv=hkv), 256), dtype=torch.uint8, device=dev)
+        mp = dL // page
+        perm = torch.randperm(dB * mp, device=dev).to(torch.int32).reshape(dB, mp)
+        to_pages = lambda t: t.reshape(dB, hkv, mp, page, dD).permute(0, 2, 1, 3, 4).reshape(dB * mp, hkv, page, dD)
+        kpool, vpool = torch.empty_like(to_pages(k)), torch.empty_like(to_pages(v))
+        kpool[perm.flatten().long()] = to_pages(k)
+        vpool[perm.flatten().long()] = to_pages(v)
+        lens = torch.full((dB,), dL, dtype=torch.int32, device=dev)
+        calls = {"dense": lambda: tt.attention_decode(q, k, v, out=out, workspace=ws, need_lse=False),
+                 "paged": lambda: tt.attention_decode_paged(q, kpool, vpool, block_table=perm, seq_lens=lens, out=out,
+                                                            workspace=ws, need_lse=False)}
+        by = 2.0 * dB * hkv * dL * dD * 2
+        res = {"workload": f"Q [{dB},32,1,128], K/V [{dB},{hkv},8192,128], pages of {page} rows"}
+        for name, fn in calls.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(20):
+                fn()
+            b.record(); torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / 20
+            res[name] = {"ms": ms, "bound": "hbm", "achieved": by / ms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": by / ms / 1e6 / peaks["hbm"]}
+        return res
     except Exception as e:  # noqa: BLE001
         return {"error": str(e)}
 
@@ -417,7 +461,7 @@ def main():
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
-    ap.add_argument("--only", choices=["softmax", "fc"], help="run just this side leg and print its block "
+    ap.add_argument("--only", choices=["softmax", "fc", "decode"], help="run just this side leg and print its block "
                     "(used for profiler captures of that kernel; not the benchmark line)")
     ap.add_argument("--fc-rows", type=int, default=16384, help="rows of x in the fully connected leg")
     ap.add_argument("--softmax-rows", type=int, default=262144, help="rows of the row-softmax leg")
@@ -451,7 +495,9 @@ def main():
 
     if args.only:
         if rank == 0:
-            res = run_fc(tt, dev, peaks, args.fc_rows) if args.only == "fc" else run_softmax(tt, dev, peaks, args.softmax_rows)
+            res = (run_fc(tt, dev, peaks, args.fc_rows) if args.only == "fc" else
+                   run_decode(tt, dev, peaks, args.decode_batch) if args.only == "decode" else
+                   run_softmax(tt, dev, peaks, args.softmax_rows))
             print(json.dumps({"leg": args.only, "result": res}), flush=True)
         return
 

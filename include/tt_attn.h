@@ -140,10 +140,10 @@ int tt_attn_bwd_padded(const tt_attn_desc* desc, const void* q, const void* k, c
  *   seq_lens != NULL: device array of B int32, batch entry b attends to its first seq_lens[b]
  *       keys (clamped to 0..L); an entry with no keys gets out = 0 and lse = -inf.
  * Grouped heads (desc->Hkv < H) read each key/value row once for the whole group when the group
- * size is 2, 4 or 8.  Groups of 4 and more over a paged cache whose page_size divides 128 or is a
- * multiple of it (>= 8) run on the tensor-core forward kernel, which gathers the pages by TMA; so
- * does tt_attn_decode on a dense, full-length cache.  Rows of the pools that no sequence owns are
- * never used in arithmetic and may hold anything.  Workspace: tt_attn_decode_workspace_bytes(desc). */
+ * size is 2, 4 or 8.  Groups of 4 and more run on the tensor-core forward kernel, as in
+ * tt_attn_decode; over a paged cache that needs a page_size that divides 128 or is a multiple of
+ * it (>= 8), and the kernel gathers the pages by TMA.  Rows that no sequence owns never reach the
+ * result and may hold anything.  Workspace: tt_attn_decode_workspace_bytes(desc). */
 int tt_attn_decode_paged(const tt_attn_desc* desc, const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* block_table, const int32_t* seq_lens, int32_t page_size, int32_t max_pages,
                          void* out, float* lse, void* workspace, size_t workspace_bytes, void* stream);

@@ -395,9 +395,9 @@ static cudaError_t launch_decode(const AttnArgs& a, const DecodePlan& pl, void* 
     return cudaGetLastError();
 }
 
-// Decode over a paged cache as a forward problem: the same [batch x key/value heads, G, D] view as
-// above, with the forward kernel's loader gathering each 128-key tile page by page through the
-// block table.  With few slices the key range is cut into `splits` ranges of `chunk` keys (work
+// Decode over a ragged and/or paged cache as a forward problem: the same [batch x key/value heads, G, D] view as
+// above, with sequence lengths per batch entry and, for a paged cache, the forward kernel's loader
+// gathering each 128-key tile page by page through the block table.  With few slices the key range is cut into `splits` ranges of `chunk` keys (work
 // items of their own, merged afterwards); a range past a sequence's end yields a zero partial with
 // log-sum-exp -inf, which the merge gives no weight.
 static AttnArgs paged_as_forward(const AttnArgs& a, const DecodeView& v, int splits, int chunk) {
@@ -405,6 +405,7 @@ static AttnArgs paged_as_forward(const AttnArgs& a, const DecodeView& v, int spl
     g.BH = a.BH / a.group * splits;
     g.q_div = splits;
     g.kv_chunk = splits > 1 ? chunk : 0;
+    g.cache_mode = 1;
     g.H = v.hkv;                    // key/value slices per batch entry
     g.kv_lens = v.seq_lens;
     g.block_table = v.block_table;
@@ -430,7 +431,7 @@ static void paged_split(const AttnArgs& a, int* splits, int* chunk) {
 }
 int attn_decode_paged_on_forward(const AttnArgs& a, const DecodeView& v, size_t* ws_bytes) {
     *ws_bytes = 0;
-    if (!(a.bf16 && a.S == 1 && a.group >= 4 && v.block_table != nullptr)) return 0;
+    if (!(a.bf16 && a.S == 1 && a.group >= 4 && (v.block_table != nullptr || v.seq_lens != nullptr))) return 0;
     const char* f = getenv("TT_DECODE_GQA_PATH");
     if (f && f[0] == 's') return 0;                           // "simt"
     int splits, chunk;

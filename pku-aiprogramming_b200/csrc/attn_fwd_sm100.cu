@@ -197,8 +197,10 @@ __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p)
 
 // kTrace: compiled with the cycle stamps (debug aid; costs registers in every role, so the
 // product launches the kTrace = false instantiation unless a trace buffer is set).
-// kPaged: K and V tiles are gathered page by page through the block table (decode over a paged
-// cache run as a [batch x key/value heads, group, D] forward problem).
+// kPaged: decode over a ragged and/or paged cache run as a [batch x key/value heads, group, D]
+// forward problem: sequences may be empty, an item may cover one key range of its slice, rows
+// behind a sequence's end are zeroed in V, and with a block table the K and V tiles are gathered
+// page by page.
 template <int D, int kPoly, bool kTrace, bool kPaged>
 __global__ void __launch_bounds__(FwdCfg<D>::kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -453,7 +455,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     const int st = t % kStages;
                     mbar_wait(&bar_kv_empty[st], ((t / kStages) & 1) ^ 1, wctx, BAR_KVEMPTY + st, (int)t);
                     __syncwarp();
-                    if constexpr (kPaged) {
+                    if (kPaged && p.block_table != nullptr) {
                         // One TMA box per page (or one 128-row box out of a larger page); lanes issue
                         // side by side.  Only pages that hold counted keys are fetched: the rows after
                         // them are masked in S and zeroed in V by the MMA warp.
@@ -474,6 +476,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                                             key - lp * p.page_size, z);
                         }
                         __syncwarp();
+                    } else if (kPaged) {   // dense ragged cache: this item's key range of its slice
+                        load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], w.key0 + j * 128, w.kvs);
                     } else {
                         load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], j * 128, kv_bh);
                     }
@@ -655,11 +659,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
 // ------------------------------------------------------------------------------ host side
 bool attn_fwd_sm100_supported(const AttnArgs& a) {
-    if (a.block_table != nullptr) {   // paged K/V: whole pages per TMA box, one query tile, no mask
-        const int ps = a.page_size;
-        if (!(ps >= 8 && (128 % ps == 0 || ps % 128 == 0) && a.max_pages >= 1 && a.causal == 0 && a.group == 1 && a.S <= 128))
-            return false;
+    if (a.block_table != nullptr && !a.cache_mode) return false;
+    if (a.cache_mode) {   // decode over a cache: one query tile, no causal mask, key ranges of whole tiles
+        if (!(a.causal == 0 && a.group == 1 && a.S <= 128)) return false;
         if (a.q_div > 1 ? !(a.kv_chunk >= 128 && a.kv_chunk % 128 == 0) : a.kv_chunk != 0) return false;
+        const int ps = a.page_size;   // paged: whole pages per TMA box
+        if (a.block_table != nullptr && !(ps >= 8 && (128 % ps == 0 || ps % 128 == 0) && a.max_pages >= 1)) return false;
     }
     return a.bf16 && (a.D == 64 || a.D == 128) && a.S >= 1 && a.L >= 1 && a.BH * (long long)((a.S + 255) / 256) < (1LL << 31);
 }
@@ -702,7 +707,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     const char* why = nullptr;
     const int q_div = a.q_div > 0 ? a.q_div : 1;
     if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH / q_div, 128, &why)) return cudaErrorInvalidValue;
-    if (kPaged) {
+    if (kPaged && a.block_table != nullptr) {
         // The pools' page count is not known here; the extent only bounds what TMA may touch, and
         // the block table names the pages that exist.
         const uint64_t slices = 0x7fffffffull;
@@ -710,8 +715,9 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
         if (!make_tmap_bf16(&tk, a.k, D, (uint64_t)a.page_size, slices, box_rows, &why)) return cudaErrorInvalidValue;
         if (!make_tmap_bf16(&tv, a.v, D, (uint64_t)a.page_size, slices, box_rows, &why)) return cudaErrorInvalidValue;
     } else {
-        if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
-        if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+        const long long kv_slices = kPaged ? a.BH / q_div : a.BH / a.group;
+        if (!make_tmap_bf16(&tk, a.k, D, a.L, kv_slices, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16(&tv, a.v, D, a.L, kv_slices, 128, &why)) return cudaErrorInvalidValue;
     }
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kPoly, kTrace, kPaged>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
@@ -760,7 +766,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
 
 template <int D>
 static cudaError_t launch_fwd_d(const AttnArgs& a, cudaStream_t st) {
-    if (a.block_table != nullptr) return launch_fwd<D, 0, false, true>(a, st);
+    if (a.cache_mode) return launch_fwd<D, 0, false, true>(a, st);
     if (g_fwd_trace != nullptr) return launch_fwd<D, 0, true>(a, st);
     return fwd_poly_setting() ? launch_fwd<D, 2, false>(a, st) : launch_fwd<D, 0, false>(a, st);
 }

@@ -26,15 +26,18 @@ struct AttnArgs {
     // forward kernel only: query slice = output slice / q_div (0 or 1: the same slice).  Lets several
     // key ranges of one slice run as work items of their own, each with its own output rows.
     int q_div;
-    // forward kernel only, used by decode over a paged cache: k and v are page pools
-    // [pages, H, page_size, D] (H = key/value heads here) and key r of batch entry b is row
-    // r % page_size of page block_table[b * max_pages + r / page_size].  kv_lens may then hold 0
-    // (an empty sequence: zero output, log-sum-exp -inf).  page_size divides 128 or is a multiple of it.
+    // forward kernel only, used by decode over a ragged and/or paged cache (cache_mode = 1): kv_lens
+    // may hold 0 (an empty sequence: zero output, log-sum-exp -inf), and what lies behind a
+    // sequence's end never reaches the result, whatever bits it holds.  block_table != null: k and v
+    // are page pools [pages, H, page_size, D] (H = key/value heads here) and key r of batch entry b
+    // is row r % page_size of page block_table[b * max_pages + r / page_size]; page_size divides
+    // 128 or is a multiple of it.
     // With kv_chunk > 0 output slice s covers keys [c * kv_chunk, (c + 1) * kv_chunk) of key/value slice
     // s / q_div, c = s % q_div (kv_chunk a multiple of 128); L stays the whole key range.
     const int* block_table;
     int page_size, max_pages;
     int kv_chunk;
+    int cache_mode;
 };
 // keys that count for batch entry b (device side)
 __device__ __forceinline__ int valid_keys(const int* kv_lens, long long b, int L) {

@@ -215,6 +215,17 @@ def test_decode_paged_grouped_heads_on_the_forward_kernel(tt, oracle, torch_cuda
     keep = lens > 0
     assert oracle.max_abs_err(got[keep], o_r[keep]) <= 2e-2
     assert oracle.max_abs_err(got_lse[keep], lse_r[keep]) <= 1e-3
+    # the same sequences in a dense [B,Hkv,cap,D] cache with NaN behind each sequence's end
+    kd, vd = k.copy(), v.copy()
+    for b in range(B):
+        kd[b, :, lens[b]:] = np.nan
+        vd[b, :, lens[b]:] = np.nan
+    out2, lse2 = tt.attention_decode_paged(tq, torch.from_numpy(kd).cuda().bfloat16(), torch.from_numpy(vd).cuda().bfloat16(), seq_lens=tl)
+    tt.check_device_status()
+    got2, got_lse2 = out2.float().cpu().numpy(), lse2.cpu().numpy()
+    assert np.isfinite(got2).all() and np.isneginf(got_lse2[1]).all() and float(np.abs(got2[1]).max()) == 0.0
+    assert oracle.max_abs_err(got2[keep], o_r[keep]) <= 2e-2
+    assert oracle.max_abs_err(got_lse2[keep], lse_r[keep]) <= 1e-3
 
 
 def test_variant_argument_errors(tt, torch_cuda):
