@@ -20,9 +20,6 @@
 
 namespace ttk {
 
-#ifndef TT_DEC_TWO_BLOCKS_UP_TO
-#define TT_DEC_TWO_BLOCKS_UP_TO 4
-#endif
 constexpr int kDecThreads = 256;
 constexpr int kDecWarps = kDecThreads / 32;
 constexpr int kUnroll = 4;
@@ -90,7 +87,7 @@ struct DecodeRows {
 // query per CTA, key/value slice = query slice / group (the group's CTAs are neighbours in the
 // grid, so the re-reads mostly hit L2).
 template <int D, int G>
-__global__ void __launch_bounds__(kDecThreads, (G == 1 ? 4 : (G <= TT_DEC_TWO_BLOCKS_UP_TO ? 2 : 1)))
+__global__ void __launch_bounds__(kDecThreads, (G == 1 ? 4 : (G <= 4 ? 2 : 1)))
 attn_decode_bf16_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                         const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ lse, float* __restrict__ partial, int L, int splits, int chunk,
