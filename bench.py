@@ -452,6 +452,35 @@ def run_fc(tt, dev, peaks, M=16384):
         return {"error": str(e)}
 
 
+def run_fp32(tt, dev, peaks):
+    """The reference's own dtype: fp32 causal forward+backward on the SIMT kernels (true fp32 FMAs;
+    the 1e-5 tolerance rules out the tensor-core formats), Q/K/V [2,8,2048,64].  Reported beside
+    the bf16 step so that the cost of staying in fp32 is visible; not part of the step metric."""
+    import torch
+    try:
+        B, H, S, D = 2, 8, 2048, 64
+        q, k, v, do = (torch.randn((B, H, S, D), device=dev) * 0.5 for _ in range(4))
+        o, lse = tt.attention_forward(q, k, v, causal=True)
+        fl_f = 4.0 * B * H * S * S * D / 2
+        res = {"workload": f"fp32 causal fwd+bwd, Q/K/V [{B},{H},{S},{D}]"}
+        legs = {"fwd": (lambda: tt.attention_forward(q, k, v, causal=True), fl_f),
+                "bwd": (lambda: tt.attention_backward(q, k, v, o, lse, do, causal=True), 2.5 * fl_f)}
+        for name, (fn, fl) in legs.items():
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(5):
+                fn()
+            b.record(); torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / 5
+            res[name] = {"ms": ms, "tflops": fl / ms / 1e9}
+        return res
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -467,6 +496,7 @@ def main():
     ap.add_argument("--softmax-rows", type=int, default=262144, help="rows of the row-softmax leg")
     ap.add_argument("--no-fc", action="store_true", help="skip the fully connected layer leg at N=1")
     ap.add_argument("--no-softmax", action="store_true", help="skip the row-softmax leg at N=1")
+    ap.add_argument("--no-fp32", action="store_true", help="skip the fp32 (SIMT kernels) side measurement at N=1")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the S=4096 side measurement at N=1")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--decode-batch", type=int, default=64, help="batch of the decode leg (64 = benchmark configuration 4)")
@@ -516,6 +546,7 @@ def main():
 
     fc = run_fc(tt, dev, peaks, args.fc_rows) if (rank == 0 and world == 1 and not args.no_fc) else None
     softmax = run_softmax(tt, dev, peaks, args.softmax_rows) if (rank == 0 and world == 1 and not args.no_softmax) else None
+    fp32 = run_fp32(tt, dev, peaks) if (rank == 0 and world == 1 and not args.no_fp32) else None
 
     # CPU baseline: the oracle on a bounded sample of the same workload (rank 0, N = 1)
     cpu = None
@@ -543,7 +574,7 @@ def main():
                        "parallelism": f"{world} x contiguous (batch,head) shards"},
             "fwd_tflops": main_res["fwd_tflops"], "pct_of_bf16_peak": main_res["pct_of_bf16_peak"],
             "roofline": main_res["roofline"], "kernels": main_res["kernels"], "cfg3": side, "decode": decode,
-            "softmax_rows": softmax, "fc": fc,
+            "softmax_rows": softmax, "fc": fc, "fp32": fp32,
             "cpu_baseline": cpu, "e2e": main_res["e2e"], "clocks": main_res["clocks"],
             "gpu_launches": main_res["gpu_launches"],
         }
