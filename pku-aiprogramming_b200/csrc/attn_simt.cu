@@ -5,11 +5,15 @@
 // 64/128).  Inputs of either dtype are widened to fp32 in shared memory; all dot
 // products, the softmax and the accumulators are fp32.
 //
-// Structure (forward and both backward kernels share it): a block owns 32 "rows", a warp
-// owns 4 of them, and the block walks over "columns" in tiles of 32.  Lane j of a warp
-// computes the score of its 4 rows against column j; row statistics are warp-shuffle
-// reductions; the D-wide accumulators live in registers, D/32 values per lane.
+// Two forms of each kernel (forward, dQ pass, dK/dV pass):
+//   register-tiled (head dims that are multiples of 4 up to 128, vector-aligned tensors): a block owns
+//     64 "rows" and walks the "columns" in tiles of 64; each of its 16 x 16 threads holds a 4 x 4 patch
+//     of scores, so a 128-bit shared-memory load feeds 16 FMAs; see the sections further down;
+//   row-per-lane (any D <= 256): a block owns 32 rows, a warp 4 of them, columns in tiles of 32; lane j
+//     of a warp computes the score of its 4 rows against column j; row statistics are warp-shuffle
+//     reductions; the D-wide accumulators live in registers, D/32 values per lane.
 #include "common.h"
+#include <cstdlib>
 
 namespace ttk {
 
@@ -338,6 +342,420 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(
     }
 }
 
+// ------------------------------------------------------------------- forward, register-tiled
+// The forward for head dims that are multiples of 4 up to 128.  A block owns 64 query rows and walks
+// the keys in tiles of 64; thread (ty, tx) of the 16 x 16 block holds the 4 x 4 scores of rows
+// ty + 16 i against keys tx + 16 j, so every 128-bit shared-memory load feeds 16 FMAs (the
+// row-per-lane kernel above fetches one operand per FMA).  The 16 lanes that share a row reduce its
+// statistics with shuffles, P goes through shared memory, and the same thread accumulates
+// O[rows ty + 16 i][4 tx + 64 jj .. + 3], so the rescale factors never leave registers.
+constexpr int kTiledM = 64, kTiledN = 64, kTiledThreads = 256, kTiledPPitch = kTiledN + 4;
+
+template <typename T>
+__device__ __forceinline__ float4 load4_f32(const T* p);
+template <>
+__device__ __forceinline__ float4 load4_f32<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 load4_f32<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                       __uint_as_float(u.y & 0xffff0000u));
+}
+template <typename T>
+__device__ __forceinline__ void store4_f32(T* p, float4 x);
+template <>
+__device__ __forceinline__ void store4_f32<float>(float* p, float4 x) { *reinterpret_cast<float4*>(p) = x; }
+template <>
+__device__ __forceinline__ void store4_f32<__nv_bfloat16>(__nv_bfloat16* p, float4 x) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(x.x, x.y), b = __floats2bfloat162_rn(x.z, x.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+// 64 rows of a [n_rows, D] matrix from row0 on into shared memory (pitch DP floats), zero past n_rows
+template <typename T>
+__device__ __forceinline__ void stage_tile64(float* dst, const T* src, long long row0, long long n_rows, int D, int DP) {
+    const int d4 = D >> 2;
+    for (int idx = threadIdx.x; idx < 64 * d4; idx += kTiledThreads) {
+        const int r = idx / d4, c = (idx - r * d4) << 2;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row0 + r < n_rows) x = load4_f32<T>(src + (row0 + r) * D + c);
+        *reinterpret_cast<float4*>(dst + r * DP + c) = x;
+    }
+}
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(kTiledThreads) attn_fwd_simt_tiled_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ out,
+    float* __restrict__ lse, int S, int L, int D, int causal, float scale, int group, const int* __restrict__ kv_lens,
+    int H) {
+    constexpr int DP = DMAX + 4;        // pitch: rows 16 bytes apart modulo 128, 128-bit loads conflict-free
+    constexpr int NJ = DMAX / 64;       // float4 column groups of O per thread
+    extern __shared__ __align__(16) float smem[];
+    float* sQ = smem;
+    float* sK = sQ + kTiledM * DP;
+    float* sV = sK + kTiledN * DP;
+    float* sP = sV + kTiledN * DP;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int nblk = (S + kTiledM - 1) / kTiledM;
+    const long long bh = blockIdx.x / nblk;
+    const int row0 = (int)(blockIdx.x % nblk) * kTiledM;
+    const int off = L - S;
+    q += bh * (long long)S * D;
+    k += (bh / group) * (long long)L * D;
+    v += (bh / group) * (long long)L * D;
+    out += bh * (long long)S * D;
+
+    // columns of sV at and past D are read by the O accumulation (and discarded): keep them finite
+    for (int idx = threadIdx.x; idx < kTiledN * DP; idx += kTiledThreads) sV[idx] = 0.f;
+    stage_tile64<T>(sQ, q, row0, S, D, DP);
+    float m[4], l[4];
+    float4 o[4][NJ];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        m[i] = -INFINITY;
+        l[i] = 0.f;
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) o[i][jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const int Lv = valid_keys(kv_lens, bh / H, L);
+    const int last_row = min(row0 + kTiledM, S) - 1;
+    const int col_end = causal ? min(Lv, last_row + off + 1) : Lv;   // exclusive
+    for (int c0 = 0; c0 < col_end; c0 += kTiledN) {
+        __syncthreads();   // the previous tile's P V is done (and sQ / the zeroed sV are in place)
+        stage_tile64<T>(sK, k, c0, L, D, DP);
+        stage_tile64<T>(sV, v, c0, L, D, DP);
+        __syncthreads();
+        float s[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll 2
+        for (int d = 0; d < D; d += 4) {
+            float4 qa[4], kb[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qa[i] = *reinterpret_cast<const float4*>(sQ + (ty + 16 * i) * DP + d);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) kb[j] = *reinterpret_cast<const float4*>(sK + (tx + 16 * j) * DP + d);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    s[i][j] = fmaf(qa[i].x, kb[j].x, s[i][j]);
+                    s[i][j] = fmaf(qa[i].y, kb[j].y, s[i][j]);
+                    s[i][j] = fmaf(qa[i].z, kb[j].z, s[i][j]);
+                    s[i][j] = fmaf(qa[i].w, kb[j].w, s[i][j]);
+                }
+        }
+        float corr[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = row0 + ty + 16 * i;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int col = c0 + tx + 16 * j;
+                const bool valid = col < Lv && (!causal || col <= row + off);
+                s[i][j] = valid ? s[i][j] * scale : -INFINITY;
+                mx = fmaxf(mx, s[i][j]);
+            }
+#pragma unroll
+            for (int o2 = 8; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
+            const float mnew = fmaxf(m[i], mx);
+            corr[i] = (m[i] == -INFINITY) ? 0.f : expf(m[i] - mnew);
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float p = (mnew == -INFINITY) ? 0.f : expf(s[i][j] - mnew);
+                sum += p;
+                sP[(ty + 16 * i) * kTiledPPitch + tx + 16 * j] = p;
+            }
+#pragma unroll
+            for (int o2 = 8; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
+            l[i] = l[i] * corr[i] + sum;
+            m[i] = mnew;
+#pragma unroll
+            for (int jj = 0; jj < NJ; ++jj) {
+                o[i][jj].x *= corr[i]; o[i][jj].y *= corr[i]; o[i][jj].z *= corr[i]; o[i][jj].w *= corr[i];
+            }
+        }
+        __syncthreads();   // P complete
+#pragma unroll 2
+        for (int n = 0; n < kTiledN; n += 4) {
+            float pa[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 t = *reinterpret_cast<const float4*>(sP + (ty + 16 * i) * kTiledPPitch + n);
+                pa[i][0] = t.x; pa[i][1] = t.y; pa[i][2] = t.z; pa[i][3] = t.w;
+            }
+#pragma unroll
+            for (int nn = 0; nn < 4; ++nn)
+#pragma unroll
+                for (int jj = 0; jj < NJ; ++jj) {
+                    const float4 vb = *reinterpret_cast<const float4*>(sV + (n + nn) * DP + 4 * tx + 64 * jj);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        o[i][jj].x = fmaf(pa[i][nn], vb.x, o[i][jj].x);
+                        o[i][jj].y = fmaf(pa[i][nn], vb.y, o[i][jj].y);
+                        o[i][jj].z = fmaf(pa[i][nn], vb.z, o[i][jj].z);
+                        o[i][jj].w = fmaf(pa[i][nn], vb.w, o[i][jj].w);
+                    }
+                }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = row0 + ty + 16 * i;
+        if (row >= S) continue;
+        const float inv = 1.0f / l[i];
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) {
+            const int d = 4 * tx + 64 * jj;
+            if (d < D)
+                store4_f32<T>(out + (long long)row * D + d,
+                              make_float4(o[i][jj].x * inv, o[i][jj].y * inv, o[i][jj].z * inv, o[i][jj].w * inv));
+        }
+        if (lse != nullptr && tx == 0) lse[bh * S + row] = m[i] + logf(l[i]);
+    }
+}
+
+// ------------------------------------------------------------------ backward, register-tiled
+// Same 16 x 16 thread layout as the tiled forward.  A block owns a 64-row tile (queries for dQ, keys
+// for dK/dV) held in shared memory together with its partner tensor (dO resp. V) and streams the
+// other side in 64-row tiles.  Both score products of a tile pair, S and dP, come out of one pass
+// over d; P and dS go through shared memory into the accumulating products.
+//
+// s[i][j] = a1[row_i] . b1[col_j],  dp[i][j] = a2[row_i] . b2[col_j]   (rows ty + 16 i, cols tx + 16 j)
+template <int DP>
+__device__ __forceinline__ void tiled_two_products(const float* a1, const float* a2, const float* b1, const float* b2,
+                                                   int ty, int tx, int D, float (&s)[4][4], float (&dp)[4][4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = dp[i][j] = 0.f;
+    for (int d = 0; d < D; d += 4) {
+        float4 xa[4], xb[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xa[i] = *reinterpret_cast<const float4*>(a1 + (ty + 16 * i) * DP + d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xb[j] = *reinterpret_cast<const float4*>(b1 + (tx + 16 * j) * DP + d);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                s[i][j] = fmaf(xa[i].x, xb[j].x, s[i][j]);
+                s[i][j] = fmaf(xa[i].y, xb[j].y, s[i][j]);
+                s[i][j] = fmaf(xa[i].z, xb[j].z, s[i][j]);
+                s[i][j] = fmaf(xa[i].w, xb[j].w, s[i][j]);
+            }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xa[i] = *reinterpret_cast<const float4*>(a2 + (ty + 16 * i) * DP + d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xb[j] = *reinterpret_cast<const float4*>(b2 + (tx + 16 * j) * DP + d);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                dp[i][j] = fmaf(xa[i].x, xb[j].x, dp[i][j]);
+                dp[i][j] = fmaf(xa[i].y, xb[j].y, dp[i][j]);
+                dp[i][j] = fmaf(xa[i].z, xb[j].z, dp[i][j]);
+                dp[i][j] = fmaf(xa[i].w, xb[j].w, dp[i][j]);
+            }
+    }
+}
+// acc[i][jj] += sum_n w[row_i][n] * b[n][4 tx + 64 jj ..]   (w: 64 x 64 in shared memory, pitch kTiledPPitch)
+template <int DP, int NJ>
+__device__ __forceinline__ void tiled_accumulate(const float* w, const float* b, int ty, int tx, float4 (&acc)[4][NJ]) {
+#pragma unroll 2
+    for (int n = 0; n < kTiledN; n += 4) {
+        float pa[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 t = *reinterpret_cast<const float4*>(w + (ty + 16 * i) * kTiledPPitch + n);
+            pa[i][0] = t.x; pa[i][1] = t.y; pa[i][2] = t.z; pa[i][3] = t.w;
+        }
+#pragma unroll
+        for (int nn = 0; nn < 4; ++nn)
+#pragma unroll
+            for (int jj = 0; jj < NJ; ++jj) {
+                const float4 vb = *reinterpret_cast<const float4*>(b + (n + nn) * DP + 4 * tx + 64 * jj);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[i][jj].x = fmaf(pa[i][nn], vb.x, acc[i][jj].x);
+                    acc[i][jj].y = fmaf(pa[i][nn], vb.y, acc[i][jj].y);
+                    acc[i][jj].z = fmaf(pa[i][nn], vb.z, acc[i][jj].z);
+                    acc[i][jj].w = fmaf(pa[i][nn], vb.w, acc[i][jj].w);
+                }
+            }
+    }
+}
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(kTiledThreads) attn_bwd_dq_simt_tiled_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ dout,
+    const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dq, int S, int L, int D,
+    int causal, float scale, int group, const int* __restrict__ kv_lens, int H) {
+    constexpr int DP = DMAX + 4, NJ = DMAX / 64;
+    extern __shared__ __align__(16) float smem[];
+    float* sQ = smem;
+    float* sdO = sQ + kTiledM * DP;
+    float* sK = sdO + kTiledM * DP;
+    float* sV = sK + kTiledN * DP;
+    float* sW = sV + kTiledN * DP;       // dS
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int nblk = (S + kTiledM - 1) / kTiledM;
+    const long long bh = blockIdx.x / nblk;
+    const int row0 = (int)(blockIdx.x % nblk) * kTiledM;
+    const int off = L - S;
+    q += bh * (long long)S * D;
+    dout += bh * (long long)S * D;
+    dq += bh * (long long)S * D;
+    k += (bh / group) * (long long)L * D;
+    v += (bh / group) * (long long)L * D;
+    lse += bh * S;
+    delta += bh * S;
+
+    // columns of sK at and past D are read by the dQ accumulation (and discarded): keep them finite
+    for (int idx = threadIdx.x; idx < kTiledN * DP; idx += kTiledThreads) sK[idx] = 0.f;
+    stage_tile64<T>(sQ, q, row0, S, D, DP);
+    stage_tile64<T>(sdO, dout, row0, S, D, DP);
+    float row_lse[4], row_delta[4];
+    float4 acc[4][NJ];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = row0 + ty + 16 * i;
+        row_lse[i] = row < S ? lse[row] : 0.f;
+        row_delta[i] = row < S ? delta[row] : 0.f;
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) acc[i][jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const int Lv = valid_keys(kv_lens, bh / H, L);
+    const int last_row = min(row0 + kTiledM, S) - 1;
+    const int col_end = causal ? min(Lv, last_row + off + 1) : Lv;
+    for (int c0 = 0; c0 < col_end; c0 += kTiledN) {
+        __syncthreads();
+        stage_tile64<T>(sK, k, c0, L, D, DP);
+        stage_tile64<T>(sV, v, c0, L, D, DP);
+        __syncthreads();
+        float s[4][4], dp[4][4];
+        tiled_two_products<DP>(sQ, sdO, sK, sV, ty, tx, D, s, dp);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = row0 + ty + 16 * i;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int col = c0 + tx + 16 * j;
+                const bool valid = col < Lv && row < S && (!causal || col <= row + off);
+                const float p = valid ? expf(s[i][j] * scale - row_lse[i]) : 0.f;
+                sW[(ty + 16 * i) * kTiledPPitch + tx + 16 * j] = p * (dp[i][j] - row_delta[i]);
+            }
+        }
+        __syncthreads();
+        tiled_accumulate<DP, NJ>(sW, sK, ty, tx, acc);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = row0 + ty + 16 * i;
+        if (row >= S) continue;
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) {
+            const int d = 4 * tx + 64 * jj;
+            if (d < D)
+                store4_f32<T>(dq + (long long)row * D + d, make_float4(acc[i][jj].x * scale, acc[i][jj].y * scale,
+                                                                        acc[i][jj].z * scale, acc[i][jj].w * scale));
+        }
+    }
+}
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(kTiledThreads) attn_bwd_dkv_simt_tiled_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ dout,
+    const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dk, T* __restrict__ dv, int S,
+    int L, int D, int causal, float scale, int group, const int* __restrict__ kv_lens, int H) {
+    constexpr int DP = DMAX + 4, NJ = DMAX / 64;
+    extern __shared__ __align__(16) float smem[];
+    float* sK = smem;
+    float* sV = sK + kTiledM * DP;
+    float* sQ = sV + kTiledM * DP;
+    float* sdO = sQ + kTiledN * DP;
+    float* sP = sdO + kTiledN * DP;                  // P^T   [key][query]
+    float* sW = sP + kTiledM * kTiledPPitch;         // dS^T  [key][query]
+    float* sLse = sW + kTiledM * kTiledPPitch;       // [64] of the streamed queries
+    float* sDelta = sLse + kTiledN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int nblk = (L + kTiledM - 1) / kTiledM;
+    const long long bh = blockIdx.x / nblk;          // key/value slice; its query heads are bh*group ...
+    const int key0 = (int)(blockIdx.x % nblk) * kTiledM;
+    const int off = L - S;
+    q += bh * group * (long long)S * D;
+    dout += bh * group * (long long)S * D;
+    k += bh * (long long)L * D;
+    v += bh * (long long)L * D;
+    dk += bh * (long long)L * D;
+    dv += bh * (long long)L * D;
+    lse += bh * group * S;
+    delta += bh * group * S;
+
+    const int Lv = valid_keys(kv_lens, (bh * group) / H, L);   // padded keys get zero gradients
+    // columns of sQ / sdO at and past D are read by the accumulations (and discarded): keep them finite
+    for (int idx = threadIdx.x; idx < 2 * kTiledN * DP; idx += kTiledThreads) sQ[idx] = 0.f;
+    stage_tile64<T>(sK, k, key0, L, D, DP);
+    stage_tile64<T>(sV, v, key0, L, D, DP);
+    float4 aK[4][NJ], aV[4][NJ];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) aK[i][jj] = aV[i][jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int i_begin = causal ? max(0, key0 - off) : 0;   // first query that can see this block's first key
+    i_begin = (i_begin / kTiledN) * kTiledN;
+    for (int hh = 0; hh < group; ++hh, q += (long long)S * D, dout += (long long)S * D, lse += S, delta += S)
+        for (int i0 = i_begin; i0 < S; i0 += kTiledN) {
+            __syncthreads();
+            stage_tile64<T>(sQ, q, i0, S, D, DP);
+            stage_tile64<T>(sdO, dout, i0, S, D, DP);
+            if (threadIdx.x < kTiledN) {
+                const int qi = i0 + threadIdx.x;
+                sLse[threadIdx.x] = qi < S ? lse[qi] : 0.f;
+                sDelta[threadIdx.x] = qi < S ? delta[qi] : 0.f;
+            }
+            __syncthreads();
+            float s[4][4], dp[4][4];
+            tiled_two_products<DP>(sK, sV, sQ, sdO, ty, tx, D, s, dp);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int qi = i0 + tx + 16 * j;
+                const float ql = sLse[tx + 16 * j], qd = sDelta[tx + 16 * j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = key0 + ty + 16 * i;
+                    const bool valid = qi < S && key < Lv && (!causal || key <= qi + off);
+                    const float p = valid ? expf(s[i][j] * scale - ql) : 0.f;
+                    sP[(ty + 16 * i) * kTiledPPitch + tx + 16 * j] = p;
+                    sW[(ty + 16 * i) * kTiledPPitch + tx + 16 * j] = p * (dp[i][j] - qd);
+                }
+            }
+            __syncthreads();
+            tiled_accumulate<DP, NJ>(sP, sdO, ty, tx, aV);
+            tiled_accumulate<DP, NJ>(sW, sQ, ty, tx, aK);
+        }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int key = key0 + ty + 16 * i;
+        if (key >= L) continue;
+#pragma unroll
+        for (int jj = 0; jj < NJ; ++jj) {
+            const int d = 4 * tx + 64 * jj;
+            if (d < D) {
+                store4_f32<T>(dk + (long long)key * D + d, make_float4(aK[i][jj].x * scale, aK[i][jj].y * scale,
+                                                                        aK[i][jj].z * scale, aK[i][jj].w * scale));
+                store4_f32<T>(dv + (long long)key * D + d, aV[i][jj]);
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------- launchers
 template <typename K>
 static cudaError_t set_smem(K kernel, size_t bytes) {
@@ -359,6 +777,42 @@ static cudaError_t launch_fwd_simt(const AttnArgs& a, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+// the tiled backward kernels: same vector requirements as the tiled forward, for every tensor they touch
+static bool simt_tiled_bwd_ok(const AttnArgs& a) {
+    const char* e = getenv("TT_SIMT_BWD");
+    if (e && e[0] == 'r') return false;
+    const uintptr_t mask = a.bf16 ? 7 : 15;
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
+                           reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.dout) |
+                           reinterpret_cast<uintptr_t>(a.dq) | reinterpret_cast<uintptr_t>(a.dk) |
+                           reinterpret_cast<uintptr_t>(a.dv);
+    return a.D % 4 == 0 && a.D <= 128 && (ptrs & mask) == 0;
+}
+template <typename T, int DMAX>
+static cudaError_t launch_bwd_simt_tiled(const AttnArgs& a, float* delta, cudaStream_t st) {
+    const size_t tile = (size_t)64 * (DMAX + 4) * sizeof(float), w = (size_t)64 * kTiledPPitch * sizeof(float);
+    const size_t smem_q = 4 * tile + w, smem_kv = 4 * tile + 2 * w + 2 * kTiledN * sizeof(float);
+    cudaError_t e = set_smem(attn_bwd_dq_simt_tiled_kernel<T, DMAX>, smem_q);
+    if (e != cudaSuccess) return e;
+    e = set_smem(attn_bwd_dkv_simt_tiled_kernel<T, DMAX>, smem_kv);
+    if (e != cudaSuccess) return e;
+    const unsigned gq = (unsigned)(((a.S + kTiledM - 1) / kTiledM) * a.BH);
+    {
+        LaunchScope ls(K_BWD_SIMT_DQ, st);
+        attn_bwd_dq_simt_tiled_kernel<T, DMAX><<<gq, kTiledThreads, smem_q, st>>>(
+            (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dq, a.S, a.L, a.D,
+            a.causal, a.scale, a.group, a.kv_lens, a.H);
+    }
+    const unsigned gk = (unsigned)(((a.L + kTiledM - 1) / kTiledM) * (a.BH / a.group));
+    {
+        LaunchScope ls(K_BWD_SIMT_DKV, st);
+        attn_bwd_dkv_simt_tiled_kernel<T, DMAX><<<gk, kTiledThreads, smem_kv, st>>>(
+            (const T*)a.q, (const T*)a.k, (const T*)a.v, (const T*)a.dout, a.lse, delta, (T*)a.dk, (T*)a.dv, a.S,
+            a.L, a.D, a.causal, a.scale, a.group, a.kv_lens, a.H);
+    }
+    return cudaGetLastError();
+}
+
 template <typename T, int NV>
 static cudaError_t launch_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t st) {
     long long n_rows = a.BH * (long long)a.S;
@@ -367,6 +821,7 @@ static cudaError_t launch_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t
         attn_bwd_delta_kernel<T><<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>((const T*)a.out, (const T*)a.dout,
                                                                               delta, n_rows, a.D);
     }
+    if (simt_tiled_bwd_ok(a)) return a.D <= 64 ? launch_bwd_simt_tiled<T, 64>(a, delta, st) : launch_bwd_simt_tiled<T, 128>(a, delta, st);
     size_t smem_q = (size_t)4 * 32 * (a.D + 1) * sizeof(float);
     size_t smem_kv = smem_q + 64 * sizeof(float);
     cudaError_t e = set_smem(attn_bwd_dq_simt_kernel<T, NV>, smem_q);
@@ -390,8 +845,34 @@ static cudaError_t launch_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t
     return cudaGetLastError();
 }
 
+template <typename T, int DMAX>
+static cudaError_t launch_fwd_simt_tiled(const AttnArgs& a, cudaStream_t st) {
+    const size_t smem = ((size_t)(kTiledM + 2 * kTiledN) * (DMAX + 4) + (size_t)kTiledM * kTiledPPitch) * sizeof(float);
+    cudaError_t e = set_smem(attn_fwd_simt_tiled_kernel<T, DMAX>, smem);
+    if (e != cudaSuccess) return e;
+    const unsigned grid = (unsigned)(((a.S + kTiledM - 1) / kTiledM) * a.BH);
+    {
+        LaunchScope ls(K_FWD_SIMT, st);
+        attn_fwd_simt_tiled_kernel<T, DMAX><<<grid, kTiledThreads, smem, st>>>(
+            (const T*)a.q, (const T*)a.k, (const T*)a.v, (T*)a.out, a.lse, a.S, a.L, a.D, a.causal, a.scale, a.group,
+            a.kv_lens, a.H);
+    }
+    return cudaGetLastError();
+}
+// the register-tiled forward needs 4-element vectors: D a multiple of 4 and 16-byte (fp32) or 8-byte
+// (bf16) aligned tensors; TT_SIMT_FWD=rows keeps the row-per-lane kernel
+static bool simt_tiled_ok(const AttnArgs& a) {
+    const char* e = getenv("TT_SIMT_FWD");
+    if (e && e[0] == 'r') return false;
+    const uintptr_t mask = a.bf16 ? 7 : 15;
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) |
+                           reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.out);
+    return a.D % 4 == 0 && a.D <= 128 && (ptrs & mask) == 0;
+}
+
 template <typename T>
 static cudaError_t dispatch_fwd(const AttnArgs& a, cudaStream_t st) {
+    if (simt_tiled_ok(a)) return a.D <= 64 ? launch_fwd_simt_tiled<T, 64>(a, st) : launch_fwd_simt_tiled<T, 128>(a, st);
     if (a.D <= 32) return launch_fwd_simt<T, 1>(a, st);
     if (a.D <= 64) return launch_fwd_simt<T, 2>(a, st);
     if (a.D <= 128) return launch_fwd_simt<T, 4>(a, st);

@@ -144,6 +144,33 @@ def test_odd_head_dims(tt, oracle, D, dtype):
             assert oracle.max_abs_err(_np(got), ref) <= BF16_TOL
 
 
+@pytest.mark.parametrize("route", ["tiled", "rows"])
+@pytest.mark.parametrize("D,dtype", [(40, "f32"), (128, "f32"), (50, "f32"), (72, "bf16")])
+def test_simt_kernel_routes(tt, oracle, monkeypatch, route, D, dtype):
+    """The fp32-arithmetic kernels come in two forms: register-tiled (head dims that are multiples
+    of 4 up to 128) and row-per-lane (everything else, or forced with TT_SIMT_FWD/BWD=rows).  Both
+    must meet the same tolerance on a ragged causal shape with L != S."""
+    if route == "rows":
+        monkeypatch.setenv("TT_SIMT_FWD", "rows")
+        monkeypatch.setenv("TT_SIMT_BWD", "rows")
+    B, H, S, L = 2, 3, 150, 201
+    q, k, v, do = oracle.make_inputs(11, B, H, S, L, D, sigma=0.7)
+    if dtype == "bf16":
+        q, k, v, do = _bf16_inputs(oracle, q, k, v, do)
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = oracle.attention_backward(q, k, v, do, True)
+    tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+    tq, tk, tv, tdo = (_dev(x, tdt) for x in (q, k, v, do))
+    out, lse = tt.attention_forward(tq, tk, tv, causal=True)
+    dq, dk, dv = tt.attention_backward(tq, tk, tv, out, lse, tdo, causal=True)
+    tt.check_device_status()
+    assert oracle.max_abs_err(_np(lse), lse_ref) <= (1e-4 if dtype == "f32" else 2e-2)
+    for got, ref in ((out, o_ref), (dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        if dtype == "f32":
+            assert oracle.rel_err(_np(got), ref) <= F32_TOL
+        else:
+            assert oracle.max_abs_err(_np(got), ref) <= BF16_TOL
+
+
 # ----------------------------------------------------------------------------- backward, bf16, tile-sized
 BWD_CASES = [
     (1, 2, 128, 128, 128, False, 1.0),
