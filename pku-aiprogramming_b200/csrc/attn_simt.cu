@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkv_simt_kernel(
 // the keys in tiles of 64; thread (ty, tx) of the 16 x 16 block holds the 4 x 4 scores of rows
 // ty + 16 i against keys tx + 16 j, so every 128-bit shared-memory load feeds 16 FMAs (the
 // row-per-lane kernel above fetches one operand per FMA).  The 16 lanes that share a row reduce its
-// statistics with shuffles, P goes through shared memory, and the same thread accumulates
+// statistics with shuffles, P goes through shared memory (in place of the K tile), and the same thread accumulates
 // O[rows ty + 16 i][4 tx + 64 jj .. + 3], so the rescale factors never leave registers.
 constexpr int kTiledM = 64, kTiledN = 64, kTiledThreads = 256, kTiledPPitch = kTiledN + 4;
 
@@ -386,7 +386,7 @@ __device__ __forceinline__ void stage_tile64(float* dst, const T* src, long long
 }
 
 template <typename T, int DMAX>
-__global__ void __launch_bounds__(kTiledThreads) attn_fwd_simt_tiled_kernel(
+__global__ void __launch_bounds__(kTiledThreads, 2) attn_fwd_simt_tiled_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ out,
     float* __restrict__ lse, int S, int L, int D, int causal, float scale, int group, const int* __restrict__ kv_lens,
     int H) {
@@ -396,7 +396,7 @@ __global__ void __launch_bounds__(kTiledThreads) attn_fwd_simt_tiled_kernel(
     float* sQ = smem;
     float* sK = sQ + kTiledM * DP;
     float* sV = sK + kTiledN * DP;
-    float* sP = sV + kTiledN * DP;
+    float* sP = sK;   // P takes the K tile's place once the scores are done: three tiles in all, two blocks per SM at D = 128
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int nblk = (S + kTiledM - 1) / kTiledM;
     const long long bh = blockIdx.x / nblk;
@@ -449,6 +449,7 @@ __global__ void __launch_bounds__(kTiledThreads) attn_fwd_simt_tiled_kernel(
                     s[i][j] = fmaf(qa[i].w, kb[j].w, s[i][j]);
                 }
         }
+        __syncthreads();   // every thread has read its K rows: the tile's space now holds P
         float corr[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -847,7 +848,7 @@ static cudaError_t launch_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t
 
 template <typename T, int DMAX>
 static cudaError_t launch_fwd_simt_tiled(const AttnArgs& a, cudaStream_t st) {
-    const size_t smem = ((size_t)(kTiledM + 2 * kTiledN) * (DMAX + 4) + (size_t)kTiledM * kTiledPPitch) * sizeof(float);
+    const size_t smem = (size_t)(kTiledM + 2 * kTiledN) * (DMAX + 4) * sizeof(float);   // Q, K (then P), V
     cudaError_t e = set_smem(attn_fwd_simt_tiled_kernel<T, DMAX>, smem);
     if (e != cudaSuccess) return e;
     const unsigned grid = (unsigned)(((a.S + kTiledM - 1) / kTiledM) * a.BH);
