@@ -115,7 +115,8 @@ def reference_fc(ops, x, w, b, dy):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("TT_REFERENCE_ROOT"), required="TT_REFERENCE_ROOT" not in os.environ,
+                    help="checkout of the reference project (or set TT_REFERENCE_ROOT)")
     args = ap.parse_args()
     ops = load_reference_ops(args.reference)
     for name, B, H, S, L, D, causal, sigma, seed in CASES:
