@@ -78,6 +78,10 @@ struct BwdParams {
     const float* delta;    // [BH,S]
     int S, L;
     int n_tiles;           // resident tiles per slice
+    // causal: the n_light lightest resident tiles of every slice are numbered after all others, so that
+    // CTAs that run out of heavy items near the end of the launch still find short ones (0: one phase)
+    int n_light;
+    int n_items_heavy;     // items of the first phase = slices * (n_tiles - n_light)
     int causal;
     float scale, scale_log2;
     unsigned int* status;
@@ -133,19 +137,28 @@ template <bool kKeysResident>
 __device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p) {
     BwdItem w;
     const int off = p.L - p.S;
-    w.bh = item / p.n_tiles;
+    int rank;   // position of the resident tile among its slice's tiles, heaviest first
+    if (item < p.n_items_heavy) {
+        const int n_heavy = p.n_tiles - p.n_light;
+        w.bh = item / n_heavy;
+        rank = item - w.bh * n_heavy;
+    } else {
+        const int r = item - p.n_items_heavy;
+        w.bh = r / p.n_light;
+        rank = (p.n_tiles - p.n_light) + (r - w.bh * p.n_light);
+    }
     // batch entry: a resident key/value slice is bh / (H / group), a resident query slice bh / H
     w.Lv = valid_keys(p.kv_lens, kKeysResident ? ((long long)w.bh * p.group) / p.H : (long long)w.bh / p.H, p.L);
     int rt;
     if (kKeysResident) {
-        rt = item % p.n_tiles;                                        // early key tiles are the heavy ones
+        rt = rank;                                                    // early key tiles are the heavy ones
         w.t_end = (p.S + 127) >> 7;
         w.t_begin = p.causal ? (max(0, rt * 128 - off) >> 7) : 0;
         // a key tile that is all padding gets zero gradients: one streamed tile keeps the pipeline's
         // hand-offs alive, the epilogue writes zeros
         if (rt * 128 >= w.Lv) w.t_end = min(w.t_end, w.t_begin + 1);
     } else {
-        rt = p.n_tiles - 1 - (item % p.n_tiles);                      // late query tiles are the heavy ones
+        rt = p.n_tiles - 1 - rank;                                    // late query tiles are the heavy ones
         const int n_kv = (w.Lv + 127) >> 7;
         w.t_begin = 0;
         w.t_end = p.causal ? min(n_kv, ((min(rt * 128 + 127, p.S - 1) + off) >> 7) + 1) : n_kv;
@@ -844,6 +857,10 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     }
     p.n_tiles = (a.L + 127) / 128;
     p.n_items = (int)(a.BH / a.group * p.n_tiles);
+    const char* two_phase = getenv("TT_BWD_TWO_PHASE");   // "0": one slice-major numbering
+    const bool phases = a.causal && !(two_phase && two_phase[0] == '0');
+    p.n_light = phases ? p.n_tiles / 4 : 0;
+    p.n_items_heavy = (int)(a.BH / a.group * (p.n_tiles - p.n_light));
     p.sched_counter = next_bwd_sched_counter(st, &e);
     if (e != cudaSuccess) return e;
     {
@@ -857,6 +874,8 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.out1 = (__nv_bfloat16*)a.dq;
     p.n_tiles = (a.S + 127) / 128;
     p.n_items = (int)(a.BH * p.n_tiles);
+    p.n_light = phases ? p.n_tiles / 4 : 0;
+    p.n_items_heavy = (int)(a.BH * (p.n_tiles - p.n_light));
     p.sched_counter = next_bwd_sched_counter(st, &e);
     if (e != cudaSuccess) return e;
     {

@@ -66,6 +66,8 @@ struct FwdParams {
     float* lse;
     int S, L;
     int n_qblk;       // 256-row query blocks per slice
+    int n_light;      // causal: the n_light lightest query blocks of every slice are numbered after all others (0: one phase)
+    int n_items_heavy;   // items of the first phase = slices * (n_qblk - n_light)
     int causal;
     float scale_log2; // scale * log2(e)
     unsigned int* status;
@@ -155,8 +157,9 @@ __device__ __forceinline__ uint64_t softmax_exp_half(const uint32_t (&sr)[4][32]
 //
 // The kernel is persistent: one CTA per SM takes work items (slice, 256-row query block) from a
 // global counter until none are left.  Items are numbered slice-major with the heavy (late)
-// query blocks of a slice first, so that concurrently running CTAs share a slice's K/V in L2 and
-// the tail of the launch consists of light items.  The loader runs up to two items ahead; the
+// query blocks of a slice first, so that concurrently running CTAs share a slice's K/V in L2.
+// Causal launches keep the lightest quarter of every slice's blocks for a second pass over the
+// slices, so that the tail of the launch consists of light items.  The loader runs up to two items ahead; the
 // first MMAs of item n+1 overlap the epilogue (normalise, store O) of item n.
 struct FwdItem {
     int bh, q0, n_tiles[2], n_max;
@@ -166,8 +169,16 @@ struct FwdItem {
 template <bool kPaged = false>
 __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p) {
     FwdItem w;
-    w.bh = item / p.n_qblk;
-    const int qb = p.n_qblk - 1 - (item % p.n_qblk);
+    int qb;
+    if (item < p.n_items_heavy) {
+        const int n_heavy = p.n_qblk - p.n_light;
+        w.bh = item / n_heavy;
+        qb = p.n_qblk - 1 - (item - w.bh * n_heavy);
+    } else {   // second phase: the light (early) query blocks, again slice-major and heavy first
+        const int r = item - p.n_items_heavy;
+        w.bh = r / p.n_light;
+        qb = p.n_light - 1 - (r - w.bh * p.n_light);
+    }
     w.q0 = qb * 256;
     const int off = p.L - p.S;
     if (kPaged) {   // a paged cache may hold empty sequences, and an item may cover one key range of its slice
@@ -750,6 +761,15 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
         p.wide_stores = ((reinterpret_cast<uintptr_t>(a.out) & 31) == 0 && !(ws && ws[0] == '0')) ? 1 : 0;
     }
     p.n_items = (int)(a.BH * p.n_qblk);
+    {
+        // Causal items weigh in proportion to their query block's position.  With one slice-major
+        // numbering the launch ends on the last slice's heaviest blocks while the other CTAs run dry;
+        // keeping the lightest quarter of every slice's blocks (1/16 of the work) for a second phase
+        // gives the CTAs that finish early something short to do.  TT_FWD_TWO_PHASE=0: one phase.
+        const char* tp = getenv("TT_FWD_TWO_PHASE");
+        p.n_light = (a.causal && !(tp && tp[0] == '0')) ? p.n_qblk / 4 : 0;
+        p.n_items_heavy = (int)(a.BH * (p.n_qblk - p.n_light));
+    }
     p.sched_counter = next_sched_counter(st, &e);
     if (e != cudaSuccess) return e;
     int dev = 0, n_sm = 148;
