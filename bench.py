@@ -45,7 +45,7 @@ WORKLOADS = {
 # summaries under profiles/ ; None until a capture of that kernel exists.
 NCU_TRAFFIC_BYTES = {
     # cfg3, one launch each: profiles/attn_fwd_bwd_sm100_cfg3.md
-    "attn_fwd_sm100": 522.5e6, "attn_bwd_sm100_dkv": 782.8e6, "attn_bwd_sm100_dq": 663.1e6,
+    "attn_fwd_sm100": 587.6e6, "attn_bwd_sm100_dkv": 850.8e6, "attn_bwd_sm100_dq": 727.3e6,
     # config 4 = 8 x the captured batch-8 launch: profiles/attn_decode_bf16_b8.md
     "attn_decode": 8.637e9,
 }
