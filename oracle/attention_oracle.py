@@ -309,6 +309,68 @@ def attention_rows(q_rows, k, v, row0, S, causal=False, scale=None):
     return o, np.log(den[:, 0])
 
 
+def attention_backward_rows(q_rows, do_rows, k, v, row0, S, causal=False, scale=None):
+    """Forward and backward for a block of query rows `[r,D]` of ONE slice against `k,v [L,D]`:
+    the same ops in the same order as `attention_backward`, on the rows' share of the graph.
+
+    Rows are independent given K and V: O, lse and dQ of the block are final, dK and dV are the
+    block's contributions (the reverse sweep sums them over all rows, MatMul.gradient,
+    operators.py:421-429).  Under the causal mask the keys behind the block's last row carry
+    probability exp(-1e30) = 0 exactly, so they are left out; the returned dK, dV partials cover
+    the first `n_keys` keys.  Returns (o, lse, dq, dk_part, dv_part, n_keys).
+    """
+    D = q_rows.shape[-1]
+    L = k.shape[0]
+    r = q_rows.shape[0]
+    sc = float(default_scale(D) if scale is None or scale <= 0 else scale)
+    n_keys = min(L, row0 + r + (L - S)) if causal else L
+    k = k[:n_keys]; v = v[:n_keys]
+    s = np.matmul(q_rows, k.T) * sc
+    if causal:
+        i = (row0 + np.arange(r))[:, None]
+        j = np.arange(n_keys)[None, :]
+        s = s + np.where(j <= i + (L - S), 0.0, MASK_VALUE).astype(s.dtype)
+    e = np.exp(s)
+    den = np.broadcast_to(np.sum(e, axis=1).reshape(r, 1), e.shape)
+    p = e / den
+    o = np.matmul(p, v)
+    dp = np.matmul(do_rows, v.T)
+    dv_part = np.matmul(p.T, do_rows)
+    de_div = dp / den
+    dden = -dp * e / (den ** 2)
+    de_sum = np.broadcast_to(np.sum(dden, axis=1).reshape(r, 1), e.shape)
+    ds = (de_div + de_sum) * np.exp(s)
+    dqk = ds * sc
+    dq = np.matmul(dqk, k)
+    dk_part = np.matmul(q_rows.T, dqk).T
+    return o, np.log(den[:, 0]), dq, dk_part, dv_part, n_keys
+
+
+def attention_backward_chunked(q, k, v, do, causal=False, scale=None, chunk=1024):
+    """`attention_backward` of ONE slice (`q,do [S,D]`, `k,v [L,D]`) in blocks of `chunk` query
+    rows, so that a long slice never holds more than `chunk x L` scores at a time.
+    Returns (o, lse, dq, dk, dv)."""
+    S, D = q.shape
+    L = k.shape[0]
+    o = np.empty((S, D), q.dtype); lse = np.empty((S,), q.dtype); dq = np.empty((S, D), q.dtype)
+    dk = np.zeros((L, D), q.dtype); dv = np.zeros((L, D), q.dtype)
+    for r0 in range(0, S, chunk):
+        r1 = min(S, r0 + chunk)
+        o[r0:r1], lse[r0:r1], dq[r0:r1], dkp, dvp, n = attention_backward_rows(q[r0:r1], do[r0:r1], k, v, r0, S, causal, scale)
+        dk[:n] += dkp
+        dv[:n] += dvp
+    return o, lse, dq, dk, dv
+
+
+def bf16_grad_tol(ref, base=2e-2) -> float:
+    """Tolerance for a bf16 gradient tensor against the fp32 oracle: `base` absolute while the
+    reference stays within 2.56 (where half a bf16 ulp, 2^-8 relative, is below 1e-2), and one
+    bf16 ulp (2^-7 relative) of the largest reference value on top of it beyond -- rounding the
+    OUTPUT to bf16 alone moves a value of magnitude m by up to m * 2^-8."""
+    m = float(np.max(np.abs(ref))) if np.size(ref) else 0.0
+    return base if m <= 2.56 else base + 2.0 ** -7 * m
+
+
 def rel_err(a, b) -> float:
     """max|a-b| / max|b| -- the per-tensor relative error the fp32 tolerance is stated in."""
     a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)

@@ -393,9 +393,9 @@ def test_random_shapes_against_oracle(tt, oracle):
         tt.check_device_status()
         tag = f"case {case}: B{B} H{H} S{S} L{L} D{D} causal={causal}"
         for got, ref, name in ((out, o_ref, "o"), (dq, dq_ref, "dq"), (dk, dk_ref, "dk"), (dv, dv_ref, "dv")):
-            # 2e-2 absolute, widened by one bf16 ulp (2^-7 relative) of the largest value: with few keys
-            # and many queries dK/dV reach magnitudes where bf16 OUTPUT rounding alone exceeds 2e-2
-            tol = BF16_TOL + 2.0 ** -7 * float(np.abs(ref).max())
+            # 2e-2 absolute; only where the reference exceeds 2.56 (few keys and many queries: dK/dV reach
+            # magnitudes where bf16 OUTPUT rounding alone exceeds 2e-2) one bf16 ulp of its largest value more
+            tol = BF16_TOL if name == "o" else oracle.bf16_grad_tol(ref)
             assert oracle.max_abs_err(_np(got), ref) <= tol, f"{tag} {name}"
         assert oracle.max_abs_err(_np(lse), lse_ref) <= 2e-2, tag
 
@@ -462,4 +462,4 @@ def test_backward_many_short_items(tt, oracle):
         o_r, _, dq_r, dk_r, dv_r = oracle.attention_backward(f(q, b, h), f(k, b, h), f(v, b, h), f(do, b, h), True)
         assert oracle.max_abs_err(f(out, b, h), o_r) <= 2e-2
         for got, ref in ((dq, dq_r), (dk, dk_r), (dv, dv_r)):
-            assert oracle.max_abs_err(f(got, b, h), ref) <= 2e-2 + 2.0 ** -7 * np.abs(ref).max()
+            assert oracle.max_abs_err(f(got, b, h), ref) <= oracle.bf16_grad_tol(ref)
