@@ -41,13 +41,15 @@ WORKLOADS = {
     "cfg5": dict(B=1, H=64, S=32768, D=128, desc="bf16 causal fwd+bwd, Q/K/V [1,64,32768,128], heads sharded over the GPUs"),
     "cfg2": dict(B=8, H=16, S=1024, D=64, desc="bf16 causal fwd+bwd, Q/K/V [8,16,1024,64] per GPU"),
 }
-# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
-# summaries under profiles/ ; None until a capture of that kernel exists.
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) measured with ncu; keyed by
+# workload, because the same kernel moves different bytes per launch on each.  "per_slice" entries were
+# captured on a few slices of the workload's slice shape and scale with the slice count (the kernels walk
+# the slices one after the other, so a slice's traffic does not depend on how many follow).
 NCU_TRAFFIC_BYTES = {
-    # cfg3, one launch each: profiles/attn_fwd_bwd_sm100_cfg3.md
-    "attn_fwd_sm100": 587.6e6, "attn_bwd_sm100_dkv": 850.8e6, "attn_bwd_sm100_dq": 727.3e6,
-    # config 4 = 8 x the captured batch-8 launch: profiles/attn_decode_bf16_b8.md
-    "attn_decode": 8.637e9,
+    "cfg3": {"attn_fwd_sm100": 587.6e6, "attn_bwd_sm100_dkv": 850.8e6, "attn_bwd_sm100_dq": 727.3e6},
+    "cfg5_per_slice": {},
+    # config 4 = 8 x the captured batch-8 launch (the full launch holds 8.6 GB, too large a capture)
+    "decode": {"attn_decode": 8.637e9},
 }
 
 
@@ -136,9 +138,19 @@ def cpu_threads():
     return os.cpu_count() or 1
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU arm is one process and takes every core."""
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=len(os.sched_getaffinity(0)), user_api="blas")
+    except Exception:
+        pass
+
+
 def run_reference_arm(args, w, rank):
     if rank != 0:
         return
+    use_all_host_threads()
     S, D = w["S"], w["D"]
     S_cpu = min(S, 4096)       # a 32768^2 fp32 score matrix does not fit a bounded step; sample query/key prefix
     for _ in range(max(args.warmup, 0)):
@@ -166,11 +178,69 @@ ALG_FWD_UNITS = {  # algorithmic FLOPs per launch, in units of the forward's cou
     "attn_fwd_sm100": 1.0,        # QK^T, PV
     "attn_bwd_sm100_dkv": 2.0,    # S recompute, dP, dV, dK  (4 of the 5 backward GEMMs)
     "attn_bwd_sm100_dq": 0.5,     # dQ (its S and dP recompute is overhead of the two-pass design)
+    "attn_bwd_fused_sm100": 2.5,  # single pass: all 5 backward GEMMs, nothing recomputed
 }
 
 
-def run_workload(tt, name, steps, warmup, world, rank, dev, peaks, e2e_steps, sample_clocks):
-    """Times `steps` forward+backward steps of workload `name`; returns the fields of the JSON line."""
+def verify_slice(tt, name, tensors, S, D, n_local):
+    """Re-checks a timed result against the CPU oracle after the timed region: one sampled local slice,
+    whole for S <= 4096, the first and last 128-row query blocks (O, lse, dQ, and dK/dV of the last key
+    block, which only those rows feed) for longer slices.  Returns the `verified` block of the line."""
+    from oracle import attention_oracle as orc
+    q, k, v, do, out, lse, dq, dk, dv = tensors
+    f = lambda t, i: t.reshape(n_local, *t.shape[2:])[i].float().cpu().numpy()
+    idx = n_local - 1
+    errs, ok = {}, True
+
+    def upd(key, got, ref, tol):
+        nonlocal ok
+        e = orc.max_abs_err(got, ref)
+        errs[key] = max(errs.get(key, 0.0), e)
+        ok = ok and (e <= tol)
+
+    if S <= 4096:
+        o_r, l_r, dq_r, dk_r, dv_r = orc.attention_backward_chunked(f(q, idx), f(k, idx), f(v, idx), f(do, idx), True)
+        upd("o", f(out, idx), o_r, 2e-2); upd("lse", f(lse, idx), l_r, 2e-2)
+        upd("dq", f(dq, idx), dq_r, orc.bf16_grad_tol(dq_r))
+        upd("dk", f(dk, idx), dk_r, orc.bf16_grad_tol(dk_r)); upd("dv", f(dv, idx), dv_r, orc.bf16_grad_tol(dv_r))
+        what = f"local slice {idx} in full against the oracle"
+    else:
+        kn, vn = f(k, idx), f(v, idx)
+        for row0 in (0, S - 128):
+            sl = slice(row0, row0 + 128)
+            o_r, l_r, dq_r, dk_p, dv_p, _ = orc.attention_backward_rows(f(q, idx)[sl], f(do, idx)[sl], kn, vn, row0, S, True)
+            upd("o", f(out, idx)[sl], o_r, 2e-2); upd("lse", f(lse, idx)[sl], l_r, 2e-2)
+            upd("dq", f(dq, idx)[sl], dq_r, orc.bf16_grad_tol(dq_r))
+            if row0 == S - 128:
+                upd("dk", f(dk, idx)[sl], dk_p[row0:], orc.bf16_grad_tol(dk_p[row0:]))
+                upd("dv", f(dv, idx)[sl], dv_p[row0:], orc.bf16_grad_tol(dv_p[row0:]))
+        what = f"local slice {idx}: first and last 128 query rows (O, lse, dQ) and last 128 keys (dK, dV) against the oracle"
+    return {"ok": bool(ok), "max_abs_err": errs, "what": what}
+
+
+def gpu_numa_affinity(gpu_index):
+    """Binds this process to the CPU cores next to its GPU (NVML's affinity mask), so that the pinned
+    host buffers it allocates afterwards land in that socket's memory.  Returns the core count or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        n_words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, n_words)
+        cores = [64 * w + b for w, word in enumerate(mask) for b in range(64) if (word >> b) & 1]
+        allowed = sorted(set(cores) & set(os.sched_getaffinity(0)))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return len(allowed)
+    except Exception:
+        pass
+    return None
+
+
+def run_workload(tt, name, steps, warmup, world, rank, dev, peaks, e2e_steps, sample_clocks, sharded=None, verify=True):
+    """Times `steps` forward+backward steps of workload `name`; returns the fields of the JSON line.
+    `sharded` (a ShardedAttention) is the library's multi-GPU path: forward + all-gather of O on the
+    library's side stream, backward overlapping it."""
     import ctypes
     import torch
     import torch.distributed as dist
@@ -192,20 +262,17 @@ def run_workload(tt, name, steps, warmup, world, rank, dev, peaks, e2e_steps, sa
     desc = capi.make_desc(Bl, Hl, S, S, D, capi.TT_BF16, True, None)
     ws = torch.empty(max(int(capi.lib.tt_attn_bwd_workspace_bytes(ctypes.byref(desc))), 256), dtype=torch.uint8, device=dev)
     grads = {}
-    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-    out_full = torch.empty((world * n_local, S, D), dtype=torch.bfloat16, device=dev) if world > 1 else None
+    use_mgpu = sharded is not None and world > 1 and strong
+    out_full = torch.empty((world * n_local, S, D), dtype=torch.bfloat16, device=dev) if use_mgpu else None
 
     def step():
-        tt.attention_forward(q, k, v, causal=True, out=out, lse=lse)
-        if world > 1:
-            ev = torch.cuda.Event()
-            ev.record()
-            with torch.cuda.stream(comm_stream):
-                comm_stream.wait_event(ev)
-                dist.all_gather_into_tensor(out_full, out.view(n_local, S, D))
-        grads["g"] = tt.attention_backward(q, k, v, out, lse, do, causal=True, workspace=ws)
-        if world > 1:
-            torch.cuda.current_stream().wait_stream(comm_stream)
+        if use_mgpu:
+            sharded.forward(q, k, v, B, H, causal=True, out=out, lse=lse, out_full=out_full)
+            grads["g"] = sharded.backward(q, k, v, out, lse, do, B, H, causal=True, workspace=ws)
+            sharded.wait()
+        else:
+            tt.attention_forward(q, k, v, causal=True, out=out, lse=lse)
+            grads["g"] = tt.attention_backward(q, k, v, out, lse, do, causal=True, workspace=ws)
 
     def barrier():
         if world > 1:
@@ -243,25 +310,41 @@ def run_workload(tt, name, steps, warmup, world, rank, dev, peaks, e2e_steps, sa
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
     ms_step = ms_total / steps
+    ms_step_local = ms_step
     f_fwd = fwd_flops(Bl, Hl, S, S, D, True)                       # this rank's forward count per step
     f_step_all = 3.5 * fwd_flops(B, H, S, S, D, True) if strong else 3.5 * f_fwd * world
     value = f_step_all / (ms_step * 1e-3) / 1e12
 
+    # the timed outputs against the oracle (rank 0 reports; every rank's result is its own shard's)
+    verified = None
+    if verify:
+        try:
+            verified = verify_slice(tt, name, (q, k, v, do, out, lse) + tuple(grads["g"][:3]), S, D, n_local)
+            if use_mgpu:
+                torch.cuda.synchronize()
+                b0 = rank * n_local
+                verified["gathered_out_matches_shard"] = bool(torch.equal(out_full[b0:b0 + n_local], out.reshape(n_local, S, D)))
+                verified["ok"] = verified["ok"] and verified["gathered_out_matches_shard"]
+        except Exception as e:  # noqa: BLE001
+            verified = {"ok": False, "error": str(e)}
+
     # per-kernel rooflines from the events recorded inside the timed region
-    traffic_scale = {"cfg3": 1.0, "cfg5": 4.0}.get(name)           # tensor bytes relative to the ncu capture (cfg3)
-    if strong and world > 1:
-        traffic_scale = None
     kernels = {}
     total_ms = max(sum(x[0] for x in prof.values()), 1e-9)
+    if name == "cfg3":
+        traffic = dict(NCU_TRAFFIC_BYTES["cfg3"]); traffic_note = None
+    elif name == "cfg5":
+        traffic = {k_: v_ * n_local for k_, v_ in NCU_TRAFFIC_BYTES["cfg5_per_slice"].items()}
+        traffic_note = "ncu capture of two S=32768 slices, scaled by the slice count of the launch"
+    else:
+        traffic, traffic_note = {}, None
     for kname, (ms, n) in prof.items():
         per = ms / n
         ent = {"launches": n, "ms_per_launch": per, "share": ms / total_ms}
         if kname in ALG_FWD_UNITS:
             ach = ALG_FWD_UNITS[kname] * f_fwd / (per * 1e-3) / 1e12
-            tr = NCU_TRAFFIC_BYTES.get(kname)
             ent.update({"bound": "tensor", "achieved": ach, "peak": peaks["bf16"], "unit": "TFLOP/s",
-                        "frac": ach / peaks["bf16"],
-                        "traffic": tr * traffic_scale if (tr and traffic_scale) else None})
+                        "frac": ach / peaks["bf16"], "traffic": traffic.get(kname)})
         kernels[kname] = ent
     dom = max((n for n in kernels if n in ALG_FWD_UNITS), key=lambda n: kernels[n]["share"], default=None)
     roofline = None
@@ -274,8 +357,8 @@ def run_workload(tt, name, steps, warmup, world, rank, dev, peaks, e2e_steps, sa
             # fraction of the sustained cuBLAS figure is given beside the (conservative) burst one
             roofline["peak_sustained"] = peaks["bf16_sustained"]
             roofline["frac_of_sustained"] = roofline["achieved"] / peaks["bf16_sustained"]
-        if traffic_scale and traffic_scale != 1.0:
-            roofline["traffic_note"] = "ncu capture of the cfg3 launch scaled by tensor bytes (x4)"
+        if traffic_note and roofline["traffic"]:
+            roofline["traffic_note"] = traffic_note
     fwd_tf = kernels.get("attn_fwd_sm100", {}).get("achieved")
 
     # end to end through the host-buffer C ABI (pinned host memory)
@@ -284,32 +367,68 @@ def run_workload(tt, name, steps, warmup, world, rank, dev, peaks, e2e_steps, sa
         hq, hk, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, do))
         ho, hl = torch.empty_like(hq).pin_memory(), torch.empty((Bl, Hl, S), dtype=torch.float32).pin_memory()
         hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(3))
+        nb = hq.numel() * 2
+        nl = hl.numel() * 4
 
         def e2e_step():
             tt.attention_step_host(hq, hk, hv, hdo, causal=True, out=ho, lse=hl, dq=hdq, dk=hdk, dv=hdv)
 
-        e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_step()
+        def timed(fn, n):
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(n):
+                fn()
+            torch.cuda.synchronize()
+            sec = (time.perf_counter() - t0) / n
+            if world > 1:
+                t = torch.tensor([sec], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                sec = float(t.item())
+            return sec
+
+        # copy-only leg: exactly the step's bytes, uploads and downloads at the same time on two streams,
+        # every rank at once -- what the host<->device links give this step with nothing to compute
+        s_up, s_dn = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        d_in = [torch.empty_like(q) for _ in range(4)]
+        d_lse = torch.empty_like(lse)
+
+        def copy_step():
+            with torch.cuda.stream(s_up):
+                for dst, src in zip(d_in, (hq, hk, hv, hdo)):
+                    dst.copy_(src, non_blocking=True)
+            with torch.cuda.stream(s_dn):
+                for dst, src in zip((ho, hdq, hdk, hdv), d_in):
+                    dst.copy_(src, non_blocking=True)
+                hl.copy_(d_lse, non_blocking=True)
+
+        for _ in range(2):
+            copy_step()
         torch.cuda.synchronize()
-        sec = (time.perf_counter() - t0) / e2e_steps
-        if world > 1:
-            t = torch.tensor([sec], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            sec = float(t.item())
-        nb = hq.numel() * 2
-        nl = hl.numel() * 4
+        copy_sec = timed(copy_step, max(3, e2e_steps))
+        del d_in, d_lse
+        for _ in range(2):
+            e2e_step()
+        sec = timed(e2e_step, e2e_steps)
+        bound_ms = max(copy_sec * 1e3, ms_step_local)
         e2e = {"value": f_step_all / sec / 1e12, "unit": "TFLOP/s", "ms_per_step": sec * 1e3,
                "h2d_bytes_per_step": int(4 * nb), "d2h_bytes_per_step": int(4 * nb + nl),
-               "steps": e2e_steps,
+               "steps": e2e_steps, "warmup": 2,
+               "copy_ms": copy_sec * 1e3,
+               "copy_gbs_each_way": {"h2d": 4 * nb / copy_sec / 1e9, "d2h": (4 * nb + nl) / copy_sec / 1e9,
+                                     "all_ranks": world * (8 * nb + nl) / copy_sec / 1e9},
+               "device_ms": ms_step_local,
+               "frac_of_copy_bound": bound_ms / (sec * 1e3),
                "api": "tt_attn_fwd_bwd_host: pinned host buffers; slice chunks pipelined over upload, compute and download streams"}
+        try:
+            ev = verify_slice(tt, name, (hq, hk, hv, hdo, ho, hl, hdq, hdk, hdv), S, D, n_local)
+            e2e["verified"] = ev
+        except Exception as e:  # noqa: BLE001
+            e2e["verified"] = {"ok": False, "error": str(e)}
         del hq, hk, hv, hdo, ho, hl, hdq, hdk, hdv
         tt.capi.lib.tt_pool_trim()
     return dict(value=value, ms_per_step=ms_step, scaling="strong" if strong else "weak", kernels=kernels,
                 roofline=roofline, fwd_tflops=fwd_tf, e2e=e2e, clocks=clocks, gpu_launches=int(launches),
-                n_local=n_local, desc=w["desc"], S=S, D=D,
+                n_local=n_local, desc=w["desc"], S=S, D=D, verified=verified,
                 pct_of_bf16_peak={"fwd": (fwd_tf / peaks["bf16"] * 100) if fwd_tf else None,
                                   "fwd_bwd": value / world / peaks["bf16"] * 100})
 
@@ -339,12 +458,24 @@ def run_decode(tt, dev, peaks, batch):
         ms = a.elapsed_time(b) / 20
         by = 2.0 * dB * dH * dL * dD * 2 + 2.0 * dB * dH * dD * 2
         kms = dprof["attn_decode"][0] / dprof["attn_decode"][1]
+        # the timed output against the oracle: the last slice (for batch 64 its last element has index
+        # 2^31 - 1 and its bytes sit behind 2^32) and one in the middle
+        from oracle import attention_oracle as orc
+        errs = []
+        for b, h in ((dB - 1, dH - 1), (dB // 2, 7)):
+            cpu = lambda t: t[b:b + 1, h:h + 1].float().cpu().numpy()
+            o_r, _ = orc.attention_forward(cpu(dq_), cpu(dk_), cpu(dv_), False)
+            errs.append(orc.max_abs_err(cpu(dout_), o_r))
+        verified = {"ok": bool(max(errs) <= 2e-2), "max_abs_err": max(errs),
+                    "what": f"slices ({dB - 1},{dH - 1}) and ({dB // 2},7) against the oracle"}
         del dk_, dv_
         return {"workload": f"bf16 decode Q [{dB},32,1,128], K/V [{dB},32,8192,128]", "ms": ms, "gbs": by / ms / 1e6,
+                "verified": verified,
                 "grouped": run_decode_grouped(tt, dev, peaks, dB),
                 "roofline": {"bound": "hbm", "achieved": by / kms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
                              "frac": by / kms / 1e6 / peaks["hbm"],
-                             "traffic": NCU_TRAFFIC_BYTES.get("attn_decode") if dB == 64 else None,
+                             "traffic": NCU_TRAFFIC_BYTES["decode"].get("attn_decode") if dB == 64 else None,
+                             "traffic_note": "ncu capture of the batch-8 launch x 8 (the full launch is too large to capture)",
                              "kernel": "attn_decode", "peak_source": f"hbm_gbs of {peaks['source']} MEASURED_PEAKS.json"}}
     except Exception as e:  # noqa: BLE001
         return {"error": str(e)}
@@ -503,7 +634,9 @@ def main():
     ap.add_argument("--no-softmax", action="store_true", help="skip the row-softmax leg at N=1")
     ap.add_argument("--no-fp32", action="store_true", help="skip the fp32 (SIMT kernels) side measurement at N=1")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the S=4096 side measurement at N=1")
-    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-cfg2", action="store_true", help="skip the S=1024, D=64 side measurement at N=1")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-verify", action="store_true", help="skip the oracle re-check of the timed outputs")
     ap.add_argument("--decode-batch", type=int, default=64, help="batch of the decode leg (64 = benchmark configuration 4)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -536,17 +669,36 @@ def main():
             print(json.dumps({"leg": args.only, "result": res}), flush=True)
         return
 
-    side = None
+    # pinned host buffers of the end-to-end leg should sit in the memory next to this rank's GPU
+    numa_cores = gpu_numa_affinity(local_rank) if args.e2e_steps > 0 else None
+    sharded = None
+    if world > 1:
+        sharder = importlib.import_module("pku-aiprogramming_b200.sharder")
+        sharded = sharder.ShardedAttention.from_process_group(device=dev)
+
+    def side_block(wname, n_steps, n_warm):
+        r = run_workload(tt, wname, n_steps, n_warm, 1, 0, dev, peaks, 0, sample_clocks=False, verify=not args.no_verify)
+        return {"workload": r["desc"], "fwd_bwd_tflops": r["value"], "ms_per_step": r["ms_per_step"],
+                "fwd_tflops": r["fwd_tflops"], "pct_of_bf16_peak": r["pct_of_bf16_peak"], "kernels": r["kernels"],
+                "verified": r["verified"]}
+
+    side = side2 = None
+    if rank == 0 and world == 1 and args.workload != "cfg2" and not args.no_cfg2:
+        side2 = side_block("cfg2", 50, 10)
     if rank == 0 and world == 1 and args.workload != "cfg3" and not args.no_cfg3:
         # the S=4096/D=128 shape the forward target (>= 60 % of bf16 peak) is stated on.  It runs BEFORE
         # the main workload: that one drives the GPU into its power cap for seconds, and a 50 ms
         # measurement taken right behind it inherits the lowered clock (its peak, the burst figure of
         # MEASURED_PEAKS.json, was taken on an idle GPU)
-        r3 = run_workload(tt, "cfg3", 20, 5, 1, 0, dev, peaks, 0, sample_clocks=False)
-        side = {"workload": r3["desc"], "fwd_bwd_tflops": r3["value"], "ms_per_step": r3["ms_per_step"],
-                "fwd_tflops": r3["fwd_tflops"], "pct_of_bf16_peak": r3["pct_of_bf16_peak"], "kernels": r3["kernels"]}
+        side = side_block("cfg3", 20, 5)
     main_res = run_workload(tt, args.workload, args.steps, args.warmup, world, rank, dev, peaks, args.e2e_steps,
-                            sample_clocks=(rank == 0))
+                            sample_clocks=(rank == 0), sharded=sharded, verify=not args.no_verify)
+    if world > 1:
+        import torch
+        okt = torch.tensor([1 if (main_res["verified"] or {}).get("ok", True) else 0], device=dev)
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        if main_res["verified"] is not None:
+            main_res["verified"]["ok_on_every_rank"] = bool(okt.item())
     decode = run_decode(tt, dev, peaks, args.decode_batch) if (rank == 0 and not args.no_decode) else None
 
     fc = run_fc(tt, dev, peaks, args.fc_rows) if (rank == 0 and world == 1 and not args.no_fc) else None
@@ -575,16 +727,21 @@ def main():
             "config": {"workload": main_res["desc"], "causal": True,
                        "flop_count": "2/MAC, fwd 2 GEMMs, bwd 5 GEMMs, causal = half",
                        "l2": "inputs per step (>= 0.5 GB) exceed the 126 MB L2",
-                       "collective": "all-gather of O over NCCL, overlapped with backward" if world > 1 else "none",
+                       "collective": ("tt_mgpu_attn_fwd: ncclAllGather of O issued by the library on its own side "
+                                      "stream, overlapped with the backward (tt_mgpu_attn_bwd), joined by tt_mgpu_wait")
+                                     if (world > 1 and main_res["scaling"] == "strong") else "none",
                        "parallelism": f"{world} x contiguous (batch,head) shards"},
             "fwd_tflops": main_res["fwd_tflops"], "pct_of_bf16_peak": main_res["pct_of_bf16_peak"],
-            "roofline": main_res["roofline"], "kernels": main_res["kernels"], "cfg3": side, "decode": decode,
+            "roofline": main_res["roofline"], "kernels": main_res["kernels"], "verified": main_res["verified"],
+            "cfg3": side, "cfg2": side2, "decode": decode,
             "softmax_rows": softmax, "fc": fc, "fp32": fp32,
             "cpu_baseline": cpu, "e2e": main_res["e2e"], "clocks": main_res["clocks"],
-            "gpu_launches": main_res["gpu_launches"],
+            "gpu_launches": main_res["gpu_launches"], "host_numa_cores": numa_cores,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()                      # every rank is between steps, nothing of ours is in flight
+        sharded.close()
         dist.barrier()
         dist.destroy_process_group()
 

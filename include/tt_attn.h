@@ -43,7 +43,8 @@ typedef enum tt_status {
     TT_ERR_WORKSPACE = 5,   /* workspace missing or smaller than *_workspace_bytes() */
     TT_ERR_CUDA = 6,        /* a CUDA runtime/driver call failed */
     TT_ERR_TIMEOUT = 7,     /* a bounded device-side wait expired (reported after a sync) */
-    TT_ERR_UNSUPPORTED = 8
+    TT_ERR_UNSUPPORTED = 8,
+    TT_ERR_NCCL = 9         /* the NCCL library is missing, or one of its calls failed */
 } tt_status;
 
 typedef enum tt_dtype { TT_F32 = 0, TT_BF16 = 1 } tt_dtype;
@@ -85,6 +86,14 @@ int tt_attn_bwd(const tt_attn_desc* desc, const void* q, const void* k, const vo
                 const void* out, const float* lse, const void* dout,
                 void* dq, void* dk, void* dv,
                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* The tensor-core backward (bf16, D = 64 or 128) exists twice.  Default (on = 0): one pass over the
+ * (key tile, query tile) pairs that produces dk, dv and dq together, dq through fp32 additions into the
+ * workspace; the additions arrive in no fixed order, so dq repeats to fp32 rounding (a few 1e-7 relative)
+ * rather than bit for bit.  on = 1: two passes (dk/dv, then dq with the scores recomputed), about a third
+ * slower, every result bit-reproducible.  Process-wide; no counterpart in the reference, whose NumPy
+ * reverse sweep (optimizer/autodiff.py:33-61) is deterministic and single-threaded. */
+int tt_attn_bwd_set_deterministic(int on);
 
 /* ---- single-query decode (S == 1) ----------------------------------------------------
  * Split-KV kernel for the memory-bound case: each (slice, key range) unit streams its
@@ -208,6 +217,47 @@ int tt_pool_stats(size_t* bytes_in_use, size_t* bytes_cached, uint64_t* n_driver
  * (The reference has no multi-GPU path; Task2/mnist.py:53-54 is torch DataParallel.) */
 int tt_shard_range(int64_t n_slices, int32_t world, int32_t rank, int64_t* begin, int64_t* count);
 
+/* ---- several GPUs: one process (or thread) per GPU, slices sharded, outputs all-gathered -------
+ * The B*H slices are independent in forward and backward, so rank r of `world` owns the contiguous
+ * range tt_shard_range(B*H, world, r) of them, keeps q, k, v, out, lse and the gradients of that
+ * range in its own memory, and runs the single-GPU kernels on it; nothing crosses between GPUs on the
+ * data path.  The one exchange is the all-gather that gives every rank the full `out` (and, if asked
+ * for, full gradients): because [B,H,S,D] is contiguous in the slice index, each rank's shard is one
+ * contiguous block of the full tensor and a single ncclAllGather lands it in place, no repacking.
+ * The communicator owns one ncclComm_t and one side stream on its device: gathers run on the side
+ * stream, ordered behind the kernels that produce their data, so the gather of `out` overlaps the
+ * backward.  NCCL is bound at run time (dlopen of libnccl.so.2, or the library TT_NCCL_LIB names);
+ * no kernel of this library reads another GPU's memory.
+ * No counterpart in the reference, whose only multi-GPU construct is torch's nn.DataParallel around
+ * a PyTorch model (Task2/mnist.py:53-54).
+ *
+ *   tt_mgpu_unique_id   rank 0 calls it and hands the TT_MGPU_ID_BYTES bytes to every rank by its own
+ *                       means (a file, a socket, MPI, torch.distributed).
+ *   tt_mgpu_init        collective over the ranks; binds the communicator to the CURRENT device.
+ *   tt_mgpu_attn_fwd    desc describes the WHOLE problem (all B*H slices); the tensor arguments are this
+ *                       rank's shard ([count,S,D] / [count/group,L,D] / [count,S]).  out_full, if not
+ *                       null, is [B*H,S,D] on this device and receives every rank's out.
+ *                       B*H must divide evenly by world, and a shard must hold whole groups of query
+ *                       heads, else TT_ERR_UNSUPPORTED.  Kernels run on `stream`; returns at once.
+ *   tt_mgpu_attn_bwd    same for the backward; dq_full / dk_full / dv_full (each may be null) receive
+ *                       the all-gathered gradients, otherwise gradients stay with their owners.
+ *                       Workspace: tt_mgpu_bwd_workspace_bytes(comm, desc), 256-byte aligned.
+ *   tt_mgpu_wait        makes `stream` wait (on the device) for every gather issued so far.
+ *   tt_mgpu_destroy     collective; frees the communicator, the side stream and the events. */
+#define TT_MGPU_ID_BYTES 128
+typedef struct tt_mgpu* tt_mgpu_t;
+int tt_mgpu_unique_id(void* id_bytes);
+int tt_mgpu_init(tt_mgpu_t* comm, int32_t world, int32_t rank, const void* id_bytes);
+int tt_mgpu_destroy(tt_mgpu_t comm);
+int tt_mgpu_shard(tt_mgpu_t comm, const tt_attn_desc* desc, int64_t* first_slice, int64_t* n_slices);
+int tt_mgpu_attn_fwd(tt_mgpu_t comm, const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                     void* out, float* lse, void* out_full, void* stream);
+size_t tt_mgpu_bwd_workspace_bytes(tt_mgpu_t comm, const tt_attn_desc* desc);
+int tt_mgpu_attn_bwd(tt_mgpu_t comm, const tt_attn_desc* desc, const void* q, const void* k, const void* v,
+                     const void* out, const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                     void* dq_full, void* dk_full, void* dv_full, void* workspace, size_t workspace_bytes, void* stream);
+int tt_mgpu_wait(tt_mgpu_t comm, void* stream);
+
 /* ---- diagnostics ---------------------------------------------------------------------*/
 const char* tt_last_error(void);
 /* Number of kernels this library has launched in this process (for launch accounting). */
@@ -234,14 +284,6 @@ int tt_profile_read(int kernel_id, double* total_ms, uint64_t* launches);
  * next tt_check_device_status() reports TT_ERR_TIMEOUT (barrier id 99, iteration 7) and clears
  * the status word: a way to test the failure-reporting path without faulting or hanging a GPU. */
 int tt_debug_wait_timeout(int64_t budget_cycles, void* stream);
-
-/* Debug aid for tuning the tensor-core forward: while `device_buf` (3*64*8 int64, device
- * memory) is non-null, CTA number `block` of every forward launch records clock64() at its
- * hand-off points (softmax warpgroups: wait for S, S loaded, max known, P half/whole written;
- * MMA issuer: waits and issues).  Pass null to switch it off. */
-int tt_debug_fwd_trace(void* device_buf, int32_t block);
-/* Same for the tensor-core backward; pass = 1 traces the dK/dV launch, 2 the dQ launch. */
-int tt_debug_bwd_trace(void* device_buf, int32_t block, int32_t pass);
 
 /* Building-block self test of the tensor-core plumbing (TMA load -> tcgen05.mma from
  * shared memory -> tcgen05.ld, tcgen05.st -> tcgen05.mma with A in tensor memory and an

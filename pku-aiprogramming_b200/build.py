@@ -19,7 +19,7 @@ OBJ = os.path.join(PKG, "build")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libtt_attn.so")
 
-KERNEL_SOURCES = ["tt_api.cu", "attn_simt.cu", "attn_decode.cu", "attn_fwd_sm100.cu", "attn_bwd_sm100.cu",
+KERNEL_SOURCES = ["tt_api.cu", "tt_mgpu.cu", "attn_simt.cu", "attn_decode.cu", "attn_fwd_sm100.cu", "attn_bwd_sm100.cu", "attn_bwd_fused_sm100.cu",
                   "softmax_rows.cu", "fc_gemm_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Wno-deprecated-gpu-targets",
@@ -71,7 +71,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 2)) as ex:
             list(ex.map(lambda c: _run(c, verbose), jobs))
     if rebuilt or not os.path.exists(LIB):
-        _run([_nvcc(), "-shared", "-Wno-deprecated-gpu-targets", "-o", LIB, *objs, "-cudart", "static"], verbose)
+        _run([_nvcc(), "-shared", "-Wno-deprecated-gpu-targets", "-o", LIB, *objs, "-cudart", "static", "-ldl"], verbose)
     return LIB
 
 

@@ -15,12 +15,12 @@ LIB_PATH = os.path.join(_PKG, "lib", "libtt_attn.so")
 
 TT_OK = 0
 TT_ERR_NULL, TT_ERR_BAD_SHAPE, TT_ERR_BAD_DTYPE, TT_ERR_BAD_DEVICE = 1, 2, 3, 4
-TT_ERR_WORKSPACE, TT_ERR_CUDA, TT_ERR_TIMEOUT, TT_ERR_UNSUPPORTED = 5, 6, 7, 8
+TT_ERR_WORKSPACE, TT_ERR_CUDA, TT_ERR_TIMEOUT, TT_ERR_UNSUPPORTED, TT_ERR_NCCL = 5, 6, 7, 8, 9
 TT_F32, TT_BF16 = 0, 1
 
 STATUS_NAMES = {
     0: "TT_OK", 1: "TT_ERR_NULL", 2: "TT_ERR_BAD_SHAPE", 3: "TT_ERR_BAD_DTYPE", 4: "TT_ERR_BAD_DEVICE",
-    5: "TT_ERR_WORKSPACE", 6: "TT_ERR_CUDA", 7: "TT_ERR_TIMEOUT", 8: "TT_ERR_UNSUPPORTED",
+    5: "TT_ERR_WORKSPACE", 6: "TT_ERR_CUDA", 7: "TT_ERR_TIMEOUT", 8: "TT_ERR_UNSUPPORTED", 9: "TT_ERR_NCCL",
 }
 
 # every symbol include/tt_attn.h declares: name -> (restype, argtypes)
@@ -34,6 +34,7 @@ _DP = POINTER(Desc)
 SIGNATURES = {
     "tt_attn_fwd": (c_int, [_DP, _P, _P, _P, _P, _P, _P]),
     "tt_attn_bwd_workspace_bytes": (c_size_t, [_DP]),
+    "tt_attn_bwd_set_deterministic": (c_int, [c_int]),
     "tt_attn_bwd": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
     "tt_attn_fwd_padded": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P]),
     "tt_attn_bwd_padded": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
@@ -56,6 +57,14 @@ SIGNATURES = {
     "tt_pool_trim": (c_int, []),
     "tt_pool_stats": (c_int, [POINTER(c_size_t), POINTER(c_size_t), POINTER(c_uint64)]),
     "tt_shard_range": (c_int, [c_int64, c_int32, c_int32, POINTER(c_int64), POINTER(c_int64)]),
+    "tt_mgpu_unique_id": (c_int, [_P]),
+    "tt_mgpu_init": (c_int, [POINTER(c_void_p), c_int32, c_int32, _P]),
+    "tt_mgpu_destroy": (c_int, [_P]),
+    "tt_mgpu_shard": (c_int, [_P, _DP, POINTER(c_int64), POINTER(c_int64)]),
+    "tt_mgpu_attn_fwd": (c_int, [_P, _DP, _P, _P, _P, _P, _P, _P, _P]),
+    "tt_mgpu_bwd_workspace_bytes": (c_size_t, [_P, _DP]),
+    "tt_mgpu_attn_bwd": (c_int, [_P, _DP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
+    "tt_mgpu_wait": (c_int, [_P, _P]),
     "tt_last_error": (c_char_p, []),
     "tt_kernel_launch_count": (c_uint64, []),
     "tt_attn_fwd_path": (c_char_p, [_DP]),
@@ -67,9 +76,15 @@ SIGNATURES = {
     "tt_profile_kernel_name": (c_char_p, [c_int]),
     "tt_profile_read": (c_int, [c_int, POINTER(ctypes.c_double), POINTER(c_uint64)]),
     "tt_debug_wait_timeout": (c_int, [c_int64, _P]),
-    "tt_debug_fwd_trace": (c_int, [_P, c_int32]),
-    "tt_debug_bwd_trace": (c_int, [_P, c_int32, c_int32]),
     "tt_debug_umma_probe": (c_int, [_P, _P, _P, c_int32, _P, _P, _P]),
+}
+
+
+# tuning aids declared in csrc/tt_debug.h (not part of the boundary)
+DEBUG_SIGNATURES = {
+    "tt_debug_fwd_trace": (c_int, [_P, c_int32, c_int32]),
+    "tt_debug_bwd_trace": (c_int, [_P, c_int32, c_int32]),
+    "tt_mgpu_set_collectives": (c_int, [_P]),
 }
 
 
@@ -89,7 +104,7 @@ def _load() -> ctypes.CDLL:
             f"{LIB_PATH} not found. Build it with `python {os.path.join(_PKG, 'build.py')}` "
             "(needs nvcc; there is no non-CUDA implementation of this package).")
     lib = ctypes.CDLL(LIB_PATH)
-    for name, (res, args) in SIGNATURES.items():
+    for name, (res, args) in list(SIGNATURES.items()) + list(DEBUG_SIGNATURES.items()):
         fn = getattr(lib, name)   # AttributeError here means header and library disagree
         fn.restype = res
         fn.argtypes = args

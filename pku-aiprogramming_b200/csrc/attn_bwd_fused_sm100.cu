@@ -1,0 +1,675 @@
+// Single-pass attention backward for B200 (sm_100a): bf16 tensors, fp32 accumulation, head dim 64 or
+// 128.  One launch computes dK, dV AND dQ: nothing is recomputed, five GEMMs per (key tile, query tile)
+// pair -- the five the backward is counted as -- against the seven of the two-pass kernel
+// (attn_bwd_sm100.cu), which stays as the bit-reproducible alternative.
+//
+//   P^T = exp(scale*K Q^T - lse)   dP^T = V dO^T   dS^T = P^T * (dP^T - delta)
+//   dV += P^T dO      dK += dS^T Q      dQ_partial = dS K  -> added to an fp32 accumulator in global memory
+//
+// A CTA owns 128 keys (K, V tiles resident in shared memory) and streams the query tiles (Q_i, dO_i)
+// that can see them; scores are computed transposed (keys on the TMEM lanes).  Per streamed tile:
+//   G1: S^T  = K Q^T        (A, B shared memory, K-major)                       -> X
+//   G2: dP^T = V dO^T       (A, B shared memory, K-major)                       -> Y
+//   G3: dV  += P^T dO       (A = bf16 P^T in tensor memory over S^T, B = dO MN-major)
+//   G4: dK  += dS^T Q       (A = bf16 dS^T in SHARED memory, K-major;  B = Q MN-major)
+//   G5: dQ_t = dS K         (A = the same dS^T bytes read MN-major;    B = K MN-major)   -> Y
+// Tensor memory (512 columns): X [0,128) S^T then P^T | Y [128,256) dP^T then dQ_t | dV [256,256+D) |
+// dK [256+D,256+2D).  dS^T cannot stay in tensor memory as in the two-pass kernel: G5 needs it with the
+// queries on the M side, and a tensor-memory operand is always M = lanes = keys here.  So the compute
+// threads write it to a 32 KB shared-memory tile in the 128-byte-swizzled layout both descriptors read.
+// The MMA warp issues, per tile t:   G3(t)  G1(t+1)  G5(t)  G4(t)  G2(t+1)
+// so that the tensor pipe always has work while the compute warpgroups turn S^T into P^T (phase A) and
+// dP^T into dS^T (phase B).  dQ_t leaves through the compute threads in the middle of the next tile's
+// phase A: tensor memory -> registers -> red.global.add.v4.f32 into a [D/4][128 rows][4] block per
+// (query slice, query tile), a layout in which the 32 lanes of a warp add to 512 contiguous bytes.  A
+// small second kernel converts the accumulator to bf16 dQ (times scale).  The additions arrive in no
+// fixed order, so dQ is reproducible to fp32 rounding only; dK and dV are bit-reproducible.
+//
+// Roles: warps 0-7 = two compute warpgroups (thread <-> resident key row; warpgroup w owns query
+// columns [64w, 64w+64) of X and Y, and columns [w*D/2, +D/2) of dQ_t, dV, dK), warp 8 = MMA issuer,
+// warp 9 = TMA loader and work-item scheduler.
+// Shared memory at D = 128: K, V, two Q slots, two dO slots, the dS^T tile (7 x 32 KB) + 3 KB of barriers
+// and per-query statistics = exactly 227 KB.
+#include "attn_bwd_common.cuh"
+#include <stdlib.h>
+#include <string.h>
+#include <algorithm>
+#include <atomic>
+#include <type_traits>
+
+namespace ttk {
+using namespace sm100;
+
+#ifndef TT_BWD1_NQ
+#define TT_BWD1_NQ 2
+#endif
+
+template <int D>
+struct Bwd1Cfg : BwdRegs {
+    static constexpr int kSub = D / 64;
+    static constexpr int kSubBytes = 128 * 128;
+    static constexpr int kTileBytes = kSub * kSubBytes;
+    static constexpr int kDsBytes = 2 * kSubBytes;               // 128 keys x 128 queries, bf16
+    // Q(t) is read by G1(t) early and by G4(t) late, Q(t+1) in between: two slots at least; dO(t) by
+    // G2(t) and G3(t).  At D = 128 four streamed slots fit beside K, V and dS^T.
+    static constexpr int kNQ = (D == 128) ? TT_BWD1_NQ : 4;
+    static constexpr int kNdO = (D == 128) ? 4 - TT_BWD1_NQ : 3;
+    static_assert(kNQ >= 2 && kNQ <= 4 && kNdO >= 1 && kNdO <= 4, "ring lengths the barrier arrays are sized for");
+    static constexpr int kTmemCols = 512;
+    static constexpr int kAuxBytes = 3072;                       // 1 KB barriers + 2 KB lse/delta staging
+    static constexpr int kSmemBytes = (2 + kNQ + kNdO) * kTileBytes + kDsBytes + kAuxBytes;
+    static_assert(kSmemBytes <= 227 * 1024, "exceeds the shared memory of one CTA");
+};
+
+enum Bwd1BarId { B1_RES = 0, B1_QFULL = 10, B1_QEMPTY = 14, B1_DOFULL = 18, B1_DOEMPTY = 22, B1_SFULL = 30, B1_DPFULL = 31,
+                 B1_PFULL = 32, B1_DSFULL = 33, B1_FINAL = 34, B1_STAT = 35, B1_DSFREE = 36, B1_DQFULL = 37, B1_DQFREE = 38,
+                 B1_ACCFREE = 39 };
+
+__device__ __forceinline__ void red_add_v4(float* gptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(gptr), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+                 : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(Bwd1Cfg<D>::kThreads, 1)
+attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                            const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                            const BwdParams p) {
+    using Cfg = Bwd1Cfg<D>;
+    constexpr int kNQ = Cfg::kNQ, kNdO = Cfg::kNdO;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = smem_raw;
+    if ((smem_u32(smem_raw) & 1023u) != 0u) {   // the 128-byte swizzle of TMA and UMMA needs 1024-byte aligned tiles
+        if (threadIdx.x == 0 && atomicCAS(p.status, 0u, (8u << 16) | (blockIdx.x & 0xffffu)) == 0u) {
+            p.status[1] = 0xA116u;   // "alignment"
+            p.status[2] = smem_u32(smem_raw);
+            p.status[3] = 0u;
+        }
+        return;                      // every thread of every CTA takes this exit together: nothing was started
+    }
+    unsigned char* sK = smem;                                   // resident K tile
+    unsigned char* sV = smem + Cfg::kTileBytes;                 // resident V tile
+    unsigned char* sQ = smem + 2 * Cfg::kTileBytes;             // kNQ slots
+    unsigned char* sdO = sQ + kNQ * Cfg::kTileBytes;            // kNdO slots
+    unsigned char* sDS = sdO + kNdO * Cfg::kTileBytes;          // dS^T: 2 sub-blocks of [128 keys x 64 queries]
+    unsigned char* aux = sDS + Cfg::kDsBytes;
+    uint64_t* bar_res_full = reinterpret_cast<uint64_t*>(aux);   // TMA -> MMA (K, V of the item)
+    uint64_t* bar_res_empty = bar_res_full + 1;                  // MMA (last reads of K, V) -> TMA
+    uint64_t* bar_q_full = bar_res_empty + 1;                    // [4]
+    uint64_t* bar_q_empty = bar_q_full + 4;                      // [4]
+    uint64_t* bar_do_full = bar_q_empty + 4;                     // [4]
+    uint64_t* bar_do_empty = bar_do_full + 4;                    // [4]
+    uint64_t* bar_s_full = bar_do_empty + 4;                     // MMA -> compute: S^T(t) is in X
+    uint64_t* bar_p_full = bar_s_full + 1;                       // compute -> MMA: P^T(t) is in X
+    uint64_t* bar_dp_full = bar_p_full + 1;                      // MMA -> compute: dP^T(t) is in Y
+    uint64_t* bar_ds_full = bar_dp_full + 1;                     // compute -> MMA: dS^T(t) is in shared memory, Y is read
+    uint64_t* bar_ds_free = bar_ds_full + 1;                     // MMA -> compute: G4(t), G5(t) are done with the dS^T tile
+    uint64_t* bar_dq_full = bar_ds_free + 1;                     // MMA -> compute: dQ_t is in Y
+    uint64_t* bar_dq_free = bar_dq_full + 1;                     // compute -> MMA: dQ_t is in registers, Y is free
+    uint64_t* bar_final = bar_dq_free + 1;                       // MMA -> compute: dV, dK of the item are complete
+    uint64_t* bar_acc_free = bar_final + 1;                      // compute (accumulators read out) -> MMA
+    uint64_t* bar_sched_full = bar_acc_free + 1;                 // [2]
+    uint64_t* bar_sched_empty = bar_sched_full + 2;              // [2]
+    uint64_t* bar_stat = bar_sched_empty + 2;                    // [2] per warpgroup: a tile's statistics are staged
+    int* sched_item = reinterpret_cast<int*>(bar_stat + 2);      // [2]
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sched_item + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+    float* s_stat = reinterpret_cast<float*>(aux + 1024);       // [2 buffers][2: -lse2, -delta][128]
+
+    const int warp = uniform_warp_idx();
+    const int lane = threadIdx.x & 31;
+    const int off = p.L - p.S;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(bar_res_full, 1);
+        mbar_init(bar_res_empty, 1);
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(&bar_q_full[s], 1);
+            mbar_init(&bar_q_empty[s], 1);
+            mbar_init(&bar_do_full[s], 1);
+            mbar_init(&bar_do_empty[s], 1);
+        }
+        mbar_init(bar_s_full, 1);
+        mbar_init(bar_p_full, 256);
+        mbar_init(bar_dp_full, 1);
+        mbar_init(bar_ds_full, 256);
+        mbar_init(bar_ds_free, 1);
+        mbar_init(bar_dq_full, 1);
+        mbar_init(bar_dq_free, 256);
+        mbar_init(bar_final, 1);
+        mbar_init(bar_acc_free, 256);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_stat[i], 128);
+            mbar_init(&bar_sched_full[i], 1);
+            mbar_init(&bar_sched_empty[i], 257);   // MMA warp (1) + 256 compute threads
+        }
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 8) {
+        tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 9 && lane == 0) {
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmdO);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+    WaitCtx wctx{p.status, abort_flag, warp};
+    constexpr uint32_t kColX = 0, kColY = 128, kColDV = 256, kColDK = 256 + D;
+
+    auto next_item = [&](int k) -> int {
+        const int slot = k & 1;
+        // a wait that gave up (this CTA has aborted) ends the sequence: the slot may hold anything
+        if (!mbar_wait(&bar_sched_full[slot], (k >> 1) & 1, wctx, 80 + slot, k)) return -1;
+        return sched_item[slot];
+    };
+
+    if (warp < 8) {
+        // ============================================================ compute warpgroups
+        setmaxnreg_inc<Cfg::kRegsCompute>();
+        const int wg = warp >> 2;
+        const int wq = warp & 3;
+        const int r_in = wq * 32 + lane;                       // this thread's TMEM lane: key row, or query row of dQ_t
+        const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
+        const uint32_t tX = tmem_base + lane_off + kColX + wg * 64;
+        const uint32_t tY = tmem_base + lane_off + kColY + wg * 64;
+        const uint32_t tYq = tmem_base + lane_off + kColY + wg * (D / 2);   // this warpgroup's half of dQ_t
+        const int ctid = threadIdx.x;                          // 0..255 among compute threads
+        const uint64_t c2 = pack_f32x2(p.scale_log2, p.scale_log2);
+        unsigned char* ds_row = sDS + wg * Cfg::kSubBytes + r_in * 128;    // this thread's 128 bytes of dS^T
+        uint32_t git = 0;      // streamed tiles processed so far, over all items (barrier phases)
+
+        // dQ_t of streamed tile (t, qs), global tile number g: tensor memory -> registers -> fp32 adds
+        auto dq_out = [&](int t, int qs, uint32_t g, int it) {
+            mbar_wait(bar_dq_full, g & 1, wctx, B1_DQFULL, it);
+            __syncwarp();
+            tc_fence_after();
+            float* base = p.dq_acc + ((size_t)((long long)qs * p.n_qt + t) * (D / 4) + (size_t)wg * (D / 8)) * 512 + r_in * 4;
+#pragma unroll
+            for (int cc = 0; cc < D / 64; ++cc) {
+                uint32_t r[32];
+                tmem_ld32(tYq + cc * 32, r);
+                tmem_wait_ld();
+                if (cc == D / 64 - 1) {          // everything is in registers: Y may take the next dP^T
+                    tc_fence_before();
+                    mbar_arrive(bar_dq_free);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) red_add_v4(base + (size_t)(cc * 8 + j) * 512, r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            }
+        };
+
+        for (int k = 0;; ++k) {
+            const int item = next_item(k);
+            __syncwarp();
+            mbar_arrive(&bar_sched_empty[k & 1]);
+            if (item < 0) break;
+            const BwdItem w = bwd_decode_item<true>(item, p);
+            const int bh = w.bh;
+            const int rrow = w.r0 + r_in;                      // this thread's key
+            const bool row_dead = rrow >= w.Lv;                // padding, or past the end of the tensor: P = dS = 0
+            // per-query statistics: each warpgroup stages -lse2 and -delta of ITS 64 streamed queries one
+            // tile ahead, split-phase through an mbarrier of its own (see the two-pass kernel)
+            const int stat_j = ctid & 127;
+            const int stat_q = wg * 64 + (stat_j & 63);
+            const int stat_slot = (stat_j >> 6) * 128 + stat_q;
+            const float* stat_src = (stat_j < 64 ? p.lse2 : p.delta);
+            const float stat_oob = (stat_j < 64) ? -INFINITY : 0.f;
+            float stat_raw = 0.f;
+            bool stat_ok = false;
+            auto stat_issue = [&](int u) {
+                int tt, qs;
+                bwd_stream_tile<true>(w, u, p.group, tt, qs);
+                const int qrow = tt * 128 + stat_q;
+                stat_ok = qrow < p.S;
+                if (stat_ok) stat_raw = stat_src[(long long)qs * p.S + qrow];
+            };
+            auto stat_publish = [&](uint32_t g) {
+                s_stat[(g & 1) * 256 + stat_slot] = stat_ok ? -stat_raw : stat_oob;
+                mbar_arrive(&bar_stat[wg]);
+            };
+            if (w.n_it > 0) {
+                stat_issue(0);
+                stat_publish(git);
+                if (w.n_it > 1) stat_issue(1);
+            }
+            int prev_t = 0, prev_qs = 0;
+            for (int u = 0; u < w.n_it; ++u, ++git) {
+                int t, qs;
+                bwd_stream_tile<true>(w, u, p.group, t, qs);
+                const int c0 = t * 128;                            // first streamed query of this tile
+                const float* st_nlse = s_stat + (git & 1) * 256;
+                const float* st_ndelta = st_nlse + 128;
+                mbar_wait(&bar_stat[wg], git & 1, wctx, B1_STAT, u);
+                // visible queries of this thread's key inside the tile: [vis_lo, 128)
+                int vis_lo = p.causal ? max(0, rrow - off - c0) : 0;
+                if (row_dead) vis_lo = 128;
+                const bool need_mask = vis_lo > 0;
+                uint64_t stat_reg[2][16];
+                auto load_stats = [&](const float* src) {
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+                        for (int e4 = 0; e4 < 8; ++e4) {
+                            const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(src + wg * 64 + cc * 32 + e4 * 4);
+                            stat_reg[cc][2 * e4] = v.x;
+                            stat_reg[cc][2 * e4 + 1] = v.y;
+                        }
+                };
+                uint64_t pf2[32];     // this thread's 64 probabilities, fp32 pairs (kept for phase B)
+                // ---------------- phase A: P^T = exp2(S^T*c - lse2) -> bf16 over the S^T columns just read
+                auto phase_a_body = [&](auto masked_c, int cc, const uint32_t (&sr)[32]) {
+                    constexpr bool kMasked = decltype(masked_c)::value;
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const int col = wg * 64 + cc * 32 + e;
+                        const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c2, stat_reg[cc][e >> 1]);
+                        float a0, a1;
+                        unpack_f32x2(x, a0, a1);
+                        float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
+                        if (kMasked) {
+                            p0 = (col >= vis_lo) ? p0 : 0.f;
+                            p1 = (col + 1 >= vis_lo) ? p1 : 0.f;
+                        }
+                        pf2[cc * 16 + (e >> 1)] = pack_f32x2(p0, p1);
+                        pk[e >> 1] = pack_bf16x2(p0, p1);
+                    }
+                    tmem_st16(tX + cc * 16, pk);
+                };
+                auto phase_a = [&](int cc) {
+                    uint32_t sr[32];
+                    tmem_ld32(tX + cc * 32, sr);
+                    tmem_wait_ld();
+                    if (need_mask) phase_a_body(std::true_type{}, cc, sr);
+                    else phase_a_body(std::false_type{}, cc, sr);
+                };
+                load_stats(st_nlse);
+                mbar_wait(bar_s_full, git & 1, wctx, B1_SFULL, u);
+                __syncwarp();
+                tc_fence_after();
+                phase_a(0);
+                // the previous tile's dQ_t: its GEMM ran while this tile's first exponentials did
+                if (u > 0) dq_out(prev_t, prev_qs, git - 1, u);
+                phase_a(1);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar_p_full);
+                load_stats(st_ndelta);
+                if (u + 1 < w.n_it) {
+                    stat_publish(git + 1);                     // its load was issued a tile ago
+                    if (u + 2 < w.n_it) stat_issue(u + 2);
+                }
+                // ---------------- phase B: dS^T = P^T * (dP^T - delta) -> bf16 -> shared memory
+                mbar_wait(bar_dp_full, git & 1, wctx, B1_DPFULL, u);
+                __syncwarp();
+                tc_fence_after();
+                if (git > 0) mbar_wait(bar_ds_free, (git - 1) & 1, wctx, B1_DSFREE, u);   // complete long ago
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t dr[32];
+                    tmem_ld32(tY + cc * 32, dr);
+                    tmem_wait_ld();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const uint64_t tdiff = add_f32x2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), stat_reg[cc][e >> 1]);
+                        const uint64_t ds = mul_f32x2(pf2[cc * 16 + (e >> 1)], tdiff);
+                        float x0, x1;
+                        unpack_f32x2(ds, x0, x1);
+                        pk[e >> 1] = pack_bf16x2(x0, x1);
+                    }
+                    // 16-byte chunk j of row r sits at chunk j ^ (r & 7) of the row (128-byte swizzle)
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj)
+                        *reinterpret_cast<uint4*>(ds_row + (((cc * 4 + jj) ^ (r_in & 7)) << 4)) =
+                            make_uint4(pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
+                }
+                fence_proxy_async_smem();          // generic-proxy stores -> visible to the MMA's async-proxy reads
+                tc_fence_before();
+                mbar_arrive(bar_ds_full);
+                prev_t = t;
+                prev_qs = qs;
+            }
+            if (w.n_it > 0) dq_out(prev_t, prev_qs, git - 1, w.n_it);
+            // ---------------- epilogue: dV, dK out of tensor memory (then the MMA warp may start the next
+            // item in them) -> bf16 -> global; warpgroup w owns columns [w*D/2, +D/2)
+            mbar_wait(bar_final, k & 1, wctx, B1_FINAL, k);
+            __syncwarp();
+            tc_fence_after();
+            constexpr int kHalf = D / 2;
+            uint32_t acc[2][kHalf / 32][32];
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+                const uint32_t tA = tmem_base + lane_off + (a == 0 ? kColDV : kColDK) + wg * kHalf;
+#pragma unroll
+                for (int cc = 0; cc < kHalf / 32; ++cc) tmem_ld32(tA + cc * 32, acc[a][cc]);
+            }
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar_acc_free);
+            if (rrow < p.L) {
+                if (row_dead) {   // gradients of padded keys are zero
+#pragma unroll
+                    for (int a = 0; a < 2; ++a)
+#pragma unroll
+                        for (int cc = 0; cc < kHalf / 32; ++cc)
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) acc[a][cc][e] = 0u;
+                }
+                const long long o = ((long long)bh * p.L + rrow) * D + wg * kHalf;
+                bwd_store_row<kHalf / 32>(p.out0 + o, acc[0], 1.0f, p.wide_stores);
+                bwd_store_row<kHalf / 32>(p.out1 + o, acc[1], p.scale, p.wide_stores);
+            }
+            __syncwarp();
+        }
+    } else {
+        setmaxnreg_dec<Cfg::kRegsOther>();
+        if (warp == 9) {
+            // ============================================================ TMA loader + scheduler (whole
+            // warp runs the control flow, one elected lane issues)
+            auto load_tile = [&](unsigned char* dst, const CUtensorMap* tm, uint64_t* bar, int row_start, int bh) {
+#pragma unroll
+                for (int sb = 0; sb < Cfg::kSub; ++sb) tma_load_3d(dst + sb * Cfg::kSubBytes, tm, bar, sb * 64, row_start, bh);
+            };
+            uint32_t git = 0;
+            for (int k = 0;; ++k) {
+                int item = 0;
+                if (lane == 0) item = (int)atomicAdd(p.sched_counter, 1u);
+                item = __shfl_sync(0xffffffffu, item, 0);
+                if (item >= p.n_items || *abort_flag) item = -1;   // an aborted CTA takes no further items
+                const int slot = k & 1;
+                mbar_wait(&bar_sched_empty[slot], ((k >> 1) & 1) ^ 1, wctx, 90 + slot, k);
+                __syncwarp();
+                if (lane == 0) {
+                    sched_item[slot] = item;
+                    mbar_arrive(&bar_sched_full[slot]);
+                }
+                __syncwarp();
+                if (item < 0) break;
+                const BwdItem w = bwd_decode_item<true>(item, p);
+                mbar_wait(bar_res_empty, (k & 1) ^ 1, wctx, B1_RES + 1, k);
+                __syncwarp();
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(bar_res_full, 2 * Cfg::kTileBytes);
+                    load_tile(sK, &tmK, bar_res_full, w.r0, w.bh);
+                    load_tile(sV, &tmV, bar_res_full, w.r0, w.bh);
+                }
+                __syncwarp();
+                for (int u = 0; u < w.n_it; ++u, ++git) {
+                    const int s0 = git % kNQ, s1 = git % kNdO;
+                    int t, ts;
+                    bwd_stream_tile<true>(w, u, p.group, t, ts);
+                    mbar_wait(&bar_q_empty[s0], ((git / kNQ) & 1) ^ 1, wctx, B1_QEMPTY + s0, (int)git);
+                    __syncwarp();
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&bar_q_full[s0], Cfg::kTileBytes);
+                        load_tile(sQ + s0 * Cfg::kTileBytes, &tmQ, &bar_q_full[s0], t * 128, ts);
+                    }
+                    __syncwarp();
+                    mbar_wait(&bar_do_empty[s1], ((git / kNdO) & 1) ^ 1, wctx, B1_DOEMPTY + s1, (int)git);
+                    __syncwarp();
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&bar_do_full[s1], Cfg::kTileBytes);
+                        load_tile(sdO + s1 * Cfg::kTileBytes, &tmdO, &bar_do_full[s1], t * 128, ts);
+                    }
+                    __syncwarp();
+                }
+            }
+        } else if (warp == 8) {
+            // ============================================================ MMA issuer (whole warp runs the
+            // control flow; each tcgen05.mma / commit is issued by one elected lane)
+            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);   // S^T, dP^T: both K-major
+            constexpr uint32_t idesc_kn = umma_idesc_bf16(128, D, false, true);     // dV, dK: A K-major, B MN-major
+            constexpr uint32_t idesc_nn = umma_idesc_bf16(128, D, true, true);      // dQ_t: A and B MN-major
+            const uint32_t sK_addr = __shfl_sync(0xffffffffu, smem_u32(sK), 0);
+            const uint32_t sV_addr = __shfl_sync(0xffffffffu, smem_u32(sV), 0);
+            const uint32_t sQ_addr = __shfl_sync(0xffffffffu, smem_u32(sQ), 0);
+            const uint32_t sdO_addr = __shfl_sync(0xffffffffu, smem_u32(sdO), 0);
+            const uint32_t sDS_addr = __shfl_sync(0xffffffffu, smem_u32(sDS), 0);
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+            const uint64_t dK_k = umma_smem_desc(sK_addr, 16, 1024);                    // K as A of G1 (K-major)
+            const uint64_t dK_mn = umma_smem_desc(sK_addr, Cfg::kSubBytes, 1024);       // K as B of G5 (MN-major)
+            const uint64_t dV_k = umma_smem_desc(sV_addr, 16, 1024);                    // V as A of G2
+            const uint64_t dQ_k = umma_smem_desc(sQ_addr, 16, 1024);                    // Q as B of G1 (K-major)
+            const uint64_t dQ_mn = umma_smem_desc(sQ_addr, Cfg::kSubBytes, 1024);       // Q as B of G4 (MN-major)
+            const uint64_t ddO_k = umma_smem_desc(sdO_addr, 16, 1024);                  // dO as B of G2
+            const uint64_t ddO_mn = umma_smem_desc(sdO_addr, Cfg::kSubBytes, 1024);     // dO as B of G3
+            const uint64_t dDS_k = umma_smem_desc(sDS_addr, 16, 1024);                  // dS^T as A of G4 (K-major: K = queries)
+            const uint64_t dDS_mn = umma_smem_desc(sDS_addr, Cfg::kSubBytes, 1024);     // dS^T as A of G5 (MN-major: M = queries)
+            // G1 / G2: tmem[col] = A B^T over K = D, both operands K-major tiles of D/64 sub-blocks
+            auto issue_score = [&](uint64_t a0, uint64_t b0, uint32_t col) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t o = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
+                    umma_ss(tmem_u + col, umma_desc_advance(a0, o), umma_desc_advance(b0, o), idesc_s, kk > 0);
+                }
+            };
+            uint32_t git = 0;      // streamed tiles issued before the current item
+            for (int k = 0;; ++k) {
+                const int item = next_item(k);
+                __syncwarp();
+                if (elect_one()) mbar_arrive(&bar_sched_empty[k & 1]);
+                __syncwarp();
+                if (item < 0) break;
+                const BwdItem w = bwd_decode_item<true>(item, p);
+                const int n_it = w.n_it;
+                mbar_wait(bar_res_full, k & 1, wctx, B1_RES, k);
+                __syncwarp();
+                if (n_it > 0) {
+                    // first scores of the item.  X is free: the G3 that read the previous P^T was issued
+                    // earlier by this warp and executes in order.  Y holds the previous tile's dQ_t until
+                    // the compute threads have taken it.
+                    const int f0 = git % kNQ, f1 = git % kNdO;
+                    mbar_wait(&bar_q_full[f0], (git / kNQ) & 1, wctx, B1_QFULL + f0, (int)git);
+                    __syncwarp();
+                    tc_fence_after();
+                    issue_score(dK_k, umma_desc_advance(dQ_k, f0 * Cfg::kTileBytes), kColX);
+                    tc_commit(bar_s_full);
+                    mbar_wait(&bar_do_full[f1], (git / kNdO) & 1, wctx, B1_DOFULL + f1, (int)git);
+                    __syncwarp();
+                    if (git > 0) {
+                        mbar_wait(bar_dq_free, (git - 1) & 1, wctx, B1_DQFREE, (int)git);
+                        __syncwarp();
+                    }
+                    tc_fence_after();
+                    issue_score(dV_k, umma_desc_advance(ddO_k, f1 * Cfg::kTileBytes), kColY);
+                    tc_commit(bar_dp_full);
+                }
+                for (int it = 0; it < n_it; ++it) {
+                    const uint32_t g = git + it;
+                    const int qs = g % kNQ, os = g % kNdO;                   // slots of this tile
+                    const bool has_next = it + 1 < n_it;
+                    const int nqs = (g + 1) % kNQ, nos = (g + 1) % kNdO;     // slots of the next tile
+                    // ---- G3: dV += P^T dO
+                    mbar_wait(bar_p_full, g & 1, wctx, B1_PFULL, it);
+                    __syncwarp();
+                    tc_fence_after();
+                    if (it == 0) {
+                        // the accumulator columns must have been read out by the previous item's epilogue
+                        mbar_wait(bar_acc_free, (k & 1) ^ 1, wctx, B1_ACCFREE, k);
+                        __syncwarp();
+                        tc_fence_after();
+                    }
+                    {
+                        const uint64_t b0 = umma_desc_advance(ddO_mn, os * Cfg::kTileBytes);
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk)   // K step = 16 queries = 8 columns of bf16 P^T
+                            umma_ts(tmem_u + kColDV, tmem_u + kColX + (kk >> 2) * 64 + (kk & 3) * 8, umma_desc_advance(b0, kk * 2048),
+                                    idesc_kn, (it > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&bar_do_empty[os]);                            // last read of dO(t)
+                    // ---- G1(t+1): the next scores, as soon as P^T(t) has been consumed (in order)
+                    if (has_next) {
+                        mbar_wait(&bar_q_full[nqs], ((g + 1) / kNQ) & 1, wctx, B1_QFULL + nqs, it + 1);
+                        __syncwarp();
+                        tc_fence_after();
+                        issue_score(dK_k, umma_desc_advance(dQ_k, nqs * Cfg::kTileBytes), kColX);
+                        tc_commit(bar_s_full);
+                    }
+                    // ---- G5: dQ_t = dS K  and  G4: dK += dS^T Q
+                    mbar_wait(bar_ds_full, g & 1, wctx, B1_DSFULL, it);
+                    __syncwarp();
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)       // K step = 16 keys = 16 rows of both tiles
+                        umma_ss(tmem_u + kColY, umma_desc_advance(dDS_mn, kk * 2048), umma_desc_advance(dK_mn, kk * 2048), idesc_nn,
+                                kk > 0 ? 1u : 0u);
+                    tc_commit(bar_dq_full);
+                    {
+                        const uint64_t b0 = umma_desc_advance(dQ_mn, qs * Cfg::kTileBytes);
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk) { // K step = 16 queries: 32 bytes along a dS^T row, 16 rows of Q
+                            const uint32_t ao = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
+                            umma_ss(tmem_u + kColDK, umma_desc_advance(dDS_k, ao), umma_desc_advance(b0, kk * 2048), idesc_kn,
+                                    (it > 0 || kk > 0) ? 1u : 0u);
+                        }
+                    }
+                    tc_commit(&bar_q_empty[qs]);                             // last read of Q(t)
+                    tc_commit(bar_ds_free);                                  // G4, G5 are done with the dS^T tile
+                    if (!has_next) tc_commit(bar_res_empty);                 // the item's last reads of K and V
+                    // ---- G2(t+1): the next dP^T, once dQ_t has left Y
+                    if (has_next) {
+                        mbar_wait(&bar_do_full[nos], ((g + 1) / kNdO) & 1, wctx, B1_DOFULL + nos, it + 1);
+                        __syncwarp();
+                        mbar_wait(bar_dq_free, g & 1, wctx, B1_DQFREE, it);
+                        __syncwarp();
+                        tc_fence_after();
+                        issue_score(dV_k, umma_desc_advance(ddO_k, nos * Cfg::kTileBytes), kColY);
+                        tc_commit(bar_dp_full);
+                    }
+                }
+                tc_commit(bar_final);
+                git += (uint32_t)n_it;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// dq[slice][row][:] = bf16(scale * accumulator): one block per (query slice, 128-row query tile), thread
+// (row, half of the head dim); reads are 16-byte and contiguous across the rows of a warp.
+template <int D>
+__global__ void __launch_bounds__(256) attn_bwd_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
+                                                                 int S, int n_qt, float scale) {
+    const long long blk = blockIdx.x;            // qs * n_qt + t
+    const int t = (int)(blk % n_qt);
+    const long long qs = blk / n_qt;
+    const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
+    const int row = t * 128 + r;
+    if (row >= S) return;
+    const float4* src = reinterpret_cast<const float4*>(acc) + (size_t)blk * (D / 4) * 128 + r;
+    __nv_bfloat16* dst = dq + ((long long)qs * S + row) * D + h * (D / 2);
+#pragma unroll
+    for (int c = 0; c < D / 8; c += 2) {
+        const float4 a = src[(size_t)(h * (D / 8) + c) * 128];
+        const float4 b = src[(size_t)(h * (D / 8) + c + 1) * 128];
+        *reinterpret_cast<uint4*>(dst + c * 4) =
+            make_uint4(pack_bf16x2(a.x * scale, a.y * scale), pack_bf16x2(a.z * scale, a.w * scale),
+                       pack_bf16x2(b.x * scale, b.y * scale), pack_bf16x2(b.z * scale, b.w * scale));
+    }
+}
+
+// ---------------------------------------------------------------- host side
+bool attn_bwd_fused_supported(const AttnArgs& a) {
+    return a.bf16 && (a.D == 64 || a.D == 128) && a.BH * (((long long)a.S + 127) / 128) < (1LL << 31);
+}
+size_t attn_bwd_fused_workspace(const AttnArgs& a) {
+    return align256((size_t)a.BH * (size_t)((a.S + 127) / 128) * 128 * a.D * sizeof(float));
+}
+
+template <int D>
+static cudaError_t launch_fused(const AttnArgs& a, void* ws, cudaStream_t st) {
+    using Cfg = Bwd1Cfg<D>;
+    const size_t stat_b = align256((size_t)a.BH * a.S * sizeof(float));
+    float* delta = reinterpret_cast<float*>(ws);
+    float* lse2 = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(ws) + stat_b);
+    float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(ws) + 2 * stat_b);
+    cudaError_t e = cudaMemsetAsync(dq_acc, 0, attn_bwd_fused_workspace(a), st);
+    if (e != cudaSuccess) return e;
+    e = attn_bwd_prep(a, delta, lse2, st);
+    if (e != cudaSuccess) return e;
+    TmapStorage tq, tk, tv, tdo;
+    const char* why = nullptr;
+    if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tdo, a.dout, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    auto M = [](TmapStorage& t) -> CUtensorMap& { return *reinterpret_cast<CUtensorMap*>(t.bytes); };
+    e = cudaFuncSetAttribute(attn_bwd_fused_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    BwdParams p;
+    memset(&p, 0, sizeof(p));
+    p.out0 = (__nv_bfloat16*)a.dv;
+    p.out1 = (__nv_bfloat16*)a.dk;
+    p.lse2 = lse2;
+    p.delta = delta;
+    p.S = a.S;
+    p.L = a.L;
+    p.causal = a.causal;
+    p.scale = a.scale;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.status = device_status_word();
+    p.group = a.group;
+    p.kv_lens = a.kv_lens;
+    p.H = a.H;
+    const uintptr_t al = reinterpret_cast<uintptr_t>(a.dk) | reinterpret_cast<uintptr_t>(a.dv);
+    p.wide_stores = (al & 31) == 0 ? 1 : 0;
+    p.n_tiles = (a.L + 127) / 128;
+    p.n_items = (int)(a.BH / a.group * p.n_tiles);
+    p.n_light = a.causal ? p.n_tiles / 4 : 0;
+    p.n_items_heavy = (int)(a.BH / a.group * (p.n_tiles - p.n_light));
+    p.dq_acc = dq_acc;
+    p.n_qt = (a.S + 127) / 128;
+    int dev = 0, n_sm = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    SchedCounter sc;
+    e = sched_counter_acquire(st, &sc);
+    if (e != cudaSuccess) return e;
+    p.sched_counter = sc.ptr;
+    {
+        LaunchScope ls(K_BWD_FUSED, st);
+        attn_bwd_fused_sm100_kernel<D><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+            M(tk), M(tv), M(tq), M(tdo), p);
+    }
+    sched_counter_release(sc, st);
+    {
+        LaunchScope ls(K_BWD_DQ_CONVERT, st);
+        attn_bwd_dq_convert_kernel<D><<<(unsigned)(a.BH * p.n_qt), 256, 0, st>>>(dq_acc, (__nv_bfloat16*)a.dq, a.S, p.n_qt, a.scale);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t attn_bwd_fused(const AttnArgs& a, void* ws, cudaStream_t st) {
+    return a.D == 128 ? launch_fused<128>(a, ws, st) : launch_fused<64>(a, ws, st);
+}
+
+// ---------------------------------------------------------------- choice between the two kernels
+static std::atomic<int> g_bwd_deterministic{1};   // the single-pass kernel becomes the default once it is validated on a GPU
+void attn_bwd_set_deterministic(int on) { g_bwd_deterministic.store(on ? 1 : 0); }
+int attn_bwd_deterministic() { return g_bwd_deterministic.load(); }
+
+cudaError_t attn_bwd_sm100(const AttnArgs& a, void* ws, cudaStream_t st) {
+    // TT_BWD_PATH=two_pass|fused overrides the setting (tests run both kernels on the same inputs)
+    const char* f = getenv("TT_BWD_PATH");
+    bool fused = !attn_bwd_deterministic();
+    if (f && f[0] == 't') fused = false;
+    if (f && f[0] == 'f') fused = true;
+    if (fused && attn_bwd_fused_supported(a)) return attn_bwd_fused(a, ws, st);
+    return attn_bwd_two_pass(a, ws, st);
+}
+
+}  // namespace ttk

@@ -29,23 +29,15 @@
 // memory, which is the scarcer bandwidth).
 // Shared memory: the resident pair plus rings of 3 (T0) and 2 (T1) streamed tiles at D = 128,
 // barriers and 2 KB of per-column statistics: exactly 227 KB.
-#include "common.h"
-#include "sm100_ptx.cuh"
-#include <stdlib.h>
+#include "attn_bwd_common.cuh"
+#include <string.h>
 #include <algorithm>
-#include <atomic>
 
 namespace ttk {
 using namespace sm100;
 
-// Registers per thread after setmaxnreg (compute warpgroups / the loader-and-MMA warpgroup).
-#ifndef TT_BWD_REGS_COMPUTE
-#define TT_BWD_REGS_COMPUTE 216
-#define TT_BWD_REGS_OTHER 72
-#endif
-
 template <int D>
-struct BwdCfg {
+struct BwdCfg : BwdRegs {
     static constexpr int kSub = D / 64;
     static constexpr int kSubBytes = 128 * 128;
     static constexpr int kTileBytes = kSub * kSubBytes;
@@ -54,14 +46,6 @@ struct BwdCfg {
     // is no slack for aligning the base by hand: the kernel declares the dynamic array 1024-byte
     // aligned and refuses to run (status word) if the base is not.
     static constexpr int kStreamTiles = (D == 128) ? 5 : 8;
-    static constexpr int kThreads = 384;
-    // The pool a CTA's setmaxnreg can draw from is what the launch allocated: kRegsLaunch per thread
-    // (the __launch_bounds__ figure rounded down to a multiple of 8).  A split above it never completes.
-    static constexpr int kRegsLaunch = 168;
-    static constexpr int kRegsCompute = TT_BWD_REGS_COMPUTE;
-    static constexpr int kRegsOther = TT_BWD_REGS_OTHER;
-    static_assert(256 * kRegsCompute + 128 * kRegsOther <= kThreads * kRegsLaunch, "register split exceeds the CTA's pool");
-    static_assert(kRegsCompute % 8 == 0 && kRegsOther % 8 == 0, "setmaxnreg takes multiples of 8");
     static constexpr int kTmemCols = 512;
     static constexpr int kAuxBytes = 3072;                           // 1 KB barriers + 2 KB lse/delta staging
     static constexpr int kSmemBytes = (2 + kStreamTiles) * kTileBytes + kAuxBytes;
@@ -71,106 +55,17 @@ struct BwdCfg {
 enum BwdBarId { BB_RES = 0, BB_STFULL = 10, BB_STEMPTY = 20, BB_SFULL = 30, BB_DPFULL = 31, BB_PFULL = 32,
                 BB_DSFULL = 33, BB_FINAL = 34, BB_STAT = 35 };
 
-struct BwdParams {
-    __nv_bfloat16* out0;   // keys resident: dV ; else unused
-    __nv_bfloat16* out1;   // keys resident: dK ; else dQ
-    const float* lse2;     // [BH,S]  lse * log2(e)
-    const float* delta;    // [BH,S]
-    int S, L;
-    int n_tiles;           // resident tiles per slice
-    // causal: the n_light lightest resident tiles of every slice are numbered after all others, so that
-    // CTAs that run out of heavy items near the end of the launch still find short ones (0: one phase)
-    int n_light;
-    int n_items_heavy;     // items of the first phase = slices * (n_tiles - n_light)
-    int causal;
-    float scale, scale_log2;
-    unsigned int* status;
-    unsigned int* sched_counter;   // zero at launch; work items are taken with atomicAdd
-    int n_items;                   // resident slices * n_tiles
-    int group;                     // query heads per key/value head (1 = ordinary multi-head attention)
-    const int* kv_lens;            // optional key padding lengths per batch entry (see AttnArgs)
-    int H;                         // query heads per batch entry
-    int wide_stores;               // 1: the outputs are 32-byte aligned, the epilogue uses 32-byte stores
-    long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
-    int trace_block;
-};
-
 #define TT_BTRACE(role, iter, slot)                                                                 \
     do {                                                                                           \
         if (p.trace != nullptr && (int)blockIdx.x == p.trace_block && (iter) < 64)                 \
             p.trace[((role) * 64 + (iter)) * 8 + (slot)] = clock64();                              \
     } while (0)
 
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
-// kPoly: of every 8 pairs of exponentials, kPoly are evaluated by a polynomial on the FMA pipes
-// instead of the special-function unit.
-//
 // Persistent like the forward: one CTA per SM takes (slice, resident tile) items from a global
 // counter, heavy items of a slice first; the loader runs up to two items ahead and the first
 // MMAs of the next item overlap the write-out of the accumulators of the current one.
-// With grouped heads (group g > 1) query slice bh reads key/value slice bh / g.  The dQ pass keeps
-// one query slice resident and streams its key/value slice; the dK/dV pass keeps one key/value
-// slice resident and streams the query tiles of its g query heads one head after the other into
-// the same accumulators, which is the sum over the group that dK and dV are.
-struct BwdItem {
-    int bh;        // resident slice (key/value slice when keys are resident, query slice otherwise)
-    int r0, t_begin, t_end;
-    int nt;        // streamed tiles per streamed slice
-    int n_it;      // streamed tiles of the item (nt x group when keys are resident)
-    int Lv;        // keys that count for this slice (<= L; fewer with key padding)
-};
-template <bool kKeysResident>
-__device__ __forceinline__ void bwd_stream_tile(const BwdItem& w, int u, int group, int& t, int& slice) {
-    if (kKeysResident) {
-        const int hh = u / w.nt;
-        t = w.t_begin + (u - hh * w.nt);
-        slice = w.bh * group + hh;
-    } else {
-        t = w.t_begin + u;
-        slice = w.bh / group;
-    }
-}
-template <bool kKeysResident>
-__device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p) {
-    BwdItem w;
-    const int off = p.L - p.S;
-    int rank;   // position of the resident tile among its slice's tiles, heaviest first
-    if (item < p.n_items_heavy) {
-        const int n_heavy = p.n_tiles - p.n_light;
-        w.bh = item / n_heavy;
-        rank = item - w.bh * n_heavy;
-    } else {
-        const int r = item - p.n_items_heavy;
-        w.bh = r / p.n_light;
-        rank = (p.n_tiles - p.n_light) + (r - w.bh * p.n_light);
-    }
-    // batch entry: a resident key/value slice is bh / (H / group), a resident query slice bh / H
-    w.Lv = valid_keys(p.kv_lens, kKeysResident ? ((long long)w.bh * p.group) / p.H : (long long)w.bh / p.H, p.L);
-    int rt;
-    if (kKeysResident) {
-        rt = rank;                                                    // early key tiles are the heavy ones
-        w.t_end = (p.S + 127) >> 7;
-        w.t_begin = p.causal ? (max(0, rt * 128 - off) >> 7) : 0;
-        // a key tile that is all padding gets zero gradients: one streamed tile keeps the pipeline's
-        // hand-offs alive, the epilogue writes zeros
-        if (rt * 128 >= w.Lv) w.t_end = min(w.t_end, w.t_begin + 1);
-    } else {
-        rt = p.n_tiles - 1 - rank;                                    // late query tiles are the heavy ones
-        const int n_kv = (w.Lv + 127) >> 7;
-        w.t_begin = 0;
-        w.t_end = p.causal ? min(n_kv, ((min(rt * 128 + 127, p.S - 1) + off) >> 7) + 1) : n_kv;
-    }
-    w.r0 = rt * 128;   // first resident row (key or query index)
-    w.nt = max(0, w.t_end - w.t_begin);
-    w.n_it = kKeysResident ? w.nt * p.group : w.nt;
-    return w;
-}
-
 // kTrace: compiled with the cycle stamps (debug aid; launched only while a trace buffer is set).
-template <int D, bool kKeysResident, int kPoly, bool kTrace>
+template <int D, bool kKeysResident, bool kTrace>
 __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_constant__ CUtensorMap tmR1,
                       const __grid_constant__ CUtensorMap tmT0, const __grid_constant__ CUtensorMap tmT1,
@@ -281,7 +176,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
 
     auto next_item = [&](int k) -> int {
         const int slot = k & 1;
-        mbar_wait(&bar_sched_full[slot], (k >> 1) & 1, wctx, 80 + slot, k);
+        // a wait that gave up (this CTA has aborted) ends the sequence: the slot may hold anything
+        if (!mbar_wait(&bar_sched_full[slot], (k >> 1) & 1, wctx, 80 + slot, k)) return -1;
         return sched_item[slot];
     };
 
@@ -440,15 +336,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                         const int col = wg * 64 + cc * 32 + e;
                         const uint64_t nl = kKeysResident ? stat_reg[cc][e >> 1] : row_nlse2;
                         const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(sr[cc][e]), __uint_as_float(sr[cc][e + 1])), c2, nl);
-                        float p0, p1;
-                        if ((((e >> 1) * kPoly) % 8) < kPoly) {   // kPoly of every 8 pairs on the FMA pipes
-                            ex2_poly_x2(x, p0, p1);
-                        } else {
-                            float a0, a1;
-                            unpack_f32x2(x, a0, a1);
-                            p0 = ex2_approx(a0);
-                            p1 = ex2_approx(a1);
-                        }
+                        float a0, a1;
+                        unpack_f32x2(x, a0, a1);
+                        float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
                         if (kMasked) {
                             p0 = (col >= vis_lo && col < vis_hi) ? p0 : 0.f;
                             p1 = (col + 1 >= vis_lo && col + 1 < vis_hi) ? p1 : 0.f;
@@ -581,7 +471,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 int item = 0;
                 if (lane == 0) item = (int)atomicAdd(p.sched_counter, 1u);
                 item = __shfl_sync(0xffffffffu, item, 0);
-                if (item >= p.n_items) item = -1;
+                if (item >= p.n_items || *abort_flag) item = -1;   // an aborted CTA takes no further items
                 const int slot = k & 1;
                 mbar_wait(&bar_sched_empty[slot], ((k >> 1) & 1) ^ 1, wctx, 90 + slot, k);
                 __syncwarp();
@@ -777,26 +667,22 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out, cons
         lse2[row] = lse[row] * 1.4426950408889634f;
     }
 }
+cudaError_t attn_bwd_prep(const AttnArgs& a, float* delta, float* lse2, cudaStream_t st) {
+    const long long n_rows = a.BH * (long long)a.S;
+    LaunchScope ls(K_BWD_PREP, st);
+    attn_bwd_prep_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>(
+        (const __nv_bfloat16*)a.out, (const __nv_bfloat16*)a.dout, a.lse, delta, lse2, n_rows, a.D);
+    return cudaGetLastError();
+}
 
 // ---------------------------------------------------------------- host side
 bool attn_bwd_sm100_supported(const AttnArgs& a) {
     long long tiles = ((long long)(a.S > a.L ? a.S : a.L) + 127) / 128;
     return a.bf16 && (a.D == 64 || a.D == 128) && a.BH * tiles < (1LL << 31);
 }
-size_t attn_bwd_sm100_workspace(const AttnArgs& a) { return 2 * align256((size_t)a.BH * a.S * sizeof(float)); }
-
-// Work-item counters of the persistent launches (see the forward): a rotating set, cleared on the
-// launch stream right before each kernel.
-constexpr int kBwdSchedCounters = 64;
-__device__ unsigned int g_bwd_sched_counters[kBwdSchedCounters];
-static unsigned int* next_bwd_sched_counter(cudaStream_t st, cudaError_t* err) {
-    static std::atomic<unsigned> rr{0};
-    unsigned int* base = nullptr;
-    *err = cudaGetSymbolAddress((void**)&base, g_bwd_sched_counters);
-    if (*err != cudaSuccess) return nullptr;
-    unsigned int* c = base + (rr.fetch_add(1) % kBwdSchedCounters);
-    *err = cudaMemsetAsync(c, 0, sizeof(unsigned int), st);
-    return c;
+static size_t stats_bytes(const AttnArgs& a) { return 2 * align256((size_t)a.BH * a.S * sizeof(float)); }
+size_t attn_bwd_sm100_workspace(const AttnArgs& a) {
+    return stats_bytes(a) + (attn_bwd_fused_supported(a) ? attn_bwd_fused_workspace(a) : 0);
 }
 
 static long long* g_bwd_trace = nullptr;
@@ -807,17 +693,13 @@ void attn_bwd_set_trace(long long* device_buf, int block, int pass) {
     g_bwd_trace_mode = device_buf ? pass : 0;
 }
 
-template <int D, int kPoly, bool kTrace>
+template <int D, bool kTrace>
 static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     using Cfg = BwdCfg<D>;
     float* delta = reinterpret_cast<float*>(ws);
     float* lse2 = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(ws) + align256((size_t)a.BH * a.S * sizeof(float)));
-    const long long n_rows = a.BH * (long long)a.S;
-    {
-        LaunchScope ls(K_BWD_PREP, st);
-        attn_bwd_prep_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>(
-            (const __nv_bfloat16*)a.out, (const __nv_bfloat16*)a.dout, a.lse, delta, lse2, n_rows, D);
-    }
+    cudaError_t e = attn_bwd_prep(a, delta, lse2, st);
+    if (e != cudaSuccess) return e;
     TmapStorage tq, tk, tv, tdo;
     const char* why = nullptr;
     if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
@@ -825,13 +707,12 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tdo, a.dout, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
     auto M = [](TmapStorage& t) -> CUtensorMap& { return *reinterpret_cast<CUtensorMap*>(t.bytes); };
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, true, kPoly, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
+    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, true, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, false, kPoly, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::kSmemBytes);
+    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, false, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     BwdParams p;
+    memset(&p, 0, sizeof(p));
     p.lse2 = lse2;
     p.delta = delta;
     p.S = a.S;
@@ -850,56 +731,48 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.group = a.group;
     p.kv_lens = a.kv_lens;
     p.H = a.H;
-    {
-        const char* ws_env = getenv("TT_ST256");
-        const uintptr_t al = reinterpret_cast<uintptr_t>(a.dq) | reinterpret_cast<uintptr_t>(a.dk) | reinterpret_cast<uintptr_t>(a.dv);
-        p.wide_stores = ((al & 31) == 0 && !(ws_env && ws_env[0] == '0')) ? 1 : 0;
-    }
+    const uintptr_t al = reinterpret_cast<uintptr_t>(a.dq) | reinterpret_cast<uintptr_t>(a.dk) | reinterpret_cast<uintptr_t>(a.dv);
+    p.wide_stores = (al & 31) == 0 ? 1 : 0;
     p.n_tiles = (a.L + 127) / 128;
     p.n_items = (int)(a.BH / a.group * p.n_tiles);
-    const char* two_phase = getenv("TT_BWD_TWO_PHASE");   // "0": one slice-major numbering
-    const bool phases = a.causal && !(two_phase && two_phase[0] == '0');
-    p.n_light = phases ? p.n_tiles / 4 : 0;
+    p.n_light = a.causal ? p.n_tiles / 4 : 0;
     p.n_items_heavy = (int)(a.BH / a.group * (p.n_tiles - p.n_light));
-    p.sched_counter = next_bwd_sched_counter(st, &e);
+    SchedCounter sc;
+    e = sched_counter_acquire(st, &sc);
     if (e != cudaSuccess) return e;
+    p.sched_counter = sc.ptr;
     {
         LaunchScope ls(K_BWD_DKV, st);
-        attn_bwd_sm100_kernel<D, true, kPoly, kTrace><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, true, kTrace><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tk), M(tv), M(tq), M(tdo), p);
     }
+    sched_counter_release(sc, st);
     // dQ: queries resident, stream (K, V)
     p.trace = g_bwd_trace_mode == 2 ? g_bwd_trace : nullptr;
     p.out0 = nullptr;
     p.out1 = (__nv_bfloat16*)a.dq;
     p.n_tiles = (a.S + 127) / 128;
     p.n_items = (int)(a.BH * p.n_tiles);
-    p.n_light = phases ? p.n_tiles / 4 : 0;
+    p.n_light = a.causal ? p.n_tiles / 4 : 0;
     p.n_items_heavy = (int)(a.BH * (p.n_tiles - p.n_light));
-    p.sched_counter = next_bwd_sched_counter(st, &e);
+    e = sched_counter_acquire(st, &sc);
     if (e != cudaSuccess) return e;
+    p.sched_counter = sc.ptr;
     {
         LaunchScope ls(K_BWD_DQ, st);
-        attn_bwd_sm100_kernel<D, false, kPoly, kTrace><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, false, kTrace><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tq), M(tdo), M(tk), M(tv), p);
     }
+    sched_counter_release(sc, st);
     return cudaGetLastError();
 }
 
-static int bwd_poly_setting() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("TT_BWD_POLY");
-        v = (e && *e && atoi(e) > 0) ? 1 : 0;   // on: 4 of every 8 pairs of exponentials by polynomial
-    }
-    return v;
-}
 template <int D>
 static cudaError_t launch_bwd_d(const AttnArgs& a, void* ws, cudaStream_t st) {
-    if (g_bwd_trace_mode != 0) return launch_bwd<D, 0, true>(a, ws, st);
-    return bwd_poly_setting() ? launch_bwd<D, 4, false>(a, ws, st) : launch_bwd<D, 0, false>(a, ws, st);
+    if (g_bwd_trace_mode != 0) return launch_bwd<D, true>(a, ws, st);
+    return launch_bwd<D, false>(a, ws, st);
 }
-cudaError_t attn_bwd_sm100(const AttnArgs& a, void* ws, cudaStream_t st) {
+cudaError_t attn_bwd_two_pass(const AttnArgs& a, void* ws, cudaStream_t st) {
     return a.D == 128 ? launch_bwd_d<128>(a, ws, st) : launch_bwd_d<64>(a, ws, st);
 }
 

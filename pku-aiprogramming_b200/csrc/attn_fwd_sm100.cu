@@ -25,9 +25,7 @@
 // sub-blocks of [128 rows x 128 bytes] with the 128-byte swizzle.
 #include "common.h"
 #include "sm100_ptx.cuh"
-#include <stdlib.h>
 #include <algorithm>
-#include <atomic>
 
 namespace ttk {
 using namespace sm100;
@@ -82,9 +80,9 @@ struct FwdParams {
     int kv_chunk;                  // kPaged: keys per output slice when a slice's keys are split (0: not split)
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
-    int trace_item;     // which of the CTA's work items gets the per-iteration stamps (TT_TRACE_ITEM, default 0)
-    int s0_ahead;       // 1: issue the next item's S_0(0) in a causal item's idle last iteration (TT_FWD_S0_AHEAD=0 disables)
-    int wide_stores;    // 1: `out` is 32-byte aligned, the epilogue uses 32-byte stores (TT_ST256=0 disables)
+    int trace_item;     // which of the CTA's work items gets the per-iteration stamps
+    int s0_ahead;       // 1: issue the next item's S_0(0) in a causal item's idle last iteration
+    int wide_stores;    // 1: `out` is 32-byte aligned, the epilogue uses 32-byte stores
 };
 
 #define TT_TRACE(role, iter, slot)                                                                  \
@@ -119,7 +117,6 @@ __device__ __forceinline__ float row_max_raw(const uint32_t (&sr)[4][32]) {
 }
 // P = exp2(S*c - m) for one half (64 keys) of this thread's row: packs P to bf16 pairs and
 // returns the two-lane partial row sum.
-template <int kPoly>
 __device__ __forceinline__ uint64_t softmax_exp_half(const uint32_t (&sr)[4][32], int h, float c, float m,
                                                      uint32_t (&pk)[32]) {
     const float nm = -m;
@@ -135,9 +132,7 @@ __device__ __forceinline__ uint64_t softmax_exp_half(const uint32_t (&sr)[4][32]
             float a0, a1, p2, p3;
             unpack_f32x2(xa, a0, a1);
             const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
-            if ((((e >> 2) * kPoly) % 4) < kPoly) {
-                ex2_poly_x2(xb, p2, p3);
-            } else {
+            {
                 float b0, b1;
                 unpack_f32x2(xb, b0, b1);
                 p2 = ex2_approx(b0);
@@ -152,9 +147,6 @@ __device__ __forceinline__ uint64_t softmax_exp_half(const uint32_t (&sr)[4][32]
     return add_f32x2(acc0, acc1);
 }
 
-// kPoly: of every 8 exponentials, kPoly are evaluated by a polynomial on the FMA pipes instead
-// of the special-function unit (0..4), to balance the two pipes.
-//
 // The kernel is persistent: one CTA per SM takes work items (slice, 256-row query block) from a
 // global counter until none are left.  Items are numbered slice-major with the heavy (late)
 // query blocks of a slice first, so that concurrently running CTAs share a slice's K/V in L2.
@@ -212,7 +204,7 @@ __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p)
 // forward problem: sequences may be empty, an item may cover one key range of its slice, rows
 // behind a sequence's end are zeroed in V, and with a block table the K and V tiles are gathered
 // page by page.
-template <int D, int kPoly, bool kTrace, bool kPaged>
+template <int D, bool kTrace, bool kPaged>
 __global__ void __launch_bounds__(FwdCfg<D>::kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -281,9 +273,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // ring; a negative value ends the sequence.
     auto next_item = [&](int k) -> int {
         const int slot = k & 1;
-        mbar_wait(&bar_sched_full[slot], (k >> 1) & 1, wctx, 80 + slot, k);
-        const int item = sched_item[slot];
-        return item;
+        // a wait that gave up (this CTA has aborted) ends the sequence: the slot may hold anything
+        if (!mbar_wait(&bar_sched_full[slot], (k >> 1) & 1, wctx, 80 + slot, k)) return -1;
+        return sched_item[slot];
     };
 
     if (warp < 8) {
@@ -370,7 +362,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     uint32_t pk[32];
-                    acc = add_f32x2(acc, softmax_exp_half<kPoly>(sr, h, c, m2, pk));
+                    acc = add_f32x2(acc, softmax_exp_half(sr, h, c, m2, pk));
 #pragma unroll
                     for (int q4 = 0; q4 < 2; ++q4) {
                         uint32_t t16[16];
@@ -444,7 +436,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 int item = 0;
                 if (lane == 0) item = (int)atomicAdd(p.sched_counter, 1u);
                 item = __shfl_sync(0xffffffffu, item, 0);
-                if (item >= p.n_items) item = -1;
+                if (item >= p.n_items || *abort_flag) item = -1;   // an aborted CTA takes no further items
                 const int slot = k & 1;
                 mbar_wait(&bar_sched_empty[slot], ((k >> 1) & 1) ^ 1, wctx, 90 + slot, k);
                 __syncwarp();
@@ -681,37 +673,14 @@ bool attn_fwd_sm100_supported(const AttnArgs& a) {
 }
 
 static long long* g_fwd_trace = nullptr;
-static int g_fwd_trace_block = 0;
-void attn_fwd_set_trace(long long* device_buf, int block) {
+static int g_fwd_trace_block = 0, g_fwd_trace_item = 0;
+void attn_fwd_set_trace(long long* device_buf, int block, int item) {
     g_fwd_trace = device_buf;
     g_fwd_trace_block = block;
+    g_fwd_trace_item = item;
 }
 
-// Work-item counters for the persistent forward: a small rotating set in device memory, so that
-// launches that overlap on different streams do not share one.  The chosen counter is cleared on
-// the launch stream right before the kernel.
-constexpr int kSchedCounters = 64;
-__device__ unsigned int g_fwd_sched_counters[kSchedCounters];
-static unsigned int* next_sched_counter(cudaStream_t st, cudaError_t* err) {
-    static std::atomic<unsigned> rr{0};
-    unsigned int* base = nullptr;
-    *err = cudaGetSymbolAddress((void**)&base, g_fwd_sched_counters);
-    if (*err != cudaSuccess) return nullptr;
-    unsigned int* c = base + (rr.fetch_add(1) % kSchedCounters);
-    *err = cudaMemsetAsync(c, 0, sizeof(unsigned int), st);
-    return c;
-}
-
-static int fwd_poly_setting() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("TT_FWD_POLY");
-        v = (e && *e && atoi(e) > 0) ? 1 : 0;   // on: 2 of every 8 exponentials by polynomial
-    }
-    return v;
-}
-
-template <int D, int kPoly, bool kTrace, bool kPaged = false>
+template <int D, bool kTrace, bool kPaged = false>
 static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     using Cfg = FwdCfg<D>;
     TmapStorage tq, tk, tv;
@@ -730,7 +699,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
         if (!make_tmap_bf16(&tk, a.k, D, a.L, kv_slices, 128, &why)) return cudaErrorInvalidValue;
         if (!make_tmap_bf16(&tv, a.v, D, a.L, kv_slices, 128, &why)) return cudaErrorInvalidValue;
     }
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kPoly, kTrace, kPaged>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kTrace, kPaged>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     FwdParams p;
@@ -752,43 +721,40 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.status = device_status_word();
     p.trace = g_fwd_trace;
     p.trace_block = g_fwd_trace_block;
-    {
-        const char* ti = getenv("TT_TRACE_ITEM");
-        p.trace_item = (ti && *ti) ? atoi(ti) : 0;
-        const char* sa = getenv("TT_FWD_S0_AHEAD");
-        p.s0_ahead = ((sa && sa[0] == '0') || kPaged) ? 0 : 1;
-        const char* ws = getenv("TT_ST256");
-        p.wide_stores = ((reinterpret_cast<uintptr_t>(a.out) & 31) == 0 && !(ws && ws[0] == '0')) ? 1 : 0;
-    }
+    p.trace_item = g_fwd_trace_item;
+    p.s0_ahead = kPaged ? 0 : 1;
+    p.wide_stores = (reinterpret_cast<uintptr_t>(a.out) & 31) == 0 ? 1 : 0;
     p.n_items = (int)(a.BH * p.n_qblk);
     {
         // Causal items weigh in proportion to their query block's position.  With one slice-major
         // numbering the launch ends on the last slice's heaviest blocks while the other CTAs run dry;
         // keeping the lightest quarter of every slice's blocks (1/16 of the work) for a second phase
-        // gives the CTAs that finish early something short to do.  TT_FWD_TWO_PHASE=0: one phase.
-        const char* tp = getenv("TT_FWD_TWO_PHASE");
-        p.n_light = (a.causal && !(tp && tp[0] == '0')) ? p.n_qblk / 4 : 0;
+        // gives the CTAs that finish early something short to do.
+        p.n_light = a.causal ? p.n_qblk / 4 : 0;
         p.n_items_heavy = (int)(a.BH * (p.n_qblk - p.n_light));
     }
-    p.sched_counter = next_sched_counter(st, &e);
+    SchedCounter sc;
+    e = sched_counter_acquire(st, &sc);
     if (e != cudaSuccess) return e;
+    p.sched_counter = sc.ptr;
     int dev = 0, n_sm = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     unsigned grid = (unsigned)std::min<long long>(p.n_items, n_sm);
     {
         LaunchScope ls(K_FWD_TC, st);
-        attn_fwd_sm100_kernel<D, kPoly, kTrace, kPaged><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_fwd_sm100_kernel<D, kTrace, kPaged><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
             *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
     }
+    sched_counter_release(sc, st);
     return cudaGetLastError();
 }
 
 template <int D>
 static cudaError_t launch_fwd_d(const AttnArgs& a, cudaStream_t st) {
-    if (a.cache_mode) return launch_fwd<D, 0, false, true>(a, st);
-    if (g_fwd_trace != nullptr) return launch_fwd<D, 0, true>(a, st);
-    return fwd_poly_setting() ? launch_fwd<D, 2, false>(a, st) : launch_fwd<D, 0, false>(a, st);
+    if (a.cache_mode) return launch_fwd<D, false, true>(a, st);
+    if (g_fwd_trace != nullptr) return launch_fwd<D, true>(a, st);
+    return launch_fwd<D, false>(a, st);
 }
 cudaError_t attn_fwd_sm100(const AttnArgs& a, cudaStream_t st) {
     return a.D == 128 ? launch_fwd_d<128>(a, st) : launch_fwd_d<64>(a, st);

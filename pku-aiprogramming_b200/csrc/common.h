@@ -46,10 +46,17 @@ __device__ __forceinline__ int valid_keys(const int* kv_lens, long long b, int L
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// Error reporting of the C-ABI layer: records the message tt_last_error() returns on this thread and
+// hands back `code` (a tt_status).
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+int check_device();   // TT_OK, or TT_ERR_BAD_DEVICE when the current device is not an sm_100 part
+
 // Kernel families, for launch accounting and the optional per-kernel event timing.
 enum KernelId {
     K_FWD_TC = 0, K_FWD_SIMT, K_BWD_PREP, K_BWD_DKV, K_BWD_DQ, K_BWD_SIMT_DELTA, K_BWD_SIMT_DQ, K_BWD_SIMT_DKV,
-    K_DECODE, K_DECODE_MERGE, K_PROBE, K_SOFTMAX_FWD, K_SOFTMAX_BWD, K_FC_GEMM, K_FC_SIMT, K_FC_COLSUM, K_COUNT
+    K_DECODE, K_DECODE_MERGE, K_PROBE, K_SOFTMAX_FWD, K_SOFTMAX_BWD, K_FC_GEMM, K_FC_SIMT, K_FC_COLSUM, K_BWD_FUSED,
+    K_BWD_DQ_CONVERT, K_COUNT
 };
 // Scoped around ONE kernel launch: counts it and, when timing is enabled, brackets it with
 // CUDA events on the launching stream.
@@ -63,6 +70,17 @@ struct LaunchScope {
 };
 unsigned int* device_status_word();  // 4 x uint32 in global memory of the current device (zeroed)
 
+// Work-item counter of one persistent launch: a slot of a small per-device set, cleared on the launch
+// stream.  `release` records the launch's completion on the slot, so that a later launch that is handed
+// the same slot while this one still runs is ordered behind it instead of sharing its counter.
+struct SchedCounter {
+    unsigned int* ptr = nullptr;
+    int slot = -1;
+};
+cudaError_t sched_counter_acquire(cudaStream_t st, SchedCounter* c);
+void sched_counter_release(const SchedCounter& c, cudaStream_t st);
+
+
 // --- SIMT fp32-arithmetic kernels (any D <= 256, float or bf16 tensors)
 cudaError_t attn_fwd_simt(const AttnArgs& a, cudaStream_t st);
 cudaError_t attn_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t st);
@@ -73,11 +91,15 @@ bool attn_fwd_sm100_supported(const AttnArgs& a);
 cudaError_t attn_fwd_sm100(const AttnArgs& a, cudaStream_t st);
 // Debug aid: when device_buf is non-null, CTA `block` of every later forward launch stamps
 // clock64() at its hand-off points into device_buf ([3 roles][64 iterations][8 stamps]).
-void attn_fwd_set_trace(long long* device_buf, int block);
+void attn_fwd_set_trace(long long* device_buf, int block, int item);
 void attn_bwd_set_trace(long long* device_buf, int block, int pass);   // pass 1: dK/dV, 2: dQ
 bool attn_bwd_sm100_supported(const AttnArgs& a);
 size_t attn_bwd_sm100_workspace(const AttnArgs& a);
 cudaError_t attn_bwd_sm100(const AttnArgs& a, void* workspace, cudaStream_t st);
+// Which tensor-core backward runs: 0 = single pass (dQ through fp32 adds in global memory: five GEMMs per
+// tile pair, dQ reproducible to fp32 rounding), 1 = two passes (seven GEMMs, every result bit-reproducible).
+void attn_bwd_set_deterministic(int on);
+int attn_bwd_deterministic();
 cudaError_t wait_timeout_probe(long long budget_cycles, cudaStream_t st);
 cudaError_t umma_probe(const void* a, const void* b, const void* vt, int D, float* s_out, float* o_out,
                        cudaStream_t st);

@@ -288,31 +288,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// 2^x for two packed floats WITHOUT the special-function unit: split x = floor(x) + f with a
-// round-down add of 1.5*2^23 (the integer lands in the low mantissa bits), evaluate a degree-3
-// minimax polynomial of 2^f on [0,1) (relative error < 9e-5, far below bf16 rounding), then add
-// floor(x) into the exponent field.  Inputs are clamped to >= -126 (so -inf gives ~1e-38).
-__device__ __forceinline__ void ex2_poly_x2(uint64_t x, float& r0, float& r1) {
-    float x0, x1;
-    unpack_f32x2(x, x0, x1);
-    const uint64_t xc = pack_f32x2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
-    const uint64_t magic = pack_f32x2(12582912.0f, 12582912.0f);
-    uint64_t xf;
-    asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(xf) : "l"(xc), "l"(magic));
-    uint64_t fl, fr;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(fl) : "l"(xf), "l"(magic));
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(fr) : "l"(xc), "l"(fl));
-    uint64_t r = fma_f32x2(pack_f32x2(0.07706617563962936f, 0.07706617563962936f), fr,
-                           pack_f32x2(0.22764593362808228f, 0.22764593362808228f));
-    r = fma_f32x2(r, fr, pack_f32x2(0.6951165795326233f, 0.6951165795326233f));
-    r = fma_f32x2(r, fr, pack_f32x2(1.0f, 1.0f));
-    float a0, a1, i0, i1;
-    unpack_f32x2(r, a0, a1);
-    unpack_f32x2(xf, i0, i1);
-    r0 = __uint_as_float(__float_as_uint(a0) + (__float_as_uint(i0) << 23));
-    r1 = __uint_as_float(__float_as_uint(a1) + (__float_as_uint(i1) << 23));
-}
-
 // 32-byte global store (one full sector per lane and instruction; sm_100).  `p` must be 32-byte
 // aligned.  Row-per-lane epilogues issue half as many store instructions with it, and those sit in
 // the same memory-instruction queue as the tensor-memory loads of the other warps.

@@ -1,7 +1,9 @@
 // C-ABI layer: argument validation, dispatch to the kernel families, pooled device
 // storage, tensor-map construction, error reporting.  See include/tt_attn.h.
 #include "../../include/tt_attn.h"
+#include "tt_debug.h"
 #include "common.h"
+#include "sched_slots.h"
 
 #include <cuda.h>
 #include <algorithm>
@@ -19,14 +21,14 @@ namespace ttk {
 
 // ------------------------------------------------------------------------------ errors
 static thread_local char g_err[512] = "";
-static int fail(int code, const char* fmt, ...) {
+int fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
     return code;
 }
-static int cuda_fail(cudaError_t e, const char* what) {
+int cuda_fail(cudaError_t e, const char* what) {
     return fail(TT_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
 }
 
@@ -37,7 +39,7 @@ static const char* const kKernelNames[K_COUNT] = {
     "attn_fwd_sm100", "attn_fwd_simt", "attn_bwd_prep", "attn_bwd_sm100_dkv", "attn_bwd_sm100_dq",
     "attn_bwd_simt_delta", "attn_bwd_simt_dq", "attn_bwd_simt_dkv", "attn_decode", "attn_decode_merge",
     "umma_probe", "softmax_rows_fwd", "softmax_rows_bwd", "fc_gemm_sm100", "fc_gemm_simt",
-    "fc_colsum"};
+    "fc_colsum", "attn_bwd_fused_sm100", "attn_bwd_dq_convert"};
 struct TimedLaunch {
     KernelId id;
     cudaEvent_t start, stop;
@@ -96,8 +98,60 @@ unsigned int* device_status_word() {
     return p;
 }
 
+// ------------------------------------------------------------------------------ work-item counters
+// One set of counters and events per device.  The events exist from the first use of a device on, so a
+// launch itself creates nothing.
+constexpr int kSchedSlots = 64;
+__device__ unsigned int g_sched_counters[kSchedSlots];
+namespace {
+struct DevSlots {
+    SlotRing ring{kSchedSlots};
+    cudaEvent_t ev[kSchedSlots] = {};
+    unsigned int* base = nullptr;
+    cudaError_t init_err = cudaSuccess;
+};
+std::mutex g_slots_mu;
+std::unordered_map<int, DevSlots*> g_slots;
+DevSlots* slots_for_current_device() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_slots_mu);
+    auto it = g_slots.find(dev);
+    if (it != g_slots.end()) return it->second;
+    DevSlots* d = new DevSlots();
+    d->init_err = cudaGetSymbolAddress((void**)&d->base, g_sched_counters);
+    for (int i = 0; i < kSchedSlots && d->init_err == cudaSuccess; ++i)
+        d->init_err = cudaEventCreateWithFlags(&d->ev[i], cudaEventDisableTiming);
+    g_slots[dev] = d;
+    return d;
+}
+}  // namespace
+cudaError_t sched_counter_acquire(cudaStream_t st, SchedCounter* c) {
+    DevSlots* d = slots_for_current_device();
+    if (d->init_err != cudaSuccess) return d->init_err;
+    bool must_wait = false;
+    const int s = d->ring.acquire([&](int i) { return cudaEventQuery(d->ev[i]) == cudaErrorNotReady; }, &must_wait);
+    cudaError_t e = cudaSuccess;
+    // the launch that last used this counter is still running: this one goes behind it
+    if (must_wait) e = cudaStreamWaitEvent(st, d->ev[s], 0);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d->base + s, 0, sizeof(unsigned int), st);
+    if (e != cudaSuccess) {
+        d->ring.release(s);
+        return e;
+    }
+    c->ptr = d->base + s;
+    c->slot = s;
+    return cudaSuccess;
+}
+void sched_counter_release(const SchedCounter& c, cudaStream_t st) {
+    if (c.slot < 0) return;
+    DevSlots* d = slots_for_current_device();
+    cudaEventRecord(d->ev[c.slot], st);
+    d->ring.release(c.slot);
+}
+
 // ------------------------------------------------------------------------------ device check
-static int check_device() {
+int check_device() {
     static thread_local int cached_dev = -1;
     static thread_local int cached_ok = 0;
     int dev = -1;
@@ -289,7 +343,7 @@ int tt_shard_range(int64_t n_slices, int32_t world, int32_t rank, int64_t* begin
 
 // ------------------------------------------------------------------------------ validation
 namespace ttk {
-static int resolve(const tt_attn_desc* d, AttnArgs* a, const char* who) {
+int resolve(const tt_attn_desc* d, AttnArgs* a, const char* who) {
     if (!d) return fail(TT_ERR_NULL, "%s: desc is null", who);
     if (d->B < 1 || d->H < 1 || d->S < 1 || d->L < 1)
         return fail(TT_ERR_BAD_SHAPE, "%s: B=%d H=%d S=%d L=%d must all be >= 1", who, d->B, d->H, d->S, d->L);
@@ -360,6 +414,11 @@ int tt_attn_fwd(const tt_attn_desc* desc, const void* q, const void* k, const vo
 int tt_attn_fwd_padded(const tt_attn_desc* desc, const void* q, const void* k, const void* v, const int32_t* kv_lens,
                        void* out, float* lse, void* stream) {
     return attn_fwd_common("tt_attn_fwd_padded", desc, q, k, v, kv_lens, out, lse, stream);
+}
+
+int tt_attn_bwd_set_deterministic(int on) {
+    attn_bwd_set_deterministic(on);
+    return TT_OK;
 }
 
 size_t tt_attn_bwd_workspace_bytes(const tt_attn_desc* desc) {
@@ -627,8 +686,8 @@ int tt_debug_wait_timeout(int64_t budget_cycles, void* stream) {
     return TT_OK;
 }
 
-int tt_debug_fwd_trace(void* device_buf, int32_t block) {
-    attn_fwd_set_trace(reinterpret_cast<long long*>(device_buf), block);
+int tt_debug_fwd_trace(void* device_buf, int32_t block, int32_t item) {
+    attn_fwd_set_trace(reinterpret_cast<long long*>(device_buf), block, item);
     return TT_OK;
 }
 
@@ -718,11 +777,31 @@ cudaStream_t host_call_stream() {
     int dev = 0;
     cudaGetDevice(&dev);
     if (!st || st_dev != dev) {
+        if (st) {   // the thread moved to another device: give the old device's stream back
+            cudaSetDevice(st_dev);
+            cudaStreamDestroy(st);
+            cudaSetDevice(dev);
+            st = nullptr;
+        }
         if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess) st = nullptr;
         st_dev = dev;
     }
     return st;
 }
+// Synchronises the streams it was given when it goes out of scope, unless dismissed.  The host-buffer
+// calls queue copies and kernels on non-blocking streams and then let pooled device buffers go: on an
+// error exit in the middle of the sequence that work may still be queued, and tt_free hands a block to
+// the next tt_alloc at once.  Declared AFTER the DevBufs, so that it runs before their destructors.
+struct SyncOnExit {
+    cudaStream_t s[3] = {nullptr, nullptr, nullptr};
+    int n = 0;
+    bool armed = true;
+    void add(cudaStream_t st) { if (n < 3) s[n++] = st; }
+    ~SyncOnExit() {
+        if (!armed) return;
+        for (int i = 0; i < n; ++i) cudaStreamSynchronize(s[i]);
+    }
+};
 #define TT_TRY(x) do { int rc__ = (x); if (rc__ != TT_OK) return rc__; } while (0)
 #define TT_CUDA(x, what) do { cudaError_t e__ = (x); if (e__ != cudaSuccess) return cuda_fail(e__, what); } while (0)
 }  // namespace
@@ -738,6 +817,8 @@ int tt_attn_fwd_host(const tt_attn_desc* d, const void* q, const void* k, const 
     DevBuf dq_, dk_, dv_, do_, dl_;
     TT_TRY(dq_.get(nq)); TT_TRY(dk_.get(nk)); TT_TRY(dv_.get(nk)); TT_TRY(do_.get(nq)); TT_TRY(dl_.get(nl));
     cudaStream_t st = host_call_stream();
+    SyncOnExit guard;
+    guard.add(st);
     TT_CUDA(cudaMemcpyAsync(dq_.p, q, nq, cudaMemcpyHostToDevice, st), "upload q");
     TT_CUDA(cudaMemcpyAsync(dk_.p, k, nk, cudaMemcpyHostToDevice, st), "upload k");
     TT_CUDA(cudaMemcpyAsync(dv_.p, v, nk, cudaMemcpyHostToDevice, st), "upload v");
@@ -762,6 +843,8 @@ int tt_attn_bwd_host(const tt_attn_desc* d, const void* q, const void* k, const 
     TT_TRY(bq.get(nq)); TT_TRY(bk.get(nk)); TT_TRY(bv.get(nk)); TT_TRY(bo.get(nq)); TT_TRY(bl.get(nl));
     TT_TRY(bdo.get(nq)); TT_TRY(bdq.get(nq)); TT_TRY(bdk.get(nk)); TT_TRY(bdv.get(nk)); TT_TRY(bws.get(nws));
     cudaStream_t st = host_call_stream();
+    SyncOnExit guard;
+    guard.add(st);
     TT_CUDA(cudaMemcpyAsync(bq.p, q, nq, cudaMemcpyHostToDevice, st), "upload q");
     TT_CUDA(cudaMemcpyAsync(bk.p, k, nk, cudaMemcpyHostToDevice, st), "upload k");
     TT_CUDA(cudaMemcpyAsync(bv.p, v, nk, cudaMemcpyHostToDevice, st), "upload v");
@@ -790,6 +873,14 @@ int pipe_streams(PipeStreams** ps) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (s.dev != dev) {
+        if (s.dev >= 0) {   // the thread moved to another device: give the old device's streams back
+            cudaSetDevice(s.dev);
+            for (cudaStream_t old : {s.in, s.comp, s.out})
+                if (old) cudaStreamDestroy(old);
+            cudaSetDevice(dev);
+            s.in = s.comp = s.out = nullptr;
+            s.dev = -1;
+        }
         TT_CUDA(cudaStreamCreateWithFlags(&s.in, cudaStreamNonBlocking), "stream");
         TT_CUDA(cudaStreamCreateWithFlags(&s.comp, cudaStreamNonBlocking), "stream");
         TT_CUDA(cudaStreamCreateWithFlags(&s.out, cudaStreamNonBlocking), "stream");
@@ -826,10 +917,12 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
     TT_TRY(check_device());
     const size_t es = a.bf16 ? 2 : 4;
     const size_t q_slice = (size_t)a.S * a.D * es, k_slice = (size_t)a.L * a.D * es, l_slice = (size_t)a.S * sizeof(float);
-    // chunk: about 32 MiB of q per chunk, at least 1 slice, at most a third of the slices
+    // chunk: about 32 MiB of q per chunk, at least 1 slice, at most an eighth of the slices: with few
+    // slices (a rank's share of a sharded problem) the pipeline still gets eight stages, so that only
+    // the first upload and the last download are exposed
     long long per = (long long)((32u << 20) / (q_slice ? q_slice : 1));
     if (per < 1) per = 1;
-    if (per > (a.BH + 2) / 3) per = (a.BH + 2) / 3;
+    if (per > a.BH / 8) per = a.BH / 8;
     if (per < 1) per = 1;
     per = (per + a.group - 1) / a.group * a.group;   // a chunk holds whole groups of query heads
     const long long n_chunks = (a.BH + per - 1) / per;
@@ -850,6 +943,10 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
     }
     PipeStreams* ps = nullptr;
     TT_TRY(pipe_streams(&ps));
+    SyncOnExit guard;
+    guard.add(ps->in);
+    guard.add(ps->comp);
+    guard.add(ps->out);
     EventSet ev;
     TT_TRY(ev.make());
     const char* hq = (const char*)q; const char* hk = (const char*)k; const char* hv = (const char*)v;
@@ -909,6 +1006,8 @@ int tt_attn_decode_host(const tt_attn_desc* d, const void* q, const void* k, con
     TT_TRY(bq.get(nq)); TT_TRY(bk.get(nk)); TT_TRY(bv.get(nk)); TT_TRY(bo.get(nq)); TT_TRY(bl.get(nl));
     TT_TRY(bws.get(nws));
     cudaStream_t st = host_call_stream();
+    SyncOnExit guard;
+    guard.add(st);
     TT_CUDA(cudaMemcpyAsync(bq.p, q, nq, cudaMemcpyHostToDevice, st), "upload q");
     TT_CUDA(cudaMemcpyAsync(bk.p, k, nk, cudaMemcpyHostToDevice, st), "upload k");
     TT_CUDA(cudaMemcpyAsync(bv.p, v, nk, cudaMemcpyHostToDevice, st), "upload v");

@@ -97,6 +97,12 @@ def attention_backward(q, k, v, out, lse, dout, causal=False, scale=None, worksp
     return dq, dk, dv
 
 
+def set_backward_deterministic(on: bool) -> None:
+    """True: the tensor-core backward runs its two-pass, bit-reproducible kernels; False (the default):
+    the single-pass kernel, whose dq repeats to fp32 rounding only.  Process-wide."""
+    capi.check(capi.lib.tt_attn_bwd_set_deterministic(1 if on else 0))
+
+
 def decode_workspace_bytes(B, H, L, D, dtype=torch.bfloat16, Hkv=None) -> int:
     d = capi.make_desc(B, H, 1, L, D, _DT[dtype], False, None, Hkv=Hkv)
     return int(capi.lib.tt_attn_decode_workspace_bytes(ctypes.byref(d)))

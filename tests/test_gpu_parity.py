@@ -291,7 +291,16 @@ def test_host_calls_match_device_calls(tt, oracle):
         assert oracle.max_abs_err(a.float().numpy(), _np(b)) <= 1e-2
 
 
-def test_pipelined_step_host_matches_device_calls(tt, oracle):
+@pytest.fixture
+def deterministic_backward(tt):
+    """The two-pass backward, whose results repeat bit for bit (the default single-pass kernel adds its
+    dQ contributions in whatever order the CTAs finish)."""
+    tt.set_backward_deterministic(True)
+    yield
+    tt.set_backward_deterministic(False)
+
+
+def test_pipelined_step_host_matches_device_calls(tt, oracle, deterministic_backward):
     """tt_attn_fwd_bwd_host cuts the slices into chunks and pipelines upload / kernels / download;
     the results must be those of the plain device calls, chunk boundaries included."""
     B, H, S, D = 3, 7, 1024, 128          # 21 slices -> several chunks, the last one ragged
@@ -400,7 +409,7 @@ def test_random_shapes_against_oracle(tt, oracle):
         assert oracle.max_abs_err(_np(lse), lse_ref) <= 2e-2, tag
 
 
-def test_many_work_items_per_cta(tt, oracle):
+def test_many_work_items_per_cta(tt, oracle, deterministic_backward):
     """More work items than SMs with unequal lengths: the persistent scheduler hands several items
     to each CTA, and results must not depend on which CTA took which item."""
     B, H, S, D = 3, 70, 384, 64           # 210 slices x 2 query blocks = 420 forward items
