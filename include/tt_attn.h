@@ -87,12 +87,14 @@ int tt_attn_bwd(const tt_attn_desc* desc, const void* q, const void* k, const vo
                 void* dq, void* dk, void* dv,
                 void* workspace, size_t workspace_bytes, void* stream);
 
-/* The tensor-core backward (bf16, D = 64 or 128) exists twice.  Default (on = 0): one pass over the
- * (key tile, query tile) pairs that produces dk, dv and dq together, dq through fp32 additions into the
- * workspace; the additions arrive in no fixed order, so dq repeats to fp32 rounding (a few 1e-7 relative)
- * rather than bit for bit.  on = 1: two passes (dk/dv, then dq with the scores recomputed), about a third
- * slower, every result bit-reproducible.  Process-wide; no counterpart in the reference, whose NumPy
- * reverse sweep (optimizer/autodiff.py:33-61) is deterministic and single-threaded. */
+/* The tensor-core backward (bf16, D = 64 or 128) exists twice.  Two passes (dk/dv with the keys resident,
+ * then dq with the queries resident and the scores recomputed): seven GEMMs per tile pair, no atomics,
+ * every result bit-reproducible.  One pass that produces dk, dv and dq together (five GEMMs), dq through
+ * fp32 additions into the workspace; those arrive in no fixed order, so dq repeats to fp32 rounding (a few
+ * 1e-7 relative) rather than bit for bit.  on = 0 (default): whichever measured faster for the shape (one
+ * pass at D = 64, two passes at D = 128).  on = 1: always the two passes.  Process-wide; no counterpart in
+ * the reference, whose NumPy reverse sweep (optimizer/autodiff.py:33-61) is deterministic and
+ * single-threaded. */
 int tt_attn_bwd_set_deterministic(int on);
 
 /* ---- single-query decode (S == 1) ----------------------------------------------------
@@ -109,9 +111,11 @@ int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const
  * it exists for hosts that run with a frozen memory map -- code inside a CUDA-graph capture
  * or a real-time serving loop that pre-allocated everything, or a plugin sandbox whose policy
  * forbids cudaMalloc -- and therefore cannot supply the partials workspace tt_attn_decode
- * wants.  Same kernels and same results as tt_attn_decode; the split-KV partials go to an
- * 8 MiB array built into the library's device image (each GPU that loads the library keeps
- * those 8 MiB until the process exits).  The call itself performs no cudaMalloc/cudaFree and
+ * wants.  It always runs the split-KV kernels described above (tt_attn_decode sends groups of
+ * four and more query heads per key/value head to the tensor-core forward kernel instead), so its
+ * results match tt_attn_decode within the bf16 tolerance, bit for bit where both take the same
+ * kernels; the split-KV partials go to an 8 MiB array built into the library's device image (each
+ * GPU that loads the library keeps those 8 MiB until the process exits).  The call itself performs no cudaMalloc/cudaFree and
  * calls no allocating library routine; q, k, v, out (and lse) are still the caller's.
  *   - bf16, D = 64 or 128, S = 1 only; problems whose partials exceed the array are refused
  *     with TT_ERR_WORKSPACE and a message naming both sizes (B*H*(D+2)*4*splits bytes; e.g.

@@ -142,6 +142,7 @@ cudaError_t attn_bwd_two_pass(const AttnArgs& a, void* workspace, cudaStream_t s
 bool attn_bwd_fused_supported(const AttnArgs& a);
 size_t attn_bwd_fused_workspace(const AttnArgs& a);
 cudaError_t attn_bwd_fused(const AttnArgs& a, void* workspace, cudaStream_t st);
+void attn_bwd_fused_set_trace(long long* device_buf, int block);
 
 // delta[row] = sum_d dO*O ; lse2[row] = lse[row] * log2(e).  One warp per row.
 cudaError_t attn_bwd_prep(const AttnArgs& a, float* delta, float* lse2, cudaStream_t st);

@@ -40,20 +40,19 @@
 namespace ttk {
 using namespace sm100;
 
-#ifndef TT_BWD1_NQ
-#define TT_BWD1_NQ 2
-#endif
-
 template <int D>
 struct Bwd1Cfg : BwdRegs {
     static constexpr int kSub = D / 64;
     static constexpr int kSubBytes = 128 * 128;
     static constexpr int kTileBytes = kSub * kSubBytes;
     static constexpr int kDsBytes = 2 * kSubBytes;               // 128 keys x 128 queries, bf16
-    // Q(t) is read by G1(t) early and by G4(t) late, Q(t+1) in between: two slots at least; dO(t) by
-    // G2(t) and G3(t).  At D = 128 four streamed slots fit beside K, V and dS^T.
-    static constexpr int kNQ = (D == 128) ? TT_BWD1_NQ : 4;
-    static constexpr int kNdO = (D == 128) ? 4 - TT_BWD1_NQ : 3;
+    // Q(t) is read by G1(t) early and by G4(t) late, Q(t+1) in between; dO(t) by G2(t) and G3(t), and
+    // dO(t+1) only by the last GEMM of the next iteration, so ONE dO slot is enough.  At D = 128 four
+    // streamed slots fit beside K, V and dS^T: three go to Q, whose loads then run a tile further ahead
+    // (the L2 is busy with the dQ additions, and loads come back late: 2 + 2 slots measured 12 % slower
+    // at S = 32768).
+    static constexpr int kNQ = (D == 128) ? 3 : 4;
+    static constexpr int kNdO = (D == 128) ? 1 : 3;
     static_assert(kNQ >= 2 && kNQ <= 4 && kNdO >= 1 && kNdO <= 4, "ring lengths the barrier arrays are sized for");
     static constexpr int kTmemCols = 512;
     static constexpr int kAuxBytes = 3072;                       // 1 KB barriers + 2 KB lse/delta staging
@@ -65,13 +64,35 @@ enum Bwd1BarId { B1_RES = 0, B1_QFULL = 10, B1_QEMPTY = 14, B1_DOFULL = 18, B1_D
                  B1_PFULL = 32, B1_DSFULL = 33, B1_FINAL = 34, B1_STAT = 35, B1_DSFREE = 36, B1_DQFULL = 37, B1_DQFREE = 38,
                  B1_ACCFREE = 39 };
 
+// The u-th streamed tile of an item: as in the two-pass kernel (heads of a group one after the other), but
+// without a causal mask every key tile of a slice meets ALL query tiles, and CTAs that started together
+// would walk them in step and add their dQ_t into the same 64 KB at the same moment; so key tile r starts
+// its walk at query tile r and wraps round.  (Under the causal mask key tile r starts at query tile r anyway.)
+__device__ __forceinline__ void fused_stream_tile(const BwdItem& w, int u, int group, int causal, int& t, int& slice) {
+    const int hh = u / w.nt;
+    int i = u - hh * w.nt;
+    if (!causal) {
+        i += (w.r0 >> 7) % w.nt;
+        if (i >= w.nt) i -= w.nt;
+    }
+    t = w.t_begin + i;
+    slice = w.bh * group + hh;
+}
+
 __device__ __forceinline__ void red_add_v4(float* gptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
                  ::"l"(gptr), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
                  : "memory");
 }
 
-template <int D>
+#define TT_B1TRACE(role, iter, slot)                                                               \
+    do {                                                                                           \
+        if (kTrace && p.trace != nullptr && (int)blockIdx.x == p.trace_block && (iter) < 64)       \
+            p.trace[((role) * 64 + (iter)) * 8 + (slot)] = clock64();                              \
+    } while (0)
+
+// kTrace: compiled with the cycle stamps (tuning aid; launched only while a trace buffer is set).
+template <int D, bool kTrace>
 __global__ void __launch_bounds__(Bwd1Cfg<D>::kThreads, 1)
 attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                             const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
@@ -187,25 +208,41 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         unsigned char* ds_row = sDS + wg * Cfg::kSubBytes + r_in * 128;    // this thread's 128 bytes of dS^T
         uint32_t git = 0;      // streamed tiles processed so far, over all items (barrier phases)
 
-        // dQ_t of streamed tile (t, qs), global tile number g: tensor memory -> registers -> fp32 adds
-        auto dq_out = [&](int t, int qs, uint32_t g, int it) {
+        // dQ_t leaves in two steps.  dq_take: tensor memory -> registers (this thread's query row, its
+        // warpgroup's D/2 columns), after which Y is released at once: the next dP^T GEMM waits for nothing
+        // but these loads.  dq_add: red.global.add.v4.f32 into the accumulator, a few at a time BETWEEN
+        // stretches of arithmetic and ahead of the waits, spread over a whole tile period: the L2 takes
+        // about 4 KB of such additions per cycle from the whole chip (measured: the 64 KB of a tile need
+        // ~2400 cycles with every SM adding), and a warp that issues sixteen of them back to back sits out
+        // most of that time in the issue stage.
+        uint32_t dqr[D / 64][32];
+        float* dq_base = nullptr;
+        int dq_owed = 0;          // additions of the registers' dQ_t not yet issued (they are issued in order)
+        auto dq_take = [&](int t, int qs, uint32_t g, int it) {
             mbar_wait(bar_dq_full, g & 1, wctx, B1_DQFULL, it);
             __syncwarp();
             tc_fence_after();
-            float* base = p.dq_acc + ((size_t)((long long)qs * p.n_qt + t) * (D / 4) + (size_t)wg * (D / 8)) * 512 + r_in * 4;
 #pragma unroll
-            for (int cc = 0; cc < D / 64; ++cc) {
-                uint32_t r[32];
-                tmem_ld32(tYq + cc * 32, r);
-                tmem_wait_ld();
-                if (cc == D / 64 - 1) {          // everything is in registers: Y may take the next dP^T
-                    tc_fence_before();
-                    mbar_arrive(bar_dq_free);
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) red_add_v4(base + (size_t)(cc * 8 + j) * 512, r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-            }
+            for (int cc = 0; cc < D / 64; ++cc) tmem_ld32(tYq + cc * 32, dqr[cc]);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar_dq_free);
+            dq_base = p.dq_acc + ((size_t)((long long)qs * p.n_qt + t) * (D / 4) + (size_t)wg * (D / 8)) * 512 + r_in * 4;
+            dq_owed = D / 8;
         };
+        // issues additions [first, first + count) of the D/8 this thread owes for the dQ_t in its registers
+        auto dq_add = [&](int first, int count) {
+            if (dq_owed == 0) return;
+#pragma unroll
+            for (int i = first; i < first + count; ++i) {
+                if (i < D / 8) {
+                    const int cc = i >> 3, j = i & 7;
+                    red_add_v4(dq_base + (size_t)i * 512, dqr[cc][4 * j], dqr[cc][4 * j + 1], dqr[cc][4 * j + 2], dqr[cc][4 * j + 3]);
+                }
+            }
+            if (first + count >= D / 8) dq_owed = 0;
+        };
+        constexpr int kQ = D / 64;     // additions per step of the schedule below (8 steps of kQ make D/8)
 
         for (int k = 0;; ++k) {
             const int item = next_item(k);
@@ -227,7 +264,7 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
             bool stat_ok = false;
             auto stat_issue = [&](int u) {
                 int tt, qs;
-                bwd_stream_tile<true>(w, u, p.group, tt, qs);
+                fused_stream_tile(w, u, p.group, p.causal, tt, qs);
                 const int qrow = tt * 128 + stat_q;
                 stat_ok = qrow < p.S;
                 if (stat_ok) stat_raw = stat_src[(long long)qs * p.S + qrow];
@@ -244,10 +281,12 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
             int prev_t = 0, prev_qs = 0;
             for (int u = 0; u < w.n_it; ++u, ++git) {
                 int t, qs;
-                bwd_stream_tile<true>(w, u, p.group, t, qs);
+                fused_stream_tile(w, u, p.group, p.causal, t, qs);
                 const int c0 = t * 128;                            // first streamed query of this tile
                 const float* st_nlse = s_stat + (git & 1) * 256;
                 const float* st_ndelta = st_nlse + 128;
+                const bool tr = kTrace && k == 0 && wq == 0 && lane == 0;
+                if (tr) TT_B1TRACE(wg, u, 0);
                 mbar_wait(&bar_stat[wg], git & 1, wctx, B1_STAT, u);
                 // visible queries of this thread's key inside the tile: [vis_lo, 128)
                 int vis_lo = p.causal ? max(0, rrow - off - c0) : 0;
@@ -264,13 +303,14 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                             stat_reg[cc][2 * e4 + 1] = v.y;
                         }
                 };
-                uint64_t pf2[32];     // this thread's 64 probabilities, fp32 pairs (kept for phase B)
+                uint32_t pb[32];      // this thread's 64 probabilities as bf16 pairs: what goes to tensor memory, kept for phase B
                 // ---------------- phase A: P^T = exp2(S^T*c - lse2) -> bf16 over the S^T columns just read
-                auto phase_a_body = [&](auto masked_c, int cc, const uint32_t (&sr)[32]) {
+                // (the mask test stays OUT of the unrolled loop, see the two-pass kernel; and the tensor-memory
+                // store stays out of the branch: it is a warp-wide instruction and rows differ in need_mask)
+                auto phase_a_body = [&](auto masked_c, int cc, int half, const uint32_t (&sr)[32]) {
                     constexpr bool kMasked = decltype(masked_c)::value;
-                    uint32_t pk[16];
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
+                    for (int e = half * 16; e < half * 16 + 16; e += 2) {
                         const int col = wg * 64 + cc * 32 + e;
                         const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c2, stat_reg[cc][e >> 1]);
                         float a0, a1;
@@ -280,49 +320,76 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                             p0 = (col >= vis_lo) ? p0 : 0.f;
                             p1 = (col + 1 >= vis_lo) ? p1 : 0.f;
                         }
-                        pf2[cc * 16 + (e >> 1)] = pack_f32x2(p0, p1);
-                        pk[e >> 1] = pack_bf16x2(p0, p1);
+                        pb[cc * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
                     }
+                };
+                auto phase_a_half = [&](int cc, int half, const uint32_t (&sr)[32]) {
+                    if (need_mask) phase_a_body(std::true_type{}, cc, half, sr);
+                    else phase_a_body(std::false_type{}, cc, half, sr);
+                };
+                auto store_p = [&](int cc) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) pk[e] = pb[cc * 16 + e];
+                    __syncwarp();
                     tmem_st16(tX + cc * 16, pk);
                 };
-                auto phase_a = [&](int cc) {
-                    uint32_t sr[32];
-                    tmem_ld32(tX + cc * 32, sr);
-                    tmem_wait_ld();
-                    if (need_mask) phase_a_body(std::true_type{}, cc, sr);
-                    else phase_a_body(std::false_type{}, cc, sr);
-                };
                 load_stats(st_nlse);
+                dq_add(6 * kQ, 2 * kQ);           // the last additions of the dQ_t taken a tile ago, ahead of the wait
                 mbar_wait(bar_s_full, git & 1, wctx, B1_SFULL, u);
                 __syncwarp();
                 tc_fence_after();
-                phase_a(0);
-                // the previous tile's dQ_t: its GEMM ran while this tile's first exponentials did
-                if (u > 0) dq_out(prev_t, prev_qs, git - 1, u);
-                phase_a(1);
+                if (tr) TT_B1TRACE(wg, u, 1);
+                {
+                    uint32_t sr[32];
+                    tmem_ld32(tX, sr);
+                    tmem_wait_ld();
+                    phase_a_half(0, 0, sr);
+                    phase_a_half(0, 1, sr);
+                    store_p(0);
+                }
+                if (tr) TT_B1TRACE(wg, u, 2);
+                // the previous tile's dQ_t: its GEMM ran during this tile's first exponentials
+                if (u > 0) dq_take(prev_t, prev_qs, git - 1, u);
+                if (tr) TT_B1TRACE(wg, u, 3);
+                {
+                    uint32_t sr[32];
+                    tmem_ld32(tX + 32, sr);
+                    tmem_wait_ld();
+                    dq_add(0, kQ);
+                    phase_a_half(1, 0, sr);
+                    dq_add(kQ, kQ);
+                    phase_a_half(1, 1, sr);
+                    store_p(1);
+                }
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar_p_full);
+                if (tr) TT_B1TRACE(wg, u, 4);
                 load_stats(st_ndelta);
                 if (u + 1 < w.n_it) {
                     stat_publish(git + 1);                     // its load was issued a tile ago
                     if (u + 2 < w.n_it) stat_issue(u + 2);
                 }
+                dq_add(2 * kQ, 2 * kQ);
                 // ---------------- phase B: dS^T = P^T * (dP^T - delta) -> bf16 -> shared memory
                 mbar_wait(bar_dp_full, git & 1, wctx, B1_DPFULL, u);
                 __syncwarp();
                 tc_fence_after();
+                if (tr) TT_B1TRACE(wg, u, 5);
                 if (git > 0) mbar_wait(bar_ds_free, (git - 1) & 1, wctx, B1_DSFREE, u);   // complete long ago
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t dr[32];
                     tmem_ld32(tY + cc * 32, dr);
                     tmem_wait_ld();
+                    dq_add((4 + cc) * kQ, kQ);
                     uint32_t pk[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
                         const uint64_t tdiff = add_f32x2(pack_f32x2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])), stat_reg[cc][e >> 1]);
-                        const uint64_t ds = mul_f32x2(pf2[cc * 16 + (e >> 1)], tdiff);
+                        const uint32_t pp = pb[cc * 16 + (e >> 1)];
+                        const uint64_t ds = mul_f32x2(pack_f32x2(__uint_as_float(pp << 16), __uint_as_float(pp & 0xffff0000u)), tdiff);
                         float x0, x1;
                         unpack_f32x2(ds, x0, x1);
                         pk[e >> 1] = pack_bf16x2(x0, x1);
@@ -336,10 +403,15 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                 fence_proxy_async_smem();          // generic-proxy stores -> visible to the MMA's async-proxy reads
                 tc_fence_before();
                 mbar_arrive(bar_ds_full);
+                if (tr) TT_B1TRACE(wg, u, 6);
                 prev_t = t;
                 prev_qs = qs;
             }
-            if (w.n_it > 0) dq_out(prev_t, prev_qs, git - 1, w.n_it);
+            if (w.n_it > 0) {   // what is still owed for the last-but-one dQ_t, then the item's last one
+                dq_add(6 * kQ, 2 * kQ);
+                dq_take(prev_t, prev_qs, git - 1, w.n_it);
+                dq_add(0, D / 8);
+            }
             // ---------------- epilogue: dV, dK out of tensor memory (then the MMA warp may start the next
             // item in them) -> bf16 -> global; warpgroup w owns columns [w*D/2, +D/2)
             mbar_wait(bar_final, k & 1, wctx, B1_FINAL, k);
@@ -407,7 +479,7 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                 for (int u = 0; u < w.n_it; ++u, ++git) {
                     const int s0 = git % kNQ, s1 = git % kNdO;
                     int t, ts;
-                    bwd_stream_tile<true>(w, u, p.group, t, ts);
+                    fused_stream_tile(w, u, p.group, p.causal, t, ts);
                     mbar_wait(&bar_q_empty[s0], ((git / kNQ) & 1) ^ 1, wctx, B1_QEMPTY + s0, (int)git);
                     __syncwarp();
                     if (elect_one()) {
@@ -430,21 +502,23 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
             constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);   // S^T, dP^T: both K-major
             constexpr uint32_t idesc_kn = umma_idesc_bf16(128, D, false, true);     // dV, dK: A K-major, B MN-major
             constexpr uint32_t idesc_nn = umma_idesc_bf16(128, D, true, true);      // dQ_t: A and B MN-major
-            const uint32_t sK_addr = __shfl_sync(0xffffffffu, smem_u32(sK), 0);
-            const uint32_t sV_addr = __shfl_sync(0xffffffffu, smem_u32(sV), 0);
-            const uint32_t sQ_addr = __shfl_sync(0xffffffffu, smem_u32(sQ), 0);
-            const uint32_t sdO_addr = __shfl_sync(0xffffffffu, smem_u32(sdO), 0);
-            const uint32_t sDS_addr = __shfl_sync(0xffffffffu, smem_u32(sDS), 0);
+            // Every operand lives at a fixed offset of the CTA's shared memory, so two descriptor templates
+            // (K-major and MN-major view of the base) plus compile-time offsets describe them all.
+            const uint32_t smem_addr = __shfl_sync(0xffffffffu, smem_u32(smem), 0);
             const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-            const uint64_t dK_k = umma_smem_desc(sK_addr, 16, 1024);                    // K as A of G1 (K-major)
-            const uint64_t dK_mn = umma_smem_desc(sK_addr, Cfg::kSubBytes, 1024);       // K as B of G5 (MN-major)
-            const uint64_t dV_k = umma_smem_desc(sV_addr, 16, 1024);                    // V as A of G2
-            const uint64_t dQ_k = umma_smem_desc(sQ_addr, 16, 1024);                    // Q as B of G1 (K-major)
-            const uint64_t dQ_mn = umma_smem_desc(sQ_addr, Cfg::kSubBytes, 1024);       // Q as B of G4 (MN-major)
-            const uint64_t ddO_k = umma_smem_desc(sdO_addr, 16, 1024);                  // dO as B of G2
-            const uint64_t ddO_mn = umma_smem_desc(sdO_addr, Cfg::kSubBytes, 1024);     // dO as B of G3
-            const uint64_t dDS_k = umma_smem_desc(sDS_addr, 16, 1024);                  // dS^T as A of G4 (K-major: K = queries)
-            const uint64_t dDS_mn = umma_smem_desc(sDS_addr, Cfg::kSubBytes, 1024);     // dS^T as A of G5 (MN-major: M = queries)
+            const uint64_t desc_k = umma_smem_desc(smem_addr, 16, 1024);                  // K-major: rows = M or N, 128 B of K per row
+            const uint64_t desc_mn = umma_smem_desc(smem_addr, Cfg::kSubBytes, 1024);     // MN-major: rows = K, 64 elements of M/N per row
+            constexpr uint32_t kOffK = 0, kOffV = Cfg::kTileBytes, kOffQ = 2 * Cfg::kTileBytes,
+                               kOffdO = (2 + kNQ) * Cfg::kTileBytes, kOffDS = (2 + kNQ + kNdO) * Cfg::kTileBytes;
+            const uint64_t dK_k = umma_desc_advance(desc_k, kOffK);        // K as A of G1
+            const uint64_t dK_mn = umma_desc_advance(desc_mn, kOffK);      // K as B of G5
+            const uint64_t dV_k = umma_desc_advance(desc_k, kOffV);        // V as A of G2
+            const uint64_t dQ_k = umma_desc_advance(desc_k, kOffQ);        // Q as B of G1
+            const uint64_t dQ_mn = umma_desc_advance(desc_mn, kOffQ);      // Q as B of G4
+            const uint64_t ddO_k = umma_desc_advance(desc_k, kOffdO);      // dO as B of G2
+            const uint64_t ddO_mn = umma_desc_advance(desc_mn, kOffdO);    // dO as B of G3
+            const uint64_t dDS_k = umma_desc_advance(desc_k, kOffDS);      // dS^T as A of G4 (K-major: K = queries)
+            const uint64_t dDS_mn = umma_desc_advance(desc_mn, kOffDS);    // dS^T as A of G5 (MN-major: M = queries)
             // G1 / G2: tmem[col] = A B^T over K = D, both operands K-major tiles of D/64 sub-blocks
             auto issue_score = [&](uint64_t a0, uint64_t b0, uint32_t col) {
 #pragma unroll
@@ -490,9 +564,12 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                     const bool has_next = it + 1 < n_it;
                     const int nqs = (g + 1) % kNQ, nos = (g + 1) % kNdO;     // slots of the next tile
                     // ---- G3: dV += P^T dO
+                    const bool tr = kTrace && k == 0 && lane == 0;
+                    if (tr) TT_B1TRACE(2, it, 0);
                     mbar_wait(bar_p_full, g & 1, wctx, B1_PFULL, it);
                     __syncwarp();
                     tc_fence_after();
+                    if (tr) TT_B1TRACE(2, it, 1);
                     if (it == 0) {
                         // the accumulator columns must have been read out by the previous item's epilogue
                         mbar_wait(bar_acc_free, (k & 1) ^ 1, wctx, B1_ACCFREE, k);
@@ -516,9 +593,11 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                         tc_commit(bar_s_full);
                     }
                     // ---- G5: dQ_t = dS K  and  G4: dK += dS^T Q
+                    if (tr) TT_B1TRACE(2, it, 2);
                     mbar_wait(bar_ds_full, g & 1, wctx, B1_DSFULL, it);
                     __syncwarp();
                     tc_fence_after();
+                    if (tr) TT_B1TRACE(2, it, 3);
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)       // K step = 16 keys = 16 rows of both tiles
                         umma_ss(tmem_u + kColY, umma_desc_advance(dDS_mn, kk * 2048), umma_desc_advance(dK_mn, kk * 2048), idesc_nn,
@@ -537,15 +616,18 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                     tc_commit(bar_ds_free);                                  // G4, G5 are done with the dS^T tile
                     if (!has_next) tc_commit(bar_res_empty);                 // the item's last reads of K and V
                     // ---- G2(t+1): the next dP^T, once dQ_t has left Y
+                    if (tr) TT_B1TRACE(2, it, 4);
                     if (has_next) {
                         mbar_wait(&bar_do_full[nos], ((g + 1) / kNdO) & 1, wctx, B1_DOFULL + nos, it + 1);
                         __syncwarp();
                         mbar_wait(bar_dq_free, g & 1, wctx, B1_DQFREE, it);
                         __syncwarp();
                         tc_fence_after();
+                        if (tr) TT_B1TRACE(2, it, 5);
                         issue_score(dV_k, umma_desc_advance(ddO_k, nos * Cfg::kTileBytes), kColY);
                         tc_commit(bar_dp_full);
                     }
+                    if (tr) TT_B1TRACE(2, it, 6);
                 }
                 tc_commit(bar_final);
                 git += (uint32_t)n_it;
@@ -561,10 +643,11 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
 }
 
 // dq[slice][row][:] = bf16(scale * accumulator): one block per (query slice, 128-row query tile), thread
-// (row, half of the head dim); reads are 16-byte and contiguous across the rows of a warp.
+// (row, half of the head dim).  Reads are 16 bytes per lane and contiguous across the rows of a warp; four
+// of them make the 32 contiguous bytes (one full sector) a lane writes.
 template <int D>
 __global__ void __launch_bounds__(256) attn_bwd_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
-                                                                 int S, int n_qt, float scale) {
+                                                                 int S, int n_qt, float scale, int wide) {
     const long long blk = blockIdx.x;            // qs * n_qt + t
     const int t = (int)(blk % n_qt);
     const long long qs = blk / n_qt;
@@ -574,12 +657,20 @@ __global__ void __launch_bounds__(256) attn_bwd_dq_convert_kernel(const float* _
     const float4* src = reinterpret_cast<const float4*>(acc) + (size_t)blk * (D / 4) * 128 + r;
     __nv_bfloat16* dst = dq + ((long long)qs * S + row) * D + h * (D / 2);
 #pragma unroll
-    for (int c = 0; c < D / 8; c += 2) {
-        const float4 a = src[(size_t)(h * (D / 8) + c) * 128];
-        const float4 b = src[(size_t)(h * (D / 8) + c + 1) * 128];
-        *reinterpret_cast<uint4*>(dst + c * 4) =
-            make_uint4(pack_bf16x2(a.x * scale, a.y * scale), pack_bf16x2(a.z * scale, a.w * scale),
-                       pack_bf16x2(b.x * scale, b.y * scale), pack_bf16x2(b.z * scale, b.w * scale));
+    for (int c = 0; c < D / 8; c += 4) {
+        uint32_t o8[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 a = src[(size_t)(h * (D / 8) + c + i) * 128];
+            o8[2 * i] = pack_bf16x2(a.x * scale, a.y * scale);
+            o8[2 * i + 1] = pack_bf16x2(a.z * scale, a.w * scale);
+        }
+        if (wide) {
+            st_global_32B(dst + c * 4, o8);
+        } else {
+            *reinterpret_cast<uint4*>(dst + c * 4) = make_uint4(o8[0], o8[1], o8[2], o8[3]);
+            *reinterpret_cast<uint4*>(dst + c * 4 + 8) = make_uint4(o8[4], o8[5], o8[6], o8[7]);
+        }
     }
 }
 
@@ -591,7 +682,14 @@ size_t attn_bwd_fused_workspace(const AttnArgs& a) {
     return align256((size_t)a.BH * (size_t)((a.S + 127) / 128) * 128 * a.D * sizeof(float));
 }
 
-template <int D>
+static long long* g_fused_trace = nullptr;
+static int g_fused_trace_block = 0;
+void attn_bwd_fused_set_trace(long long* device_buf, int block) {
+    g_fused_trace = device_buf;
+    g_fused_trace_block = block;
+}
+
+template <int D, bool kTrace>
 static cudaError_t launch_fused(const AttnArgs& a, void* ws, cudaStream_t st) {
     using Cfg = Bwd1Cfg<D>;
     const size_t stat_b = align256((size_t)a.BH * a.S * sizeof(float));
@@ -609,7 +707,7 @@ static cudaError_t launch_fused(const AttnArgs& a, void* ws, cudaStream_t st) {
     if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16(&tdo, a.dout, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
     auto M = [](TmapStorage& t) -> CUtensorMap& { return *reinterpret_cast<CUtensorMap*>(t.bytes); };
-    e = cudaFuncSetAttribute(attn_bwd_fused_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    e = cudaFuncSetAttribute(attn_bwd_fused_sm100_kernel<D, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     BwdParams p;
     memset(&p, 0, sizeof(p));
@@ -634,6 +732,8 @@ static cudaError_t launch_fused(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.n_items_heavy = (int)(a.BH / a.group * (p.n_tiles - p.n_light));
     p.dq_acc = dq_acc;
     p.n_qt = (a.S + 127) / 128;
+    p.trace = kTrace ? g_fused_trace : nullptr;
+    p.trace_block = g_fused_trace_block;
     int dev = 0, n_sm = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     SchedCounter sc;
@@ -642,30 +742,37 @@ static cudaError_t launch_fused(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.sched_counter = sc.ptr;
     {
         LaunchScope ls(K_BWD_FUSED, st);
-        attn_bwd_fused_sm100_kernel<D><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_fused_sm100_kernel<D, kTrace><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tk), M(tv), M(tq), M(tdo), p);
     }
     sched_counter_release(sc, st);
     {
         LaunchScope ls(K_BWD_DQ_CONVERT, st);
-        attn_bwd_dq_convert_kernel<D><<<(unsigned)(a.BH * p.n_qt), 256, 0, st>>>(dq_acc, (__nv_bfloat16*)a.dq, a.S, p.n_qt, a.scale);
+        attn_bwd_dq_convert_kernel<D><<<(unsigned)(a.BH * p.n_qt), 256, 0, st>>>(dq_acc, (__nv_bfloat16*)a.dq, a.S, p.n_qt, a.scale,
+                                                                                  (reinterpret_cast<uintptr_t>(a.dq) & 31) == 0 ? 1 : 0);
     }
     return cudaGetLastError();
 }
 
 cudaError_t attn_bwd_fused(const AttnArgs& a, void* ws, cudaStream_t st) {
-    return a.D == 128 ? launch_fused<128>(a, ws, st) : launch_fused<64>(a, ws, st);
+    if (g_fused_trace != nullptr) return a.D == 128 ? launch_fused<128, true>(a, ws, st) : launch_fused<64, true>(a, ws, st);
+    return a.D == 128 ? launch_fused<128, false>(a, ws, st) : launch_fused<64, false>(a, ws, st);
 }
 
 // ---------------------------------------------------------------- choice between the two kernels
-static std::atomic<int> g_bwd_deterministic{1};   // the single-pass kernel becomes the default once it is validated on a GPU
+static std::atomic<int> g_bwd_deterministic{0};
 void attn_bwd_set_deterministic(int on) { g_bwd_deterministic.store(on ? 1 : 0); }
 int attn_bwd_deterministic() { return g_bwd_deterministic.load(); }
 
 cudaError_t attn_bwd_sm100(const AttnArgs& a, void* ws, cudaStream_t st) {
     // TT_BWD_PATH=two_pass|fused overrides the setting (tests run both kernels on the same inputs)
     const char* f = getenv("TT_BWD_PATH");
-    bool fused = !attn_bwd_deterministic();
+    // By measurement (both kernels alternating in one process on one GPU): at D = 128 the two passes win or
+    // draw everywhere -- S = 4096 causal 1.60 ms against 1.66, S = 32768 x 64 heads 46.4 ms against 47.1 under
+    // the power cap -- because the single pass spends what it saves in GEMMs on its dQ additions (see the
+    // kernel's header); at D = 64 a tile's additions are half the bytes against the same exponentials and the
+    // single pass wins ([8,16,1024,64]: 0.172 ms against 0.201).
+    bool fused = !attn_bwd_deterministic() && a.D == 64;
     if (f && f[0] == 't') fused = false;
     if (f && f[0] == 'f') fused = true;
     if (fused && attn_bwd_fused_supported(a)) return attn_bwd_fused(a, ws, st);

@@ -96,8 +96,9 @@ void attn_bwd_set_trace(long long* device_buf, int block, int pass);   // pass 1
 bool attn_bwd_sm100_supported(const AttnArgs& a);
 size_t attn_bwd_sm100_workspace(const AttnArgs& a);
 cudaError_t attn_bwd_sm100(const AttnArgs& a, void* workspace, cudaStream_t st);
-// Which tensor-core backward runs: 0 = single pass (dQ through fp32 adds in global memory: five GEMMs per
-// tile pair, dQ reproducible to fp32 rounding), 1 = two passes (seven GEMMs, every result bit-reproducible).
+// Which tensor-core backward runs: 0 = the faster one for the shape (the single pass -- dQ through fp32 adds
+// in global memory, five GEMMs per tile pair, dQ reproducible to fp32 rounding -- or the two passes),
+// 1 = always the two passes (seven GEMMs, every result bit-reproducible).
 void attn_bwd_set_deterministic(int on);
 int attn_bwd_deterministic();
 cudaError_t wait_timeout_probe(long long budget_cycles, cudaStream_t st);

@@ -3,6 +3,7 @@
 #include "../../include/tt_attn.h"
 #include "tt_debug.h"
 #include "common.h"
+#include "attn_bwd_common.cuh"
 #include "sched_slots.h"
 
 #include <cuda.h>
@@ -692,7 +693,8 @@ int tt_debug_fwd_trace(void* device_buf, int32_t block, int32_t item) {
 }
 
 int tt_debug_bwd_trace(void* device_buf, int32_t block, int32_t pass) {
-    attn_bwd_set_trace(reinterpret_cast<long long*>(device_buf), block, pass);
+    if (pass == 3 || device_buf == nullptr) attn_bwd_fused_set_trace(reinterpret_cast<long long*>(device_buf), block);
+    if (pass != 3) attn_bwd_set_trace(reinterpret_cast<long long*>(device_buf), block, pass);
     return TT_OK;
 }
 

@@ -18,7 +18,8 @@ extern "C" {
  * P half/whole written; MMA issuer: waits and issues) for its work item number `item`, and a start
  * stamp for each of its first 64 items.  Pass null to switch it off. */
 int tt_debug_fwd_trace(void* device_buf, int32_t block, int32_t item);
-/* Same for the two-pass tensor-core backward; pass = 1 traces the dK/dV launch, 2 the dQ launch. */
+/* Same for the tensor-core backward; pass = 1 traces the dK/dV launch of the two-pass kernels, 2 their dQ
+ * launch, 3 the single-pass kernel. */
 int tt_debug_bwd_trace(void* device_buf, int32_t block, int32_t pass);
 
 /* The collective calls tt_mgpu_* makes, as a table, so that a test can put stand-ins in their place

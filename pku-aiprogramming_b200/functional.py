@@ -98,8 +98,9 @@ def attention_backward(q, k, v, out, lse, dout, causal=False, scale=None, worksp
 
 
 def set_backward_deterministic(on: bool) -> None:
-    """True: the tensor-core backward runs its two-pass, bit-reproducible kernels; False (the default):
-    the single-pass kernel, whose dq repeats to fp32 rounding only.  Process-wide."""
+    """True: the tensor-core backward always runs its two-pass, bit-reproducible kernels; False (the
+    default): whichever kernel measured faster for the shape, which at head dim 64 is the single-pass one,
+    whose dq repeats to fp32 rounding only.  Process-wide."""
     capi.check(capi.lib.tt_attn_bwd_set_deterministic(1 if on else 0))
 
 

@@ -50,10 +50,11 @@ def test_fused_backward_vs_oracle_and_two_pass(tt, oracle, monkeypatch, B, H, Hk
         for got, ref, name in zip(res[path], (dq_r, dk_r, dv_r), ("dq", "dk", "dv")):
             err = oracle.max_abs_err(_np(got), ref)
             assert err <= oracle.bf16_grad_tol(ref), f"{path} {name}: {err}"
-    # same arithmetic up to the order of the dQ sums and the rounding of dS^T's path: within one bf16 ulp
+    # same mathematics, different rounding points (the single pass forms dS^T from the bf16 P^T it feeds to
+    # the dV product) and a different order of the dQ sums: the two agree within two bf16 ulps
     for a, b, name in zip(res["fused"], res["two_pass"], ("dq", "dk", "dv")):
         ulp = 2.0 ** -7 * max(float(b.float().abs().max()), 1.0)
-        assert float((a.float() - b.float()).abs().max()) <= ulp, name
+        assert float((a.float() - b.float()).abs().max()) <= 2 * ulp, name
     monkeypatch.setenv("TT_BWD_PATH", "fused")
     again = tt.attention_backward(tq, tk, tv, out, lse, tdo, causal=causal)
     tt.check_device_status()
