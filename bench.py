@@ -523,6 +523,53 @@ def run_decode_grouped(tt, dev, peaks, dB, hkv=8, page=64):
         return {"error": str(e)}
 
 
+def run_varlen(tt, dev, peaks):
+    """A packed variable-length batch: 16 sequences of seeded lengths between 300 and 4096 tokens, 32 heads,
+    D = 128, causal, token-major [total, H, D].  FLOPs as for the dense workloads, summed over the sequences
+    (forward 4*H*S_b^2*D / 2, backward 2.5 x)."""
+    import torch
+    try:
+        H, D = 32, 128
+        rng = np.random.default_rng(16)
+        lens = [int(x) for x in rng.integers(300, 4097, size=16)]
+        total = sum(lens)
+        g = torch.Generator(device=dev).manual_seed(16)
+        mk = lambda sig: (torch.randn((total, H, D), generator=g, device=dev) * sig).to(torch.bfloat16)
+        q, k, v, do = mk(0.5), mk(0.5), mk(0.5), mk(1.0)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=dev)
+        mx = max(lens)
+        out, lse = tt.attention_forward_varlen(q, k, v, cu, cu, mx, mx, causal=True)
+        fl_f = sum(4.0 * H * n * n * D * 0.5 for n in lens)
+        legs = {"fwd": (lambda: tt.attention_forward_varlen(q, k, v, cu, cu, mx, mx, causal=True, out=out, lse=lse), fl_f),
+                "bwd": (lambda: tt.attention_backward_varlen(q, k, v, cu, cu, mx, mx, out, lse, do, causal=True), 2.5 * fl_f)}
+        res = {"workload": f"bf16 causal, 16 packed sequences of {min(lens)}..{mx} tokens ({total} in all), H={H}, D={D}"}
+        for name, (fn, fl) in legs.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                fn()
+            b.record(); torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / 10
+            res[name] = {"ms": ms, "bound": "tensor", "achieved": fl / ms / 1e9, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                         "frac": fl / ms / 1e9 / peaks["bf16"]}
+        # one sequence re-checked against the oracle (the last one)
+        from oracle import attention_oracle as orc
+        lo, hi = int(cu[-2]), int(cu[-1])
+        f = lambda t: t[lo:hi, 0].float().cpu().numpy()
+        dq, dk, dv = tt.attention_backward_varlen(q, k, v, cu, cu, mx, mx, out, lse, do, causal=True)
+        o_r, l_r, dq_r, dk_r, dv_r = orc.attention_backward_chunked(f(q), f(k), f(v), f(do), True)
+        errs = {"o": orc.max_abs_err(f(out), o_r), "dq": orc.max_abs_err(f(dq), dq_r), "dk": orc.max_abs_err(f(dk), dk_r),
+                "dv": orc.max_abs_err(f(dv), dv_r)}
+        ok = errs["o"] <= 2e-2 and all(errs[n] <= orc.bf16_grad_tol(r) for n, r in (("dq", dq_r), ("dk", dk_r), ("dv", dv_r)))
+        res["verified"] = {"ok": bool(ok), "max_abs_err": errs, "what": "last sequence, head 0, in full against the oracle"}
+        return res
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e)}
+
+
 def run_softmax(tt, dev, peaks, rows=262144):
     """Row softmax forward and backward on a score-matrix sized input (HBM-bound): fp32
     [262144, 1024] = 1 GiB per tensor, far above L2.  Algorithmic bytes: forward reads x and
@@ -633,6 +680,7 @@ def main():
     ap.add_argument("--no-fc", action="store_true", help="skip the fully connected layer leg at N=1")
     ap.add_argument("--no-softmax", action="store_true", help="skip the row-softmax leg at N=1")
     ap.add_argument("--no-fp32", action="store_true", help="skip the fp32 (SIMT kernels) side measurement at N=1")
+    ap.add_argument("--no-varlen", action="store_true", help="skip the packed variable-length side measurement at N=1")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the S=4096 side measurement at N=1")
     ap.add_argument("--no-cfg2", action="store_true", help="skip the S=1024, D=64 side measurement at N=1")
     ap.add_argument("--e2e-steps", type=int, default=5)
@@ -704,6 +752,7 @@ def main():
     fc = run_fc(tt, dev, peaks, args.fc_rows) if (rank == 0 and world == 1 and not args.no_fc) else None
     softmax = run_softmax(tt, dev, peaks, args.softmax_rows) if (rank == 0 and world == 1 and not args.no_softmax) else None
     fp32 = run_fp32(tt, dev, peaks) if (rank == 0 and world == 1 and not args.no_fp32) else None
+    varlen = run_varlen(tt, dev, peaks) if (rank == 0 and world == 1 and not args.no_varlen) else None
 
     # CPU baseline: the oracle on a bounded sample of the same workload (rank 0, N = 1)
     cpu = None
@@ -734,7 +783,7 @@ def main():
             "fwd_tflops": main_res["fwd_tflops"], "pct_of_bf16_peak": main_res["pct_of_bf16_peak"],
             "roofline": main_res["roofline"], "kernels": main_res["kernels"], "verified": main_res["verified"],
             "cfg3": side, "cfg2": side2, "decode": decode,
-            "softmax_rows": softmax, "fc": fc, "fp32": fp32,
+            "softmax_rows": softmax, "fc": fc, "fp32": fp32, "varlen": varlen,
             "cpu_baseline": cpu, "e2e": main_res["e2e"], "clocks": main_res["clocks"],
             "gpu_launches": main_res["gpu_launches"], "host_numa_cores": numa_cores,
         }

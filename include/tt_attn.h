@@ -143,6 +143,32 @@ int tt_attn_bwd_padded(const tt_attn_desc* desc, const void* q, const void* k, c
                        const void* out, const float* lse, const void* dout, void* dq, void* dk, void* dv,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- packed variable-length batches ----------------------------------------------------------
+ * n_seq sequences of different lengths stored back to back, token-major, without padding (no counterpart
+ * in the reference, whose tensors are dense [B,H,S,D], src/TinyTensor.h:14-17): q, out, dout, dq are
+ * [total_q, H, D]; k, v, dk, dv [total_k, Hkv, D]; lse [H, total_q].  cu_q, cu_k: device arrays of
+ * n_seq + 1 int32, cumulative token counts (cu[0] = 0, cu[n_seq] = total): sequence b owns query tokens
+ * [cu_q[b], cu_q[b+1]) and key tokens [cu_k[b], cu_k[b+1]).  max_q, max_k: upper bounds of the longest
+ * sequence (host values: they size the launch; the kernels read the real lengths from cu_q / cu_k).
+ * Every sequence is its own attention problem with the conventions above (causal: bottom-right aligned
+ * per sequence; a row that sees no key -- an empty key sequence, or causal with fewer keys than queries --
+ * gets out = 0, lse = -inf and zero gradients).  bf16 with D = 64 or 128 only (tensor-core kernels);
+ * anything else returns TT_ERR_UNSUPPORTED.  The backward runs the two-pass kernels (bit-reproducible);
+ * workspace: tt_attn_bwd_varlen_workspace_bytes(), 256-byte aligned. */
+typedef struct tt_varlen_desc {
+    int32_t n_seq, H, Hkv;   /* Hkv: 0 or H, or a divisor of H (grouped heads) */
+    int32_t D, dtype, causal;
+    float scale;             /* <= 0 -> 1/sqrt(D) */
+    int32_t max_q, max_k;
+    int64_t total_q, total_k;
+} tt_varlen_desc;
+int tt_attn_fwd_varlen(const tt_varlen_desc* desc, const void* q, const void* k, const void* v, const int32_t* cu_q,
+                       const int32_t* cu_k, void* out, float* lse, void* stream);
+size_t tt_attn_bwd_varlen_workspace_bytes(const tt_varlen_desc* desc);
+int tt_attn_bwd_varlen(const tt_varlen_desc* desc, const void* q, const void* k, const void* v, const int32_t* cu_q,
+                       const int32_t* cu_k, const void* out, const float* lse, const void* dout, void* dq, void* dk,
+                       void* dv, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- decode over a paged and/or ragged key/value cache -----------------------------------
  * tt_attn_decode for serving-style caches (no counterpart in the reference).  bf16, D = 64 or
  * 128, S = 1; desc->L is the longest sequence any batch entry may have.

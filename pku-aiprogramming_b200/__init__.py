@@ -12,5 +12,5 @@ from .functional import (  # noqa: F401
     attention_forward, attention_backward, attention_decode, decode_workspace_bytes,
     attention_forward_host, attention_backward_host, attention_decode_host, attention_step_host,
     check_device_status, softmax_forward, softmax_backward, fc_forward, fc_backward, attention_decode_paged,
-    set_backward_deterministic,
+    set_backward_deterministic, attention_forward_varlen, attention_backward_varlen,
 )

@@ -29,8 +29,15 @@ class Desc(ctypes.Structure):
                 ("dtype", c_int32), ("causal", c_int32), ("scale", c_float), ("Hkv", c_int32)]
 
 
+class VarlenDesc(ctypes.Structure):
+    _fields_ = [("n_seq", c_int32), ("H", c_int32), ("Hkv", c_int32), ("D", c_int32), ("dtype", c_int32),
+                ("causal", c_int32), ("scale", c_float), ("max_q", c_int32), ("max_k", c_int32),
+                ("total_q", c_int64), ("total_k", c_int64)]
+
+
 _P = c_void_p
 _DP = POINTER(Desc)
+_VP = POINTER(VarlenDesc)
 SIGNATURES = {
     "tt_attn_fwd": (c_int, [_DP, _P, _P, _P, _P, _P, _P]),
     "tt_attn_bwd_workspace_bytes": (c_size_t, [_DP]),
@@ -38,6 +45,9 @@ SIGNATURES = {
     "tt_attn_bwd": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
     "tt_attn_fwd_padded": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P]),
     "tt_attn_bwd_padded": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
+    "tt_attn_fwd_varlen": (c_int, [_VP, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "tt_attn_bwd_varlen_workspace_bytes": (c_size_t, [_VP]),
+    "tt_attn_bwd_varlen": (c_int, [_VP, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
     "tt_attn_decode_workspace_bytes": (c_size_t, [_DP]),
     "tt_attn_decode": (c_int, [_DP, _P, _P, _P, _P, _P, _P, c_size_t, _P]),
     "tt_attn_decode_paged": (c_int, [_DP, _P, _P, _P, _P, _P, c_int32, c_int32, _P, _P, _P, c_size_t, _P]),

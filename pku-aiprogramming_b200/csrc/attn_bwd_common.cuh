@@ -50,6 +50,12 @@ struct BwdParams {
     int n_qt;
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
+    // packed variable-length batches (two-pass kernel only; see AttnArgs): per-sequence geometry from cu_q /
+    // cu_k, token-major tensors, statistics as [H, total_q]; S and L above are the longest sequence's counts
+    const int* cu_q;
+    const int* cu_k;
+    int total_q;
+    int Hkv;                       // key/value heads per batch entry
 };
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
@@ -67,22 +73,27 @@ struct BwdItem {
     int nt;        // streamed tiles per streamed slice
     int n_it;      // streamed tiles of the item (nt x group when keys are resident)
     int Lv;        // keys that count for this slice (<= L; fewer with key padding)
+    // geometry of the item's slice: the launch's own S, L for dense tensors, the sequence's for packed ones
+    int S, L;
+    // packed batches only: first query / key token of the sequence, and the resident slice's head
+    int q_lo, k_lo, head;
 };
-template <bool kKeysResident>
+// The u-th streamed tile of an item: its tile index and the slice it belongs to (for packed batches the
+// slice is a head: tensors are token-major and the sequence's first token is added to the row instead).
+template <bool kKeysResident, bool kVarlen = false>
 __device__ __forceinline__ void bwd_stream_tile(const BwdItem& w, int u, int group, int& t, int& slice) {
     if (kKeysResident) {
         const int hh = u / w.nt;
         t = w.t_begin + (u - hh * w.nt);
-        slice = w.bh * group + hh;
+        slice = (kVarlen ? w.head : w.bh) * group + hh;
     } else {
         t = w.t_begin + u;
-        slice = w.bh / group;
+        slice = (kVarlen ? w.head : w.bh) / group;
     }
 }
-template <bool kKeysResident>
+template <bool kKeysResident, bool kVarlen = false>
 __device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p) {
     BwdItem w;
-    const int off = p.L - p.S;
     int rank;   // position of the resident tile among its slice's tiles, heaviest first
     if (item < p.n_items_heavy) {
         const int n_heavy = p.n_tiles - p.n_light;
@@ -93,12 +104,28 @@ __device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p)
         w.bh = r / p.n_light;
         rank = (p.n_tiles - p.n_light) + (r - w.bh * p.n_light);
     }
-    // batch entry: a resident key/value slice is bh / (H / group), a resident query slice bh / H
-    w.Lv = valid_keys(p.kv_lens, kKeysResident ? ((long long)w.bh * p.group) / p.H : (long long)w.bh / p.H, p.L);
+    int S = p.S, L = p.L;
+    if (kVarlen) {
+        const int heads = kKeysResident ? p.Hkv : p.H;
+        const int b = w.bh / heads;
+        w.head = w.bh - b * heads;
+        w.q_lo = p.cu_q[b];
+        w.k_lo = p.cu_k[b];
+        S = p.cu_q[b + 1] - w.q_lo;
+        L = p.cu_k[b + 1] - w.k_lo;
+        w.Lv = L;
+    } else {
+        // batch entry: a resident key/value slice is bh / (H / group), a resident query slice bh / H
+        w.Lv = valid_keys(p.kv_lens, kKeysResident ? ((long long)w.bh * p.group) / p.H : (long long)w.bh / p.H, p.L);
+        w.q_lo = w.k_lo = w.head = 0;
+    }
+    w.S = S;
+    w.L = L;
+    const int off = L - S;
     int rt;
     if (kKeysResident) {
         rt = rank;                                                    // early key tiles are the heavy ones
-        w.t_end = (p.S + 127) >> 7;
+        w.t_end = (S + 127) >> 7;
         w.t_begin = p.causal ? (max(0, rt * 128 - off) >> 7) : 0;
         // a key tile that is all padding gets zero gradients: one streamed tile keeps the pipeline's
         // hand-offs alive, the epilogue writes zeros
@@ -107,10 +134,11 @@ __device__ __forceinline__ BwdItem bwd_decode_item(int item, const BwdParams& p)
         rt = p.n_tiles - 1 - rank;                                    // late query tiles are the heavy ones
         const int n_kv = (w.Lv + 127) >> 7;
         w.t_begin = 0;
-        w.t_end = p.causal ? min(n_kv, ((min(rt * 128 + 127, p.S - 1) + off) >> 7) + 1) : n_kv;
+        w.t_end = p.causal ? min(n_kv, ((min(rt * 128 + 127, S - 1) + off) >> 7) + 1) : n_kv;
     }
     w.r0 = rt * 128;   // first resident row (key or query index)
     w.nt = max(0, w.t_end - w.t_begin);
+    if (kVarlen && w.r0 >= (kKeysResident ? L : S)) w.nt = 0;   // the sequence is shorter than the longest one: nothing here
     w.n_it = kKeysResident ? w.nt * p.group : w.nt;
     return w;
 }

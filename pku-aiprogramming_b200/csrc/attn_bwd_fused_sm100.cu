@@ -775,7 +775,7 @@ cudaError_t attn_bwd_sm100(const AttnArgs& a, void* ws, cudaStream_t st) {
     bool fused = !attn_bwd_deterministic() && a.D == 64;
     if (f && f[0] == 't') fused = false;
     if (f && f[0] == 'f') fused = true;
-    if (fused && attn_bwd_fused_supported(a)) return attn_bwd_fused(a, ws, st);
+    if (fused && attn_bwd_fused_supported(a) && a.cu_q == nullptr) return attn_bwd_fused(a, ws, st);   // packed batches: two passes
     return attn_bwd_two_pass(a, ws, st);
 }
 

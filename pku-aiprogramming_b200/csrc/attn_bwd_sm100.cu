@@ -65,7 +65,8 @@ enum BwdBarId { BB_RES = 0, BB_STFULL = 10, BB_STEMPTY = 20, BB_SFULL = 30, BB_D
 // counter, heavy items of a slice first; the loader runs up to two items ahead and the first
 // MMAs of the next item overlap the write-out of the accumulators of the current one.
 // kTrace: compiled with the cycle stamps (debug aid; launched only while a trace buffer is set).
-template <int D, bool kKeysResident, bool kTrace>
+// kVarlen: packed variable-length batches (per-item sequence geometry, token-major addressing).
+template <int D, bool kKeysResident, bool kTrace, bool kVarlen>
 __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_constant__ CUtensorMap tmR1,
                       const __grid_constant__ CUtensorMap tmT0, const __grid_constant__ CUtensorMap tmT1,
@@ -116,7 +117,6 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
 
     const int warp = uniform_warp_idx();
     const int lane = threadIdx.x & 31;
-    const int off = p.L - p.S;
     // With queries resident only one accumulator (dQ) is needed, which leaves 128 tensor-memory
     // columns free.  The compute threads copy the resident Q and dO tiles there at the start of an
     // item (bf16, D/2 columns each), and from the item's second tile on they are the A operands of
@@ -197,9 +197,15 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             __syncwarp();
             mbar_arrive(&bar_sched_empty[k & 1]);
             if (item < 0) break;
-            const BwdItem w = bwd_decode_item<kKeysResident>(item, p);
+            const BwdItem w = bwd_decode_item<kKeysResident, kVarlen>(item, p);
             const int bh = w.bh;
             const int rrow = w.r0 + wq * 32 + lane;            // this thread's resident row
+            const int off = w.L - w.S;
+            // where the statistics of query row r of query slice qs live: [slices, S] for dense tensors,
+            // [H, total_q] for packed ones (qs is then the query head and the row is offset by the sequence start)
+            auto stat_index = [&](int qs, int r) -> long long {
+                return kVarlen ? (long long)qs * p.total_q + w.q_lo + r : (long long)qs * p.S + r;
+            };
             // per-item stamps of the traced CTA: row k of warpgroup wg, slots 6 (start) and 7 (tiles)
             if (kTrace && p.trace != nullptr && (int)blockIdx.x == p.trace_block && wq == 0 && lane == 0 && k < 64) {
                 p.trace[(wg * 64 + k) * 8 + 6] = clock64();
@@ -232,9 +238,10 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             // row constants (queries resident) as packed pairs of the NEGATED values
             uint64_t row_nlse2 = 0, row_ndelta2 = 0;
             if (!kKeysResident) {
-                const bool ok = rrow < p.S;
-                const float nl = ok ? -p.lse2[(long long)bh * p.S + rrow] : -INFINITY;
-                const float nd = ok ? -p.delta[(long long)bh * p.S + rrow] : 0.f;
+                const bool ok = rrow < w.S;
+                const long long si = stat_index(kVarlen ? w.head : bh, rrow);
+                const float nl = ok ? -p.lse2[si] : -INFINITY;
+                const float nd = ok ? -p.delta[si] : 0.f;
                 row_nlse2 = pack_f32x2(nl, nl);
                 row_ndelta2 = pack_f32x2(nd, nd);
             }
@@ -256,10 +263,10 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             bool stat_ok = false;
             auto stat_issue = [&](int u) {   // this thread's statistic of streamed tile u
                 int tt, qs;
-                bwd_stream_tile<kKeysResident>(w, u, p.group, tt, qs);
+                bwd_stream_tile<kKeysResident, kVarlen>(w, u, p.group, tt, qs);
                 const int qrow = tt * 128 + stat_q;
-                stat_ok = qrow < p.S;
-                if (stat_ok) stat_raw = stat_src[(long long)qs * p.S + qrow];
+                stat_ok = qrow < w.S;
+                if (stat_ok) stat_raw = stat_src[stat_index(qs, qrow)];
             };
             // Staging runs one tile ahead and is split-phase: the statistic of tile u+1 is written to
             // the other half of the double buffer in the MIDDLE of tile u, followed by an arrive on the
@@ -411,7 +418,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             mbar_wait(bar_final, k & 1, wctx, BB_FINAL, k);
             __syncwarp();
             tc_fence_after();
-            const int n_rows = kKeysResident ? p.L : p.S;
+            const int n_rows = kKeysResident ? w.L : w.S;
             constexpr int kHalf = D / 2;
             constexpr int kAccs = kKeysResident ? 2 : 1;
             uint32_t acc[kAccs][kHalf / 32][32];
@@ -428,7 +435,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
 #pragma unroll
                 for (int a = 0; a < kAccs; ++a) {
                     const bool is_acc0 = kKeysResident && a == 0;
-                    __nv_bfloat16* dst = (is_acc0 ? p.out0 : p.out1) + ((long long)bh * n_rows + rrow) * D + wg * kHalf;
+                    // dense: row rrow of slice bh of [slices, rows, D]; packed: token (first token + rrow), head
+                    const long long o_el = kVarlen
+                        ? ((long long)((kKeysResident ? w.k_lo : w.q_lo) + rrow) * (kKeysResident ? p.Hkv : p.H) + w.head) * D
+                        : ((long long)bh * n_rows + rrow) * D;
+                    __nv_bfloat16* dst = (is_acc0 ? p.out0 : p.out1) + o_el + wg * kHalf;
                     const float mul = is_acc0 ? 1.0f : p.scale;
                     if (kKeysResident && rrow >= w.Lv) {   // gradients of padded keys are zero
 #pragma unroll
@@ -469,9 +480,18 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
             uint32_t git = 0;
             for (int k = 0;; ++k) {
                 int item = 0;
-                if (lane == 0) item = (int)atomicAdd(p.sched_counter, 1u);
-                item = __shfl_sync(0xffffffffu, item, 0);
-                if (item >= p.n_items || *abort_flag) item = -1;   // an aborted CTA takes no further items
+                BwdItem w;
+                for (;;) {
+                    if (lane == 0) item = (int)atomicAdd(p.sched_counter, 1u);
+                    item = __shfl_sync(0xffffffffu, item, 0);
+                    if (item >= p.n_items || *abort_flag) item = -1;   // an aborted CTA takes no further items
+                    if (item < 0) break;
+                    w = bwd_decode_item<kKeysResident, kVarlen>(item, p);
+                    // packed batches number their items for the longest sequence: what lies past a shorter
+                    // sequence's end, or sees nothing under the causal mask, is never published (the
+                    // outputs were cleared before the launch)
+                    if (!kVarlen || w.n_it > 0) break;
+                }
                 const int slot = k & 1;
                 mbar_wait(&bar_sched_empty[slot], ((k >> 1) & 1) ^ 1, wctx, 90 + slot, k);
                 __syncwarp();
@@ -481,31 +501,35 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 }
                 __syncwarp();
                 if (item < 0) break;
-                const BwdItem w = bwd_decode_item<kKeysResident>(item, p);
+                // TMA coordinates: (row, slice) of [slices, rows, D] for dense tensors; for packed ones the row is
+                // offset by the sequence's first token and the slice is the head
+                const int res_y0 = kVarlen ? (kKeysResident ? w.k_lo : w.q_lo) : 0;
+                const int str_y0 = kVarlen ? (kKeysResident ? w.q_lo : w.k_lo) : 0;
+                const int res_z = kVarlen ? w.head : w.bh;
                 mbar_wait(bar_res_empty, (k & 1) ^ 1, wctx, BB_RES + 1, k);
                 __syncwarp();
                 if (elect_one()) {
                     mbar_arrive_expect_tx(bar_res_full, 2 * Cfg::kTileBytes);
-                    load_tile(sR, &tmR0, bar_res_full, w.r0, w.bh);
-                    load_tile(sR + Cfg::kTileBytes, &tmR1, bar_res_full, w.r0, w.bh);
+                    load_tile(sR, &tmR0, bar_res_full, res_y0 + w.r0, res_z);
+                    load_tile(sR + Cfg::kTileBytes, &tmR1, bar_res_full, res_y0 + w.r0, res_z);
                 }
                 __syncwarp();
                 for (int u = 0; u < w.n_it; ++u, ++git) {
                     const int s0 = git % kN0, s1 = git % kN1;
                     int t, ts;
-                    bwd_stream_tile<kKeysResident>(w, u, p.group, t, ts);
+                    bwd_stream_tile<kKeysResident, kVarlen>(w, u, p.group, t, ts);
                     mbar_wait(&bar_t0_empty[s0], ((git / kN0) & 1) ^ 1, wctx, BB_STEMPTY + s0, (int)git);
                     __syncwarp();
                     if (elect_one()) {
                         mbar_arrive_expect_tx(&bar_t0_full[s0], Cfg::kTileBytes);
-                        load_tile(sT + s0 * Cfg::kTileBytes, &tmT0, &bar_t0_full[s0], t * 128, ts);
+                        load_tile(sT + s0 * Cfg::kTileBytes, &tmT0, &bar_t0_full[s0], str_y0 + t * 128, ts);
                     }
                     __syncwarp();
                     mbar_wait(&bar_t1_empty[s1], ((git / kN1) & 1) ^ 1, wctx, BB_STEMPTY + 6 + s1, (int)git);
                     __syncwarp();
                     if (elect_one()) {
                         mbar_arrive_expect_tx(&bar_t1_full[s1], Cfg::kTileBytes);
-                        load_tile(sT + (kN0 + s1) * Cfg::kTileBytes, &tmT1, &bar_t1_full[s1], t * 128, ts);
+                        load_tile(sT + (kN0 + s1) * Cfg::kTileBytes, &tmT1, &bar_t1_full[s1], str_y0 + t * 128, ts);
                     }
                     __syncwarp();
                 }
@@ -558,7 +582,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
                 if (elect_one()) mbar_arrive(&bar_sched_empty[k & 1]);
                 __syncwarp();
                 if (item < 0) break;
-                const BwdItem w = bwd_decode_item<kKeysResident>(item, p);
+                const BwdItem w = bwd_decode_item<kKeysResident, kVarlen>(item, p);
                 const int n_it = w.n_it;
                 mbar_wait(bar_res_full, k & 1, wctx, BB_RES, k);
                 __syncwarp();
@@ -667,9 +691,44 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out, cons
         lse2[row] = lse[row] * 1.4426950408889634f;
     }
 }
+// The same for packed batches: out, dout are [total_q, H, D], lse, delta, lse2 are [H, total_q].
+__global__ void attn_bwd_prep_varlen_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                                            const float* __restrict__ lse, float* __restrict__ delta,
+                                            float* __restrict__ lse2, long long total_q, int H, int D) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp;   // token * H + head
+    if (row >= total_q * H) return;
+    const long long tok = row / H;
+    const int h = (int)(row - tok * H);
+    const uint2* o2 = reinterpret_cast<const uint2*>(out + row * D);
+    const uint2* d2 = reinterpret_cast<const uint2*>(dout + row * D);
+    float acc = 0.f;
+    for (int i = lane; i < D / 4; i += 32) {
+        uint2 a = o2[i], b = d2[i];
+        acc = fmaf(__uint_as_float(a.x << 16), __uint_as_float(b.x << 16), acc);
+        acc = fmaf(__uint_as_float(a.x & 0xffff0000u), __uint_as_float(b.x & 0xffff0000u), acc);
+        acc = fmaf(__uint_as_float(a.y << 16), __uint_as_float(b.y << 16), acc);
+        acc = fmaf(__uint_as_float(a.y & 0xffff0000u), __uint_as_float(b.y & 0xffff0000u), acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        const long long i = (long long)h * total_q + tok;
+        delta[i] = acc;
+        // a row that saw no key has lse = -inf: +inf here makes its recomputed probabilities exp2(-inf) = 0
+        const float l = lse[i];
+        lse2[i] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+    }
+}
 cudaError_t attn_bwd_prep(const AttnArgs& a, float* delta, float* lse2, cudaStream_t st) {
-    const long long n_rows = a.BH * (long long)a.S;
     LaunchScope ls(K_BWD_PREP, st);
+    if (a.cu_q != nullptr) {
+        const long long rows = a.total_q * a.H;
+        attn_bwd_prep_varlen_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+            (const __nv_bfloat16*)a.out, (const __nv_bfloat16*)a.dout, a.lse, delta, lse2, a.total_q, a.H, a.D);
+        return cudaGetLastError();
+    }
+    const long long n_rows = a.BH * (long long)a.S;
     attn_bwd_prep_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>(
         (const __nv_bfloat16*)a.out, (const __nv_bfloat16*)a.dout, a.lse, delta, lse2, n_rows, a.D);
     return cudaGetLastError();
@@ -680,9 +739,11 @@ bool attn_bwd_sm100_supported(const AttnArgs& a) {
     long long tiles = ((long long)(a.S > a.L ? a.S : a.L) + 127) / 128;
     return a.bf16 && (a.D == 64 || a.D == 128) && a.BH * tiles < (1LL << 31);
 }
-static size_t stats_bytes(const AttnArgs& a) { return 2 * align256((size_t)a.BH * a.S * sizeof(float)); }
+// statistics: one float per query row of every slice, twice (delta, lse2)
+static size_t stats_rows(const AttnArgs& a) { return a.cu_q ? (size_t)a.total_q * a.H : (size_t)a.BH * a.S; }
+static size_t stats_bytes(const AttnArgs& a) { return 2 * align256(stats_rows(a) * sizeof(float)); }
 size_t attn_bwd_sm100_workspace(const AttnArgs& a) {
-    return stats_bytes(a) + (attn_bwd_fused_supported(a) ? attn_bwd_fused_workspace(a) : 0);
+    return stats_bytes(a) + ((attn_bwd_fused_supported(a) && !a.cu_q) ? attn_bwd_fused_workspace(a) : 0);
 }
 
 static long long* g_bwd_trace = nullptr;
@@ -693,23 +754,37 @@ void attn_bwd_set_trace(long long* device_buf, int block, int pass) {
     g_bwd_trace_mode = device_buf ? pass : 0;
 }
 
-template <int D, bool kTrace>
+template <int D, bool kTrace, bool kVarlen = false>
 static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     using Cfg = BwdCfg<D>;
     float* delta = reinterpret_cast<float*>(ws);
-    float* lse2 = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(ws) + align256((size_t)a.BH * a.S * sizeof(float)));
+    float* lse2 = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(ws) + align256(stats_rows(a) * sizeof(float)));
     cudaError_t e = attn_bwd_prep(a, delta, lse2, st);
     if (e != cudaSuccess) return e;
     TmapStorage tq, tk, tv, tdo;
     const char* why = nullptr;
-    if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
-    if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
-    if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
-    if (!make_tmap_bf16(&tdo, a.dout, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    const int hkv = a.H / a.group;
+    if (kVarlen) {
+        // work items are numbered for the longest sequence and skipped where a sequence is shorter or sees
+        // nothing: whatever no item writes must read as zero
+        const size_t es = sizeof(__nv_bfloat16);
+        if ((e = cudaMemsetAsync(a.dq, 0, (size_t)a.total_q * a.H * D * es, st)) != cudaSuccess) return e;
+        if ((e = cudaMemsetAsync(a.dk, 0, (size_t)a.total_k * hkv * D * es, st)) != cudaSuccess) return e;
+        if ((e = cudaMemsetAsync(a.dv, 0, (size_t)a.total_k * hkv * D * es, st)) != cudaSuccess) return e;
+        if (!make_tmap_bf16_strided(&tq, a.q, D, a.total_q, a.H, (uint64_t)a.H * D, D, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16_strided(&tdo, a.dout, D, a.total_q, a.H, (uint64_t)a.H * D, D, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16_strided(&tk, a.k, D, a.total_k, hkv, (uint64_t)hkv * D, D, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16_strided(&tv, a.v, D, a.total_k, hkv, (uint64_t)hkv * D, D, 128, &why)) return cudaErrorInvalidValue;
+    } else {
+        if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16(&tdo, a.dout, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    }
     auto M = [](TmapStorage& t) -> CUtensorMap& { return *reinterpret_cast<CUtensorMap*>(t.bytes); };
-    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, true, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, true, kTrace, kVarlen>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, false, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    e = cudaFuncSetAttribute(attn_bwd_sm100_kernel<D, false, kTrace, kVarlen>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     BwdParams p;
     memset(&p, 0, sizeof(p));
@@ -731,6 +806,10 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.group = a.group;
     p.kv_lens = a.kv_lens;
     p.H = a.H;
+    p.Hkv = hkv;
+    p.cu_q = a.cu_q;
+    p.cu_k = a.cu_k;
+    p.total_q = (int)a.total_q;
     const uintptr_t al = reinterpret_cast<uintptr_t>(a.dq) | reinterpret_cast<uintptr_t>(a.dk) | reinterpret_cast<uintptr_t>(a.dv);
     p.wide_stores = (al & 31) == 0 ? 1 : 0;
     p.n_tiles = (a.L + 127) / 128;
@@ -743,7 +822,7 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.sched_counter = sc.ptr;
     {
         LaunchScope ls(K_BWD_DKV, st);
-        attn_bwd_sm100_kernel<D, true, kTrace><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, true, kTrace, kVarlen><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tk), M(tv), M(tq), M(tdo), p);
     }
     sched_counter_release(sc, st);
@@ -760,7 +839,7 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.sched_counter = sc.ptr;
     {
         LaunchScope ls(K_BWD_DQ, st);
-        attn_bwd_sm100_kernel<D, false, kTrace><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_bwd_sm100_kernel<D, false, kTrace, kVarlen><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             M(tq), M(tdo), M(tk), M(tv), p);
     }
     sched_counter_release(sc, st);
@@ -769,6 +848,7 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
 
 template <int D>
 static cudaError_t launch_bwd_d(const AttnArgs& a, void* ws, cudaStream_t st) {
+    if (a.cu_q != nullptr) return launch_bwd<D, false, true>(a, ws, st);
     if (g_bwd_trace_mode != 0) return launch_bwd<D, true>(a, ws, st);
     return launch_bwd<D, false>(a, ws, st);
 }

@@ -78,6 +78,12 @@ struct FwdParams {
     const int* block_table;        // kPaged only: K and V are page pools (see AttnArgs)
     int page_size, max_pages;
     int kv_chunk;                  // kPaged: keys per output slice when a slice's keys are split (0: not split)
+    // kVarlen: packed batches.  q/out are [total_q, H, D], k/v [total_k, H / group, D]; sequence b owns query
+    // tokens [cu_q[b], cu_q[b+1]) and key tokens [cu_k[b], cu_k[b+1]); slices are (sequence, head) pairs,
+    // S and L above are the LONGEST sequence's counts (they size the grid); lse is [H, total_q].
+    const int* cu_q;
+    const int* cu_k;
+    int total_q;
     long long* trace;   // optional cycle trace of one CTA (debug aid): [3 roles][64 iterations][8 stamps]
     int trace_block;
     int trace_item;     // which of the CTA's work items gets the per-iteration stamps
@@ -157,9 +163,17 @@ struct FwdItem {
     int bh, q0, n_tiles[2], n_max;
     int Lv;   // keys that count for this slice (<= L; fewer with key padding)
     int kvs, key0;   // kPaged: key/value slice and first key of this item
+    // geometry of the item's slice: queries and causal offset (L - S), which are the launch's own for dense
+    // tensors and the sequence's for packed ones; TMA coordinates (first row, slice index) of its Q and K/V
+    // rows; where its output rows and log-sum-exps go
+    int S, off;
+    int qy0, qz, ky0, kz;
+    long long out_row0;   // output row r of the slice is row out_row0 + r of a [rows, out_pitch] matrix, at column out_col
+    int out_pitch, out_col;
+    long long lse0;       // lse[lse0 + r]
 };
-template <bool kPaged = false>
-__device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p) {
+template <bool kPaged = false, bool kVarlen = false>
+__device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p, int D) {
     FwdItem w;
     int qb;
     if (item < p.n_items_heavy) {
@@ -172,12 +186,30 @@ __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p)
         qb = p.n_light - 1 - (r - w.bh * p.n_light);
     }
     w.q0 = qb * 256;
-    const int off = p.L - p.S;
+    int S = p.S, L = p.L;
+    if (kVarlen) {
+        const int b = w.bh / p.H, h = w.bh - b * p.H;
+        const int q_lo = p.cu_q[b], k_lo = p.cu_k[b];
+        S = p.cu_q[b + 1] - q_lo;
+        L = p.cu_k[b + 1] - k_lo;
+        w.qy0 = q_lo; w.qz = h; w.ky0 = k_lo; w.kz = h / p.group;
+        w.out_row0 = q_lo; w.out_pitch = p.H * D; w.out_col = h * D;
+        w.lse0 = (long long)h * p.total_q + q_lo;
+    } else {
+        w.qy0 = 0; w.qz = w.bh / p.q_div; w.ky0 = 0; w.kz = w.bh / p.group;
+        w.out_row0 = (long long)w.bh * p.S; w.out_pitch = D; w.out_col = 0;
+        w.lse0 = (long long)w.bh * p.S;
+    }
+    w.S = S;
+    const int off = L - S;
+    w.off = off;
     if (kPaged) {   // a paged cache may hold empty sequences, and an item may cover one key range of its slice
         w.kvs = w.bh / p.q_div;
         w.key0 = (w.bh - w.kvs * p.q_div) * p.kv_chunk;
         const int len = p.kv_lens ? min(p.L, max(0, p.kv_lens[w.kvs / p.H])) : p.L;
         w.Lv = p.kv_chunk > 0 ? max(0, min(len - w.key0, p.kv_chunk)) : len;
+    } else if (kVarlen) {
+        w.Lv = L;
     } else {
         w.Lv = valid_keys(p.kv_lens, w.bh / p.H, p.L);
     }
@@ -185,11 +217,11 @@ __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p)
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r0 = w.q0 + 128 * i;
-        if (r0 >= p.S) {
+        if (r0 >= S) {
             w.n_tiles[i] = 0;
         } else if (p.causal) {
-            const int last_row = min(r0 + 127, p.S - 1);
-            w.n_tiles[i] = min(n_kv_total, ((last_row + off) >> 7) + 1);
+            const int last_row = min(r0 + 127, S - 1);
+            w.n_tiles[i] = max(0, min(n_kv_total, ((last_row + off) >> 7) + 1));   // off < 0: early rows may see no key
         } else {
             w.n_tiles[i] = n_kv_total;
         }
@@ -204,7 +236,8 @@ __device__ __forceinline__ FwdItem fwd_decode_item(int item, const FwdParams& p)
 // forward problem: sequences may be empty, an item may cover one key range of its slice, rows
 // behind a sequence's end are zeroed in V, and with a block table the K and V tiles are gathered
 // page by page.
-template <int D, bool kTrace, bool kPaged>
+// kVarlen: packed variable-length batches (see FwdParams): per-item sequence geometry, token-major addressing.
+template <int D, bool kTrace, bool kPaged, bool kVarlen>
 __global__ void __launch_bounds__(FwdCfg<D>::kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -232,7 +265,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
     const int warp = uniform_warp_idx();
     const int lane = threadIdx.x & 31;
-    const int off = p.L - p.S;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -295,7 +327,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             __syncwarp();
             mbar_arrive(&bar_sched_empty[k & 1]);
             if (item < 0) break;
-            const FwdItem w = fwd_decode_item<kPaged>(item, p);
+            const FwdItem w = fwd_decode_item<kPaged, kVarlen>(item, p, D);
             const int nt = w.n_tiles[i];
             // per-item stamps of the traced CTA (role slot 0/1 = query tile, row = item number k)
             if (kTrace && p.trace != nullptr && (int)blockIdx.x == p.trace_block && wq == 0 && (threadIdx.x & 31) == 0 && k < 64) {
@@ -303,11 +335,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 p.trace[(i * 64 + k) * 8 + 7] = nt;
             }
             const int row = w.q0 + 128 * i + wq * 32 + lane;
-            if (kPaged && w.Lv == 0 && row < p.S) {   // empty sequence: zero output, log-sum-exp -inf
-                uint4* orow = reinterpret_cast<uint4*>(p.out + ((long long)w.bh * p.S + row) * D);
+            const int off = w.off;
+            if ((kPaged || kVarlen) && nt == 0 && row < w.S) {   // no key at all for this tile's rows: zero output, log-sum-exp -inf
+                uint4* orow = reinterpret_cast<uint4*>(p.out + (w.out_row0 + row) * w.out_pitch + w.out_col);
 #pragma unroll
                 for (int e = 0; e < D / 8; ++e) orow[e] = make_uint4(0u, 0u, 0u, 0u);
-                if (p.lse != nullptr) p.lse[(long long)w.bh * p.S + row] = -INFINITY;
+                if (p.lse != nullptr) p.lse[w.lse0 + row] = -INFINITY;
             }
             if (nt == 0) continue;
             float m2 = -INFINITY;   // running max in the scaled log2 domain
@@ -362,7 +395,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     uint32_t pk[32];
-                    acc = add_f32x2(acc, softmax_exp_half(sr, h, c, m2, pk));
+                    // (packed batches: a row that has met no visible key yet has m2 = -inf; subtracting 0 instead keeps
+                    // its probabilities at exp2(-inf) = 0 rather than NaN)
+                    acc = add_f32x2(acc, softmax_exp_half(sr, h, c, (kVarlen && m2 == -INFINITY) ? 0.f : m2, pk));
 #pragma unroll
                     for (int q4 = 0; q4 < 2; ++q4) {
                         uint32_t t16[16];
@@ -393,9 +428,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(&bar_o_free[i]);
-            const float inv = 1.0f / l;
-            if (row < p.S) {
-                __nv_bfloat16* orow = p.out + ((long long)w.bh * p.S + row) * D;
+            // (a packed sequence with fewer keys than queries under the causal mask has rows that see no key:
+            // their l is 0 and they get a zero output and log-sum-exp -inf)
+            const float inv = (kVarlen && !(l > 0.f)) ? 0.f : 1.0f / l;
+            if (row < w.S) {
+                __nv_bfloat16* orow = p.out + (w.out_row0 + row) * w.out_pitch + w.out_col;
 #pragma unroll
                 for (int cc = 0; cc < D / 32; ++cc) {
 #pragma unroll
@@ -412,7 +449,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                         }
                     }
                 }
-                if (p.lse != nullptr) p.lse[(long long)w.bh * p.S + row] = (m2 + log2f(l)) * 0.6931471805599453f;
+                if (p.lse != nullptr) p.lse[w.lse0 + row] = (kVarlen && !(l > 0.f)) ? -INFINITY : (m2 + log2f(l)) * 0.6931471805599453f;
             }
             __syncwarp();
         }
@@ -446,12 +483,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
                 __syncwarp();
                 if (item < 0) break;
-                const FwdItem w = fwd_decode_item<kPaged>(item, p);
-                const int q_bh = w.bh / p.q_div, kv_bh = w.bh / p.group;   // slices of Q and of K/V this item reads
+                const FwdItem w = fwd_decode_item<kPaged, kVarlen>(item, p, D);
                 auto load_q = [&](int i) {
                     mbar_wait(&bar_q_empty[i], (q_uses[i] & 1) ^ 1, wctx, 5 + i, k);
                     __syncwarp();
-                    load_tile(sQ + i * Cfg::kTileBytes, &tmQ, &bar_q_full[i], w.q0 + 128 * i, q_bh);
+                    load_tile(sQ + i * Cfg::kTileBytes, &tmQ, &bar_q_full[i], w.qy0 + w.q0 + 128 * i, w.qz);
                     ++q_uses[i];
                 };
                 auto load_kv = [&](const CUtensorMap* tm, int j) {   // ring order: K_0, V_0, K_1, V_1, ...
@@ -482,7 +518,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     } else if (kPaged) {   // dense ragged cache: this item's key range of its slice
                         load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], w.key0 + j * 128, w.kvs);
                     } else {
-                        load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], j * 128, kv_bh);
+                        load_tile(sKV + st * Cfg::kTileBytes, tm, &bar_kv_full[st], w.ky0 + j * 128, w.kz);
                     }
                     ++t;
                 };
@@ -547,7 +583,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 if (elect_one()) mbar_arrive(&bar_sched_empty[k & 1]);
                 __syncwarp();
                 if (item < 0) break;
-                const FwdItem w = fwd_decode_item<kPaged>(item, p);
+                const FwdItem w = fwd_decode_item<kPaged, kVarlen>(item, p, D);
                 // S_i(0) for both tiles.  The S/P columns are free: the P V MMAs of the previous item
                 // were issued earlier by this warp and execute in order.
                 if (w.n_max > 0) {
@@ -629,7 +665,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                         ahead_item = next_item(k + 1);
                         __syncwarp();
                         if (ahead_item >= 0) {
-                            const FwdItem wn = fwd_decode_item<kPaged>(ahead_item, p);
+                            const FwdItem wn = fwd_decode_item<kPaged, kVarlen>(ahead_item, p, D);
                             if (wn.n_tiles[0] > 0) {
                                 const uint32_t tn = t + 2 * (uint32_t)w.n_max;
                                 wait_item(tn);
@@ -680,26 +716,32 @@ void attn_fwd_set_trace(long long* device_buf, int block, int item) {
     g_fwd_trace_item = item;
 }
 
-template <int D, bool kTrace, bool kPaged = false>
+template <int D, bool kTrace, bool kPaged = false, bool kVarlen = false>
 static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     using Cfg = FwdCfg<D>;
     TmapStorage tq, tk, tv;
     const char* why = nullptr;
     const int q_div = a.q_div > 0 ? a.q_div : 1;
-    if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH / q_div, 128, &why)) return cudaErrorInvalidValue;
-    if (kPaged && a.block_table != nullptr) {
+    if (kVarlen) {
+        // token-major [tokens, heads, D]: row pitch heads*D elements, "slice" = head at pitch D
+        if (!make_tmap_bf16_strided(&tq, a.q, D, a.total_q, a.H, (uint64_t)a.H * D, D, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16_strided(&tk, a.k, D, a.total_k, a.H / a.group, (uint64_t)(a.H / a.group) * D, D, 128, &why)) return cudaErrorInvalidValue;
+        if (!make_tmap_bf16_strided(&tv, a.v, D, a.total_k, a.H / a.group, (uint64_t)(a.H / a.group) * D, D, 128, &why)) return cudaErrorInvalidValue;
+    } else if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH / q_div, 128, &why)) {
+        return cudaErrorInvalidValue;
+    } else if (kPaged && a.block_table != nullptr) {
         // The pools' page count is not known here; the extent only bounds what TMA may touch, and
         // the block table names the pages that exist.
         const uint64_t slices = 0x7fffffffull;
         const uint32_t box_rows = (uint32_t)std::min(a.page_size, 128);
         if (!make_tmap_bf16(&tk, a.k, D, (uint64_t)a.page_size, slices, box_rows, &why)) return cudaErrorInvalidValue;
         if (!make_tmap_bf16(&tv, a.v, D, (uint64_t)a.page_size, slices, box_rows, &why)) return cudaErrorInvalidValue;
-    } else {
+    } else if (!kVarlen) {
         const long long kv_slices = kPaged ? a.BH / q_div : a.BH / a.group;
         if (!make_tmap_bf16(&tk, a.k, D, a.L, kv_slices, 128, &why)) return cudaErrorInvalidValue;
         if (!make_tmap_bf16(&tv, a.v, D, a.L, kv_slices, 128, &why)) return cudaErrorInvalidValue;
     }
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kTrace, kPaged>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<D, kTrace, kPaged, kVarlen>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     FwdParams p;
@@ -717,12 +759,15 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     p.page_size = a.page_size;
     p.max_pages = a.max_pages;
     p.kv_chunk = a.kv_chunk;
+    p.cu_q = a.cu_q;
+    p.cu_k = a.cu_k;
+    p.total_q = (int)a.total_q;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = device_status_word();
     p.trace = g_fwd_trace;
     p.trace_block = g_fwd_trace_block;
     p.trace_item = g_fwd_trace_item;
-    p.s0_ahead = kPaged ? 0 : 1;
+    p.s0_ahead = (kPaged || kVarlen) ? 0 : 1;
     p.wide_stores = (reinterpret_cast<uintptr_t>(a.out) & 31) == 0 ? 1 : 0;
     p.n_items = (int)(a.BH * p.n_qblk);
     {
@@ -742,7 +787,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
     unsigned grid = (unsigned)std::min<long long>(p.n_items, n_sm);
     {
         LaunchScope ls(K_FWD_TC, st);
-        attn_fwd_sm100_kernel<D, kTrace, kPaged><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        attn_fwd_sm100_kernel<D, kTrace, kPaged, kVarlen><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
             *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
             *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
     }
@@ -753,6 +798,7 @@ static cudaError_t launch_fwd(const AttnArgs& a, cudaStream_t st) {
 template <int D>
 static cudaError_t launch_fwd_d(const AttnArgs& a, cudaStream_t st) {
     if (a.cache_mode) return launch_fwd<D, false, true>(a, st);
+    if (a.cu_q != nullptr) return launch_fwd<D, false, false, true>(a, st);
     if (g_fwd_trace != nullptr) return launch_fwd<D, true>(a, st);
     return launch_fwd<D, false>(a, st);
 }

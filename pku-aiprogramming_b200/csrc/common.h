@@ -38,6 +38,12 @@ struct AttnArgs {
     int page_size, max_pages;
     int kv_chunk;
     int cache_mode;
+    // packed variable-length batches (tensor-core kernels only): cu_q / cu_k are device int32 [n_seq + 1]
+    // cumulative token counts; q, out, dout, dq are [total_q, H, D], k, v, dk, dv [total_k, H / group, D],
+    // lse [H, total_q]; BH = n_seq * H slices; S and L hold the longest sequence's counts.
+    const int* cu_q;
+    const int* cu_k;
+    long long total_q, total_k;
 };
 // keys that count for batch entry b (device side)
 __device__ __forceinline__ int valid_keys(const int* kv_lens, long long b, int L) {
@@ -166,5 +172,9 @@ cudaError_t attn_decode_static(const AttnArgs& a, const DecodePlan& plan, cudaSt
 struct TmapStorage { alignas(64) unsigned char bytes[128]; };
 bool make_tmap_bf16(TmapStorage* out, const void* base, uint64_t cols, uint64_t rows, uint64_t slices,
                     uint32_t box_rows, const char** why);
+// Same box over an array whose rows are `row_pitch` elements apart and whose slices `slice_pitch` elements
+// (token-major [rows, slices, cols]: row_pitch = slices * cols, slice_pitch = cols).
+bool make_tmap_bf16_strided(TmapStorage* out, const void* base, uint64_t cols, uint64_t rows, uint64_t slices,
+                            uint64_t row_pitch, uint64_t slice_pitch, uint32_t box_rows, const char** why);
 
 }  // namespace ttk

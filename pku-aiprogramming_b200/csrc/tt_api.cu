@@ -189,19 +189,24 @@ static EncodeTiledFn get_encode_fn() {
 
 bool make_tmap_bf16(TmapStorage* out, const void* base, uint64_t cols, uint64_t rows, uint64_t slices,
                     uint32_t box_rows, const char** why) {
+    return make_tmap_bf16_strided(out, base, cols, rows, slices, cols, cols * rows, box_rows, why);
+}
+
+bool make_tmap_bf16_strided(TmapStorage* out, const void* base, uint64_t cols, uint64_t rows, uint64_t slices,
+                            uint64_t row_pitch, uint64_t slice_pitch, uint32_t box_rows, const char** why) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) {
         *why = "cuTensorMapEncodeTiled entry point not available";
         fail(TT_ERR_CUDA, "%s", *why);
         return false;
     }
-    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (cols * 2) % 16 != 0) {
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_pitch * 2) % 16 != 0 || (slice_pitch * 2) % 16 != 0) {
         *why = "tensor base or row pitch not 16-byte aligned";
         fail(TT_ERR_BAD_SHAPE, "%s", *why);
         return false;
     }
     cuuint64_t gdim[3] = {cols, rows, slices};
-    cuuint64_t gstride[2] = {cols * 2, cols * rows * 2};
+    cuuint64_t gstride[2] = {row_pitch * 2, slice_pitch * 2};
     cuuint32_t box[3] = {64, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(reinterpret_cast<CUtensorMap*>(out->bytes), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
@@ -472,6 +477,94 @@ int tt_attn_bwd_padded(const tt_attn_desc* desc, const void* q, const void* k, c
                        void* workspace, size_t workspace_bytes, void* stream) {
     return attn_bwd_common("tt_attn_bwd_padded", desc, q, k, v, kv_lens, out, lse, dout, dq, dk, dv, workspace,
                            workspace_bytes, stream);
+}
+
+// ---- packed variable-length batches
+static int resolve_varlen(const tt_varlen_desc* d, AttnArgs* a, const char* who) {
+    if (!d) return fail(TT_ERR_NULL, "%s: desc is null", who);
+    if (d->n_seq < 1 || d->H < 1 || d->max_q < 1 || d->max_k < 1 || d->total_q < 1 || d->total_k < 1)
+        return fail(TT_ERR_BAD_SHAPE, "%s: n_seq=%d H=%d max_q=%d max_k=%d total_q=%lld total_k=%lld must all be >= 1", who,
+                    d->n_seq, d->H, d->max_q, d->max_k, (long long)d->total_q, (long long)d->total_k);
+    if (d->max_q > d->total_q || d->max_k > d->total_k)
+        return fail(TT_ERR_BAD_SHAPE, "%s: the longest sequence (%d / %d) cannot exceed the token totals", who, d->max_q, d->max_k);
+    if (d->total_q >= (1LL << 31) || d->total_k >= (1LL << 31))
+        return fail(TT_ERR_BAD_SHAPE, "%s: more than 2^31-1 tokens", who);
+    if (d->dtype != TT_F32 && d->dtype != TT_BF16) return fail(TT_ERR_BAD_DTYPE, "%s: dtype %d unknown", who, d->dtype);
+    if (d->dtype != TT_BF16 || !(d->D == 64 || d->D == 128))
+        return fail(TT_ERR_UNSUPPORTED, "%s: packed batches run on the tensor-core kernels only: bf16 with D = 64 or 128 "
+                    "(got dtype %d, D=%d)", who, d->dtype, d->D);
+    if (!std::isfinite(d->scale)) return fail(TT_ERR_BAD_SHAPE, "%s: scale is not finite", who);
+    const int hkv = d->Hkv > 0 ? d->Hkv : d->H;
+    if (hkv > d->H || d->H % hkv != 0) return fail(TT_ERR_BAD_SHAPE, "%s: Hkv=%d must divide H=%d", who, d->Hkv, d->H);
+    memset(a, 0, sizeof(*a));
+    a->BH = (long long)d->n_seq * d->H;
+    a->group = d->H / hkv;
+    a->H = d->H;
+    a->S = d->max_q;
+    a->L = d->max_k;
+    a->D = d->D;
+    a->causal = d->causal ? 1 : 0;
+    a->bf16 = 1;
+    a->scale = d->scale > 0.f ? d->scale : 1.0f / sqrtf((float)d->D);
+    a->total_q = d->total_q;
+    a->total_k = d->total_k;
+    const long long tiles = ((long long)std::max(d->max_q, d->max_k) + 127) / 128;
+    if (a->BH * tiles >= (1LL << 31)) return fail(TT_ERR_BAD_SHAPE, "%s: problem too large for the work-item numbering", who);
+    return TT_OK;
+}
+
+int tt_attn_fwd_varlen(const tt_varlen_desc* desc, const void* q, const void* k, const void* v, const int32_t* cu_q,
+                       const int32_t* cu_k, void* out, float* lse, void* stream) {
+    AttnArgs a;
+    int rc = resolve_varlen(desc, &a, "tt_attn_fwd_varlen");
+    if (rc != TT_OK) return rc;
+    if (!q || !k || !v || !out || !cu_q || !cu_k)
+        return fail(TT_ERR_NULL, "tt_attn_fwd_varlen: q, k, v, out, cu_q and cu_k must be non-null");
+    if (!(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out)))
+        return fail(TT_ERR_BAD_SHAPE, "tt_attn_fwd_varlen: q, k, v, out must be 16-byte aligned");
+    if ((rc = check_device()) != TT_OK) return rc;
+    g_err[0] = 0;
+    a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
+    a.cu_q = cu_q; a.cu_k = cu_k;
+    cudaError_t e = attn_fwd_sm100(a, (cudaStream_t)stream);
+    if (e == cudaErrorInvalidValue && g_err[0]) return TT_ERR_CUDA;
+    if (e != cudaSuccess) return cuda_fail(e, "tt_attn_fwd_varlen");
+    return TT_OK;
+}
+
+size_t tt_attn_bwd_varlen_workspace_bytes(const tt_varlen_desc* desc) {
+    AttnArgs a;
+    if (resolve_varlen(desc, &a, "tt_attn_bwd_varlen_workspace_bytes") != TT_OK) return 0;
+    static const int one = 0;
+    a.cu_q = a.cu_k = &one;   // marks the packed layout for the size computation; never dereferenced
+    return attn_bwd_sm100_workspace(a);
+}
+
+int tt_attn_bwd_varlen(const tt_varlen_desc* desc, const void* q, const void* k, const void* v, const int32_t* cu_q,
+                       const int32_t* cu_k, const void* out, const float* lse, const void* dout, void* dq, void* dk,
+                       void* dv, void* workspace, size_t workspace_bytes, void* stream) {
+    AttnArgs a;
+    int rc = resolve_varlen(desc, &a, "tt_attn_bwd_varlen");
+    if (rc != TT_OK) return rc;
+    if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv || !cu_q || !cu_k)
+        return fail(TT_ERR_NULL, "tt_attn_bwd_varlen: all tensor pointers, cu_q and cu_k must be non-null");
+    if (!(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(dout) && aligned16(dq) && aligned16(dk) &&
+          aligned16(dv)))
+        return fail(TT_ERR_BAD_SHAPE, "tt_attn_bwd_varlen: tensors must be 16-byte aligned");
+    const size_t need = tt_attn_bwd_varlen_workspace_bytes(desc);
+    if (!workspace || workspace_bytes < need)
+        return fail(TT_ERR_WORKSPACE, "tt_attn_bwd_varlen: workspace of %zu bytes required, %zu given", need, workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+        return fail(TT_ERR_WORKSPACE, "tt_attn_bwd_varlen: workspace must be 256-byte aligned");
+    if ((rc = check_device()) != TT_OK) return rc;
+    g_err[0] = 0;
+    a.q = q; a.k = k; a.v = v; a.out = const_cast<void*>(out); a.lse = const_cast<float*>(lse); a.dout = dout;
+    a.dq = dq; a.dk = dk; a.dv = dv;
+    a.cu_q = cu_q; a.cu_k = cu_k;
+    cudaError_t e = attn_bwd_two_pass(a, workspace, (cudaStream_t)stream);
+    if (e == cudaErrorInvalidValue && g_err[0]) return TT_ERR_CUDA;
+    if (e != cudaSuccess) return cuda_fail(e, "tt_attn_bwd_varlen");
+    return TT_OK;
 }
 
 size_t tt_attn_decode_workspace_bytes(const tt_attn_desc* desc) {

@@ -97,6 +97,47 @@ def attention_backward(q, k, v, out, lse, dout, causal=False, scale=None, worksp
     return dq, dk, dv
 
 
+def _varlen_desc(q, k, cu_q, cu_k, max_q, max_k, causal, scale):
+    for name, t in (("q", q), ("k", k)):
+        if t.dim() != 3 or not t.is_cuda or not t.is_contiguous() or t.dtype != torch.bfloat16:
+            raise ValueError(f"{name} must be a contiguous CUDA bfloat16 tensor [tokens, heads, D]")
+    for name, t in (("cu_q", cu_q), ("cu_k", cu_k)):
+        if t.dtype != torch.int32 or not t.is_cuda or not t.is_contiguous() or t.dim() != 1 or t.numel() != cu_q.numel():
+            raise ValueError(f"{name} must be a contiguous CUDA int32 vector of n_seq + 1 cumulative token counts")
+    H, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
+    if k.shape[2] != D or H % Hkv != 0:
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)} k {tuple(k.shape)}")
+    return capi.VarlenDesc(cu_q.numel() - 1, H, Hkv, D, capi.TT_BF16, 1 if causal else 0, float(scale) if scale else 0.0,
+                           int(max_q), int(max_k), q.shape[0], k.shape[0])
+
+
+def attention_forward_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal=False, scale=None, out=None, lse=None):
+    """Packed variable-length batch: q `[total_q,H,D]`, k, v `[total_k,Hkv,D]`, cu_q / cu_k int32 `[n_seq+1]`
+    (CUDA) cumulative token counts, max_q / max_k the longest sequence.  Returns (out `[total_q,H,D]`,
+    lse `[H,total_q]`)."""
+    d = _varlen_desc(q, k, cu_q, cu_k, max_q, max_k, causal, scale)
+    with torch.cuda.device(q.device):
+        out = torch.empty_like(q) if out is None else out
+        lse = torch.empty((q.shape[1], q.shape[0]), dtype=torch.float32, device=q.device) if lse is None else lse
+        capi.check(capi.lib.tt_attn_fwd_varlen(ctypes.byref(d), _p(q), _p(k), _p(v), _p(cu_q), _p(cu_k), _p(out), _p(lse),
+                                               _stream_ptr(q)))
+    return out, lse
+
+
+def attention_backward_varlen(q, k, v, cu_q, cu_k, max_q, max_k, out, lse, dout, causal=False, scale=None, workspace=None):
+    """(dq, dk, dv) of the packed batch; `out`, `lse` from `attention_forward_varlen`."""
+    d = _varlen_desc(q, k, cu_q, cu_k, max_q, max_k, causal, scale)
+    with torch.cuda.device(q.device):
+        need = int(capi.lib.tt_attn_bwd_varlen_workspace_bytes(ctypes.byref(d)))
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        capi.check(capi.lib.tt_attn_bwd_varlen(ctypes.byref(d), _p(q), _p(k), _p(v), _p(cu_q), _p(cu_k), _p(out), _p(lse),
+                                               _p(dout), _p(dq), _p(dk), _p(dv), _p(workspace),
+                                               workspace.numel() * workspace.element_size(), _stream_ptr(q)))
+    return dq, dk, dv
+
+
 def set_backward_deterministic(on: bool) -> None:
     """True: the tensor-core backward always runs its two-pass, bit-reproducible kernels; False (the
     default): whichever kernel measured faster for the shape, which at head dim 64 is the single-pass one,
