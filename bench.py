@@ -46,8 +46,10 @@ WORKLOADS = {
 # captured on a few slices of the workload's slice shape and scale with the slice count (the kernels walk
 # the slices one after the other, so a slice's traffic does not depend on how many follow).
 NCU_TRAFFIC_BYTES = {
-    "cfg3": {"attn_fwd_sm100": 587.6e6, "attn_bwd_sm100_dkv": 850.8e6, "attn_bwd_sm100_dq": 727.3e6},
-    "cfg5_per_slice": {},
+    "cfg3": {"attn_fwd_sm100": 591.5e6, "attn_bwd_sm100_dkv": 851.6e6, "attn_bwd_sm100_dq": 728.4e6,
+             "attn_bwd_fused_sm100": 1507.7e6},
+    "cfg2": {"attn_fwd_sm100": 52.3e6, "attn_bwd_fused_sm100": 132.1e6},
+    "cfg5_per_slice": {"attn_fwd_sm100": 26.08e6, "attn_bwd_sm100_dkv": 35.10e6, "attn_bwd_sm100_dq": 34.66e6},
     # config 4 = 8 x the captured batch-8 launch (the full launch holds 8.6 GB, too large a capture)
     "decode": {"attn_decode": 8.637e9},
 }
@@ -335,7 +337,10 @@ def run_workload(tt, name, steps, warmup, world, rank, dev, peaks, e2e_steps, sa
         traffic = dict(NCU_TRAFFIC_BYTES["cfg3"]); traffic_note = None
     elif name == "cfg5":
         traffic = {k_: v_ * n_local for k_, v_ in NCU_TRAFFIC_BYTES["cfg5_per_slice"].items()}
-        traffic_note = "ncu capture of two S=32768 slices, scaled by the slice count of the launch"
+        traffic_note = ("ncu capture of two S=32768 slices, scaled by the slice count of the launch (inputs cross DRAM "
+                        "once; the outputs of the two-slice capture stayed in L2, add 8.4-16.8 MB per slice for them)")
+    elif name == "cfg2":
+        traffic = dict(NCU_TRAFFIC_BYTES["cfg2"]); traffic_note = None
     else:
         traffic, traffic_note = {}, None
     for kname, (ms, n) in prof.items():
@@ -683,11 +688,16 @@ def main():
     ap.add_argument("--no-varlen", action="store_true", help="skip the packed variable-length side measurement at N=1")
     ap.add_argument("--no-cfg3", action="store_true", help="skip the S=4096 side measurement at N=1")
     ap.add_argument("--no-cfg2", action="store_true", help="skip the S=1024, D=64 side measurement at N=1")
+    ap.add_argument("--heads", type=int, default=0, help="override the head count of the main workload (small profiler "
+                    "captures of the same slice shape; the line is then not the benchmark line)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-verify", action="store_true", help="skip the oracle re-check of the timed outputs")
     ap.add_argument("--decode-batch", type=int, default=64, help="batch of the decode leg (64 = benchmark configuration 4)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.heads > 0:
+        WORKLOADS[args.workload] = dict(WORKLOADS[args.workload], H=args.heads,
+                                        desc=WORKLOADS[args.workload]["desc"] + f" (heads overridden: {args.heads})")
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
