@@ -239,6 +239,16 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* desc, const void* q, const void* k,
  * blocks go to size-bucketed free lists of the current device and are reused. */
 int tt_alloc(size_t bytes, void** out_ptr);
 int tt_free(void* ptr);   /* does not synchronise: free a block only after the work that uses it has completed */
+/* Host storage of the tensor class goes through the library too (plain malloc/free underneath), so that
+ * the two rules below cover host and device buffers alike. */
+int tt_host_alloc(size_t bytes, void** out_ptr);
+int tt_host_free(void* ptr);
+/* Shared ownership for zero-copy views (DLPack exports of the tensor class, src/bind_Tensor.cpp of the
+ * reference has no such export): while a buffer is retained, tt_free / tt_host_free of it only mark it;
+ * the block goes back to the pool (or the heap) when the last holder releases it.  So a tensor may be
+ * resized, moved between host and device or destroyed while a view of its old buffer is alive. */
+int tt_buffer_retain(void* ptr);
+int tt_buffer_release(void* ptr);
 int tt_pool_trim(void);                                     /* return cached blocks to the driver */
 int tt_pool_stats(size_t* bytes_in_use, size_t* bytes_cached, uint64_t* n_driver_allocs);
 

@@ -64,6 +64,10 @@ SIGNATURES = {
     "tt_attn_fwd_bwd_host": (c_int, [_DP, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "tt_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
     "tt_free": (c_int, [_P]),
+    "tt_host_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),
+    "tt_host_free": (c_int, [_P]),
+    "tt_buffer_retain": (c_int, [_P]),
+    "tt_buffer_release": (c_int, [_P]),
     "tt_pool_trim": (c_int, []),
     "tt_pool_stats": (c_int, [POINTER(c_size_t), POINTER(c_size_t), POINTER(c_uint64)]),
     "tt_shard_range": (c_int, [c_int64, c_int32, c_int32, POINTER(c_int64), POINTER(c_int64)]),

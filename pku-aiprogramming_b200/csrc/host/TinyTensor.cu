@@ -1,5 +1,5 @@
 // Implementation of TinyTensor<T> (see TinyTensor.h).  Device storage is pooled (tt_alloc /
-// tt_free); host storage is plain new[]/delete[].  The element-wise helpers are simple
+// tt_free); host storage comes from tt_host_alloc / tt_host_free.  The element-wise helpers are simple
 // grid-stride kernels with 64-bit indices: they exist for API completeness, the attention
 // kernels do the heavy lifting elsewhere.
 #include "TinyTensor.h"
@@ -116,15 +116,17 @@ void require_device(const std::string& device) {
 template <typename T>
 T* allocate(const std::string& device, size_t n) {
     if (n == 0) return nullptr;
-    if (device == "cpu") return new T[n];
     void* p = nullptr;
-    tt_check(tt_alloc(n * sizeof(T), &p), "device allocation");
+    // host and device storage both come from the library, which keeps a buffer alive while an
+    // exported view (DLPack) of it exists, whatever happens to the tensor meanwhile
+    if (device == "cpu") tt_check(tt_host_alloc(n * sizeof(T), &p), "host allocation");
+    else tt_check(tt_alloc(n * sizeof(T), &p), "device allocation");
     return static_cast<T*>(p);
 }
 template <typename T>
 void release(const std::string& device, T* p) noexcept {
     if (!p) return;
-    if (device == "cpu") delete[] p;
+    if (device == "cpu") tt_host_free(p);
     else tt_free(p);
 }
 // copy n elements between any two placements

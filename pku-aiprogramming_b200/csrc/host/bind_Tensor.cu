@@ -12,13 +12,17 @@
 #include <sstream>
 
 #include "TinyTensor.h"
+#include "tt_attn.h"
 
 namespace py = pybind11;
 
 // ---- DLPack exchange -------------------------------------------------------------------------
 // Export (`__dlpack__`, `__dlpack_device__`): zero-copy view of the tensor's buffer for any
 // consumer of the protocol (torch.from_dlpack, np.from_dlpack for host tensors).  The capsule
-// keeps the Python tensor object alive until the consumer's deleter runs.  Import
+// keeps the Python tensor object alive until the consumer's deleter runs, and retains the BUFFER
+// (tt_buffer_retain): if the tensor is resized, moved to the other device, assigned to or used as a
+// layer output of another shape meanwhile, its old block stays with the view and goes back to the
+// pool only when the view's deleter has run.  Import
 // (`from_dlpack`): a deep copy (device to device when the producer's data is on a GPU), because a
 // TinyTensor owns its buffer.  The reference has neither; its only way out of a tensor is
 // get_data() -> Python list (src/bind_Tensor.cpp:26 of the reference project).
@@ -32,6 +36,7 @@ template <> DLDataType dl_dtype<__nv_bfloat16>() { return DLDataType{kDLBfloat, 
 
 struct DlExport {
     py::object owner;                 // keeps the TinyTensor alive
+    void* retained = nullptr;         // the buffer the view shows (shared ownership until the deleter runs)
     std::vector<int64_t> shape, strides;
     DLManagedTensor managed;
 };
@@ -39,7 +44,9 @@ struct DlExport {
 void dl_export_deleter(DLManagedTensor* m) {
     if (!m) return;
     py::gil_scoped_acquire gil;
-    delete static_cast<DlExport*>(m->manager_ctx);
+    auto* ex = static_cast<DlExport*>(m->manager_ctx);
+    if (ex->retained) tt_buffer_release(ex->retained);
+    delete ex;
 }
 
 void dl_capsule_destructor(PyObject* cap) {
@@ -97,6 +104,8 @@ py::capsule dlpack_export(py::object self, py::object /*stream*/) {
     } else {
         d.device = DLDevice{kDLCPU, 0};
     }
+    ex->retained = t.p_data;
+    tt_buffer_retain(ex->retained);
     ex->managed.manager_ctx = ex;
     ex->managed.deleter = dl_export_deleter;
     return py::capsule(&ex->managed, "dltensor", dl_capsule_destructor);

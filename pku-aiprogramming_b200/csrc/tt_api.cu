@@ -12,6 +12,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -242,6 +243,25 @@ static Pool* pool_for_current_device() {
     g_pools[dev] = p;
     return p;
 }
+// Buffers with live views (tt_buffer_retain): pointer -> holders, and what a free that arrived meanwhile
+// asked for (0 nothing, 1 back to this pool, 2 host free).
+struct Retained {
+    int holders = 0;
+    int pending = 0;
+    Pool* pool = nullptr;
+};
+static std::mutex g_retained_mu;
+static std::unordered_map<void*, Retained> g_retained;
+// true: the buffer has holders, the free was recorded and must not happen now
+static bool defer_free(void* ptr, int kind, Pool* pool) {
+    std::lock_guard<std::mutex> lk(g_retained_mu);
+    auto it = g_retained.find(ptr);
+    if (it == g_retained.end() || it->second.holders <= 0) return false;
+    it->second.pending = kind;
+    it->second.pool = pool;
+    return true;
+}
+
 // Buckets: powers of two up to 1 MiB, multiples of 2 MiB above.
 static size_t bucket_of(size_t n) {
     if (n <= 512) return 512;
@@ -298,9 +318,59 @@ int tt_alloc(size_t bytes, void** out_ptr) {
     return TT_OK;
 }
 
+static int pool_put_back(Pool* pool, void* ptr) {
+    std::lock_guard<std::mutex> lk(pool->mu);
+    auto it = pool->live.find(ptr);
+    if (it == pool->live.end()) return fail(TT_ERR_NULL, "tt_free: pointer %p was not allocated by tt_alloc on this device", ptr);
+    size_t b = it->second;
+    pool->live.erase(it);
+    pool->in_use -= b;
+    pool->cached += b;
+    pool->free_by_size[b].push_back(ptr);
+    return TT_OK;
+}
+
+int tt_host_alloc(size_t bytes, void** out_ptr) {
+    if (!out_ptr) return fail(TT_ERR_NULL, "tt_host_alloc: out_ptr is null");
+    *out_ptr = nullptr;
+    if (bytes == 0) return TT_OK;
+    void* p = malloc(bytes);
+    if (!p) return fail(TT_ERR_CUDA, "tt_host_alloc: out of host memory (%zu bytes)", bytes);
+    *out_ptr = p;
+    return TT_OK;
+}
+int tt_host_free(void* ptr) {
+    if (!ptr) return TT_OK;
+    if (defer_free(ptr, 2, nullptr)) return TT_OK;
+    free(ptr);
+    return TT_OK;
+}
+int tt_buffer_retain(void* ptr) {
+    if (!ptr) return TT_OK;
+    std::lock_guard<std::mutex> lk(g_retained_mu);
+    g_retained[ptr].holders += 1;
+    return TT_OK;
+}
+int tt_buffer_release(void* ptr) {
+    if (!ptr) return TT_OK;
+    Retained r;
+    {
+        std::lock_guard<std::mutex> lk(g_retained_mu);
+        auto it = g_retained.find(ptr);
+        if (it == g_retained.end()) return fail(TT_ERR_NULL, "tt_buffer_release: pointer %p is not retained", ptr);
+        if (--it->second.holders > 0) return TT_OK;
+        r = it->second;
+        g_retained.erase(it);
+    }
+    if (r.pending == 1) return pool_put_back(r.pool, ptr);   // the free that arrived while views were alive
+    if (r.pending == 2) free(ptr);
+    return TT_OK;
+}
+
 int tt_free(void* ptr) {
     if (!ptr) return TT_OK;
     Pool* pool = pool_for_current_device();
+    if (defer_free(ptr, 1, pool)) return TT_OK;
     std::lock_guard<std::mutex> lk(pool->mu);
     auto it = pool->live.find(ptr);
     if (it == pool->live.end()) return fail(TT_ERR_NULL, "tt_free: pointer %p was not allocated by tt_alloc on this device", ptr);

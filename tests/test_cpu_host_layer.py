@@ -163,3 +163,22 @@ def test_ops_without_device_form_are_marked(opt):
     ok = {n for n in dir(opt) if isinstance(getattr(opt, n), type) and getattr(getattr(opt, n), "device_ok", False)}
     assert {"EWiseAdd", "AddScalar", "MulScalar", "Negate", "Attention", "Softmax", "FC"} <= ok
     assert not ({"Exp", "MatMul", "Summation", "EWiseDiv", "Reshape"} & ok)
+
+
+def test_exported_view_keeps_its_buffer_when_the_tensor_changes(mods):
+    """A DLPack view shares ownership of the buffer it shows: resizing the tensor (which gives it a new
+    buffer) or dropping it leaves the view's data intact, and the old block is handed back only when the
+    view goes away."""
+    import gc
+    mt, _ = mods
+    t = mt.Tensor_float(np.arange(12, dtype=np.float32).reshape(3, 4), "cpu")
+    view = np.from_dlpack(t)
+    keep = view.copy()
+    t.resize([64, 64])                       # different element count: the tensor takes a new buffer
+    other = [mt.Tensor_float(np.full((3, 4), 7.0, np.float32), "cpu") for _ in range(8)]   # would reuse a freed block
+    assert np.array_equal(view, keep)
+    del t
+    gc.collect()
+    assert np.array_equal(view, keep)
+    del view, other
+    gc.collect()
