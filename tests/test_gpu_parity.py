@@ -472,3 +472,32 @@ def test_backward_many_short_items(tt, oracle):
         assert oracle.max_abs_err(f(out, b, h), o_r) <= 2e-2
         for got, ref in ((dq, dq_r), (dk, dk_r), (dv, dv_r)):
             assert oracle.max_abs_err(f(got, b, h), ref) <= oracle.bf16_grad_tol(ref)
+
+
+def test_short_launches_beside_a_long_one_never_share_a_work_counter(tt, oracle):
+    """The persistent kernels draw their work items from counters of a small per-device set.  More short
+    launches than the set has counters run on one stream while ONE long launch is still in flight on
+    another: the counter of the long launch comes round again, and the launch that is handed it must
+    queue behind the long one instead of sharing it (two kernels on one counter steal each other's items
+    and leave output rows unwritten).  Both streams' results must equal those of the same calls run
+    alone."""
+    g = torch.Generator(device="cuda").manual_seed(123)
+    mk = lambda *shape: (torch.randn(shape, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    ql, kl, vl = mk(1, 16, 16384, 128), mk(1, 16, 16384, 128), mk(1, 16, 16384, 128)      # ~2 ms of forward
+    qs, ks, vs = mk(1, 2, 256, 128), mk(1, 2, 256, 128), mk(1, 2, 256, 128)
+    want_long, _ = tt.attention_forward(ql, kl, vl, causal=True)
+    want_short, _ = tt.attention_forward(qs, ks, vs, causal=True)
+    torch.cuda.synchronize()
+    sa, sb = torch.cuda.Stream(), torch.cuda.Stream()
+    out_long = torch.full_like(ql, float("nan"))
+    outs_short = [torch.full_like(qs, float("nan")) for _ in range(100)]
+    with torch.cuda.stream(sa):
+        tt.attention_forward(ql, kl, vl, causal=True, out=out_long)
+    with torch.cuda.stream(sb):
+        for o in outs_short:
+            tt.attention_forward(qs, ks, vs, causal=True, out=o)
+    torch.cuda.synchronize()
+    tt.check_device_status()
+    assert torch.equal(out_long, want_long)
+    for o in outs_short:
+        assert torch.equal(o, want_short)
