@@ -108,15 +108,15 @@ int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const
                    void* out, float* lse, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Decode for callers that cannot allocate device memory.  No counterpart in the reference:
- * it exists for hosts that run with a frozen memory map -- code inside a CUDA-graph capture
- * or a real-time serving loop that pre-allocated everything, or a plugin sandbox whose policy
- * forbids cudaMalloc -- and therefore cannot supply the partials workspace tt_attn_decode
- * wants.  It always runs the split-KV kernels described above (tt_attn_decode sends groups of
+ * it exists for hosts that run with a frozen memory map -- a real-time serving loop that
+ * pre-allocated everything at start-up and may not touch the allocator again, or a plugin sandbox
+ * whose policy forbids cudaMalloc -- and therefore cannot supply the partials workspace
+ * tt_attn_decode wants.  It always runs the split-KV kernels described above (tt_attn_decode sends groups of
  * four and more query heads per key/value head to the tensor-core forward kernel instead), so its
  * results match tt_attn_decode within the bf16 tolerance, bit for bit where both take the same
  * kernels; the split-KV partials go to an 8 MiB array built into the library's device image (each
- * GPU that loads the library keeps those 8 MiB until the process exits).  The call itself performs no cudaMalloc/cudaFree and
- * calls no allocating library routine; q, k, v, out (and lse) are still the caller's.
+ * GPU that loads the library keeps those 8 MiB until the process exits).  The call itself performs
+ * no cudaMalloc/cudaFree and calls no allocating library routine; q, k, v, out (and lse) are still the caller's.
  *   - bf16, D = 64 or 128, S = 1 only; problems whose partials exceed the array are refused
  *     with TT_ERR_WORKSPACE and a message naming both sizes (B*H*(D+2)*4*splits bytes; e.g.
  *     B*H up to ~4000 slices at D = 128 with 4 key ranges each).

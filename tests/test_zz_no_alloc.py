@@ -1,7 +1,7 @@
 """Decode through the entry point that allocates nothing (`tt_attn_decode_static`).
 
 Some hosts of this library may not allocate device memory at call time -- a serving loop
-that froze its memory map, a capture region, a sandboxed plugin -- so they cannot hand
+that froze its memory map after start-up, a sandboxed plugin -- so they cannot hand
 `tt_attn_decode` its partials workspace.  For them the library carries a fixed 8 MiB scratch
 array of its own.  This test drives that entry point through the C ABI twice in a row (the
 second call finds the array dirty from the first) and checks both results against the
