@@ -99,6 +99,8 @@ DEBUG_SIGNATURES = {
     "tt_debug_fwd_trace": (c_int, [_P, c_int32, c_int32]),
     "tt_debug_bwd_trace": (c_int, [_P, c_int32, c_int32]),
     "tt_mgpu_set_collectives": (c_int, [_P]),
+    "tt_debug_fail_host_call_after": (c_int, [c_int64]),
+    "tt_debug_guard_syncs": (c_int64, []),
 }
 
 

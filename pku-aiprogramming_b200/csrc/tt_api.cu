@@ -957,6 +957,7 @@ cudaStream_t host_call_stream() {
 // calls queue copies and kernels on non-blocking streams and then let pooled device buffers go: on an
 // error exit in the middle of the sequence that work may still be queued, and tt_free hands a block to
 // the next tt_alloc at once.  Declared AFTER the DevBufs, so that it runs before their destructors.
+std::atomic<long long> g_guard_syncs{0};
 struct SyncOnExit {
     cudaStream_t s[3] = {nullptr, nullptr, nullptr};
     int n = 0;
@@ -965,11 +966,27 @@ struct SyncOnExit {
     ~SyncOnExit() {
         if (!armed) return;
         for (int i = 0; i < n; ++i) cudaStreamSynchronize(s[i]);
+        g_guard_syncs.fetch_add(1);
     }
 };
+// Host-made failure for tests: while the countdown is armed, the check that brings it to zero reports
+// cudaErrorUnknown although the runtime call it guards was made and succeeded -- so the call returns in
+// the middle of its sequence with copies and kernels still queued, which is the case SyncOnExit exists
+// for.  Nothing on the device fails.
+std::atomic<long long> g_fail_countdown{-1};
+inline cudaError_t injected(cudaError_t e) {
+    if (e != cudaSuccess || g_fail_countdown.load(std::memory_order_relaxed) < 0) return e;
+    return g_fail_countdown.fetch_sub(1) == 0 ? cudaErrorUnknown : e;
+}
 #define TT_TRY(x) do { int rc__ = (x); if (rc__ != TT_OK) return rc__; } while (0)
-#define TT_CUDA(x, what) do { cudaError_t e__ = (x); if (e__ != cudaSuccess) return cuda_fail(e__, what); } while (0)
+#define TT_CUDA(x, what) do { cudaError_t e__ = injected(x); if (e__ != cudaSuccess) return cuda_fail(e__, what); } while (0)
 }  // namespace
+
+int tt_debug_fail_host_call_after(int64_t checks) {
+    g_fail_countdown.store(checks < 0 ? -1 : (long long)checks);
+    return TT_OK;
+}
+int64_t tt_debug_guard_syncs(void) { return (int64_t)g_guard_syncs.load(); }
 
 int tt_attn_fwd_host(const tt_attn_desc* d, const void* q, const void* k, const void* v, void* out, float* lse) {
     AttnArgs a;

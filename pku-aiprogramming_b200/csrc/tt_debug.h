@@ -22,6 +22,16 @@ int tt_debug_fwd_trace(void* device_buf, int32_t block, int32_t item);
  * launch, 3 the single-pass kernel. */
 int tt_debug_bwd_trace(void* device_buf, int32_t block, int32_t pass);
 
+/* A failure made on the host, for tests of the error exits of the host-buffer calls (tt_attn_*_host):
+ * the (checks+1)-th CUDA runtime result those calls inspect from now on is reported as cudaErrorUnknown
+ * although the runtime call was made and succeeded, so the entry point returns TT_ERR_CUDA in the middle
+ * of its sequence with copies and kernels still queued.  Nothing fails on the device.  Negative = off;
+ * the countdown disarms itself once it has fired.  Process-wide: not for use beside concurrent callers. */
+int tt_debug_fail_host_call_after(int64_t checks);
+/* How many times a host-buffer call has synchronised its streams on the way out before handing its
+ * pooled device buffers back (every exit, successful or not, does). */
+int64_t tt_debug_guard_syncs(void);
+
 /* The collective calls tt_mgpu_* makes, as a table, so that a test can put stand-ins in their place
  * (each returns an ncclResult_t value: 0 = success).  tt_mgpu_set_collectives(NULL) restores the NCCL
  * library's own entry points; communicators made under one table must be destroyed under it. */
