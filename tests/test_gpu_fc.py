@@ -140,3 +140,46 @@ def test_fc_projection_size_properties(tt, torch_cuda):
     refx = dy[rows].double() @ w.double().t()
     assert float((dx[rows].double() - refx).abs().max()) <= 2.0 ** -8 * float(refx.abs().max()) + 1e-3
     tt.check_device_status()
+
+
+# the CTA-pair kernel (clusters of two, 256x256 tiles) is chosen by size; force each kernel on shapes
+# around the pair tile's edges and compare both with the oracle
+@pytest.mark.parametrize("path", ["1cta", "2cta"])
+@pytest.mark.parametrize("rows,fin,fout", [(256, 64, 256), (257, 72, 264), (300, 200, 520), (130, 4096, 512),
+                                           (2500, 136, 776), (4096, 512, 4104)])
+def test_fc_both_tensor_core_kernels(tt, oracle, torch_cuda, monkeypatch, path, rows, fin, fout):
+    torch = torch_cuda
+    monkeypatch.setenv("TT_FC_PATH", path)
+    rng = np.random.default_rng(rows * 11 + fout)
+    xn = oracle.bf16_round(rng.standard_normal((rows, fin)).astype(np.float32))
+    wn = oracle.bf16_round((rng.standard_normal((fin, fout)) / np.sqrt(fin)).astype(np.float32))
+    bn = oracle.bf16_round(rng.standard_normal(fout).astype(np.float32))
+    dyn = oracle.bf16_round(rng.standard_normal((rows, fout)).astype(np.float32))
+    x, w, b, dy = (torch.from_numpy(a).cuda().bfloat16() for a in (xn, wn, bn, dyn))
+    y = tt.fc_forward(x, w, b)
+    dx, dw, db = tt.fc_backward(x, w, dy)
+    tt.check_device_status()
+    dx_r, dw_r, db_r = oracle.fc_backward(xn, wn, dyn)
+    for got, ref, name in ((y, oracle.fc_forward(xn, wn, bn), "y"), (dx, dx_r, "dx"), (dw, dw_r, "dw"), (db, db_r, "db")):
+        assert bf16_close(oracle, got.float().cpu().numpy(), ref), name
+
+
+def test_fc_large_shape_takes_the_pair_kernel_and_matches(tt, oracle, torch_cuda):
+    """[8192,1024]x[1024,2048] has 256 pair tiles (>= the SM count): the size rule picks the CTA-pair kernel.
+    Both kernels accumulate each output in fp32 over K in the same order, so they agree bit for bit."""
+    torch = torch_cuda
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(8192, 1024, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(1024, 2048, device="cuda", generator=g) / 32).bfloat16()
+    dy = torch.randn(8192, 2048, device="cuda", generator=g).bfloat16()
+    got = (tt.fc_forward(x, w),) + tuple(tt.fc_backward(x, w, dy))[:2]
+    tt.check_device_status()
+    os.environ["TT_FC_PATH"] = "1cta"
+    try:
+        one = (tt.fc_forward(x, w),) + tuple(tt.fc_backward(x, w, dy))[:2]
+    finally:
+        del os.environ["TT_FC_PATH"]
+    for a, b in zip(got, one):
+        assert torch.equal(a, b)
+    ref = x[:256].float() @ w.float()
+    assert bf16_close(oracle, got[0][:256].float().cpu().numpy(), ref.cpu().numpy())
