@@ -172,6 +172,10 @@ size_t attn_bwd_fused_workspace(const AttnArgs& a);
 cudaError_t attn_bwd_fused(const AttnArgs& a, void* workspace, cudaStream_t st);
 void attn_bwd_fused_set_trace(long long* device_buf, int block);
 
+// dK/dV pass on CTA pairs (attn_bwd_pair_sm100.cu): same results as the one-CTA keys-resident pass.
+bool attn_bwd_dkv_pair_supported(const AttnArgs& a);
+cudaError_t attn_bwd_dkv_pair(const AttnArgs& a, const float* delta, const float* lse2, cudaStream_t st);
+
 // delta[row] = sum_d dO*O ; lse2[row] = lse[row] * log2(e).  One warp per row.
 cudaError_t attn_bwd_prep(const AttnArgs& a, float* delta, float* lse2, cudaStream_t st);
 

@@ -817,15 +817,20 @@ static cudaError_t launch_bwd(const AttnArgs& a, void* ws, cudaStream_t st) {
     p.n_light = a.causal ? p.n_tiles / 4 : 0;
     p.n_items_heavy = (int)(a.BH / a.group * (p.n_tiles - p.n_light));
     SchedCounter sc;
-    e = sched_counter_acquire(st, &sc);
-    if (e != cudaSuccess) return e;
-    p.sched_counter = sc.ptr;
-    {
-        LaunchScope ls(K_BWD_DKV, st);
-        attn_bwd_sm100_kernel<D, true, kTrace, kVarlen><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
-            M(tk), M(tv), M(tq), M(tdo), p);
+    if (D == 128 && !kTrace && !kVarlen && attn_bwd_dkv_pair_supported(a)) {
+        // same pass on CTA pairs: each MMA reads half of its streamed operand per SM
+        if ((e = attn_bwd_dkv_pair(a, delta, lse2, st)) != cudaSuccess) return e;
+    } else {
+        e = sched_counter_acquire(st, &sc);
+        if (e != cudaSuccess) return e;
+        p.sched_counter = sc.ptr;
+        {
+            LaunchScope ls(K_BWD_DKV, st);
+            attn_bwd_sm100_kernel<D, true, kTrace, kVarlen><<<(unsigned)std::min(p.n_items, n_sm), Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+                M(tk), M(tv), M(tq), M(tdo), p);
+        }
+        sched_counter_release(sc, st);
     }
-    sched_counter_release(sc, st);
     // dQ: queries resident, stream (K, V)
     p.trace = g_bwd_trace_mode == 2 ? g_bwd_trace : nullptr;
     p.out0 = nullptr;

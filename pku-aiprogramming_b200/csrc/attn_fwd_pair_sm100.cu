@@ -1,0 +1,575 @@
+// Fused attention forward on CTA pairs (clusters of two, tcgen05 cta_group::2) for B200, bf16,
+// head dim 128, dense [B,H,S,D] tensors.  Same arithmetic and the same roles as the one-CTA kernel
+// (attn_fwd_sm100.cu); what changes is who holds the key/value tiles.
+//
+// A pair owns 512 consecutive query rows of one (batch, head) slice as four 128-row tiles.  The CTA
+// of cluster rank r works on tiles r and 2 + r, in its two "slots" (slot i = tile 2i + r), with one
+// softmax warpgroup per slot exactly as in the one-CTA kernel.  Every MMA spans the pair (M = 256:
+// slot i of both CTAs at once, accumulators in each CTA's own tensor memory) and is issued by one
+// thread of the rank-0 CTA:
+//     S_i  = Q_i K_j^T   A = each CTA's own Q tile; B = K_j, keys [64r, 64r + 64) from CTA r
+//     O_i += P_i V_j     A = P_i in tensor memory;  B = V_j, columns [64r, 64r + 64) from CTA r
+// so a CTA loads and keeps HALF of every K and V tile: 32 KB instead of 64 KB of TMA traffic per key
+// tile step, and every MMA reads half as much of its B operand from each SM's shared memory -- the
+// one-CTA kernel runs both at the 128 B/clk the shared memory can deliver.
+//
+// Under the causal mask slot i streams the key tiles its later tile (the rank-1 CTA's) needs; the
+// rank-0 CTA's tile meets one fully masked key tile at the end of each slot, which its softmax turns
+// into probabilities of exactly 0.
+//
+// Barriers: both CTAs' loads count on the rank-0 CTA's `full` barriers (the issuer waits there); the
+// issuer hands stages, scores and finished accumulators to both CTAs with one tcgen05.commit each;
+// the softmax warps of both CTAs arrive (one lane per warp) on the rank-0 CTA's P-ready and
+// O-read barriers.  Work items come from one global counter: the rank-0 loader takes them and
+// publishes each to both CTAs.  Every wait is bounded; the two cluster-wide barriers (after set-up,
+// before tear-down) sit where every thread of both CTAs is certain to arrive.
+#include "attn_fwd_common.cuh"
+
+#include <algorithm>
+#include <stdlib.h>
+
+namespace ttk {
+using namespace sm100;
+
+namespace {
+
+struct PairCfg {
+    static constexpr int D = 128;
+    static constexpr int kQTileBytes = 128 * D * 2;   // 32 KB: two sub-blocks of [128 rows x 128 B]
+    static constexpr int kSubBytes = 128 * 128;       // 16 KB
+    static constexpr int kKvBytes = 16384;            // one ring entry: this CTA's half of a K tile or of a V tile
+    static constexpr int kStages = 10;
+    static constexpr int kThreads = 384;
+    static constexpr int kRegsLaunch = 168;
+    static constexpr int kRegsSoftmax = 216;
+    static constexpr int kRegsOther = 72;
+    static_assert(256 * kRegsSoftmax + 128 * kRegsOther <= kThreads * kRegsLaunch, "register split exceeds the CTA's pool");
+    static constexpr int kTmemCols = 512;
+    static constexpr int kBarBytes = 1024;
+    static constexpr int kSmemBytes = 2 * kQTileBytes + kStages * kKvBytes + kBarBytes + 1024;   // +1024: alignment slack
+};
+
+// Work item = (slice, 512-row query block); the numbering (heavy blocks first, the lightest quarter of
+// every slice in a second phase) is the one-CTA kernel's.
+struct PairItem {
+    int bh, q0, n_slot[2], n_max;
+    int Lv;   // keys that count for this slice
+    int kz;   // key/value slice
+};
+__device__ __forceinline__ PairItem pair_decode_item(int item, const FwdParams& p) {
+    PairItem w;
+    int qb;
+    if (item < p.n_items_heavy) {
+        const int n_heavy = p.n_qblk - p.n_light;
+        w.bh = item / n_heavy;
+        qb = p.n_qblk - 1 - (item - w.bh * n_heavy);
+    } else {
+        const int r = item - p.n_items_heavy;
+        w.bh = r / p.n_light;
+        qb = p.n_light - 1 - (r - w.bh * p.n_light);
+    }
+    w.q0 = qb * 512;
+    w.kz = w.bh / p.group;
+    w.Lv = valid_keys(p.kv_lens, w.bh / p.H, p.L);
+    const int off = p.L - p.S;
+    const int n_kv_total = (w.Lv + 127) >> 7;
+    int n[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const int r0 = w.q0 + 128 * t;
+        if (r0 >= p.S) n[t] = 0;
+        else if (p.causal) n[t] = max(0, min(n_kv_total, ((min(r0 + 127, p.S - 1) + off) >> 7) + 1));
+        else n[t] = n_kv_total;
+    }
+    w.n_slot[0] = max(n[0], n[1]);
+    w.n_slot[1] = max(n[2], n[3]);
+    w.n_max = max(w.n_slot[0], w.n_slot[1]);
+    return w;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::kThreads, 1)
+attn_fwd_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                           const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+    using Cfg = PairCfg;
+    constexpr int D = Cfg::D;
+    constexpr int kStages = Cfg::kStages;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = smem;                                  // this CTA's two Q tiles
+    unsigned char* sKV = smem + 2 * Cfg::kQTileBytes;          // ring of half tiles: K_0, V_0, K_1, V_1, ...
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * Cfg::kQTileBytes + kStages * Cfg::kKvBytes);
+    // (R0) = only the rank-0 CTA's copy is waited on
+    uint64_t* bar_q_full = bars;                     // [2]  both loaders -> MMA (R0)
+    uint64_t* bar_q_empty = bar_q_full + 2;          // [2]  MMA -> this CTA's loader
+    uint64_t* bar_kv_full = bar_q_empty + 2;         // [kStages] (R0)
+    uint64_t* bar_kv_empty = bar_kv_full + kStages;  // [kStages]
+    uint64_t* bar_s_full = bar_kv_empty + kStages;   // [2]  MMA -> this CTA's softmax
+    uint64_t* bar_p_full = bar_s_full + 2;           // [2 slots][2 halves of the key tile] softmax warps of both CTAs -> MMA (R0)
+    uint64_t* bar_o_final = bar_p_full + 4;          // [2]  MMA -> this CTA's softmax (epilogue)
+    uint64_t* bar_o_free = bar_o_final + 2;          // [2]  softmax warps of both CTAs (O read out) -> MMA (R0)
+    uint64_t* bar_sched_full = bar_o_free + 2;       // [2]  rank-0 loader -> everyone in this CTA
+    uint64_t* bar_sched_empty = bar_sched_full + 2;  // [2]  every consumer of both CTAs -> rank-0 loader (R0)
+    int* sched_item = reinterpret_cast<int*>(bar_sched_empty + 2);   // [2]
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sched_item + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp = uniform_warp_idx();
+    const int lane = threadIdx.x & 31;
+    const int rank = (int)cluster_cta_rank();
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_q_full[i], 1);
+            mbar_init(&bar_q_empty[i], 1);
+            mbar_init(&bar_s_full[i], 1);
+            mbar_init(&bar_p_full[2 * i], 8);       // 4 softmax warps of the slot in each CTA
+            mbar_init(&bar_p_full[2 * i + 1], 8);
+            mbar_init(&bar_o_final[i], 1);
+            mbar_init(&bar_o_free[i], 8);
+            mbar_init(&bar_sched_full[i], 1);
+            mbar_init(&bar_sched_empty[i], 18);     // rank 0: 8 softmax warps + MMA warp; rank 1: 8 softmax warps + loader
+        }
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bar_kv_full[s], 1);
+            mbar_init(&bar_kv_empty[s], 1);
+        }
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 8) {
+        tmem_alloc_pair(tmem_base_slot, Cfg::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    if (warp == 9 && lane == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // the peer's barriers exist and its tensor memory is allocated
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+    WaitCtx wctx{p.status, abort_flag, warp};
+
+    // Every role of both CTAs walks the same item sequence, published in a two-slot ring per CTA; a
+    // negative value ends it.
+    auto next_item = [&](int k) -> int {
+        const int slot = k & 1;
+        if (!mbar_wait_cluster(&bar_sched_full[slot], (k >> 1) & 1, wctx, 80 + slot, k)) return -1;
+        return sched_item[slot];
+    };
+    const uint32_t sched_empty_r0 = map_to_cta(smem_u32(&bar_sched_empty[0]), 0);   // [slot]: + 8 * slot
+
+    if (warp < 8) {
+        // =========================================================== softmax warpgroups (both CTAs)
+        setmaxnreg_inc<Cfg::kRegsSoftmax>();
+        const int i = warp >> 2;                    // slot
+        const int wq = warp & 3;                    // TMEM lane quarter of this warp
+        const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_off + (uint32_t)(i * 128);
+        const uint32_t tP = tS;
+        const uint32_t tO = tmem_base + lane_off + (uint32_t)(256 + i * D);
+        const uint32_t p_full_r0[2] = {map_to_cta(smem_u32(&bar_p_full[2 * i]), 0), map_to_cta(smem_u32(&bar_p_full[2 * i + 1]), 0)};
+        const uint32_t o_free_r0 = map_to_cta(smem_u32(&bar_o_free[i]), 0);
+        const float c = p.scale_log2;
+        const int off = p.L - p.S;
+        uint32_t s_cnt = 0;    // S tiles of this slot consumed so far (barrier phase)
+        uint32_t o_cnt = 0;    // items in which this slot was active
+        for (int k = 0;; ++k) {
+            const int item = next_item(k);
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(sched_empty_r0 + 8u * (uint32_t)(k & 1));
+            if (item < 0) break;
+            const PairItem w = pair_decode_item(item, p);
+            const int nt = w.n_slot[i];
+            if (nt == 0) continue;
+            const int tile_row0 = w.q0 + 128 * (2 * i + rank);
+            const int row = tile_row0 + wq * 32 + lane;
+            float m2 = -INFINITY;   // running max in the scaled log2 domain
+            float l = 0.f;          // running sum of exp2(s*c - m2)
+            for (int j = 0; j < nt; ++j, ++s_cnt) {
+                mbar_wait(&bar_s_full[i], s_cnt & 1, wctx, 50 + i, j);
+                __syncwarp();
+                tc_fence_after();
+                // visible columns of this row inside the tile: [0, lim); lim <= 0 on a fully masked tile
+                const int kv0 = j << 7;
+                const bool need_mask = (kv0 + 128 > w.Lv) || (p.causal && (kv0 + 127 > tile_row0 + off));
+                int lim = 128;
+                if (need_mask) {
+                    lim = w.Lv;
+                    if (p.causal) lim = min(lim, row + off + 1);
+                    lim -= kv0;
+                }
+                uint32_t sr[4][32];
+                load_s_row(tS, sr, need_mask, lim);
+                const float mx = row_max_raw(sr) * c;
+                float resc = 1.0f;
+                bool grow = false;
+                if (j == 0) {
+                    m2 = mx;
+                } else if (mx > m2 + 8.0f) {   // lazy rescale: only when the max grew by more than 2^8
+                    resc = ex2_approx(m2 - mx);
+                    m2 = mx;
+                    l *= resc;
+                    grow = true;
+                }
+                if (__any_sync(0xffffffffu, grow)) {
+                    // O_i *= resc (the previous P V of this slot has completed: its commit precedes the
+                    // S commit waited on above)
+#pragma unroll
+                    for (int cc = 0; cc < D / 32; ++cc) {
+                        uint32_t orr[32];
+                        tmem_ld32(tO + cc * 32, orr);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * resc);
+                        tmem_st32(tO + cc * 32, orr);
+                    }
+                }
+                // P = exp2(S*c - m2) in two halves of 64 keys; the P V MMAs of a half start as soon as
+                // that half is in the tensor memory of both CTAs
+                uint64_t acc = pack_f32x2(0.f, 0.f);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t pk[32];
+                    // (rows past the end of the slice may have met no visible key: subtracting 0 keeps their
+                    // unused probabilities at exp2(-inf) = 0 rather than NaN)
+                    acc = add_f32x2(acc, softmax_exp_half(sr, h, c, (m2 == -INFINITY) ? 0.f : m2, pk));
+#pragma unroll
+                    for (int q4 = 0; q4 < 2; ++q4) {
+                        uint32_t t16[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) t16[e] = pk[q4 * 16 + e];
+                        tmem_st16(tP + h * 32 + q4 * 16, t16);
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(p_full_r0[h]);
+                }
+                {
+                    float t0, t1;
+                    unpack_f32x2(acc, t0, t1);
+                    l += t0 + t1;
+                }
+            }
+            // ---- epilogue: O_i out of tensor memory (then the issuer may start the next item's
+            // accumulation in it), O_i / l -> bf16 -> global, LSE
+            mbar_wait(&bar_o_final[i], o_cnt & 1, wctx, 70 + i, k);
+            ++o_cnt;
+            __syncwarp();
+            tc_fence_after();
+            uint32_t orr[D / 32][32];
+#pragma unroll
+            for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(tO + cc * 32, orr[cc]);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(o_free_r0);
+            const float inv = 1.0f / l;
+            if (row < p.S) {
+                __nv_bfloat16* orow = p.out + ((long long)w.bh * p.S + row) * D;
+#pragma unroll
+                for (int cc = 0; cc < D / 32; ++cc) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 16) {
+                        uint32_t o8[8];
+#pragma unroll
+                        for (int q2 = 0; q2 < 8; ++q2)
+                            o8[q2] = pack_bf16x2(__uint_as_float(orr[cc][e + 2 * q2]) * inv, __uint_as_float(orr[cc][e + 2 * q2 + 1]) * inv);
+                        if (p.wide_stores) {
+                            st_global_32B(orow + cc * 32 + e, o8);
+                        } else {
+                            *reinterpret_cast<uint4*>(orow + cc * 32 + e) = make_uint4(o8[0], o8[1], o8[2], o8[3]);
+                            *reinterpret_cast<uint4*>(orow + cc * 32 + e + 8) = make_uint4(o8[4], o8[5], o8[6], o8[7]);
+                        }
+                    }
+                }
+                if (p.lse != nullptr) p.lse[(long long)w.bh * p.S + row] = (m2 + log2f(l)) * 0.6931471805599453f;
+            }
+            __syncwarp();
+        }
+    } else {
+        setmaxnreg_dec<Cfg::kRegsOther>();
+        if (warp == 9) {
+            // ======================================================= TMA loader (both CTAs; the rank-0
+            // CTA's also takes the work items and publishes them to both)
+            uint32_t t = 0;                    // K/V ring entry counter (runs across work items)
+            uint32_t q_uses[2] = {0, 0};       // how often each Q buffer has been filled
+            for (int k = 0;; ++k) {
+                int item = 0;
+                const int slot = k & 1;
+                if (rank == 0) {
+                    if (lane == 0) item = (int)atomicAdd(p.sched_counter, 1u);
+                    item = __shfl_sync(0xffffffffu, item, 0);
+                    if (item >= p.n_items || *abort_flag) item = -1;   // an aborted pair takes no further items
+                    mbar_wait(&bar_sched_empty[slot], ((k >> 1) & 1) ^ 1, wctx, 90 + slot, k);
+                    __syncwarp();
+                    if (lane == 0) {
+                        sched_item[slot] = item;
+                        st_shared_cluster_u32(map_to_cta(smem_u32(&sched_item[slot]), 1), (uint32_t)item);
+                        mbar_arrive(&bar_sched_full[slot]);
+                        mbar_arrive_cluster_release(map_to_cta(smem_u32(&bar_sched_full[slot]), 1));
+                    }
+                    __syncwarp();
+                } else {
+                    item = next_item(k);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(sched_empty_r0 + 8u * (uint32_t)slot);
+                    __syncwarp();
+                }
+                if (item < 0) break;
+                const PairItem w = pair_decode_item(item, p);
+                auto load_q = [&](int i) {
+                    mbar_wait(&bar_q_empty[i], (q_uses[i] & 1) ^ 1, wctx, 5 + i, k);
+                    __syncwarp();
+                    if (elect_one()) {
+                        if (rank == 0) mbar_arrive_expect_tx(&bar_q_full[i], 2 * Cfg::kQTileBytes);   // both CTAs' tiles
+                        const uint32_t full0 = map_to_cta(smem_u32(&bar_q_full[i]), 0);
+#pragma unroll
+                        for (int sb = 0; sb < 2; ++sb)
+                            tma_load_3d_pair(sQ + i * Cfg::kQTileBytes + sb * Cfg::kSubBytes, &tmQ, full0, sb * 64,
+                                             w.q0 + 128 * (2 * i + rank), w.bh);
+                    }
+                    __syncwarp();
+                    ++q_uses[i];
+                };
+                auto load_kv = [&](bool is_v, int j) {
+                    const int st = t % kStages;
+                    mbar_wait(&bar_kv_empty[st], ((t / kStages) & 1) ^ 1, wctx, 30 + st, (int)t);
+                    __syncwarp();
+                    if (elect_one()) {
+                        if (rank == 0) mbar_arrive_expect_tx(&bar_kv_full[st], 2 * Cfg::kKvBytes);   // both CTAs' halves
+                        const uint32_t full0 = map_to_cta(smem_u32(&bar_kv_full[st]), 0);
+                        unsigned char* dst = sKV + st * Cfg::kKvBytes;
+                        if (is_v) {   // columns [64 rank, 64 rank + 64) of all 128 keys: one sub-block
+                            tma_load_3d_pair(dst, &tmV, full0, 64 * rank, j * 128, w.kz);
+                        } else {      // keys [64 rank, 64 rank + 64), all columns: two sub-blocks of 64 rows
+#pragma unroll
+                            for (int sb = 0; sb < 2; ++sb)
+                                tma_load_3d_pair(dst + sb * (Cfg::kKvBytes / 2), &tmK, full0, sb * 64, j * 128 + 64 * rank, w.kz);
+                        }
+                    }
+                    __syncwarp();
+                    ++t;
+                };
+                if (w.n_slot[0] > 0) load_q(0);
+                if (w.n_max > 0) load_kv(false, 0);
+                if (w.n_slot[1] > 0) load_q(1);
+                for (int j = 0; j < w.n_max; ++j) {
+                    load_kv(true, j);
+                    if (j + 1 < w.n_max) load_kv(false, j + 1);
+                }
+            }
+        } else if (warp == 8 && rank == 0) {
+            // ======================================================= MMA issuer (rank-0 CTA; the whole warp
+            // runs the control flow, each tcgen05.mma / commit is issued by one elected lane)
+            constexpr uint32_t idesc_s = umma_idesc_bf16(256, 128, false, false);
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(256, D, false, true);
+            const uint32_t sQ_addr = __shfl_sync(0xffffffffu, smem_u32(sQ), 0);
+            const uint32_t sKV_addr = __shfl_sync(0xffffffffu, smem_u32(sKV), 0);
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);   // warp-uniform copy
+            const uint64_t dq_base = umma_smem_desc(sQ_addr, 16, 1024);
+            const uint64_t dk_base = umma_smem_desc(sKV_addr, 16, 1024);                 // K-major (S = Q K^T), 64 key rows
+            const uint64_t dv_base = umma_smem_desc(sKV_addr, Cfg::kSubBytes, 1024);     // MN-major (O += P V), 64 columns
+            uint32_t t = 0;                  // ring entries consumed before the current work item
+            uint32_t q_uses[2] = {0, 0}, p_cnt[2] = {0, 0}, o_uses[2] = {0, 0};
+            auto commit_both = [&](uint64_t* bar) {   // one arrival on this barrier in each CTA of the pair
+                const uint32_t a = smem_u32(bar);
+                tc_commit_pair(a);
+                tc_commit_pair(map_to_cta(a, 1));
+            };
+            auto wait_entry = [&](uint32_t ri) {
+                const int st = ri % kStages;
+                mbar_wait(&bar_kv_full[st], (ri / kStages) & 1, wctx, 10 + st, (int)ri);
+                __syncwarp();
+            };
+            auto release_entry = [&](uint32_t ri) { commit_both(&bar_kv_empty[ri % kStages]); };
+            auto issue_s = [&](int i, uint32_t ri) {   // S_i = Q_i K^T with K in ring entry ri
+                const uint64_t a0 = umma_desc_advance(dq_base, i * Cfg::kQTileBytes);
+                const uint64_t b0 = umma_desc_advance(dk_base, (ri % kStages) * Cfg::kKvBytes);
+                const uint32_t d = tmem_u + (uint32_t)(i * 128);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t oa = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
+                    const uint32_t ob = (kk >> 2) * (Cfg::kKvBytes / 2) + (kk & 3) * 32;
+                    umma_ss_pair(d, umma_desc_advance(a0, oa), umma_desc_advance(b0, ob), idesc_s, kk > 0);
+                }
+            };
+            auto issue_pv = [&](int i, uint32_t ri, bool accumulate, int half) {   // O_i (+)= P_i V
+                const uint64_t b0 = umma_desc_advance(dv_base, (ri % kStages) * Cfg::kKvBytes);
+                const uint32_t d = tmem_u + (uint32_t)(256 + i * D);
+                const uint32_t a = tmem_u + (uint32_t)(i * 128);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const int kk = half * 4 + k4;
+                    umma_ts_pair(d, a + kk * 8, umma_desc_advance(b0, kk * 2048), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+                }
+            };
+            for (int k = 0;; ++k) {
+                const int item = next_item(k);
+                __syncwarp();
+                if (elect_one()) mbar_arrive(&bar_sched_empty[k & 1]);
+                __syncwarp();
+                if (item < 0) break;
+                const PairItem w = pair_decode_item(item, p);
+                // S_i(0) for both slots.  The S/P columns are free: the P V MMAs of the previous item
+                // were issued earlier by this warp and execute in order.
+                if (w.n_max > 0) {
+                    wait_entry(t);   // K_0
+                    tc_fence_after();
+                    for (int i = 0; i < 2; ++i) {
+                        if (w.n_slot[i] > 0) {
+                            mbar_wait(&bar_q_full[i], q_uses[i] & 1, wctx, i, k);
+                            ++q_uses[i];
+                            __syncwarp();
+                            tc_fence_after();
+                            issue_s(i, t);
+                            commit_both(&bar_s_full[i]);
+                            if (w.n_slot[i] == 1) commit_both(&bar_q_empty[i]);   // that was this slot's last S
+                        }
+                    }
+                    release_entry(t);
+                }
+                for (int j = 0; j < w.n_max; ++j) {
+                    const uint32_t ent_v = t + 2 * j + 1, ent_k = t + 2 * j + 2;
+                    wait_entry(ent_v);
+                    bool k_waited = false;
+                    for (int i = 0; i < 2; ++i) {
+                        if (j < w.n_slot[i]) {
+                            if (j == 0) {
+                                // the accumulator columns must have been read out by the previous item's epilogues
+                                mbar_wait(&bar_o_free[i], (o_uses[i] & 1) ^ 1, wctx, 75 + i, k);
+                                ++o_uses[i];
+                                __syncwarp();
+                            }
+                            mbar_wait(&bar_p_full[2 * i], p_cnt[i] & 1, wctx, 60 + 2 * i, j);
+                            __syncwarp();
+                            tc_fence_after();
+                            issue_pv(i, ent_v, j > 0, 0);
+                            mbar_wait(&bar_p_full[2 * i + 1], p_cnt[i] & 1, wctx, 60 + 2 * i + 1, j);
+                            ++p_cnt[i];
+                            __syncwarp();
+                            tc_fence_after();
+                            issue_pv(i, ent_v, j > 0, 1);
+                            if (j + 1 < w.n_slot[i]) {
+                                if (!k_waited) {
+                                    wait_entry(ent_k);
+                                    tc_fence_after();
+                                    k_waited = true;
+                                }
+                                issue_s(i, ent_k);
+                                commit_both(&bar_s_full[i]);
+                                if (j + 2 == w.n_slot[i]) commit_both(&bar_q_empty[i]);   // this slot's last S
+                            } else {
+                                commit_both(&bar_o_final[i]);
+                            }
+                        }
+                    }
+                    release_entry(ent_v);
+                    if (j + 1 < w.n_max) release_entry(ent_k);
+                }
+                t += 2 * (uint32_t)w.n_max;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // neither CTA leaves while the other may still read its shared memory or arrive on its barriers
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+int max_resident_pairs() {
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!cached[dev]) {
+        int n_sm = 148;
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        cudaFuncSetAttribute(attn_fwd_pair_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)n_sm & ~1u);
+        cfg.blockDim = dim3(PairCfg::kThreads);
+        cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 2;
+        at.val.clusterDim.y = 1;
+        at.val.clusterDim.z = 1;
+        cfg.attrs = &at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, attn_fwd_pair_sm100_kernel, &cfg) != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            n = n_sm / 2;
+        }
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+}  // namespace
+
+// Takes dense bf16 tensors with head dim 128; under the causal mask every query must see a key (L >= S).
+// Not chosen by default: measured on B200 it computes the same bits as the one-CTA kernel 1-4 % slower
+// (S = 4096, 32 heads, batch 4: 0.500 against 0.495 ms causal, 0.946 against 0.914 ms non-causal) -- the
+// forward is paced by the chain softmax -> P V -> next S of each slot, which the hand-offs between the
+// two CTAs lengthen by more than the lighter shared-memory traffic shortens the MMAs.  TT_FWD_PATH=2cta
+// selects it (tests, measurements).
+bool attn_fwd_pair_sm100_supported(const AttnArgs& a) {
+    const char* f = getenv("TT_FWD_PATH");
+    if (!(f && f[0] == '2')) return false;
+    if (!a.bf16 || a.D != 128 || a.cache_mode || a.block_table != nullptr || a.cu_q != nullptr || a.q_div > 1) return false;
+    if (a.S < 1 || a.L < 1 || (a.causal && a.L < a.S)) return false;
+    return a.BH * (long long)((a.S + 511) / 512) < (1LL << 31);
+}
+
+cudaError_t attn_fwd_pair_sm100(const AttnArgs& a, cudaStream_t st) {
+    using Cfg = PairCfg;
+    constexpr int D = Cfg::D;
+    TmapStorage tq, tk, tv;
+    const char* why = nullptr;
+    if (!make_tmap_bf16(&tq, a.q, D, a.S, a.BH, 128, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tk, a.k, D, a.L, a.BH / a.group, 64, &why)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16(&tv, a.v, D, a.L, a.BH / a.group, 128, &why)) return cudaErrorInvalidValue;
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_pair_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    FwdParams p = {};
+    p.out = (__nv_bfloat16*)a.out;
+    p.lse = a.lse;
+    p.S = a.S;
+    p.L = a.L;
+    p.n_qblk = (a.S + 511) / 512;
+    p.causal = a.causal;
+    p.group = a.group;
+    p.kv_lens = a.kv_lens;
+    p.H = a.H;
+    p.q_div = 1;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.status = device_status_word();
+    p.wide_stores = (reinterpret_cast<uintptr_t>(a.out) & 31) == 0 ? 1 : 0;
+    p.n_items = (int)(a.BH * p.n_qblk);
+    p.n_light = a.causal ? p.n_qblk / 4 : 0;
+    p.n_items_heavy = (int)(a.BH * (p.n_qblk - p.n_light));
+    SchedCounter sc;
+    e = sched_counter_acquire(st, &sc);
+    if (e != cudaSuccess) return e;
+    p.sched_counter = sc.ptr;
+    const unsigned pairs = (unsigned)std::min<long long>(p.n_items, max_resident_pairs());
+    {
+        LaunchScope ls(K_FWD_TC, st);
+        attn_fwd_pair_sm100_kernel<<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+            *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
+            *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
+    }
+    sched_counter_release(sc, st);
+    return cudaGetLastError();
+}
+
+}  // namespace ttk

@@ -259,7 +259,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
     return r;
 }
+// (release at CTA scope, the default: what the barrier orders here is tensor-memory traffic fenced by
+// tcgen05.fence, or TMA bytes; mbar_arrive_cluster_release is for ordinary stores to the peer's memory)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // Both CTAs of the cluster (all their threads) arrive and wait.  A hardware barrier without a
@@ -267,6 +272,41 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 // the common exit that every role reaches after its bounded waits).
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// mbar_wait for a barrier that threads of the peer CTA arrive on: acquires at cluster scope, so that
+// what the arriving thread wrote before its (release.cluster) arrival is visible afterwards.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int bar_id,
+                                                  int iter) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*ctx.abort_flag) return false;
+        if (clock64() - t0 > ctx.budget) break;
+    }
+    *ctx.abort_flag = 1;
+    if (atomicCAS(ctx.gstatus, 0u, (7u << 16) | (blockIdx.x & 0xffffu)) == 0u) {
+        ctx.gstatus[1] = (unsigned)bar_id;
+        ctx.gstatus[2] = (unsigned)iter;
+        ctx.gstatus[3] = (unsigned)ctx.role;
+    }
+    return false;
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 // The same warp index of both CTAs calls these.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
@@ -298,6 +338,17 @@ __device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, u
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem of both CTAs] (+)= A[tmem, each CTA its own rows] * B[smem, split along N over the pair]
+__device__ __forceinline__ void umma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    if (elect_one())
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // One arrival on the mbarrier at `cluster_addr` (this CTA's or the peer's) once every MMA this
