@@ -19,7 +19,7 @@ OBJ = os.path.join(PKG, "build")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libtt_attn.so")
 
-KERNEL_SOURCES = ["tt_api.cu", "tt_mgpu.cu", "attn_simt.cu", "attn_decode.cu", "attn_fwd_sm100.cu", "attn_fwd_pair_sm100.cu", "attn_bwd_sm100.cu", "attn_bwd_pair_sm100.cu", "attn_bwd_fused_sm100.cu",
+KERNEL_SOURCES = ["tt_api.cu", "tt_mgpu.cu", "attn_simt.cu", "attn_decode.cu", "attn_decode_gq_sm100.cu", "attn_fwd_sm100.cu", "attn_fwd_pair_sm100.cu", "attn_bwd_sm100.cu", "attn_bwd_pair_sm100.cu", "attn_bwd_fused_sm100.cu",
                   "softmax_rows.cu", "fc_gemm_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Wno-deprecated-gpu-targets",

@@ -271,6 +271,11 @@ static bool decode_group_instantiated(int g) { return g == 1 || g == 2 || g == 4
 // [slices * splits, L / splits, D] are `splits` independent problems per slice (the forward kernel
 // reads the query rows of slice s / splits), whose normalised partial outputs and log-sum-exps a
 // second kernel merges.
+// The forward view of a grouped decode runs on the keys-on-rows decode kernel where that takes it (head
+// dim 128, groups of up to 16), else on the general forward kernel.
+static cudaError_t run_forward_view(const AttnArgs& g, cudaStream_t st) {
+    return attn_decode_gq_sm100_supported(g) ? attn_decode_gq_sm100(g, st) : attn_fwd_sm100(g, st);
+}
 static AttnArgs decode_as_forward(const AttnArgs& a, int splits) {
     AttnArgs g = a;
     g.BH = a.BH / a.group * splits;
@@ -442,12 +447,12 @@ cudaError_t attn_decode_paged_forward(const AttnArgs& a, const DecodeView& v, in
     paged_split(a, &s2, &chunk);
     if (s2 != splits) return cudaErrorInvalidValue;
     AttnArgs g = paged_as_forward(a, v, splits, chunk);
-    if (splits == 1) return attn_fwd_sm100(g, st);
+    if (splits == 1) return run_forward_view(g, st);
     __nv_bfloat16* po = (__nv_bfloat16*)ws;
     float* plse = (float*)((unsigned char*)ws + align256((size_t)a.BH * splits * a.D * 2));
     g.out = po;
     g.lse = plse;
-    cudaError_t e = attn_fwd_sm100(g, st);
+    cudaError_t e = run_forward_view(g, st);
     if (e != cudaSuccess) return e;
     LaunchScope ls(K_DECODE_MERGE, st);
     if (a.D == 128)
@@ -459,14 +464,14 @@ cudaError_t attn_decode_paged_forward(const AttnArgs& a, const DecodeView& v, in
 
 cudaError_t attn_decode(const AttnArgs& a, const DecodePlan& pl, void* ws, cudaStream_t st, const DecodeView* view) {
     const bool plain = !(view && (view->block_table || view->seq_lens));
-    if (plain && pl.tc_splits == 1) return attn_fwd_sm100(decode_as_forward(a, 1), st);
+    if (plain && pl.tc_splits == 1) return run_forward_view(decode_as_forward(a, 1), st);
     if (plain && pl.tc_splits > 1) {
         AttnArgs g = decode_as_forward(a, pl.tc_splits);
         __nv_bfloat16* po = (__nv_bfloat16*)ws;
         float* plse = (float*)((unsigned char*)ws + align256((size_t)a.BH * pl.tc_splits * a.D * 2));
         g.out = po;
         g.lse = plse;
-        cudaError_t e = attn_fwd_sm100(g, st);
+        cudaError_t e = run_forward_view(g, st);
         if (e != cudaSuccess) return e;
         LaunchScope ls(K_DECODE_MERGE, st);
         if (a.D == 128)

@@ -62,7 +62,7 @@ int check_device();   // TT_OK, or TT_ERR_BAD_DEVICE when the current device is 
 enum KernelId {
     K_FWD_TC = 0, K_FWD_SIMT, K_BWD_PREP, K_BWD_DKV, K_BWD_DQ, K_BWD_SIMT_DELTA, K_BWD_SIMT_DQ, K_BWD_SIMT_DKV,
     K_DECODE, K_DECODE_MERGE, K_PROBE, K_SOFTMAX_FWD, K_SOFTMAX_BWD, K_FC_GEMM, K_FC_SIMT, K_FC_COLSUM, K_BWD_FUSED,
-    K_BWD_DQ_CONVERT, K_COUNT
+    K_BWD_DQ_CONVERT, K_DECODE_GQ, K_COUNT
 };
 // Scoped around ONE kernel launch: counts it and, when timing is enabled, brackets it with
 // CUDA events on the launching stream.
@@ -91,6 +91,11 @@ void sched_counter_release(const SchedCounter& c, cudaStream_t st);
 cudaError_t attn_fwd_simt(const AttnArgs& a, cudaStream_t st);
 cudaError_t attn_bwd_simt(const AttnArgs& a, float* delta, cudaStream_t st);
 size_t attn_bwd_simt_workspace(const AttnArgs& a);
+
+// --- grouped-head decode with keys on the accumulator rows (attn_decode_gq_sm100.cu); `a` is the forward
+// view of the decode (S = query heads per key/value head)
+bool attn_decode_gq_sm100_supported(const AttnArgs& a);
+cudaError_t attn_decode_gq_sm100(const AttnArgs& a, cudaStream_t st);
 
 // --- tcgen05 / TMA kernels (bf16, D in {64,128})
 bool attn_fwd_sm100_supported(const AttnArgs& a);

@@ -41,7 +41,7 @@ static const char* const kKernelNames[K_COUNT] = {
     "attn_fwd_sm100", "attn_fwd_simt", "attn_bwd_prep", "attn_bwd_sm100_dkv", "attn_bwd_sm100_dq",
     "attn_bwd_simt_delta", "attn_bwd_simt_dq", "attn_bwd_simt_dkv", "attn_decode", "attn_decode_merge",
     "umma_probe", "softmax_rows_fwd", "softmax_rows_bwd", "fc_gemm_sm100", "fc_gemm_simt",
-    "fc_colsum", "attn_bwd_fused_sm100", "attn_bwd_dq_convert"};
+    "fc_colsum", "attn_bwd_fused_sm100", "attn_bwd_dq_convert", "attn_decode_gq_sm100"};
 struct TimedLaunch {
     KernelId id;
     cudaEvent_t start, stop;
