@@ -51,7 +51,7 @@ NCU_TRAFFIC_BYTES = {
     "cfg2": {"attn_fwd_sm100": 52.3e6, "attn_bwd_fused_sm100": 132.1e6},
     "cfg5_per_slice": {"attn_fwd_sm100": 26.08e6, "attn_bwd_sm100_dkv": 35.10e6, "attn_bwd_sm100_dq": 34.66e6},
     # config 4 = 8 x the captured batch-8 launch (the full launch holds 8.6 GB, too large a capture)
-    "decode": {"attn_decode": 8.637e9},
+    "decode": {"attn_decode": 8.637e9, "attn_decode_gq_sm100": 8.637e9},
 }
 
 
@@ -462,7 +462,9 @@ def run_decode(tt, dev, peaks, batch):
         dprof = capi.profile_read()
         ms = a.elapsed_time(b) / 20
         by = 2.0 * dB * dH * dL * dD * 2 + 2.0 * dB * dH * dD * 2
-        kms = dprof["attn_decode"][0] / dprof["attn_decode"][1]
+        # head dim 128 runs on the keys-on-rows tensor-core kernel; the split-KV kernel serves the other shapes
+        kname = "attn_decode_gq_sm100" if dprof.get("attn_decode_gq_sm100", (0.0, 0))[1] > 0 else "attn_decode"
+        kms = dprof[kname][0] / dprof[kname][1]
         # the timed output against the oracle: the last slice (for batch 64 its last element has index
         # 2^31 - 1 and its bytes sit behind 2^32) and one in the middle
         from oracle import attention_oracle as orc
@@ -479,18 +481,18 @@ def run_decode(tt, dev, peaks, batch):
                 "grouped": run_decode_grouped(tt, dev, peaks, dB),
                 "roofline": {"bound": "hbm", "achieved": by / kms / 1e6, "peak": peaks["hbm"], "unit": "GB/s",
                              "frac": by / kms / 1e6 / peaks["hbm"],
-                             "traffic": NCU_TRAFFIC_BYTES["decode"].get("attn_decode") if dB == 64 else None,
+                             "traffic": NCU_TRAFFIC_BYTES["decode"].get(kname) if dB == 64 else None,
                              "traffic_note": "ncu capture of the batch-8 launch x 8 (the full launch is too large to capture)",
-                             "kernel": "attn_decode", "peak_source": f"hbm_gbs of {peaks['source']} MEASURED_PEAKS.json"}}
+                             "kernel": kname, "peak_source": f"hbm_gbs of {peaks['source']} MEASURED_PEAKS.json"}}
     except Exception as e:  # noqa: BLE001
         return {"error": str(e)}
 
 
 def run_decode_grouped(tt, dev, peaks, dB, hkv=8, page=64):
     """The serving form of the decode configuration: 32 query heads over 8 key/value heads (groups
-    of 4), cache dense and as a shuffled pool of 64-row pages.  Both run as a [B*Hkv, 4, D]
-    problem on the tcgen05 forward kernel (the paged one gathers its tiles page by page); GB/s
-    counts the K and V bytes, which cross HBM once per group."""
+    of 4), cache dense and as a shuffled pool of 64-row pages.  Both run on the keys-on-rows
+    tensor-core decode kernel (the paged one gathers its tiles page by page); GB/s counts the K and
+    V bytes, which cross HBM once per group."""
     import torch
     try:
         dH, dL, dD = 32, 8192, 128

@@ -287,21 +287,35 @@ static AttnArgs decode_as_forward(const AttnArgs& a, int splits) {
     g.kv_lens = nullptr;
     return g;
 }
-static int decode_tc_splits(const AttnArgs& a) {   // 0: do not use the forward kernel
-    if (!(a.bf16 && a.S == 1 && a.group >= 4)) return 0;
+// true: the tensor-core route of this decode is the keys-on-rows kernel.  It runs two CTAs per SM, one per
+// (slice, key range), without a persistent loop, so it wants several times as many ranges as there are SMs
+// (the tail of the last wave is what is lost), where the forward kernel wants about two items per SM.
+static bool decode_on_gq_kernel(const AttnArgs& a) {
     const char* f = getenv("TT_DECODE_GQA_PATH");
+    return a.bf16 && a.D == 128 && a.S == 1 && a.group <= 16 && !(f && f[0] == 'f');
+}
+static int decode_tc_splits(const AttnArgs& a) {   // 0: do not use the forward kernel
+    const char* f = getenv("TT_DECODE_GQA_PATH");
+    // head dim 128: the keys-on-rows kernel takes every group size up to 16 (measured faster than the split-KV
+    // kernel even for single heads); head dim 64: the forward kernel from groups of 4 on
+    const int min_group = a.D == 128 ? 1 : 4;
+    if (!(a.bf16 && a.S == 1 && a.group >= min_group)) return 0;
     if (f && f[0] == 's') return 0;                           // "simt"
     if (!attn_fwd_sm100_supported(decode_as_forward(a, 1))) return 0;
     int dev = 0, n_sm = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     const long long slices = a.BH / a.group;
-    if (slices >= n_sm) return 1;
-    // about two items per SM, ranges of at least 256 keys that divide L exactly
-    const long long want = (2LL * n_sm + slices - 1) / slices;
-    for (long long s = want; s <= 64 && a.L / s >= 256; ++s)
+    const bool gq = decode_on_gq_kernel(a);
+    const long long full = gq ? 8LL * n_sm : n_sm;            // items that fill the GPU
+    const long long min_chunk = gq ? 512 : 256;
+    if (slices >= full) return 1;
+    // `full` items (forward kernel: about two per SM), ranges of at least min_chunk keys that divide L exactly
+    const long long want = gq ? (full + slices - 1) / slices : (2LL * n_sm + slices - 1) / slices;
+    for (long long s = want; s <= 64 && a.L / s >= min_chunk; ++s)
         if (a.L % s == 0) return (int)s;
     for (long long s = want - 1; s >= 2; --s)
-        if (a.L % s == 0 && a.L / s >= 256) return (int)s;
+        if (a.L % s == 0 && a.L / s >= min_chunk) return (int)s;
+    if (gq) return 1;                                         // short or indivisible key range: one range per slice
     return (f && f[0] == 't') ? 1 : 0;                        // "tc": unsplit rather than SIMT
 }
 
@@ -421,11 +435,13 @@ static void paged_split(const AttnArgs& a, int* splits, int* chunk) {
     const long long slices = a.BH / a.group;
     *splits = 1;
     *chunk = a.L;
-    if (2 * slices >= n_sm) return;
-    // about two items per SM, ranges of whole 128-key tiles and at least 256 keys
-    const long long want = (2LL * n_sm + slices - 1) / slices;
+    const bool gq = decode_on_gq_kernel(a);
+    if (gq ? slices >= 8LL * n_sm : 2 * slices >= n_sm) return;
+    // items that fill the GPU (forward kernel: about two per SM), ranges of whole 128-key tiles
+    const long long want = gq ? (8LL * n_sm + slices - 1) / slices : (2LL * n_sm + slices - 1) / slices;
+    const long long min_chunk = gq ? 512 : 256;
     long long c = ((a.L + want - 1) / want + 127) / 128 * 128;
-    if (c < 256) c = 256;
+    if (c < min_chunk) c = min_chunk;
     const long long n = (a.L + c - 1) / c;
     if (n < 2) return;
     *splits = (int)n;
@@ -433,7 +449,7 @@ static void paged_split(const AttnArgs& a, int* splits, int* chunk) {
 }
 int attn_decode_paged_on_forward(const AttnArgs& a, const DecodeView& v, size_t* ws_bytes) {
     *ws_bytes = 0;
-    if (!(a.bf16 && a.S == 1 && a.group >= 4 && (v.block_table != nullptr || v.seq_lens != nullptr))) return 0;
+    if (!(a.bf16 && a.S == 1 && a.group >= (a.D == 128 ? 1 : 4) && (v.block_table != nullptr || v.seq_lens != nullptr))) return 0;
     const char* f = getenv("TT_DECODE_GQA_PATH");
     if (f && f[0] == 's') return 0;                           // "simt"
     int splits, chunk;

@@ -266,30 +266,40 @@ attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 for (int sb = 0; sb < 2; ++sb) tma_load_3d(sQ + sb * 2048, &tmQ, bar_q_full, sb * 64, qslice * p.G, 0);
             }
             __syncwarp();
+            // paged cache: lane i fetches the i-th page (or 128-row part of a larger page) of a tile.  The table
+            // entry of the NEXT tile is read while this tile's two entries wait for their ring slots, so the
+            // look-up's latency stays off the loader's critical path; K and V of a tile share it.
+            const bool paged = kCache && p.block_table != nullptr;
+            const int box_rows = paged ? min(p.page_size, 128) : 128;
+            auto page_of = [&](int tile) -> int {
+                const int key = key0 + tile * 128 + lane * box_rows;
+                if (!paged || tile >= n_tiles || lane * box_rows >= 128 || tile * 128 + lane * box_rows >= Lv) return 0;
+                return __ldg(p.block_table + (long long)(zslice / p.H) * p.max_pages + key / p.page_size);
+            };
+            int page_next = page_of(0);
             for (int e = 0; e < 2 * n_tiles; ++e) {   // entry e: K of tile e/2 (even), V (odd)
                 const int st = e % kStages;
+                const int tile = e >> 1;
+                const int page = page_next;
+                if (e & 1) page_next = page_of(tile + 1);             // issued now, consumed two entries later
                 if (!mbar_wait(&bar_kv_empty[st], ((e / kStages) & 1) ^ 1, wctx, 40 + st, e)) break;
                 __syncwarp();
                 const CUtensorMap* tm = (e & 1) ? &tmV : &tmK;
                 unsigned char* dst = sKV + st * kTileBytes;
-                const int k_first = (e >> 1) * 128;                   // first key of the tile inside the range
-                if (kCache && p.block_table != nullptr) {
-                    // one TMA box per page (or one 128-row box out of a larger page); lanes issue side by side.
+                const int k_first = tile * 128;                       // first key of the tile inside the range
+                if (paged) {
                     // Only pages that hold counted keys are fetched: what the rest of the tile holds is masked
                     // in S^T and zeroed in V.
-                    const int box_rows = min(p.page_size, 128);
                     const int n_box = min(128 / box_rows, (Lv - k_first + box_rows - 1) / box_rows);
                     if (lane == 0) mbar_arrive_expect_tx(&bar_kv_full[st], (uint32_t)(n_box * box_rows * kD * 2));
                     __syncwarp();
                     if (lane < n_box) {
                         const int key = key0 + k_first + lane * box_rows;
-                        const int lp = key / p.page_size;
-                        const int page = __ldg(p.block_table + (long long)(zslice / p.H) * p.max_pages + lp);
                         const int z = page * p.H + (zslice % p.H);
 #pragma unroll
                         for (int sb = 0; sb < 2; ++sb)
                             tma_load_3d(dst + sb * kSubBytes + lane * box_rows * 128, tm, &bar_kv_full[st], sb * 64,
-                                        key - lp * p.page_size, z);
+                                        key % p.page_size, z);
                     }
                     __syncwarp();
                 } else {

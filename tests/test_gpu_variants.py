@@ -110,8 +110,10 @@ def test_decode_grouped_heads_on_the_forward_kernel(tt, oracle, torch_cuda, monk
         before = tt.capi.launch_count()
         out, lse = tt.attention_decode(tq, tk, tv)
         tt.check_device_status()
-        # both routes split the 1000 keys here (few slices): forward kernel + merge | split kernel + merge
-        assert tt.capi.launch_count() - before == 2, route
+        # few slices: the split-KV kernel and the forward kernel (head dim 64) cut the 1000 keys into ranges and
+        # merge them (two launches); the keys-on-rows kernel (head dim 128, groups up to 16) keeps ranges of at least 512 keys
+        # that divide the key count, which 1000 keys do not offer: one launch
+        assert tt.capi.launch_count() - before == (1 if (route == "tc" and D == 128 and H // Hkv <= 16) else 2), route
         assert oracle.max_abs_err(out.float().cpu().numpy(), o_r) <= 2e-2, route
         assert oracle.max_abs_err(lse.cpu().numpy(), lse_r) <= 1e-3, route
     monkeypatch.delenv("TT_DECODE_GQA_PATH")
