@@ -288,8 +288,9 @@ static AttnArgs decode_as_forward(const AttnArgs& a, int splits) {
     return g;
 }
 // true: the tensor-core route of this decode is the keys-on-rows kernel.  It runs two CTAs per SM, one per
-// (slice, key range), without a persistent loop, so it wants several times as many ranges as there are SMs
-// (the tail of the last wave is what is lost), where the forward kernel wants about two items per SM.
+// (slice, key range).  As many slices as SMs already keep HBM busy (the CTAs share its bandwidth, so a
+// partial last wave costs little: measured, 256 and 512 unsplit slices beat any split); with fewer, the
+// keys are cut into about four ranges per SM of at least 512 keys.
 static bool decode_on_gq_kernel(const AttnArgs& a) {
     const char* f = getenv("TT_DECODE_GQA_PATH");
     return a.bf16 && a.D == 128 && a.S == 1 && a.group <= 16 && !(f && f[0] == 'f');
@@ -306,11 +307,10 @@ static int decode_tc_splits(const AttnArgs& a) {   // 0: do not use the forward 
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     const long long slices = a.BH / a.group;
     const bool gq = decode_on_gq_kernel(a);
-    const long long full = gq ? 8LL * n_sm : n_sm;            // items that fill the GPU
     const long long min_chunk = gq ? 512 : 256;
-    if (slices >= full) return 1;
-    // `full` items (forward kernel: about two per SM), ranges of at least min_chunk keys that divide L exactly
-    const long long want = gq ? (full + slices - 1) / slices : (2LL * n_sm + slices - 1) / slices;
+    if (slices >= n_sm) return 1;
+    // about four (forward kernel: two) items per SM, ranges of at least min_chunk keys that divide L exactly
+    const long long want = ((gq ? 4LL : 2LL) * n_sm + slices - 1) / slices;
     for (long long s = want; s <= 64 && a.L / s >= min_chunk; ++s)
         if (a.L % s == 0) return (int)s;
     for (long long s = want - 1; s >= 2; --s)
@@ -436,9 +436,9 @@ static void paged_split(const AttnArgs& a, int* splits, int* chunk) {
     *splits = 1;
     *chunk = a.L;
     const bool gq = decode_on_gq_kernel(a);
-    if (gq ? slices >= 8LL * n_sm : 2 * slices >= n_sm) return;
-    // items that fill the GPU (forward kernel: about two per SM), ranges of whole 128-key tiles
-    const long long want = gq ? (8LL * n_sm + slices - 1) / slices : (2LL * n_sm + slices - 1) / slices;
+    if (gq ? slices >= n_sm : 2 * slices >= n_sm) return;
+    // about four (forward kernel: two) items per SM, ranges of whole 128-key tiles
+    const long long want = ((gq ? 4LL : 2LL) * n_sm + slices - 1) / slices;
     const long long min_chunk = gq ? 512 : 256;
     long long c = ((a.L + want - 1) / want + 127) / 128 * 128;
     if (c < min_chunk) c = min_chunk;
