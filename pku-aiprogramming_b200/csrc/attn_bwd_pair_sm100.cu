@@ -13,8 +13,9 @@
 // The hardware splits B along N over the pair, and N is the query index in G1/G2 but the head
 // dimension in G3/G4, so a CTA holds two views of each streamed tile -- a row half for the score GEMMs
 // and a column half for the accumulation GEMMs, 16 KB each: it loads as many bytes as the one-CTA
-// kernel, but every MMA reads half as much B from each SM's shared memory (the one-CTA kernel's
-// score GEMMs run at the 128 B/clk the shared memory can deliver).
+// kernel, but every MMA reads half as much B from each SM's shared memory.  (That traffic turned out
+// not to be what paces the one-CTA pass: see the measurements at attn_bwd_dkv_pair_supported below.
+// The kernel is kept as an opt-in path.)
 //
 // Under the causal mask the pair streams the query tiles its earlier key tile (rank 0) can see; for
 // the rank-1 CTA the first of them is fully masked, which its compute threads turn into P = dS = 0.

@@ -10,8 +10,9 @@
 //     S_i  = Q_i K_j^T   A = each CTA's own Q tile; B = K_j, keys [64r, 64r + 64) from CTA r
 //     O_i += P_i V_j     A = P_i in tensor memory;  B = V_j, columns [64r, 64r + 64) from CTA r
 // so a CTA loads and keeps HALF of every K and V tile: 32 KB instead of 64 KB of TMA traffic per key
-// tile step, and every MMA reads half as much of its B operand from each SM's shared memory -- the
-// one-CTA kernel runs both at the 128 B/clk the shared memory can deliver.
+// tile step, and every MMA reads half as much of its B operand from each SM's shared memory.
+// (That traffic turned out not to be what paces the one-CTA kernel: see the measurements at
+// attn_fwd_pair_sm100_supported below.  The kernel is kept as an opt-in path.)
 //
 // Under the causal mask slot i streams the key tiles its later tile (the rank-1 CTA's) needs; the
 // rank-0 CTA's tile meets one fully masked key tile at the end of each slot, which its softmax turns
