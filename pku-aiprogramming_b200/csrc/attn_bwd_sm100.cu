@@ -667,70 +667,79 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmR0, const __grid_con
 }
 
 // ---------------------------------------------------------------- preprocessing
-// delta[row] = sum_d dO*O ; lse2[row] = lse[row] * log2(e).  One warp per row.
-__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
-                                     const float* __restrict__ lse, float* __restrict__ delta,
-                                     float* __restrict__ lse2, long long n_rows, int D) {
+// delta[row] = sum_d dO*O ; lse2[row] = lse[row] * log2(e).  HBM-bound: D/8 lanes share a row (16 bytes
+// of O and of dO per lane), a warp covers 32/(D/8) rows per load instruction and keeps kPrepUnroll of
+// them in flight before it starts to add.
+constexpr int kPrepUnroll = 4;
+__device__ __forceinline__ uint4 ld_nc16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+// kVarlen: packed batches -- out, dout are [total_q, H, D] (row = token * H + head), lse, delta, lse2 are
+// [H, total_q]; a row that saw no key has lse = -inf: +inf in lse2 makes its recomputed probabilities
+// exp2(-inf) = 0.
+template <int D, bool kVarlen>
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                                                            const float* __restrict__ lse, float* __restrict__ delta,
+                                                            float* __restrict__ lse2, long long n_rows, long long total_q, int H) {
+    constexpr int kLanesPerRow = D / 8, kRowsPerStep = 32 / kLanesPerRow;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
-    if (row >= n_rows) return;
-    const uint2* o2 = reinterpret_cast<const uint2*>(out + row * D);
-    const uint2* d2 = reinterpret_cast<const uint2*>(dout + row * D);
-    float acc = 0.f;
-    for (int i = lane; i < D / 4; i += 32) {
-        uint2 a = o2[i], b = d2[i];
-        acc = fmaf(__uint_as_float(a.x << 16), __uint_as_float(b.x << 16), acc);
-        acc = fmaf(__uint_as_float(a.x & 0xffff0000u), __uint_as_float(b.x & 0xffff0000u), acc);
-        acc = fmaf(__uint_as_float(a.y << 16), __uint_as_float(b.y << 16), acc);
-        acc = fmaf(__uint_as_float(a.y & 0xffff0000u), __uint_as_float(b.y & 0xffff0000u), acc);
+    const int sub = lane / kLanesPerRow, li = lane % kLanesPerRow;
+    const long long row0 = ((long long)blockIdx.x * (blockDim.x >> 5) + warp) * (kRowsPerStep * kPrepUnroll) + sub;
+    uint4 a[kPrepUnroll], b[kPrepUnroll];
+#pragma unroll
+    for (int u = 0; u < kPrepUnroll; ++u) {
+        const long long row = row0 + u * kRowsPerStep;
+        a[u] = b[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (row < n_rows) {
+            a[u] = ld_nc16(out + row * D + li * 8);
+            b[u] = ld_nc16(dout + row * D + li * 8);
+        }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) {
-        delta[row] = acc;
-        lse2[row] = lse[row] * 1.4426950408889634f;
+    for (int u = 0; u < kPrepUnroll; ++u) {
+        const long long row = row0 + u * kRowsPerStep;
+        const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            acc = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(bw[e] << 16), acc);
+            acc = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(bw[e] & 0xffff0000u), acc);
+        }
+#pragma unroll
+        for (int o = kLanesPerRow / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (li == 0 && row < n_rows) {
+            if (kVarlen) {
+                const long long tok = row / H;
+                const long long i = (row - tok * H) * total_q + tok;
+                const float l = lse[i];
+                delta[i] = acc;
+                lse2[i] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+            } else {
+                delta[row] = acc;
+                lse2[row] = lse[row] * 1.4426950408889634f;
+            }
+        }
     }
 }
-// The same for packed batches: out, dout are [total_q, H, D], lse, delta, lse2 are [H, total_q].
-__global__ void attn_bwd_prep_varlen_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
-                                            const float* __restrict__ lse, float* __restrict__ delta,
-                                            float* __restrict__ lse2, long long total_q, int H, int D) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp;   // token * H + head
-    if (row >= total_q * H) return;
-    const long long tok = row / H;
-    const int h = (int)(row - tok * H);
-    const uint2* o2 = reinterpret_cast<const uint2*>(out + row * D);
-    const uint2* d2 = reinterpret_cast<const uint2*>(dout + row * D);
-    float acc = 0.f;
-    for (int i = lane; i < D / 4; i += 32) {
-        uint2 a = o2[i], b = d2[i];
-        acc = fmaf(__uint_as_float(a.x << 16), __uint_as_float(b.x << 16), acc);
-        acc = fmaf(__uint_as_float(a.x & 0xffff0000u), __uint_as_float(b.x & 0xffff0000u), acc);
-        acc = fmaf(__uint_as_float(a.y << 16), __uint_as_float(b.y << 16), acc);
-        acc = fmaf(__uint_as_float(a.y & 0xffff0000u), __uint_as_float(b.y & 0xffff0000u), acc);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) {
-        const long long i = (long long)h * total_q + tok;
-        delta[i] = acc;
-        // a row that saw no key has lse = -inf: +inf here makes its recomputed probabilities exp2(-inf) = 0
-        const float l = lse[i];
-        lse2[i] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
-    }
+template <int D, bool kVarlen>
+static void launch_prep(const AttnArgs& a, float* delta, float* lse2, long long n_rows, cudaStream_t st) {
+    const long long per_cta = 8LL * (32 / (D / 8)) * kPrepUnroll;
+    attn_bwd_prep_kernel<D, kVarlen><<<(unsigned)((n_rows + per_cta - 1) / per_cta), 256, 0, st>>>(
+        (const __nv_bfloat16*)a.out, (const __nv_bfloat16*)a.dout, a.lse, delta, lse2, n_rows, a.total_q, a.H);
 }
 cudaError_t attn_bwd_prep(const AttnArgs& a, float* delta, float* lse2, cudaStream_t st) {
     LaunchScope ls(K_BWD_PREP, st);
-    if (a.cu_q != nullptr) {
-        const long long rows = a.total_q * a.H;
-        attn_bwd_prep_varlen_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
-            (const __nv_bfloat16*)a.out, (const __nv_bfloat16*)a.dout, a.lse, delta, lse2, a.total_q, a.H, a.D);
-        return cudaGetLastError();
+    const bool varlen = a.cu_q != nullptr;
+    const long long n_rows = varlen ? a.total_q * a.H : a.BH * (long long)a.S;
+    if (a.D == 128) {
+        if (varlen) launch_prep<128, true>(a, delta, lse2, n_rows, st);
+        else launch_prep<128, false>(a, delta, lse2, n_rows, st);
+    } else {
+        if (varlen) launch_prep<64, true>(a, delta, lse2, n_rows, st);
+        else launch_prep<64, false>(a, delta, lse2, n_rows, st);
     }
-    const long long n_rows = a.BH * (long long)a.S;
-    attn_bwd_prep_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>(
-        (const __nv_bfloat16*)a.out, (const __nv_bfloat16*)a.dout, a.lse, delta, lse2, n_rows, a.D);
     return cudaGetLastError();
 }
 
