@@ -959,10 +959,10 @@ cudaStream_t host_call_stream() {
 // the next tt_alloc at once.  Declared AFTER the DevBufs, so that it runs before their destructors.
 std::atomic<long long> g_guard_syncs{0};
 struct SyncOnExit {
-    cudaStream_t s[3] = {nullptr, nullptr, nullptr};
+    cudaStream_t s[4] = {nullptr, nullptr, nullptr, nullptr};
     int n = 0;
     bool armed = true;
-    void add(cudaStream_t st) { if (n < 3) s[n++] = st; }
+    void add(cudaStream_t st) { if (n < 4) s[n++] = st; }
     ~SyncOnExit() {
         if (!armed) return;
         for (int i = 0; i < n; ++i) cudaStreamSynchronize(s[i]);
@@ -1042,12 +1042,14 @@ int tt_attn_bwd_host(const tt_attn_desc* d, const void* q, const void* k, const 
 
 // ---- pipelined host-buffer training step ----------------------------------------------------
 // The (batch, head) slices are independent, so the step is cut into chunks of slices that flow
-// through three streams: upload (q,k,v,dout of chunk c+1) | forward+backward (chunk c) |
+// through the streams: upload (q,k,v,dout of chunk c+1) | forward+backward (chunk c) |
 // download (out,lse,dq,dk,dv of chunk c-1).  With pinned host memory the PCIe transfers of both
-// directions overlap the kernels instead of preceding and following them.
+// directions overlap the kernels instead of preceding and following them.  Chunks alternate between
+// two compute streams: the kernels are persistent (one CTA per SM), so the next chunk's first CTAs
+// take over SMs as the previous chunk's last items finish instead of waiting for its whole tail.
 namespace {
 struct PipeStreams {
-    cudaStream_t in = nullptr, comp = nullptr, out = nullptr;
+    cudaStream_t in = nullptr, comp = nullptr, comp2 = nullptr, out = nullptr;
     int dev = -1;
 };
 int pipe_streams(PipeStreams** ps) {
@@ -1057,14 +1059,15 @@ int pipe_streams(PipeStreams** ps) {
     if (s.dev != dev) {
         if (s.dev >= 0) {   // the thread moved to another device: give the old device's streams back
             cudaSetDevice(s.dev);
-            for (cudaStream_t old : {s.in, s.comp, s.out})
+            for (cudaStream_t old : {s.in, s.comp, s.comp2, s.out})
                 if (old) cudaStreamDestroy(old);
             cudaSetDevice(dev);
-            s.in = s.comp = s.out = nullptr;
+            s.in = s.comp = s.comp2 = s.out = nullptr;
             s.dev = -1;
         }
         TT_CUDA(cudaStreamCreateWithFlags(&s.in, cudaStreamNonBlocking), "stream");
         TT_CUDA(cudaStreamCreateWithFlags(&s.comp, cudaStreamNonBlocking), "stream");
+        TT_CUDA(cudaStreamCreateWithFlags(&s.comp2, cudaStreamNonBlocking), "stream");
         TT_CUDA(cudaStreamCreateWithFlags(&s.out, cudaStreamNonBlocking), "stream");
         s.dev = dev;
     }
@@ -1107,7 +1110,29 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
     if (per > a.BH / 8) per = a.BH / 8;
     if (per < 1) per = 1;
     per = (per + a.group - 1) / a.group * a.group;   // a chunk holds whole groups of query heads
-    const long long n_chunks = (a.BH + per - 1) / per;
+    // Chunk sizes: `per` slices, but the first two and the last two chunks are a quarter and a half of that
+    // (whole groups): the upload of the first chunk and the download of the last are the only transfers
+    // nothing overlaps, and the two compute streams hide the short launches of small chunks.
+    std::vector<long long> starts;   // first slice of every chunk, then BH
+    {
+        const long long g = a.group;
+        const long long quarter = std::max<long long>(g, per / 4 / g * g), half = std::max<long long>(g, per / 2 / g * g);
+        long long left = a.BH, at = 0;
+        const long long back = quarter + half;
+        auto push = [&](long long n) { starts.push_back(at); at += n; left -= n; };
+        if (a.BH >= 2 * back + per) {
+            push(quarter);
+            push(half);
+            while (left - back >= per) push(per);
+            if (left > back) push(left - back);
+            push(half);
+            push(quarter);
+        } else {
+            while (left > 0) push(std::min(per, left));
+        }
+        starts.push_back(a.BH);
+    }
+    const long long n_chunks = (long long)starts.size() - 1;
     constexpr int NB = EventSet::kN;
     tt_attn_desc dc = *d;
     dc.B = 1;
@@ -1128,6 +1153,7 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
     SyncOnExit guard;
     guard.add(ps->in);
     guard.add(ps->comp);
+    guard.add(ps->comp2);
     guard.add(ps->out);
     EventSet ev;
     TT_TRY(ev.make());
@@ -1136,8 +1162,8 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
     char* ho = (char*)out; char* hdq = (char*)dq; char* hdk = (char*)dk; char* hdv = (char*)dv;
     for (long long c = 0; c < n_chunks; ++c) {
         const int b = (int)(c % NB);
-        const long long s0 = c * per;
-        const long long cnt = (s0 + per <= a.BH) ? per : (a.BH - s0);
+        const long long s0 = starts[(size_t)c];
+        const long long cnt = starts[(size_t)c + 1] - s0;
         const long long k0 = s0 / a.group, kcnt = cnt / a.group;   // the chunk's key/value slices
         if (c >= NB) TT_CUDA(cudaStreamWaitEvent(ps->in, ev.out[b], 0), "wait buffer");   // chunk c-NB downloaded
         TT_CUDA(cudaMemcpyAsync(bq[b].p, hq + s0 * q_slice, cnt * q_slice, cudaMemcpyHostToDevice, ps->in), "upload q");
@@ -1148,17 +1174,18 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
         TT_CUDA(cudaEventRecord(ev.in[b], ps->in), "record");
         TT_CUDA(cudaMemcpyAsync(bdo[b].p, hdo + s0 * q_slice, cnt * q_slice, cudaMemcpyHostToDevice, ps->in), "upload dout");
         TT_CUDA(cudaEventRecord(ev.in_do[b], ps->in), "record");
-        TT_CUDA(cudaStreamWaitEvent(ps->comp, ev.in[b], 0), "wait upload");
+        const cudaStream_t cs = (c & 1) ? ps->comp2 : ps->comp;
+        TT_CUDA(cudaStreamWaitEvent(cs, ev.in[b], 0), "wait upload");
         tt_attn_desc di = *d;
         di.B = 1;
         di.H = (int32_t)cnt;
         di.Hkv = (int32_t)kcnt;
-        TT_TRY(tt_attn_fwd(&di, bq[b].p, bk[b].p, bv[b].p, bo[b].p, (float*)bl[b].p, ps->comp));
-        TT_CUDA(cudaEventRecord(ev.fwd[b], ps->comp), "record");
-        TT_CUDA(cudaStreamWaitEvent(ps->comp, ev.in_do[b], 0), "wait upload");
+        TT_TRY(tt_attn_fwd(&di, bq[b].p, bk[b].p, bv[b].p, bo[b].p, (float*)bl[b].p, cs));
+        TT_CUDA(cudaEventRecord(ev.fwd[b], cs), "record");
+        TT_CUDA(cudaStreamWaitEvent(cs, ev.in_do[b], 0), "wait upload");
         TT_TRY(tt_attn_bwd(&di, bq[b].p, bk[b].p, bv[b].p, bo[b].p, (const float*)bl[b].p, bdo[b].p, bdq[b].p, bdk[b].p,
-                           bdv[b].p, bws[b].p, ws_bytes, ps->comp));
-        TT_CUDA(cudaEventRecord(ev.comp[b], ps->comp), "record");
+                           bdv[b].p, bws[b].p, ws_bytes, cs));
+        TT_CUDA(cudaEventRecord(ev.comp[b], cs), "record");
         TT_CUDA(cudaStreamWaitEvent(ps->out, ev.fwd[b], 0), "wait forward");
         TT_CUDA(cudaMemcpyAsync(ho + s0 * q_slice, bo[b].p, cnt * q_slice, cudaMemcpyDeviceToHost, ps->out), "download out");
         if (lse) TT_CUDA(cudaMemcpyAsync(lse + s0 * a.S, bl[b].p, cnt * l_slice, cudaMemcpyDeviceToHost, ps->out), "download lse");
@@ -1170,6 +1197,7 @@ int tt_attn_fwd_bwd_host(const tt_attn_desc* d, const void* q, const void* k, co
     }
     TT_CUDA(cudaStreamSynchronize(ps->in), "synchronize");
     TT_CUDA(cudaStreamSynchronize(ps->comp), "synchronize");
+    TT_CUDA(cudaStreamSynchronize(ps->comp2), "synchronize");
     return tt_check_device_status(ps->out);
 }
 
