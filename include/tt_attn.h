@@ -99,7 +99,7 @@ int tt_attn_bwd_set_deterministic(int on);
 
 /* ---- single-query decode (S == 1) ----------------------------------------------------
  * The memory-bound case: every K and V row is streamed once.  Same mathematics as
- * tt_attn_fwd with S == 1, no mask.  bf16 at D = 128 with up to 16 query heads per key/value
+ * tt_attn_fwd with S == 1, no mask.  bf16 at D = 128 or 64 with up to 16 query heads per key/value
  * head runs a tensor-core kernel whose accumulator rows are the keys (K and V tiles by TMA,
  * the group's query heads as 16 B-operand rows, one CTA per (key/value slice, key range));
  * other shapes a split-KV kernel with 16-byte loads.  With more than one key range per slice
@@ -114,8 +114,8 @@ int tt_attn_decode(const tt_attn_desc* desc, const void* q, const void* k, const
  * it exists for hosts that run with a frozen memory map -- a real-time serving loop that
  * pre-allocated everything at start-up and may not touch the allocator again, or a plugin sandbox
  * whose policy forbids cudaMalloc -- and therefore cannot supply the partials workspace
- * tt_attn_decode wants.  It always runs the split-KV kernels named above (tt_attn_decode sends D = 128
- * to the tensor-core decode kernel instead), so its results match tt_attn_decode within the bf16
+ * tt_attn_decode wants.  It always runs the split-KV kernels named above (tt_attn_decode prefers the
+ * tensor-core decode kernel), so its results match tt_attn_decode within the bf16
  * tolerance, bit for bit where both take the same
  * kernels; the split-KV partials go to an 8 MiB array built into the library's device image (each
  * GPU that loads the library keeps those 8 MiB until the process exits).  The call itself performs
@@ -181,9 +181,9 @@ int tt_attn_bwd_varlen(const tt_varlen_desc* desc, const void* q, const void* k,
  *   block_table == NULL: k_pool, v_pool are dense [B, Hkv, L, D] as in tt_attn_decode.
  *   seq_lens != NULL: device array of B int32, batch entry b attends to its first seq_lens[b]
  *       keys (clamped to 0..L); an entry with no keys gets out = 0 and lse = -inf.
- * Grouped heads (desc->Hkv < H) read each key/value row once for the whole group: at D = 128 for
- * groups of up to 16 (tensor-core decode kernel, as in tt_attn_decode), at D = 64 for groups of 2, 4
- * and 8 (groups of 4 and more on the tensor-core forward kernel).  Over a paged cache the tensor-core
+ * Grouped heads (desc->Hkv < H) read each key/value row once for the whole group: groups of up to
+ * 16 on the tensor-core decode kernel, as in tt_attn_decode, larger ones on the tensor-core forward
+ * kernel.  Over a paged cache the tensor-core
  * kernels need a page_size that divides 128 or is a multiple of it (>= 8) and gather the pages by
  * TMA; other page sizes take the split-KV kernel.  Rows that no sequence owns never reach the
  * result and may hold anything.  Workspace: tt_attn_decode_workspace_bytes(desc). */

@@ -293,13 +293,13 @@ static AttnArgs decode_as_forward(const AttnArgs& a, int splits) {
 // keys are cut into about four ranges per SM of at least 512 keys.
 static bool decode_on_gq_kernel(const AttnArgs& a) {
     const char* f = getenv("TT_DECODE_GQA_PATH");
-    return a.bf16 && a.D == 128 && a.S == 1 && a.group <= 16 && !(f && f[0] == 'f');
+    return a.bf16 && (a.D == 128 || a.D == 64) && a.S == 1 && a.group <= 16 && !(f && f[0] == 'f');
 }
 static int decode_tc_splits(const AttnArgs& a) {   // 0: do not use the forward kernel
     const char* f = getenv("TT_DECODE_GQA_PATH");
-    // head dim 128: the keys-on-rows kernel takes every group size up to 16 (measured faster than the split-KV
-    // kernel even for single heads); head dim 64: the forward kernel from groups of 4 on
-    const int min_group = a.D == 128 ? 1 : 4;
+    // the keys-on-rows kernel takes every group size up to 16 (measured faster than the split-KV kernel even for
+    // single heads); larger groups take the forward kernel
+    const int min_group = decode_on_gq_kernel(a) ? 1 : 4;
     if (!(a.bf16 && a.S == 1 && a.group >= min_group)) return 0;
     if (f && f[0] == 's') return 0;                           // "simt"
     if (!attn_fwd_sm100_supported(decode_as_forward(a, 1))) return 0;
@@ -449,7 +449,7 @@ static void paged_split(const AttnArgs& a, int* splits, int* chunk) {
 }
 int attn_decode_paged_on_forward(const AttnArgs& a, const DecodeView& v, size_t* ws_bytes) {
     *ws_bytes = 0;
-    if (!(a.bf16 && a.S == 1 && a.group >= (a.D == 128 ? 1 : 4) && (v.block_table != nullptr || v.seq_lens != nullptr))) return 0;
+    if (!(a.bf16 && a.S == 1 && a.group >= (decode_on_gq_kernel(a) ? 1 : 4) && (v.block_table != nullptr || v.seq_lens != nullptr))) return 0;
     const char* f = getenv("TT_DECODE_GQA_PATH");
     if (f && f[0] == 's') return 0;                           // "simt"
     int splits, chunk;

@@ -1,5 +1,5 @@
 // Single-query attention (decode) for grouped heads on the tensor cores, keys on the accumulator rows.
-// bf16, head dim 128, 4..16 query heads per key/value head, dense, ragged or paged cache.
+// bf16, head dim 128 or 64, 1..16 query heads per key/value head, dense, ragged or paged cache.
 //
 // Run as a forward problem with the G query heads of a key/value head as G query rows, the general
 // forward kernel spends a whole 128-row query tile on G rows: its softmax threads are rows, so per
@@ -33,16 +33,19 @@ using namespace sm100;
 
 namespace {
 
-constexpr int kD = 128;
-constexpr int kStages = 3;                    // ring of K/V tiles: K_0, V_0, K_1, V_1, ...
 constexpr int kSubBytes = 128 * 128;          // [128 rows x 128 B]
-constexpr int kTileBytes = 2 * kSubBytes;     // 32 KB
-constexpr int kQBytes = 4096;                 // [16 query rows x 128 d]: two sub-blocks of [16 rows x 128 B]
-constexpr int kPBytes = 4096;                 // [16 query rows x 128 keys], same layout
+constexpr int kPBytes = 4096;                 // [16 query rows x 128 keys]: two sub-blocks of [16 rows x 128 B]
 constexpr int kAuxBytes = 2048;               // barriers, reduction scratch
-constexpr int kSmemBytes = kStages * kTileBytes + kQBytes + 2 * kPBytes + kAuxBytes + 1024;   // +1024: alignment slack
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 64;                 // S^T buffers at [0,16) and [16,32), O^T at [32,48)
+template <int kD>
+struct GqCfg {
+    static constexpr int kSub = kD / 64;                       // 64-column sub-blocks per K/V tile
+    static constexpr int kTileBytes = kSub * kSubBytes;        // 32 KB (D = 128), 16 KB (D = 64)
+    static constexpr int kStages = 96 * 1024 / kTileBytes;     // ring of K/V tiles: K_0, V_0, K_1, V_1, ...
+    static constexpr int kQBytes = kSub * 2048;                // [16 query rows x D]: sub-blocks of [16 rows x 128 B]
+    static constexpr int kSmemBytes = kStages * kTileBytes + 4096 /*Q*/ + 2 * kPBytes + kAuxBytes + 1024;   // +1024: alignment slack
+};
 
 struct GqParams {
     __nv_bfloat16* out;
@@ -67,16 +70,20 @@ __device__ __forceinline__ int float_key(float x) {
 __device__ __forceinline__ float key_float(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
 __device__ __forceinline__ void bar_sync_128(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
+// kD: head dim, 128 or 64.  At 64 the accumulator still has 128 rows: the V tile is one 64-wide block, and the
+// descriptor's stride to the "second" block is 0, so rows 64..127 of O^T repeat rows 0..63 and are never read.
 // kG: columns of S^T / O^T the softmax evaluates (G <= kG <= 16).  kCache: ragged and/or paged cache.
-template <int kG, bool kCache>
+template <int kD, int kG, bool kCache>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                             const __grid_constant__ CUtensorMap tmV, const GqParams p) {
+    using Cfg = GqCfg<kD>;
+    constexpr int kStages = Cfg::kStages, kTileBytes = Cfg::kTileBytes, kSub = Cfg::kSub, kQBytes = Cfg::kQBytes;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* sKV = smem;
     unsigned char* sQ = smem + kStages * kTileBytes;
-    unsigned char* sP = sQ + kQBytes;
+    unsigned char* sP = sQ + 4096;
     unsigned char* aux = sP + 2 * kPBytes;
     uint64_t* bar_q_full = reinterpret_cast<uint64_t*>(aux);
     uint64_t* bar_kv_full = bar_q_full + 1;          // [kStages]
@@ -143,7 +150,8 @@ attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
         const float c = p.scale_log2;
         if (n_tiles == 0) {   // an empty range (cache mode): zero output, log-sum-exp -inf; the merge gives it no weight
-            for (int g = 0; g < p.G; ++g) p.out[((long long)bh * p.G + g) * kD + t] = __float2bfloat16_rn(0.f);
+            if (t < kD)
+                for (int g = 0; g < p.G; ++g) p.out[((long long)bh * p.G + g) * kD + t] = __float2bfloat16_rn(0.f);
             if (t < p.G && p.lse != nullptr) p.lse[(long long)bh * p.G + t] = -INFINITY;
         } else {
             float m_ref[kG], l_t[kG];
@@ -250,7 +258,7 @@ attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             for (int g = 0; g < kG; ++g) {
                 const float l = red_sum[g] + red_sum[16 + g] + red_sum[32 + g] + red_sum[48 + g];
                 if (g < p.G) {
-                    p.out[((long long)bh * p.G + g) * kD + t] = __float2bfloat16_rn(__uint_as_float(o[g]) / l);
+                    if (t < kD) p.out[((long long)bh * p.G + g) * kD + t] = __float2bfloat16_rn(__uint_as_float(o[g]) / l);
                     if (t == g && p.lse != nullptr) p.lse[(long long)bh * p.G + g] = (m_ref[g] + log2f(l)) * 0.6931471805599453f;
                 }
             }
@@ -263,7 +271,7 @@ attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 // 16 query rows from row qslice * G of q viewed as [rows, D]; rows past the group belong to other
                 // heads (or are zero past the end): their columns of S^T and O^T are never read
 #pragma unroll
-                for (int sb = 0; sb < 2; ++sb) tma_load_3d(sQ + sb * 2048, &tmQ, bar_q_full, sb * 64, qslice * p.G, 0);
+                for (int sb = 0; sb < kSub; ++sb) tma_load_3d(sQ + sb * 2048, &tmQ, bar_q_full, sb * 64, qslice * p.G, 0);
             }
             __syncwarp();
             // paged cache: lane i fetches the i-th page (or 128-row part of a larger page) of a tile.  The table
@@ -297,7 +305,7 @@ attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                         const int key = key0 + k_first + lane * box_rows;
                         const int z = page * p.H + (zslice % p.H);
 #pragma unroll
-                        for (int sb = 0; sb < 2; ++sb)
+                        for (int sb = 0; sb < kSub; ++sb)
                             tma_load_3d(dst + sb * kSubBytes + lane * box_rows * 128, tm, &bar_kv_full[st], sb * 64,
                                         key % p.page_size, z);
                     }
@@ -306,7 +314,7 @@ attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                     if (elect_one()) {
                         mbar_arrive_expect_tx(&bar_kv_full[st], kTileBytes);
 #pragma unroll
-                        for (int sb = 0; sb < 2; ++sb)
+                        for (int sb = 0; sb < kSub; ++sb)
                             tma_load_3d(dst + sb * kSubBytes, tm, &bar_kv_full[st], sb * 64, key0 + k_first, zslice);
                     }
                     __syncwarp();
@@ -320,7 +328,7 @@ attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         const uint32_t sKV_addr = __shfl_sync(0xffffffffu, smem_u32(sKV), 0);
         const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
         const uint64_t dK_base = umma_smem_desc(sKV_addr, 16, 1024);             // K-major A, 128 key rows
-        const uint64_t dV_base = umma_smem_desc(sKV_addr, kSubBytes, 1024);      // MN-major A: M = d over two 64-wide blocks
+        const uint64_t dV_base = umma_smem_desc(sKV_addr, kSub == 2 ? kSubBytes : 0, 1024);   // MN-major A: M = d over two 64-wide blocks (D = 64: the same block twice)
         const uint64_t dQ = umma_smem_desc(__shfl_sync(0xffffffffu, smem_u32(sQ), 0), 16, 1024);   // K-major B, 16 rows
         const uint64_t dP_base = umma_smem_desc(__shfl_sync(0xffffffffu, smem_u32(sP), 0), 16, 1024);
         auto issue_s = [&](int j) {
@@ -371,7 +379,7 @@ attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 // their P is exactly 0, but 0 x NaN is not, so they are zeroed.
                 unsigned char* vt = sKV + ((2 * j + 1) % kStages) * kTileBytes;
 #pragma unroll
-                for (int sb = 0; sb < 2; ++sb)
+                for (int sb = 0; sb < kSub; ++sb)
                     for (int o = rv * 128 + lane * 16; o < 128 * 128; o += 32 * 16)
                         *reinterpret_cast<uint4*>(vt + sb * kSubBytes + o) = make_uint4(0u, 0u, 0u, 0u);
                 fence_proxy_async_smem();
@@ -394,7 +402,7 @@ attn_decode_gq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     }
 }
 
-template <int kG, bool kCache>
+template <int kD, int kG, bool kCache>
 cudaError_t launch_gq(const AttnArgs& a, cudaStream_t st) {
     TmapStorage tq, tk, tv;
     const char* why = nullptr;
@@ -413,7 +421,7 @@ cudaError_t launch_gq(const AttnArgs& a, cudaStream_t st) {
         if (!make_tmap_bf16(&tk, a.k, kD, a.L, kv_slices, 128, &why)) return cudaErrorInvalidValue;
         if (!make_tmap_bf16(&tv, a.v, kD, a.L, kv_slices, 128, &why)) return cudaErrorInvalidValue;
     }
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_gq_sm100_kernel<kG, kCache>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_gq_sm100_kernel<kD, kG, kCache>, cudaFuncAttributeMaxDynamicSharedMemorySize, GqCfg<kD>::kSmemBytes);
     if (e != cudaSuccess) return e;
     GqParams p;
     p.out = (__nv_bfloat16*)a.out;
@@ -430,7 +438,7 @@ cudaError_t launch_gq(const AttnArgs& a, cudaStream_t st) {
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = device_status_word();
     LaunchScope ls(K_DECODE_GQ, st);
-    attn_decode_gq_sm100_kernel<kG, kCache><<<(unsigned)a.BH, kThreads, kSmemBytes, st>>>(
+    attn_decode_gq_sm100_kernel<kD, kG, kCache><<<(unsigned)a.BH, kThreads, GqCfg<kD>::kSmemBytes, st>>>(
         *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
         *reinterpret_cast<CUtensorMap*>(tv.bytes), p);
     return cudaGetLastError();
@@ -442,7 +450,7 @@ cudaError_t launch_gq(const AttnArgs& a, cudaStream_t st) {
 // attn_decode.cu): S = query heads per key/value head, BH = key/value slices x key ranges.
 // TT_DECODE_GQA_PATH=fwd keeps such problems on the general forward kernel (tests, measurements).
 bool attn_decode_gq_sm100_supported(const AttnArgs& a) {
-    if (!a.bf16 || a.D != 128 || a.causal || a.group != 1 || a.S < 1 || a.S > 16 || a.L < 1 || a.cu_q != nullptr) return false;
+    if (!a.bf16 || (a.D != 128 && a.D != 64) || a.causal || a.group != 1 || a.S < 1 || a.S > 16 || a.L < 1 || a.cu_q != nullptr) return false;
     if (a.BH < 1 || a.BH >= (1LL << 31)) return false;
     if (a.cache_mode) {
         if (a.q_div > 1 ? !(a.kv_chunk >= 128 && a.kv_chunk % 128 == 0) : a.kv_chunk != 0) return false;
@@ -455,11 +463,15 @@ bool attn_decode_gq_sm100_supported(const AttnArgs& a) {
     return !(f && f[0] == 'f');
 }
 
-cudaError_t attn_decode_gq_sm100(const AttnArgs& a, cudaStream_t st) {
+template <int kD>
+static cudaError_t dispatch_gq(const AttnArgs& a, cudaStream_t st) {
     const bool cache = a.cache_mode != 0;
-    if (a.S <= 4) return cache ? launch_gq<4, true>(a, st) : launch_gq<4, false>(a, st);
-    if (a.S <= 8) return cache ? launch_gq<8, true>(a, st) : launch_gq<8, false>(a, st);
-    return cache ? launch_gq<16, true>(a, st) : launch_gq<16, false>(a, st);
+    if (a.S <= 4) return cache ? launch_gq<kD, 4, true>(a, st) : launch_gq<kD, 4, false>(a, st);
+    if (a.S <= 8) return cache ? launch_gq<kD, 8, true>(a, st) : launch_gq<kD, 8, false>(a, st);
+    return cache ? launch_gq<kD, 16, true>(a, st) : launch_gq<kD, 16, false>(a, st);
+}
+cudaError_t attn_decode_gq_sm100(const AttnArgs& a, cudaStream_t st) {
+    return a.D == 128 ? dispatch_gq<128>(a, st) : dispatch_gq<64>(a, st);
 }
 
 }  // namespace ttk

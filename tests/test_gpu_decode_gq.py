@@ -125,3 +125,55 @@ def test_paged_and_ragged_cache(tt, oracle, torch_cuda, monkeypatch, B, H, Hkv, 
         assert np.isneginf(got_lse[1]).all() and float(np.abs(got[1]).max()) == 0.0, name   # the empty sequence
         assert oracle.max_abs_err(got[keep], o_r[keep]) <= 2e-2, name
         assert oracle.max_abs_err(got_lse[keep], lse_r[keep]) <= 1e-3, name
+
+
+@pytest.mark.parametrize("B,H,Hkv,L", [(3, 8, 2, 1500), (2, 12, 12, 777), (64, 16, 4, 640), (1, 32, 2, 16384)])
+def test_head_dim_64(tt, oracle, torch_cuda, monkeypatch, B, H, Hkv, L):
+    """Head dim 64: the V tile is one 64-wide block and the accumulator's upper 64 rows repeat the lower ones."""
+    torch = torch_cuda
+    q, k, v, _ = make_grouped(oracle, 640 + H + L, B, H, Hkv, 1, L, 64, True)
+    tq, tk, tv = (torch.from_numpy(a).cuda().bfloat16() for a in (q, k, v))
+    o_r, lse_r = dense_decode_ref(oracle, q, k, v)
+    for route in (None, "simt"):
+        if route is None:
+            monkeypatch.delenv("TT_DECODE_GQA_PATH", raising=False)
+        else:
+            monkeypatch.setenv("TT_DECODE_GQA_PATH", route)
+        tt.capi.profile_reset()
+        tt.capi.profile_enable(True)
+        out, lse = tt.attention_decode(tq, tk, tv)
+        tt.check_device_status()
+        tt.capi.profile_enable(False)
+        prof = tt.capi.profile_read()
+        assert (prof.get("attn_decode_gq_sm100", (0.0, 0))[1] == 1) == (route is None), (route, prof)
+        assert oracle.max_abs_err(out.float().cpu().numpy(), o_r) <= 2e-2, route
+        assert oracle.max_abs_err(lse.cpu().numpy(), lse_r) <= 1e-3, route
+
+
+def test_head_dim_64_paged(tt, oracle, torch_cuda, monkeypatch):
+    torch = torch_cuda
+    monkeypatch.delenv("TT_DECODE_GQA_PATH", raising=False)
+    rng = np.random.default_rng(64)
+    B, H, Hkv, page, max_pages = 4, 8, 2, 32, 21
+    cap = page * max_pages
+    lens = np.array([cap, 0, 129, 500], np.int32)
+    q, k, v, _ = make_grouped(oracle, 964, B, H, Hkv, 1, cap, 64, True)
+    n_pages = B * max_pages + 3
+    perm = rng.permutation(n_pages)[:B * max_pages].astype(np.int32).reshape(B, max_pages)
+    k_pool = np.full((n_pages, Hkv, page, 64), np.nan, np.float32)
+    v_pool = np.full((n_pages, Hkv, page, 64), np.nan, np.float32)
+    for b in range(B):
+        for pg in range(max_pages):
+            n = int(np.clip(lens[b] - pg * page, 0, page))
+            k_pool[perm[b, pg], :, :n] = k[b, :, pg * page:pg * page + n]
+            v_pool[perm[b, pg], :, :n] = v[b, :, pg * page:pg * page + n]
+    tq = torch.from_numpy(q).cuda().bfloat16()
+    tkp, tvp = (torch.from_numpy(a).cuda().bfloat16() for a in (k_pool, v_pool))
+    out, lse = tt.attention_decode_paged(tq, tkp, tvp, block_table=torch.from_numpy(perm).cuda(), seq_lens=torch.from_numpy(lens).cuda())
+    tt.check_device_status()
+    o_r, lse_r = dense_decode_ref(oracle, q, k, v, lens)
+    got, got_lse = out.float().cpu().numpy(), lse.cpu().numpy()
+    keep = lens > 0
+    assert np.isfinite(got).all() and np.isneginf(got_lse[1]).all() and float(np.abs(got[1]).max()) == 0.0
+    assert oracle.max_abs_err(got[keep], o_r[keep]) <= 2e-2
+    assert oracle.max_abs_err(got_lse[keep], lse_r[keep]) <= 1e-3
