@@ -1,4 +1,4 @@
-// Single-query attention (decode) for grouped heads on the tensor cores, keys on the accumulator rows.
+// Single-query attention (decode) on the tensor cores with keys on the accumulator rows, single or grouped heads.
 // bf16, head dim 128 or 64, 1..16 query heads per key/value head, dense, ragged or paged cache.
 //
 // Run as a forward problem with the G query heads of a key/value head as G query rows, the general
@@ -21,7 +21,8 @@
 // normalised (out bf16 [slices*ranges, G, D], log-sum-exp fp32): with more than one range a merge
 // kernel combines them, exactly as for the forward-kernel route this replaces.
 //   warps 0-3  softmax (thread = key of the tile = row d of O^T),  warp 4  MMA issuer,  warp 5  TMA loader
-// Every wait is bounded (sm100_ptx.cuh).
+// Every mbarrier wait is bounded (sm100_ptx.cuh); the one bar.sync per tile among the softmax warps is reached
+// by all 128 threads whatever the waits returned (they never leave the tile loop early).
 #include "common.h"
 #include "sm100_ptx.cuh"
 
